@@ -1,0 +1,212 @@
+/*
+ * ssd_b200.h - C ABI of the B200 (sm_100a) Mamba-2 SSD operator library.
+ *
+ * Every entry point takes plain pointers and sizes: raw CUDA device pointers (what
+ * `at_data_ptr` returns for a tch tensor, vendor/torch-sys-0.25.0/libtch/torch_api.h:41),
+ * a caller-owned workspace, and the CUDA stream to launch on.  The library never allocates
+ * or frees device memory, never synchronises the host with the device, never changes the
+ * current device, and keeps no pointer after a call returns, so every call may be issued
+ * while the caller's stream is being captured into a CUDA graph (the PPO update of the
+ * reference runs its forward+backward inside one: trading_bots/src/torch/train/update.rs:206-328,
+ * vendor/torch-sys-0.25.0/libtch/torch_api.cpp:403-436).
+ *
+ * Error convention (mirrors libtch's PROTECT / torch_last_err,
+ * vendor/torch-sys-0.25.0/libtch/torch_api.h:9,18-23): functions return 0 on success or a
+ * negative SsdStatus; a human-readable message is kept per thread and read with
+ * ssd_last_error().
+ *
+ * Operator (per batch b, head h with group g = h*ngroups/nheads, time t, state S [P x N]):
+ *     a_t = exp(dt[b,t,h] * A[h])
+ *     S_t = a_t * S_{t-1} + dt[b,t,h] * x[b,t,h,:] (outer) B[b,t,g,:]
+ *     y_t = S_t . C[b,t,g,:] + D[h] * x[b,t,h,:]          (then y_t *= silu(z_t) if z given)
+ */
+#ifndef SSD_B200_H
+#define SSD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SSD_API __attribute__((visibility("default")))
+#else
+#define SSD_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum SsdStatus {
+  SSD_OK = 0,
+  SSD_ERR_BAD_SHAPE = -1,
+  SSD_ERR_BAD_ALIGNMENT = -2,
+  SSD_ERR_UNSUPPORTED = -3,
+  SSD_ERR_WORKSPACE_TOO_SMALL = -4,
+  SSD_ERR_CUDA = -5,
+  SSD_ERR_NULL_POINTER = -6,
+  SSD_ERR_TIMEOUT = -7
+} SsdStatus;
+
+typedef enum SsdDtype { SSD_F32 = 0, SSD_BF16 = 1 } SsdDtype;
+
+typedef enum SsdPass { SSD_PASS_FWD = 0, SSD_PASS_BWD = 1 } SsdPass;
+
+/* Kernel family selection.  AUTO picks the tcgen05 tensor-core kernels when dtype is bf16 and
+ * the shape is one they cover, else the exact-fp32 CUDA-core kernels. */
+typedef enum SsdAlgo { SSD_ALGO_AUTO = 0, SSD_ALGO_FP32_CORES = 1, SSD_ALGO_TENSOR = 2 } SsdAlgo;
+
+/*
+ * Problem geometry.  `dtype` is the storage type of x, dt, B, C, z, y and of dx, dB, dC, dz, dy;
+ * A, D, states, ddt, dA, dD are always fp32.  All arithmetic accumulates in fp32.
+ * Strides are in ELEMENTS for the batch and sequence dims; the remaining dims are dense
+ * (x/z/y/dy: [.., H, P]; dt: [.., H]; B/C: [.., G, N]).  A stride of 0 means "dense default".
+ * This is how a narrowed / non-contiguous tch view is passed (the reference accepts those on
+ * its attention path, trading_bots/src/torch/fa4.rs:283-305).
+ */
+typedef struct SsdDims {
+  int32_t batch, seqlen, nheads, headdim, dstate, ngroups, chunk;
+  int32_t dtype;     /* SsdDtype */
+  int32_t algo;      /* SsdAlgo  */
+  int32_t device;    /* CUDA ordinal the pointers live on; -1 = do not check */
+  int32_t has_z;     /* 1 if a z gate is passed (sizes the backward workspace) */
+  int32_t reserved;
+  int64_t x_stride_b, x_stride_l;
+  int64_t dt_stride_b, dt_stride_l;
+  int64_t b_stride_b, b_stride_l;
+  int64_t c_stride_b, c_stride_l;
+  int64_t z_stride_b, z_stride_l;
+  int64_t y_stride_b, y_stride_l;   /* y in forward, dy in backward */
+} SsdDims;
+
+/* Forward operands.  Optional pointers may be NULL. */
+typedef struct SsdFwdPtrs {
+  const void* x;           /* [B,L,H,P]  dtype */
+  const void* dt;          /* [B,L,H]    dtype  (already positive: softplus stays with the caller) */
+  const float* A;          /* [H]        fp32, negative */
+  const void* Bm;          /* [B,L,G,N]  dtype */
+  const void* Cm;          /* [B,L,G,N]  dtype */
+  const float* D;          /* [H]        fp32, optional */
+  const void* z;           /* [B,L,H,P]  dtype, optional gate: y *= silu(z) */
+  const float* init_state; /* [B,H,P,N]  fp32, optional */
+  void* y;                 /* [B,L,H,P]  dtype, out */
+  float* final_state;      /* [B,H,P,N]  fp32, out, optional */
+} SsdFwdPtrs;
+
+/* Backward operands: the forward inputs again, the incoming gradients, the outputs. */
+typedef struct SsdBwdPtrs {
+  const void* x; const void* dt; const float* A; const void* Bm; const void* Cm;
+  const float* D; const void* z; const float* init_state;
+  const void* dy;            /* [B,L,H,P] dtype: gradient w.r.t. the (gated) output */
+  const float* dfinal_state; /* [B,H,P,N] fp32, optional */
+  void* dx;                  /* [B,L,H,P] dtype, dense */
+  float* ddt;                /* [B,L,H]   fp32,  dense */
+  float* dA;                 /* [H]       fp32 */
+  void* dB;                  /* [B,L,G,N] dtype, dense */
+  void* dC;                  /* [B,L,G,N] dtype, dense */
+  float* dD;                 /* [H]       fp32, optional (required iff D given) */
+  void* dz;                  /* [B,L,H,P] dtype, dense, required iff z given */
+  float* dinit_state;        /* [B,H,P,N] fp32, optional */
+  int32_t fwd_saved;         /* 1: `workspace` is the buffer ssd_forward ran in for these same
+                                inputs (its chunk cumsums and chunk-entry states are reused);
+                                0: recompute them */
+} SsdBwdPtrs;
+
+/* Single-timestep recurrence for streamed rollout (in place on `state`). */
+typedef struct SsdStepDims {
+  int32_t streams, nheads, headdim, dstate, ngroups;
+  int32_t dtype;        /* SsdDtype of x, dt, B, C, z, y; state is always fp32 */
+  int32_t device;       /* -1 = do not check */
+  int32_t reserved;
+  int64_t x_stride_s;   /* elements between streams; 0 = dense */
+  int64_t dt_stride_s, b_stride_s, c_stride_s, z_stride_s, y_stride_s;
+} SsdStepDims;
+
+typedef struct SsdStepPtrs {
+  float* state;        /* [S,H,P,N] fp32, updated in place */
+  const void* x;       /* [S,H,P] */
+  const void* dt;      /* [S,H]   */
+  const float* A;      /* [H] */
+  const void* Bm;      /* [S,G,N] */
+  const void* Cm;      /* [S,G,N] */
+  const float* D;      /* [H], optional */
+  const void* z;       /* [S,H,P], optional */
+  void* y;             /* [S,H,P], out */
+} SsdStepPtrs;
+
+/* Bytes of workspace ssd_forward / ssd_backward need for `dims` (0 on invalid dims, with the
+ * error string set).  The backward workspace begins with the forward layout, so one buffer of
+ * the backward size serves both calls.  Replaces: nothing in the reference (its SSD layer was
+ * removed; only its timings remain, benchmark_results/bench_20260112_070055.json:6-41). */
+SSD_API size_t ssd_workspace_bytes(const SsdDims* dims, int32_t pass);
+
+/* y, final_state = SSD(x, dt, A, B, C, D, z, init_state), chunked evaluation.  Sits where the
+ * reference's blocks call their sequence mixer today
+ * (`Tensor::scaled_dot_product_attention`, trading_bots/src/torch/model/blocks/gqa.rs:95-104;
+ * FA4 prefill, trading_bots/src/torch/world_model.rs:1099-1103). */
+SSD_API int32_t ssd_forward(const SsdDims* dims, const SsdFwdPtrs* p, void* workspace, size_t workspace_bytes,
+                    void* cuda_stream);
+
+/* Gradients of ssd_forward.  The reference never hand-writes a backward (autograd through
+ * SDPA / FA4, trading_bots/src/torch/fa4.rs:98-138); tch-rs has no custom autograd node, so the
+ * contract is an explicit call. */
+SSD_API int32_t ssd_backward(const SsdDims* dims, const SsdBwdPtrs* p, void* workspace, size_t workspace_bytes,
+                     void* cuda_stream);
+
+/* One timestep over `streams` independent recurrences, in place on `state`.  Takes the slot of
+ * `TradingModel::step_on_device` (trading_bots/src/torch/model/stream/live.rs:257-320) and of
+ * the Q=1 decode (trading_bots/src/torch/world_model.rs:1213-1247) in the rollout loop
+ * (trading_bots/src/torch/train/rollout.rs:209-235). */
+SSD_API int32_t ssd_state_update(const SsdStepDims* dims, const SsdStepPtrs* p, void* cuda_stream);
+
+/* Zero the state rows of the streams listed in `stream_idx` (device int64 indices, `count` of
+ * them) without a host sync: the per-environment reset of the reference
+ * (trading_bots/src/torch/model/stream/live.rs:114-158, which avoids a sync at :155-157). */
+SSD_API int32_t ssd_state_reset_rows(float* state, int64_t row_elems, const int64_t* stream_idx, int64_t count,
+                             int64_t streams, void* cuda_stream);
+
+/*
+ * Sequence-parallel split.  A rank that owns a contiguous slice of the sequence cannot finish
+ * its scan before it knows the state entering the slice, so both passes are exposed in stages:
+ *   SSD_STAGE_LOCAL  - per-chunk work that needs no cross-chunk state (cumsum, chunk states;
+ *                      in backward also the forward recompute and the local state gradients)
+ *   SSD_STAGE_TOTAL  - read-only scan giving the slice total for a ZERO boundary state:
+ *                      forward writes it to final_state, backward to dinit_state
+ *   SSD_STAGE_FINISH - the scan with the true boundary state (init_state / dfinal_state) and
+ *                      everything downstream of it
+ * ssd_forward == stages LOCAL|FINISH.  Between TOTAL and FINISH the host gathers every rank's
+ * (total state, total log-decay) record with one all-gather, and ssd_sp_prefix_state folds the
+ * records of the ranks before (direction +1) or after (direction -1) this one:
+ *   +1: acc = boundary; for q = 0 .. rank-1:          acc = exp(logdecay_q) * acc + state_q
+ *   -1: acc = boundary; for q = world-1 .. rank+1:    acc = exp(logdecay_q) * acc + state_q
+ * No counterpart in the reference (it is a single-GPU program with no collective anywhere).
+ */
+enum { SSD_STAGE_LOCAL = 1, SSD_STAGE_TOTAL = 2, SSD_STAGE_FINISH = 4 };
+
+SSD_API int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* workspace, size_t workspace_bytes,
+                           void* cuda_stream, int32_t stages);
+SSD_API int32_t ssd_backward_staged(const SsdDims* dims, const SsdBwdPtrs* p, void* workspace, size_t workspace_bytes,
+                            void* cuda_stream, int32_t stages);
+
+/* out[b,h] = sum over this slice of dt*A, read from the chunk cumsums a LOCAL stage left in
+ * `workspace`. */
+SSD_API int32_t ssd_sp_total_logdecay(const SsdDims* dims, const void* workspace, size_t workspace_bytes, float* out,
+                              void* cuda_stream);
+
+/* gathered_states [world, batch_heads, state_elems] fp32, gathered_logdecay [world, batch_heads]
+ * fp32, boundary [batch_heads, state_elems] fp32 or NULL (zero), state_in out, same shape. */
+SSD_API int32_t ssd_sp_prefix_state(const float* gathered_states, const float* gathered_logdecay, int32_t world,
+                            int32_t rank, int32_t direction, int64_t batch_heads, int64_t state_elems,
+                            const float* boundary, float* state_in, void* cuda_stream);
+
+/* Message for the last failing call on this thread ("" if none); valid until the next call on
+ * this thread.  Mirrors `get_and_reset_last_err` (trading_bots/src/torch/cuda/graph.rs:107-118). */
+SSD_API const char* ssd_last_error(void);
+
+/* Library version and the SM architecture it was compiled for (100 for sm_100a). */
+SSD_API int32_t ssd_version(void);
+SSD_API int32_t ssd_compiled_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSD_B200_H */

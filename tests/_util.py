@@ -1,0 +1,60 @@
+"""Shared helpers for the parity tests: error metrics and oracle evaluation."""
+from __future__ import annotations
+
+import dataclasses
+
+import numpy as np
+import torch
+
+from oracle import ssd_oracle as O
+
+# Parity gates of the workload definition.
+FP32_REL = 1e-4          # fp32 mode: max-abs error relative to the reference's max-abs
+BF16_MAX_ABS = 2e-2      # bf16 mode: max-abs error ...
+BF16_MEAN_REL = 1e-2     # ... and mean-abs error relative to the reference's mean-abs
+
+
+def rel_err(got, ref) -> float:
+    got = torch.as_tensor(got).double().cpu()
+    ref = torch.as_tensor(ref).double().cpu()
+    return float((got - ref).abs().max() / (ref.abs().max() + 1e-300))
+
+
+def max_abs(got, ref) -> float:
+    return float((torch.as_tensor(got).double().cpu() - torch.as_tensor(ref).double().cpu()).abs().max())
+
+
+def mean_rel(got, ref) -> float:
+    got = torch.as_tensor(got).double().cpu()
+    ref = torch.as_tensor(ref).double().cpu()
+    return float((got - ref).abs().mean() / (ref.abs().mean() + 1e-300))
+
+
+def assert_close(name, got, ref, mode):
+    """mode 'fp32': 1e-4 relative.  mode 'bf16': 2e-2 max-abs (scaled by max(1, max|ref|), since the
+    gate is stated for O(1) outputs) and 1e-2 mean-rel."""
+    assert torch.isfinite(torch.as_tensor(got).float()).all(), f"{name}: non-finite values"
+    if mode == "fp32":
+        e = rel_err(got, ref)
+        assert e <= FP32_REL, f"{name}: rel err {e:.3e} > {FP32_REL}"
+    else:
+        scale = max(1.0, float(torch.as_tensor(ref).double().abs().max()))
+        ma, mr = max_abs(got, ref), mean_rel(got, ref)
+        assert ma <= BF16_MAX_ABS * scale, f"{name}: max-abs {ma:.3e} > {BF16_MAX_ABS * scale:.3e}"
+        assert mr <= BF16_MEAN_REL, f"{name}: mean-rel {mr:.3e} > {BF16_MEAN_REL}"
+
+
+def cfg_like(base: int, **kw) -> O.SsdConfig:
+    return dataclasses.replace(O.CONFIGS[base], **kw)
+
+
+def oracle_all(inp, dfinal=None):
+    """fp64 ground truth (hand-derived reverse recurrence) on the given, already rounded, inputs."""
+    r = O.ssd_sequential_grads_manual(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"],
+                                      inp["D"] if inp.get("D") is not None else torch.zeros_like(inp["A"]),
+                                      inp["dy"], inp.get("z"), inp.get("init_state"), dfinal)
+    return {k: (None if v is None else torch.from_numpy(np.asarray(v))) for k, v in r.items()}
+
+
+def to_dev(inp, device):
+    return {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in inp.items()}

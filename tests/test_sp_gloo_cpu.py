@@ -1,0 +1,122 @@
+"""Host-side logic of the sequence-parallel path, run as 2 and 3 gloo ranks on CPU.
+
+The device operations are replaced by the CPU oracle (injected through `ops`), so what is under
+test is the slice bookkeeping, the packed all-gather, the direction of both prefix scans, the
+boundary-state handling and the dA/dD reduction."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import ssd_oracle as O
+from tests._util import rel_err
+from trading_bot_0_b200 import _lib as L
+from trading_bot_0_b200 import sp
+
+
+class OracleOps:
+    """fp64 CPU stand-in for the CUDA operations behind `sp_forward` / `sp_backward`."""
+
+    def _leaves(self, x, dt, A, Bm, Cm, D, z, init):
+        f = lambda t: None if t is None else t.detach().double().requires_grad_(True)
+        return [f(t) for t in (x, dt, A, Bm, Cm, D, z, init)]
+
+    def forward(self, stages, x, dt, A, Bm, Cm, D, z, init_state, chunk, algo, workspace, y, final_state):
+        if stages & L.STAGE_TOTAL:
+            _, total = O.ssd_sequential(x, dt, A, Bm, Cm, D, z, None)
+            return None, total.float(), {"ws": True}
+        yy, fin = O.ssd_sequential(x, dt, A, Bm, Cm, D, z, init_state)
+        return yy, fin.float(), workspace
+
+    def total_logdecay(self, x, dt, A, Bm, Cm, z, chunk, algo, workspace):
+        return (dt.double() * A.double()).sum(1).float()
+
+    def prefix_state(self, gs, gl, world, rank, direction, boundary):
+        acc = torch.zeros_like(gs[0]) if boundary is None else boundary.clone()
+        order = range(rank) if direction > 0 else range(world - 1, rank, -1)
+        for q in order:
+            acc = torch.exp(gl[q])[..., None, None] * acc + gs[q]
+        return acc
+
+    def backward(self, stages, dy, x, dt, A, Bm, Cm, D, z, init_state, dfinal, chunk, algo, workspace, out):
+        lv = self._leaves(x, dt, A, Bm, Cm, D, z, init_state)
+        yy, fin = O.ssd_sequential(*lv)
+        loss = (yy * dy.double()).sum()
+        if stages & L.STAGE_FINISH and dfinal is not None:
+            loss = loss + (fin * dfinal.double()).sum()
+        loss.backward()
+        names = ("dx", "ddt", "dA", "dB", "dC", "dD", "dz", "dinit")
+        for n, t in zip(names, lv):
+            if t is not None:
+                out[n] = t.grad.float()
+        return out
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        cfg = O.SsdConfig("sp", 2, 96, 2, 4, 8, 1, 16, "fp32", True)
+        inp = O.make_inputs(cfg, with_init_state=True)
+        dfin = torch.randn(2, 2, 4, 8, generator=torch.Generator().manual_seed(9))
+        a, b = sp.slice_bounds(cfg.seqlen, world, rank, cfg.chunk)
+        loc = {k: inp[k][:, a:b] for k in ("x", "dt", "B", "C", "z", "dy")}
+        ops = OracleOps()
+        y, fin, ctx = sp.sp_forward(loc["x"], loc["dt"], inp["A"], loc["B"], loc["C"], inp["D"], loc["z"],
+                                    inp["init_state"], chunk=cfg.chunk, ops=ops)
+        g = sp.sp_backward(loc["dy"], ctx, dfin, ops=ops)
+        q.put((rank, a, b, y.detach(), fin.detach(), {k: v.detach() for k, v in g.items() if isinstance(v, torch.Tensor)}))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sp_forward_backward_over_gloo(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = sorted([q.get(timeout=90) for _ in range(world)], key=lambda t: t[0])
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert all(p.exitcode == 0 for p in procs)
+    cfg = O.SsdConfig("sp", 2, 96, 2, 4, 8, 1, 16, "fp32", True)
+    inp = O.make_inputs(cfg, with_init_state=True)
+    dfin = torch.randn(2, 2, 4, 8, generator=torch.Generator().manual_seed(9))
+    ref = O.ssd_grads_autograd(O.ssd_sequential, inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"],
+                               inp["dy"], inp["z"], inp["init_state"], dfin)
+    assert rel_err(torch.cat([r[3] for r in res], 1), ref["y"]) < 1e-5
+    assert rel_err(res[-1][4], ref["final_state"]) < 1e-5
+    for k in ("dx", "ddt", "dB", "dC", "dz"):
+        assert rel_err(torch.cat([r[5][k] for r in res], 1), ref[k]) < 1e-5, k
+    for r in res:  # replicated-parameter gradients are already summed on every rank
+        assert rel_err(r[5]["dA"], ref["dA"]) < 1e-5 and rel_err(r[5]["dD"], ref["dD"]) < 1e-5
+    assert rel_err(res[0][5]["dinit"], ref["dinit"]) < 1e-5
+
+
+def test_slice_bounds():
+    assert [sp.slice_bounds(1024, 4, r, 128) for r in range(4)] == [(0, 256), (256, 512), (512, 768), (768, 1024)]
+    assert sp.slice_bounds(1000, 2, 1, 128) == (512, 1000)
+    with pytest.raises(ValueError):
+        sp.slice_bounds(128, 4, 3, 128)
+    with pytest.raises(ValueError):
+        sp.slice_bounds(128, 2, 2, 64)

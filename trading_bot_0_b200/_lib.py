@@ -1,0 +1,105 @@
+"""ctypes binding of the C ABI declared in include/ssd_b200.h.
+
+The structures below mirror the header field for field; this is the same raw-pointer contract a
+Rust `extern "C"` block over tch tensors would use (`at_data_ptr`,
+vendor/torch-sys-0.25.0/libtch/torch_api.h:41).  There is no CPU or eager fallback: if the
+compiled library is missing the import fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libssd_b200.so"
+
+SSD_F32, SSD_BF16 = 0, 1
+PASS_FWD, PASS_BWD = 0, 1
+ALGO_AUTO, ALGO_FP32_CORES, ALGO_TENSOR = 0, 1, 2
+STAGE_LOCAL, STAGE_TOTAL, STAGE_FINISH = 1, 2, 4
+
+EXPORTS = [
+    "ssd_workspace_bytes", "ssd_forward", "ssd_backward", "ssd_forward_staged", "ssd_backward_staged",
+    "ssd_state_update", "ssd_state_reset_rows", "ssd_sp_total_logdecay", "ssd_sp_prefix_state",
+    "ssd_last_error", "ssd_version", "ssd_compiled_arch",
+]
+
+
+class SsdDims(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seqlen", "nheads", "headdim", "dstate", "ngroups", "chunk",
+                                         "dtype", "algo", "device", "has_z", "reserved")] + \
+               [(n, C.c_int64) for n in ("x_stride_b", "x_stride_l", "dt_stride_b", "dt_stride_l",
+                                         "b_stride_b", "b_stride_l", "c_stride_b", "c_stride_l",
+                                         "z_stride_b", "z_stride_l", "y_stride_b", "y_stride_l")]
+
+
+class SsdFwdPtrs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("x", "dt", "A", "Bm", "Cm", "D", "z", "init_state", "y", "final_state")]
+
+
+class SsdBwdPtrs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("x", "dt", "A", "Bm", "Cm", "D", "z", "init_state", "dy",
+                                          "dfinal_state", "dx", "ddt", "dA", "dB", "dC", "dD", "dz",
+                                          "dinit_state")] + [("fwd_saved", C.c_int32)]
+
+
+class SsdStepDims(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("streams", "nheads", "headdim", "dstate", "ngroups", "dtype", "device",
+                                         "reserved")] + \
+               [(n, C.c_int64) for n in ("x_stride_s", "dt_stride_s", "b_stride_s", "c_stride_s", "z_stride_s",
+                                         "y_stride_s")]
+
+
+class SsdStepPtrs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("state", "x", "dt", "A", "Bm", "Cm", "D", "z", "y")]
+
+
+class SsdError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"ssd_b200 error {code}: {msg}")
+        self.code = code
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built "
+            "(run `python -m trading_bot_0_b200.build`). There is no CPU fallback.")
+    lib = C.CDLL(str(LIB_PATH))
+    vp, i32, i64, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
+    lib.ssd_workspace_bytes.restype = sz
+    lib.ssd_workspace_bytes.argtypes = [C.POINTER(SsdDims), i32]
+    for name in ("ssd_forward", "ssd_backward"):
+        f = getattr(lib, name)
+        f.restype = i32
+        f.argtypes = [C.POINTER(SsdDims), vp, vp, sz, vp]
+    lib.ssd_forward.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdFwdPtrs), vp, sz, vp]
+    lib.ssd_backward.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdBwdPtrs), vp, sz, vp]
+    lib.ssd_forward_staged.restype = i32
+    lib.ssd_forward_staged.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdFwdPtrs), vp, sz, vp, i32]
+    lib.ssd_backward_staged.restype = i32
+    lib.ssd_backward_staged.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdBwdPtrs), vp, sz, vp, i32]
+    lib.ssd_state_update.restype = i32
+    lib.ssd_state_update.argtypes = [C.POINTER(SsdStepDims), C.POINTER(SsdStepPtrs), vp]
+    lib.ssd_state_reset_rows.restype = i32
+    lib.ssd_state_reset_rows.argtypes = [vp, i64, vp, i64, i64, vp]
+    lib.ssd_sp_total_logdecay.restype = i32
+    lib.ssd_sp_total_logdecay.argtypes = [C.POINTER(SsdDims), vp, sz, vp, vp]
+    lib.ssd_sp_prefix_state.restype = i32
+    lib.ssd_sp_prefix_state.argtypes = [vp, vp, i32, i32, i32, i64, i64, vp, vp, vp]
+    lib.ssd_last_error.restype = C.c_char_p
+    lib.ssd_last_error.argtypes = []
+    lib.ssd_version.restype = i32
+    lib.ssd_compiled_arch.restype = i32
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise SsdError(rc, load().ssd_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,52 @@
+// Shared device/host helpers for the SSD kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ssd_b200.h"
+
+namespace ssd {
+
+// Internal, fully-resolved geometry handed to every kernel by value.
+struct Geo {
+  int B, L, H, P, N, G, Q, nc, hpg;  // hpg = heads per group
+  long long xsb, xsl, dtsb, dtsl, bsb, bsl, csb, csl, zsb, zsl, ysb, ysl;
+};
+
+// Workspace segments (offsets in bytes from the workspace base; 0-size segments unused).
+struct WsLayout {
+  size_t cs, dtf, states, fin, cb;                   // forward
+  size_t dstates, dyp, dcsp, ddtd, ddot, sdot, dapart, ddpart, dini;  // backward extras
+  size_t total_fwd, total_bwd;
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return __ldg(p); }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + __expf(-z)); }
+
+// Thread-local error string shared by every translation unit of the library.
+void set_error(const char* fmt, ...);
+void clear_error();
+
+#define SSD_CUDA_CHECK_LAUNCH(what)                                              \
+  do {                                                                           \
+    cudaError_t e__ = cudaGetLastError();                                        \
+    if (e__ != cudaSuccess) {                                                    \
+      ::ssd::set_error("%s: launch failed: %s", what, cudaGetErrorString(e__));  \
+      return SSD_ERR_CUDA;                                                       \
+    }                                                                            \
+  } while (0)
+
+static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace ssd

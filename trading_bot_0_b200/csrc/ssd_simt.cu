@@ -1,0 +1,740 @@
+// Exact-fp32 CUDA-core kernels for the SSD operator: every stage of forward and backward for
+// any storage dtype, any chunk <= 256 and ragged sequence tails.  This family is the fp32-mode
+// path (1e-4 relative parity) and the building block the sequence-parallel split reuses; the
+// bf16 throughput path lives in ssd_tensor.cu.
+//
+// All contractions share one tile routine: a 256-thread block accumulates a 64x64 output tile,
+// 4x4 per thread, staging 16-deep slabs of both operands in shared memory through element
+// functors, so a stage is defined by "what is A(m,k), what is B(n,k), what does the epilogue do".
+#include "common.cuh"
+#include "ssd_internal.h"
+
+namespace ssd {
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16, LDS = 68, NT = 256;
+
+template <bool A_KFAST, bool B_KFAST, class FA, class FB>
+__device__ __forceinline__ void tile_mac(float (&acc)[4][4], int kbeg, int kend, FA fa, FB fb,
+                                         float* As, float* Bs) {
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int k0 = kbeg; k0 < kend; k0 += TK) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int m, kk;
+      if (A_KFAST) { kk = tid & 15; m = (tid >> 4) + 16 * r; } else { m = tid & 63; kk = (tid >> 6) + 4 * r; }
+      int k = k0 + kk;
+      As[kk * LDS + m] = (k < kend) ? fa(m, k) : 0.f;
+      if (B_KFAST) { kk = tid & 15; m = (tid >> 4) + 16 * r; } else { m = tid & 63; kk = (tid >> 6) + 4 * r; }
+      k = k0 + kk;
+      Bs[kk * LDS + m] = (k < kend) ? fb(m, k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[kk * LDS + ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Bs[kk * LDS + tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(av[r], bv[c], acc[r][c]);
+    }
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void zero_acc(float (&acc)[4][4]) {
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+}
+
+// Sum over the 16 threads (tx) that share a tile row; every lane of the half-warp gets the sum.
+__device__ __forceinline__ float row_reduce16(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v;
+}
+
+__device__ __forceinline__ size_t cs_idx(const Geo& g, int b, int h, int c) {
+  return ((size_t)(b * g.H + h) * g.nc + c) * g.Q;
+}
+__device__ __forceinline__ size_t st_idx(const Geo& g, int b, int c, int h) {
+  return ((size_t)(b * g.nc + c) * g.H + h) * g.P * g.N;
+}
+__device__ __forceinline__ size_t cb_idx(const Geo& g, int b, int c, int grp) {
+  return ((size_t)(b * g.nc + c) * g.G + grp) * g.Q * g.Q;
+}
+
+// Gradient w.r.t. the pre-gate output: either the fp32 workspace copy (gated case) or dy itself.
+template <typename T>
+struct DySrc {
+  const float* f;
+  const T* t;
+  long long sb, sl;
+  __device__ __forceinline__ float get(const Geo& g, int b, int tt, int h, int p) const {
+    if (f) return f[((size_t)(b * (size_t)g.L + tt) * g.H + h) * g.P + p];
+    return ldf(t + b * sb + tt * sl + (long long)h * g.P + p);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Stage 1: cs = inclusive within-chunk cumsum of dt*A (fp32), dtf = dt as fp32, both [B,H,nc,Q].
+template <typename T>
+__global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ A,
+                                               float* __restrict__ cs, float* __restrict__ dtf) {
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, q = threadIdx.x;
+  __shared__ float wsum[NT / 32];
+  const int t = c * g.Q + q;
+  float d = 0.f;
+  if (q < g.Q && t < g.L) d = ldf(dt + b * g.dtsb + t * g.dtsl + h);
+  float v = d * A[h];
+  const int lane = q & 31, w = q >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += n;
+  }
+  if (lane == 31) wsum[w] = v;
+  __syncthreads();
+  float base = 0.f;
+  for (int i = 0; i < w; ++i) base += wsum[i];
+  v += base;
+  if (q < g.Q) {
+    const size_t o = cs_idx(g, b, h, c) + q;
+    cs[o] = v;
+    dtf[o] = d;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stage 2 (and its backward twin): out[b,c,h,p,n] = sum_l w_l * X[l,h,p] * Y[l,g,n]
+//   MODE 0: w_l = exp(cs_end - cs_l) * dt_l   (chunk_state: X = x, Y = B)
+//   MODE 1: w_l = exp(cs_l)                    (local state gradient: X = dy, Y = C)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(NT) k_chunk_state(Geo g, const T* __restrict__ x, long long xsb, long long xsl,
+                                                    DySrc<T> dys, const T* __restrict__ Y, long long ysb,
+                                                    long long ysl, const float* __restrict__ cs,
+                                                    const float* __restrict__ dtf, float* __restrict__ out) {
+  __shared__ __align__(16) float As[TK * LDS];
+  __shared__ __align__(16) float Bs[TK * LDS];
+  __shared__ float wl[256];
+  const int ntn = (g.N + TN - 1) / TN;
+  const int p0 = (blockIdx.x / ntn) * TM, n0 = (blockIdx.x % ntn) * TN;
+  const int c = blockIdx.y / g.H, h = blockIdx.y % g.H, b = blockIdx.z, grp = h / g.hpg;
+  const size_t co = cs_idx(g, b, h, c);
+  const float cs_end = cs[co + g.Q - 1];
+  for (int l = threadIdx.x; l < g.Q; l += NT)
+    wl[l] = (MODE == 0) ? expf(cs_end - cs[co + l]) * dtf[co + l] : expf(cs[co + l]);
+  __syncthreads();
+  float acc[4][4];
+  zero_acc(acc);
+  const int tbase = c * g.Q;
+  auto fa = [&](int m, int k) -> float {
+    const int p = p0 + m, t = tbase + k;
+    if (p >= g.P || t >= g.L) return 0.f;
+    float v = (MODE == 0) ? ldf(x + b * xsb + t * xsl + (long long)h * g.P + p) : dys.get(g, b, t, h, p);
+    return v * wl[k];
+  };
+  auto fb = [&](int n, int k) -> float {
+    const int nn = n0 + n, t = tbase + k;
+    if (nn >= g.N || t >= g.L) return 0.f;
+    return ldf(Y + b * ysb + t * ysl + (long long)grp * g.N + nn);
+  };
+  tile_mac<false, false>(acc, 0, g.Q, fa, fb, As, Bs);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float* o = out + st_idx(g, b, c, h);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int p = p0 + ty * 4 + r;
+    if (p >= g.P) continue;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int n = n0 + tx * 4 + cc;
+      if (n < g.N) o[(size_t)p * g.N + n] = acc[r][cc];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stage 3: exclusive scan over chunks, in place.  Forward direction turns per-chunk states into
+// the state ENTERING each chunk and emits the final state; reverse direction does the same for
+// the state gradient (entering from the right) and emits the gradient of the initial state.
+//   WRITE=false only produces `last` (used by the sequence-parallel split to get the slice total).
+template <bool WRITE>
+__global__ void __launch_bounds__(NT) k_state_passing(Geo g, float* __restrict__ st, const float* __restrict__ cs,
+                                                      const float* __restrict__ init, float* __restrict__ last,
+                                                      int reverse) {
+  const int e = blockIdx.x * NT + threadIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int PN = g.P * g.N;
+  if (e >= PN) return;
+  float run = init ? init[((size_t)(b * g.H + h)) * PN + e] : 0.f;
+  for (int s = 0; s < g.nc; ++s) {
+    const int c = reverse ? g.nc - 1 - s : s;
+    float* ptr = st + st_idx(g, b, c, h) + e;
+    const float v = *ptr;
+    if (WRITE) *ptr = run;
+    run = expf(cs[cs_idx(g, b, h, c) + g.Q - 1]) * run + v;
+  }
+  if (last) last[((size_t)(b * g.H + h)) * PN + e] = run;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stage 4a: cb[b,c,g,i,j] = C_i . B_j for j-tiles at or below the diagonal.
+template <typename T>
+__global__ void __launch_bounds__(NT) k_cb(Geo g, const T* __restrict__ Bm, const T* __restrict__ Cm,
+                                           float* __restrict__ cb) {
+  __shared__ __align__(16) float As[TK * LDS];
+  __shared__ __align__(16) float Bs[TK * LDS];
+  const int nt = (g.Q + TM - 1) / TM;
+  const int it = blockIdx.x / nt, jt = blockIdx.x % nt;
+  if (jt > it) return;
+  const int i0 = it * TM, j0 = jt * TN;
+  const int c = blockIdx.y / g.G, grp = blockIdx.y % g.G, b = blockIdx.z;
+  const int tbase = c * g.Q;
+  float acc[4][4];
+  zero_acc(acc);
+  auto fa = [&](int m, int k) -> float {
+    const int i = i0 + m, t = tbase + i;
+    if (i >= g.Q || t >= g.L) return 0.f;
+    return ldf(Cm + b * g.csb + t * g.csl + (long long)grp * g.N + k);
+  };
+  auto fb = [&](int n, int k) -> float {
+    const int j = j0 + n, t = tbase + j;
+    if (j >= g.Q || t >= g.L) return 0.f;
+    return ldf(Bm + b * g.bsb + t * g.bsl + (long long)grp * g.N + k);
+  };
+  tile_mac<true, true>(acc, 0, g.N, fa, fb, As, Bs);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float* o = cb + cb_idx(g, b, c, grp);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = i0 + ty * 4 + r;
+    if (i >= g.Q) continue;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int j = j0 + tx * 4 + cc;
+      if (j < g.Q) o[(size_t)i * g.Q + j] = acc[r][cc];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Stage 4b: chunk_scan.  acc[i,p] = sum_{j<=i} cb[i,j] exp(cs_i-cs_j) dt_j x[j,p]
+//                                   + exp(cs_i) sum_n C[i,n] prev[p,n]
+//   EPI 0 (forward):  y = acc + D x, optional silu gate, store.
+//   EPI 1 (backward recompute): from acc form dz and the pre-gate gradient, and the per-position
+//                     sums  dcsp[i] = sum_p dyp*acc  and  ddot[i] = sum_p dyp*x.
+template <typename T, int EPI>
+__global__ void __launch_bounds__(NT) k_chunk_scan(Geo g, const T* __restrict__ x, const T* __restrict__ Cm,
+                                                   const float* __restrict__ D, const T* __restrict__ z,
+                                                   const float* __restrict__ cs, const float* __restrict__ dtf,
+                                                   const float* __restrict__ cb, const float* __restrict__ prev,
+                                                   T* __restrict__ y, const T* __restrict__ dy,
+                                                   float* __restrict__ dyp, T* __restrict__ dz,
+                                                   float* __restrict__ dcsp, float* __restrict__ ddot) {
+  __shared__ __align__(16) float As[TK * LDS];
+  __shared__ __align__(16) float Bs[TK * LDS];
+  __shared__ float css[256], dts[256];
+  const int ntp = (g.P + TN - 1) / TN;
+  const int i0 = (blockIdx.x / ntp) * TM, p0 = (blockIdx.x % ntp) * TN;
+  const int c = blockIdx.y / g.H, h = blockIdx.y % g.H, b = blockIdx.z, grp = h / g.hpg;
+  const int tbase = c * g.Q;
+  const size_t co = cs_idx(g, b, h, c);
+  for (int l = threadIdx.x; l < g.Q; l += NT) { css[l] = cs[co + l]; dts[l] = dtf[co + l]; }
+  __syncthreads();
+  float acc[4][4];
+  zero_acc(acc);
+  const float* cbp = cb + cb_idx(g, b, c, grp);
+  {
+    auto fa = [&](int m, int k) -> float {
+      const int i = i0 + m;
+      if (i >= g.Q || k > i) return 0.f;
+      return cbp[(size_t)i * g.Q + k] * expf(css[i] - css[k]) * dts[k];
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int p = p0 + n, t = tbase + k;
+      if (p >= g.P || t >= g.L) return 0.f;
+      return ldf(x + b * g.xsb + t * g.xsl + (long long)h * g.P + p);
+    };
+    const int kend = min(g.Q, i0 + TM);
+    tile_mac<true, false>(acc, 0, kend, fa, fb, As, Bs);
+  }
+  {
+    const float* pv = prev + st_idx(g, b, c, h);
+    auto fa = [&](int m, int k) -> float {
+      const int i = i0 + m, t = tbase + i;
+      if (i >= g.Q || t >= g.L) return 0.f;
+      return expf(css[i]) * ldf(Cm + b * g.csb + t * g.csl + (long long)grp * g.N + k);
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int p = p0 + n;
+      if (p >= g.P) return 0.f;
+      return pv[(size_t)p * g.N + k];
+    };
+    tile_mac<true, true>(acc, 0, g.N, fa, fb, As, Bs);
+  }
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const float Dh = D ? D[h] : 0.f;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = i0 + ty * 4 + r, t = tbase + i;
+    const bool rowok = (i < g.Q) && (t < g.L);
+    float s_cs = 0.f, s_dd = 0.f;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int p = p0 + tx * 4 + cc;
+      if (!rowok || p >= g.P) continue;
+      const float xv = ldf(x + b * g.xsb + t * g.xsl + (long long)h * g.P + p);
+      if (EPI == 0) {
+        float v = acc[r][cc] + Dh * xv;
+        if (z) {
+          const float zv = ldf(z + b * g.zsb + t * g.zsl + (long long)h * g.P + p);
+          v *= zv * sigmoidf_(zv);
+        }
+        stf(y + b * g.ysb + t * g.ysl + (long long)h * g.P + p, v);
+      } else {
+        float dyv = ldf(dy + b * g.ysb + t * g.ysl + (long long)h * g.P + p);
+        if (z) {
+          const float zv = ldf(z + b * g.zsb + t * g.zsl + (long long)h * g.P + p);
+          const float sg = 1.f / (1.f + expf(-zv));
+          const float ypre = acc[r][cc] + Dh * xv;
+          const size_t od = ((size_t)(b * (size_t)g.L + t) * g.H + h) * g.P + p;
+          stf(dz + od, dyv * ypre * sg * (1.f + zv * (1.f - sg)));
+          dyv *= zv * sg;
+          dyp[od] = dyv;
+        }
+        s_cs += dyv * acc[r][cc];
+        s_dd += dyv * xv;
+      }
+    }
+    if (EPI == 1) {
+      s_cs = row_reduce16(s_cs);
+      s_dd = row_reduce16(s_dd);
+      if (tx == 0 && rowok) {
+        atomicAdd(dcsp + co + i, s_cs);
+        atomicAdd(ddot + co + i, s_dd);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward, dx:  u[j,p] = sum_{i>=j} cb[i,j] exp(cs_i-cs_j) dyp[i,p] + exp(cs_end-cs_j) sum_n B[j,n] dS[p,n]
+//                dx = D*dyp + dt_j*u ;  ddtd[j] = sum_p x[j,p]*u[j,p]
+template <typename T>
+__global__ void __launch_bounds__(NT) k_dx(Geo g, const T* __restrict__ x, const T* __restrict__ Bm,
+                                           const float* __restrict__ D, DySrc<T> dys,
+                                           const float* __restrict__ cs, const float* __restrict__ dtf,
+                                           const float* __restrict__ cb, const float* __restrict__ dS,
+                                           T* __restrict__ dx, float* __restrict__ ddtd) {
+  __shared__ __align__(16) float As[TK * LDS];
+  __shared__ __align__(16) float Bs[TK * LDS];
+  __shared__ float css[256];
+  const int ntp = (g.P + TN - 1) / TN;
+  const int j0 = (blockIdx.x / ntp) * TM, p0 = (blockIdx.x % ntp) * TN;
+  const int c = blockIdx.y / g.H, h = blockIdx.y % g.H, b = blockIdx.z, grp = h / g.hpg;
+  const int tbase = c * g.Q;
+  const size_t co = cs_idx(g, b, h, c);
+  for (int l = threadIdx.x; l < g.Q; l += NT) css[l] = cs[co + l];
+  __syncthreads();
+  const float cs_end = css[g.Q - 1];
+  float acc[4][4];
+  zero_acc(acc);
+  const float* cbp = cb + cb_idx(g, b, c, grp);
+  {
+    auto fa = [&](int m, int k) -> float {  // m -> j, k -> i
+      const int j = j0 + m;
+      if (j >= g.Q || k < j) return 0.f;
+      return cbp[(size_t)k * g.Q + j] * expf(css[k] - css[j]);
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int p = p0 + n, t = tbase + k;
+      if (p >= g.P || t >= g.L) return 0.f;
+      return dys.get(g, b, t, h, p);
+    };
+    tile_mac<false, false>(acc, j0, g.Q, fa, fb, As, Bs);
+  }
+  {
+    const float* ds = dS + st_idx(g, b, c, h);
+    auto fa = [&](int m, int k) -> float {
+      const int j = j0 + m, t = tbase + j;
+      if (j >= g.Q || t >= g.L) return 0.f;
+      return expf(cs_end - css[j]) * ldf(Bm + b * g.bsb + t * g.bsl + (long long)grp * g.N + k);
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int p = p0 + n;
+      if (p >= g.P) return 0.f;
+      return ds[(size_t)p * g.N + k];
+    };
+    tile_mac<true, true>(acc, 0, g.N, fa, fb, As, Bs);
+  }
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const float Dh = D ? D[h] : 0.f;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int j = j0 + ty * 4 + r, t = tbase + j;
+    const bool rowok = (j < g.Q) && (t < g.L);
+    const float dtj = rowok ? dtf[co + j] : 0.f;
+    float s = 0.f;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int p = p0 + tx * 4 + cc;
+      if (!rowok || p >= g.P) continue;
+      const float xv = ldf(x + b * g.xsb + t * g.xsl + (long long)h * g.P + p);
+      const float u = acc[r][cc];
+      const float dyv = dys.get(g, b, t, h, p);
+      stf(dx + ((size_t)(b * (size_t)g.L + t) * g.H + h) * g.P + p, Dh * dyv + dtj * u);
+      s += xv * u;
+    }
+    s = row_reduce16(s);
+    if (tx == 0 && rowok) atomicAdd(ddtd + co + j, s);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward, W:  wsum[b,c,g,i,j] = sum_{h in g} exp(cs_h,i-cs_h,j) dt_h,j (dyp[i,h,:] . x[j,h,:]),  j<=i
+template <typename T>
+__global__ void __launch_bounds__(NT) k_dw(Geo g, const T* __restrict__ x, DySrc<T> dys,
+                                           const float* __restrict__ cs, const float* __restrict__ dtf,
+                                           float* __restrict__ wsum) {
+  __shared__ __align__(16) float As[TK * LDS];
+  __shared__ __align__(16) float Bs[TK * LDS];
+  const int nt = (g.Q + TM - 1) / TM;
+  const int it = blockIdx.x / nt, jt = blockIdx.x % nt;
+  if (jt > it) return;
+  const int i0 = it * TM, j0 = jt * TN;
+  const int c = blockIdx.y / g.G, grp = blockIdx.y % g.G, b = blockIdx.z;
+  const int tbase = c * g.Q;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float sum[4][4];
+  zero_acc(sum);
+  for (int hh = 0; hh < g.hpg; ++hh) {
+    const int h = grp * g.hpg + hh;
+    float acc[4][4];
+    zero_acc(acc);
+    auto fa = [&](int m, int k) -> float {
+      const int i = i0 + m, t = tbase + i;
+      if (i >= g.Q || t >= g.L) return 0.f;
+      return dys.get(g, b, t, h, k);
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int j = j0 + n, t = tbase + j;
+      if (j >= g.Q || t >= g.L) return 0.f;
+      return ldf(x + b * g.xsb + t * g.xsl + (long long)h * g.P + k);
+    };
+    tile_mac<true, true>(acc, 0, g.P, fa, fb, As, Bs);
+    const size_t co = cs_idx(g, b, h, c);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = i0 + ty * 4 + r;
+      if (i >= g.Q) continue;
+      const float ci = cs[co + i];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        const int j = j0 + tx * 4 + cc;
+        if (j < g.Q && j <= i) sum[r][cc] += acc[r][cc] * expf(ci - cs[co + j]) * dtf[co + j];
+      }
+    }
+  }
+  float* o = wsum + cb_idx(g, b, c, grp);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = i0 + ty * 4 + r;
+    if (i >= g.Q) continue;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int j = j0 + tx * 4 + cc;
+      if (j < g.Q) o[(size_t)i * g.Q + j] = (j <= i) ? sum[r][cc] : 0.f;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward, dC (MODE 0) and dB (MODE 1):
+//   dC[i,n] = sum_{j<=i} wsum[i,j] B[j,n] + sum_{h,p} exp(cs_h,i) dyp[i,h,p] prev[h,p,n]
+//   dB[j,n] = sum_{i>=j} wsum[i,j] C[i,n] + sum_{h,p} exp(cs_h,end-cs_h,j) dt_h,j x[j,h,p] dS[h,p,n]
+template <typename T, int MODE>
+__global__ void __launch_bounds__(NT) k_dbc(Geo g, const T* __restrict__ x, const T* __restrict__ Other,
+                                            long long osb, long long osl, DySrc<T> dys,
+                                            const float* __restrict__ cs, const float* __restrict__ dtf,
+                                            const float* __restrict__ wsum, const float* __restrict__ st,
+                                            T* __restrict__ out) {
+  __shared__ __align__(16) float As[TK * LDS];
+  __shared__ __align__(16) float Bs[TK * LDS];
+  const int ntn = (g.N + TN - 1) / TN;
+  const int r0 = (blockIdx.x / ntn) * TM, n0 = (blockIdx.x % ntn) * TN;
+  const int c = blockIdx.y / g.G, grp = blockIdx.y % g.G, b = blockIdx.z;
+  const int tbase = c * g.Q;
+  float acc[4][4];
+  zero_acc(acc);
+  const float* wp = wsum + cb_idx(g, b, c, grp);
+  {
+    auto fa = [&](int m, int k) -> float {
+      const int rr = r0 + m;
+      if (rr >= g.Q) return 0.f;
+      if (MODE == 0) return (k <= rr) ? wp[(size_t)rr * g.Q + k] : 0.f;
+      return (k >= rr) ? wp[(size_t)k * g.Q + rr] : 0.f;
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int nn = n0 + n, t = tbase + k;
+      if (nn >= g.N || t >= g.L) return 0.f;
+      return ldf(Other + b * osb + t * osl + (long long)grp * g.N + nn);
+    };
+    if (MODE == 0) tile_mac<true, false>(acc, 0, min(g.Q, r0 + TM), fa, fb, As, Bs);
+    else tile_mac<false, false>(acc, r0, g.Q, fa, fb, As, Bs);
+  }
+  {
+    const int K2 = g.hpg * g.P;
+    auto fa = [&](int m, int k) -> float {
+      const int rr = r0 + m, t = tbase + rr;
+      if (rr >= g.Q || t >= g.L) return 0.f;
+      const int h = grp * g.hpg + k / g.P, p = k % g.P;
+      const size_t co = cs_idx(g, b, h, c);
+      if (MODE == 0) return expf(cs[co + rr]) * dys.get(g, b, t, h, p);
+      return expf(cs[co + g.Q - 1] - cs[co + rr]) * dtf[co + rr] *
+             ldf(x + b * g.xsb + t * g.xsl + (long long)h * g.P + p);
+    };
+    auto fb = [&](int n, int k) -> float {
+      const int nn = n0 + n;
+      if (nn >= g.N) return 0.f;
+      const int h = grp * g.hpg + k / g.P, p = k % g.P;
+      return st[st_idx(g, b, c, h) + (size_t)p * g.N + nn];
+    };
+    tile_mac<true, false>(acc, 0, K2, fa, fb, As, Bs);
+  }
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int rr = r0 + ty * 4 + r, t = tbase + rr;
+    if (rr >= g.Q || t >= g.L) continue;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int n = n0 + tx * 4 + cc;
+      if (n < g.N) stf(out + ((size_t)(b * (size_t)g.L + t) * g.G + grp) * g.N + n, acc[r][cc]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward: sdot[b,c,h] = <dS_end_c, S_end_c>, with S_end_c = state entering chunk c+1 (or final).
+__global__ void __launch_bounds__(NT) k_sdot(Geo g, const float* __restrict__ dS, const float* __restrict__ prev,
+                                             const float* __restrict__ fin, float* __restrict__ sdot) {
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int PN = g.P * g.N;
+  const float* a = dS + st_idx(g, b, c, h);
+  const float* s = (c + 1 < g.nc) ? prev + st_idx(g, b, c + 1, h) : fin + ((size_t)(b * g.H + h)) * PN;
+  float v = 0.f;
+  for (int e = threadIdx.x; e < PN; e += NT) v = fmaf(a[e], s[e], v);
+  __shared__ float red[NT / 32];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < NT / 32; ++i) t += red[i];
+    sdot[(size_t)(b * g.nc + c) * g.H + h] = t;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward: da_k = sum_{i>=k in chunk}(dcsp_i - dt_i*ddtd_i) + sdot ; ddt_k = ddtd_k + A*da_k ;
+// per-chunk partial sums for dA (= sum dt*da) and dD (= sum ddot).
+__global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, const float* __restrict__ dtf,
+                                            const float* __restrict__ dcsp, const float* __restrict__ ddtd,
+                                            const float* __restrict__ ddot, const float* __restrict__ sdot,
+                                            float* __restrict__ ddt, float* __restrict__ dapart,
+                                            float* __restrict__ ddpart) {
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, q = threadIdx.x;
+  __shared__ float wsum[NT / 32], red1[NT / 32], red2[NT / 32];
+  const size_t co = cs_idx(g, b, h, c);
+  // reverse the chunk so an inclusive prefix scan yields the suffix sum
+  const int qr = g.Q - 1 - q;
+  const bool ok = (q < g.Q);
+  const float d = ok ? dtf[co + qr] : 0.f;
+  const float dd = ok ? ddtd[co + qr] : 0.f;
+  float v = ok ? dcsp[co + qr] - d * dd : 0.f;
+  const int lane = q & 31, w = q >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    float n = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += n;
+  }
+  if (lane == 31) wsum[w] = v;
+  __syncthreads();
+  float base = 0.f;
+  for (int i = 0; i < w; ++i) base += wsum[i];
+  const float da = v + base + sdot[(size_t)(b * g.nc + c) * g.H + h];
+  const int t = c * g.Q + qr;
+  if (ok && t < g.L) ddt[((size_t)b * g.L + t) * g.H + h] = dd + A[h] * da;
+  float s1 = ok ? d * da : 0.f, s2 = ok ? ddot[co + qr] : 0.f;
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if (lane == 0) { red1[w] = s1; red2[w] = s2; }
+  __syncthreads();
+  if (q == 0) {
+    float a1 = 0.f, a2 = 0.f;
+    for (int i = 0; i < NT / 32; ++i) { a1 += red1[i]; a2 += red2[i]; }
+    dapart[(size_t)(b * g.nc + c) * g.H + h] = a1;
+    ddpart[(size_t)(b * g.nc + c) * g.H + h] = a2;
+  }
+}
+
+// dA[h] = sum over (b,c) of dapart ; dD likewise.  One block per head, fixed summation order.
+__global__ void __launch_bounds__(NT) k_reduce_heads(int rows, int H, const float* __restrict__ dapart,
+                                                     const float* __restrict__ ddpart, float* __restrict__ dA,
+                                                     float* __restrict__ dD) {
+  const int h = blockIdx.x;
+  float a = 0.f, d = 0.f;
+  for (int r = threadIdx.x; r < rows; r += NT) {
+    a += dapart[(size_t)r * H + h];
+    d += ddpart[(size_t)r * H + h];
+  }
+  __shared__ float r1[NT / 32], r2[NT / 32];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    d += __shfl_xor_sync(0xffffffffu, d, o);
+  }
+  if ((threadIdx.x & 31) == 0) { r1[threadIdx.x >> 5] = a; r2[threadIdx.x >> 5] = d; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ta = 0.f, td = 0.f;
+    for (int i = 0; i < NT / 32; ++i) { ta += r1[i]; td += r2[i]; }
+    dA[h] = ta;
+    if (dD) dD[h] = td;
+  }
+}
+
+}  // namespace
+
+// =============================================================================================
+// Host launchers
+// =============================================================================================
+template <typename T>
+static int fwd_stages_t(const Geo& g, const SsdFwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                        int stages) {
+  float* cs = (float*)(ws + w.cs);
+  float* dtf = (float*)(ws + w.dtf);
+  float* states = (float*)(ws + w.states);
+  float* cb = (float*)(ws + w.cb);
+  float* fin = p.final_state ? p.final_state : (float*)(ws + w.fin);
+  const T* x = (const T*)p.x;
+  const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
+  if (stages & SSD_STAGE_LOCAL) {
+    k_cumsum<T><<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf);
+    SSD_CUDA_CHECK_LAUNCH("cumsum");
+    DySrc<T> none{nullptr, nullptr, 0, 0};
+    k_chunk_state<T, 0><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, none, (const T*)p.Bm,
+                                                                       g.bsb, g.bsl, cs, dtf, states);
+    SSD_CUDA_CHECK_LAUNCH("chunk_state");
+  }
+  if (stages & SSD_STAGE_TOTAL) {
+    k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, nullptr, fin, 0);
+    SSD_CUDA_CHECK_LAUNCH("state_total");
+  }
+  if (stages & SSD_STAGE_FINISH) {
+    k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, p.init_state, fin, 0);
+    SSD_CUDA_CHECK_LAUNCH("state_passing");
+    k_cb<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, (const T*)p.Bm, (const T*)p.Cm, cb);
+    SSD_CUDA_CHECK_LAUNCH("cb");
+    if (p.y) {
+      k_chunk_scan<T, 0><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
+          g, x, (const T*)p.Cm, p.D, (const T*)p.z, cs, dtf, cb, states, (T*)p.y, nullptr, nullptr, nullptr,
+          nullptr, nullptr);
+      SSD_CUDA_CHECK_LAUNCH("chunk_scan");
+    }
+  }
+  return SSD_OK;
+}
+
+int simt_forward(const Geo& g, int dtype, const SsdFwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                 int stages) {
+  return dtype == SSD_BF16 ? fwd_stages_t<__nv_bfloat16>(g, p, ws, w, s, stages)
+                           : fwd_stages_t<float>(g, p, ws, w, s, stages);
+}
+
+template <typename T>
+static int bwd_stages_t(const Geo& g, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                        int stages) {
+  float* cs = (float*)(ws + w.cs);
+  float* dtf = (float*)(ws + w.dtf);
+  float* states = (float*)(ws + w.states);
+  float* cb = (float*)(ws + w.cb);
+  float* fin = (float*)(ws + w.fin);
+  float* dst = (float*)(ws + w.dstates);
+  float* dyp = (float*)(ws + w.dyp);
+  float* dcsp = (float*)(ws + w.dcsp);
+  float* ddtd = (float*)(ws + w.ddtd);
+  float* ddot = (float*)(ws + w.ddot);
+  float* sdot = (float*)(ws + w.sdot);
+  float* dapart = (float*)(ws + w.dapart);
+  float* ddpart = (float*)(ws + w.ddpart);
+  float* dini = p.dinit_state ? p.dinit_state : (float*)(ws + w.dini);
+  const T* x = (const T*)p.x;
+  const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
+  DySrc<T> dys{p.z ? dyp : nullptr, (const T*)p.dy, g.ysb, g.ysl};
+  if (stages & SSD_STAGE_LOCAL) {
+    if (!p.fwd_saved) {
+      SsdFwdPtrs f{};
+      f.x = p.x; f.dt = p.dt; f.A = p.A; f.Bm = p.Bm; f.Cm = p.Cm; f.D = p.D; f.z = p.z;
+      f.init_state = p.init_state; f.y = nullptr; f.final_state = fin;
+      int rc = fwd_stages_t<T>(g, f, ws, w, s, SSD_STAGE_LOCAL | SSD_STAGE_FINISH);
+      if (rc) return rc;
+    }
+    const size_t nq = (size_t)g.B * g.H * g.nc * g.Q * sizeof(float);
+    cudaMemsetAsync(dcsp, 0, nq, s);
+    cudaMemsetAsync(ddtd, 0, nq, s);
+    cudaMemsetAsync(ddot, 0, nq, s);
+    // forward recompute with the backward epilogue: dz, pre-gate dy, dcsp, ddot
+    k_chunk_scan<T, 1><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
+        g, x, (const T*)p.Cm, p.D, (const T*)p.z, cs, dtf, cb, states, nullptr, (const T*)p.dy, dyp, (T*)p.dz,
+        dcsp, ddot);
+    SSD_CUDA_CHECK_LAUNCH("chunk_scan_bwd_epilogue");
+    k_chunk_state<T, 1><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, dys, (const T*)p.Cm,
+                                                                       g.csb, g.csl, cs, dtf, dst);
+    SSD_CUDA_CHECK_LAUNCH("dstates_local");
+  }
+  if (stages & SSD_STAGE_TOTAL) {
+    k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, nullptr, dini, 1);
+    SSD_CUDA_CHECK_LAUNCH("dstate_total");
+  }
+  if (stages & SSD_STAGE_FINISH) {
+    k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, p.dfinal_state, dini, 1);
+    SSD_CUDA_CHECK_LAUNCH("dstate_passing");
+    k_sdot<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, dst, states, fin, sdot);
+    SSD_CUDA_CHECK_LAUNCH("sdot");
+    k_dx<T><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, p.D, dys, cs, dtf, cb, dst,
+                                                           (T*)p.dx, ddtd);
+    SSD_CUDA_CHECK_LAUNCH("dx");
+    k_dw<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, x, dys, cs, dtf, cb /* reused as wsum */);
+    SSD_CUDA_CHECK_LAUNCH("dw");
+    k_dbc<T, 0><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, g.bsb, g.bsl, dys, cs, dtf,
+                                                               cb, states, (T*)p.dC);
+    SSD_CUDA_CHECK_LAUNCH("dC");
+    k_dbc<T, 1><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Cm, g.csb, g.csl, dys, cs, dtf,
+                                                               cb, dst, (T*)p.dB);
+    SSD_CUDA_CHECK_LAUNCH("dB");
+    k_ddt<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, p.ddt, dapart, ddpart);
+    SSD_CUDA_CHECK_LAUNCH("ddt");
+    k_reduce_heads<<<g.H, NT, 0, s>>>(g.B * g.nc, g.H, dapart, ddpart, p.dA, p.dD);
+    SSD_CUDA_CHECK_LAUNCH("reduce_heads");
+  }
+  return SSD_OK;
+}
+
+int simt_backward(const Geo& g, int dtype, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                  int stages) {
+  return dtype == SSD_BF16 ? bwd_stages_t<__nv_bfloat16>(g, p, ws, w, s, stages)
+                           : bwd_stages_t<float>(g, p, ws, w, s, stages);
+}
+
+}  // namespace ssd
