@@ -1,0 +1,492 @@
+#!/usr/bin/env python
+"""Benchmark of the SSD hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg1|cfg2|cfg3|cfg4] [--impl reference]
+
+A step is one pass of the hot path over one batch of seeded synthetic input:
+  cfg1 (default, the policy-scale training batch)   forward + backward, metric tokens/s
+  cfg3 (Mamba-2-130M layer shapes, gated)           forward + backward, metric tokens/s
+  cfg4 (long sequence, sequence-parallel over ranks) forward + backward, metric tokens/s
+  cfg2 (streamed rollout, 8192 streams)              one state-update step, metric steps/s
+For N > 1 the driver launches one rank per GPU with torch.distributed.run; cfg1/cfg2/cfg3 shard
+the batch with no data-path collective (weak scaling: every rank runs the full per-GPU batch),
+cfg4 shards the sequence and exchanges slice totals over NCCL.  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the same path (plain torch ops on the host
+cores, standing in for the reference's tch-on-CPU path, which has no SSD code of its own) on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 20260811
+CFGS = {  # B, L, H, P, N, G, Q, has_z
+    "cfg1": dict(B=512, L=1024, H=8, P=32, N=64, G=1, Q=128, z=False, name="cfg1_policy_train"),
+    "cfg3": dict(B=16, L=4096, H=24, P=64, N=128, G=1, Q=256, z=True, name="cfg3_mamba2_130m_layer"),
+    "cfg4": dict(B=2, L=131072, H=24, P=64, N=128, G=1, Q=256, z=False, name="cfg4_long_seq_parallel"),
+    "cfg2": dict(B=8192, L=1, H=8, P=32, N=64, G=1, Q=1, z=False, name="cfg2_rollout_decode"),
+}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return float(j["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- algorithmic bytes (per token / per stream-step) -----------------------------------------
+def fwd_bytes_per_token(c, e=2):
+    hp, gn = c["H"] * c["P"], c["G"] * c["N"]
+    return (hp + c["H"] + 2 * gn + (hp if c["z"] else 0)) * e + hp * e
+
+
+def bwd_bytes_per_token(c, e=2):
+    hp, gn = c["H"] * c["P"], c["G"] * c["N"]
+    rd = (hp + c["H"] + 2 * gn + (hp if c["z"] else 0)) * e + hp * e
+    wr = hp * e + 4 * c["H"] + 2 * gn * e + (hp * e if c["z"] else 0)
+    return rd + wr
+
+
+def decode_bytes_per_stream(c, e=2):
+    return 2 * c["H"] * c["P"] * c["N"] * 4 + (2 * c["H"] * c["P"] + c["H"] + 2 * c["G"] * c["N"]) * e
+
+
+def kernel_bytes_per_token(name, c, e=2):
+    """Bytes of the operator's own inputs/outputs a kernel has to touch, per token; for the two
+    scan-over-chunks kernels (whose only operands are the fp32 chunk states) the state traffic."""
+    hp, gn, H = c["H"] * c["P"], c["G"] * c["N"], c["H"]
+    zb = hp * e if c["z"] else 0
+    st = 2 * H * c["P"] * c["N"] * 4 / c["Q"]
+    table = {
+        "cumsum": H * e, "chunk_state": (hp + gn) * e, "cb": 2 * gn * e,
+        "state_passing": st, "dstate_passing": st, "state_total": st / 2, "dstate_total": st / 2,
+        "chunk_scan": (2 * hp + gn) * e + zb, "chunk_scan_bwd_epilogue": (2 * hp + gn) * e + 2 * zb,
+        "dstates_local": (hp + gn) * e, "dx": (3 * hp + gn) * e, "dw": 2 * hp * e,
+        "dC": (2 * gn + hp) * e, "dB": (2 * gn + hp) * e, "ddt": 4 * H, "sdot": st / 2,
+    }
+    return table.get(name)
+
+
+# ---- synthetic inputs --------------------------------------------------------------------------
+def make_inputs(c, device, seed, dtype=torch.bfloat16, batch=None, seqlen=None):
+    """The workload's value distributions, drawn with a seeded generator on `device`."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    B, L, H, P, N, G = batch or c["B"], seqlen or c["L"], c["H"], c["P"], c["N"], c["G"]
+    r = lambda *s: torch.randn(*s, generator=g, device=device)
+    x = r(B, L, H, P)
+    u = torch.rand(H, generator=g, device=device)
+    dt0 = torch.exp(math.log(1e-3) + u * math.log(100.0))
+    dt_bias = dt0 + torch.log(-torch.expm1(-dt0))
+    dt = F.softplus(0.5 * r(B, L, H) + dt_bias)
+    A = -torch.exp(torch.rand(H, generator=g, device=device) * math.log(16.0))
+    out = dict(x=x.to(dtype), dt=dt.to(dtype), A=A, B=(r(B, L, G, N) / math.sqrt(N)).to(dtype),
+               C=(r(B, L, G, N) / math.sqrt(N)).to(dtype), D=torch.ones(H, device=device))
+    if c["z"]:
+        out["z"] = r(B, L, H, P).to(dtype)
+    out["dy"] = r(B, L, H, P).to(dtype)
+    return out
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, f"/tmp/ssd_bench_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in open(self.path):
+            p = [t.strip() for t in line.split(",")]
+            if len(p) < 8:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2])); pw.append(float(p[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, p[4:8]):
+                if v == "Active":
+                    reasons.add(n)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU baseline (the oracle's chunked torch restatement on the host cores) --------------------
+def cpu_fwd_bwd(c, sample_batch, threads, iters=2):
+    from oracle import ssd_oracle as O
+    torch.set_num_threads(threads)
+    inp = make_inputs(c, "cpu", SEED, batch=sample_batch, seqlen=min(c["L"], 16384))
+    L = inp["x"].shape[1]
+
+    def once():
+        leaves = {k: inp[k].float().requires_grad_(True) for k in ("x", "dt", "A", "B", "C", "D") + (("z",) if c["z"] else ())}
+        y, _ = O.ssd_chunked(leaves["x"], leaves["dt"], leaves["A"], leaves["B"], leaves["C"], leaves["D"],
+                             leaves.get("z"), None, chunk=c["Q"], dtype=torch.float32)
+        (y * inp["dy"].float()).sum().backward()
+
+    once()
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        once()
+    dt = (time.perf_counter() - t0) / iters
+    return sample_batch * L / dt, dt, L
+
+
+def cpu_decode(c, sample_streams, threads, steps=16):
+    from oracle import ssd_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(SEED)
+    S, H, P, N, G = sample_streams, c["H"], c["P"], c["N"], c["G"]
+    state = 0.1 * torch.randn(S, H, P, N, generator=g)
+    A = -torch.exp(torch.rand(H, generator=g) * math.log(16.0))
+    D = torch.ones(H)
+    xs = torch.randn(steps, S, H, P, generator=g).bfloat16()
+    dts = F.softplus(0.5 * torch.randn(steps, S, H, generator=g) - 3.0).bfloat16()
+    Bs = (torch.randn(steps, S, G, N, generator=g) / math.sqrt(N)).bfloat16()
+    Cs = (torch.randn(steps, S, G, N, generator=g) / math.sqrt(N)).bfloat16()
+    with torch.no_grad():
+        O.state_update(state, xs[0], dts[0], A, Bs[0], Cs[0], D)
+        t0 = time.perf_counter()
+        for t in range(steps):
+            _, state = O.state_update(state, xs[t], dts[t], A, Bs[t], Cs[t], D)
+        dt = (time.perf_counter() - t0) / steps
+    return dt
+
+
+def run_reference(args, c):
+    """The CPU path on all host cores, bounded sample per step; rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cores = os.cpu_count() or 1
+    decode = args.workload == "cfg2"
+    times = []
+    if decode:
+        sample = 512
+        for _ in range(args.warmup + args.steps):
+            times.append(cpu_decode(c, sample, cores, steps=4))
+        times = times[args.warmup:]
+        step_s = statistics.mean(times) * (c["B"] / sample)      # scaled to the full stream count
+        value, unit, metric = 1.0 / step_s, "steps/s", "ssd_decode_steps_per_s"
+        desc = f"{sample} of {c['B']} streams per step, time scaled by {c['B'] // sample}"
+    else:
+        sample = 64 if args.workload == "cfg1" else 1
+        for _ in range(args.warmup + args.steps):
+            tps, dt, L = cpu_fwd_bwd(c, sample, cores, iters=1)
+            times.append(dt)
+        times = times[args.warmup:]
+        tokens = sample * min(c["L"], 16384)
+        value, unit, metric = tokens / statistics.mean(times), "tokens/s", "ssd_fwd_bwd_tokens_per_s"
+        desc = f"batch {sample} of {c['B']}, seqlen {min(c['L'], 16384)} of {c['L']}, fwd+bwd, fp32 torch ops"
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(times),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": c["name"], "sample": desc},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arms ------------------------------------------------------------------------------------
+def dist_setup(n):
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def max_over_ranks(ms, world, device):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed(fn, steps, world, device):
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world, device)
+
+
+def kernel_profile(fn, reps, device):
+    from trading_bot_0_b200 import _lib
+    agg = {}
+    for _ in range(reps):
+        with _lib.profile(torch.cuda.current_stream(device).cuda_stream) as p:
+            fn()
+        for name, ms in p.entries:
+            a = agg.setdefault(name, [0, 0.0])
+            a[0] += 1
+            a[1] += ms
+    return {k: (v[0] // reps, v[1] / v[0]) for k, v in agg.items()}   # launches per step, avg ms per launch
+
+
+def run_train(args, c, rank, world, local):
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib
+    from trading_bot_0_b200.host import HostFwdBwd
+    dev = torch.device("cuda", local)
+    sp_mode = args.workload == "cfg4"
+    L_loc = c["L"] // world if sp_mode else c["L"]
+    inp = make_inputs(c, dev, SEED + rank, seqlen=L_loc)
+    z = inp.get("z")
+    tokens_rank = c["B"] * L_loc
+    dims = T.make_dims(inp["x"], inp["dt"], inp["B"], inp["C"], c["Q"], z=z, algo=args.algo)
+    ws = T.alloc_workspace(dims, dev, backward=True)
+    y = torch.empty_like(inp["x"])
+    out = {}
+
+    if sp_mode and world > 1:
+        from trading_bot_0_b200 import sp
+
+        def step():
+            yy, fin, ctx = sp.sp_forward(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"], z, None,
+                                         chunk=c["Q"], algo=args.algo)
+            sp.sp_backward(inp["dy"], ctx)
+    else:
+        def step():
+            T.forward(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"], z, chunk=c["Q"], algo=args.algo,
+                      workspace=ws, y=y, return_final_state=False)
+            T.backward(inp["dy"], inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"], z, chunk=c["Q"],
+                       algo=args.algo, workspace=ws, fwd_saved=True, out=out)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = _lib.launch_count()
+    ms = timed(step, args.steps, world, dev)
+    launches = _lib.launch_count() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms / args.steps
+    tokens_job = tokens_rank * world
+    value = tokens_job / (ms_step * 1e-3)
+
+    prof = kernel_profile(step, 3, dev) if not (sp_mode and world > 1) else {}
+
+    # end to end through the host-buffer entry point: pinned host tensors in, pinned host tensors out
+    e2e = None
+    if not sp_mode:
+        hb = HostFwdBwd(c["B"], c["L"], c["H"], c["P"], c["N"], c["G"], c["Q"], torch.bfloat16, has_z=c["z"], device=dev,
+                        algo=args.algo)
+        hin = {k: inp[k].cpu().pin_memory() for k in ("x", "dt", "B", "C", "dy") + (("z",) if c["z"] else ())}
+        hout = {"y": torch.empty_like(hin["x"]), "dx": torch.empty_like(hin["x"]),
+                "ddt": torch.empty(c["B"], c["L"], c["H"], dtype=torch.float32).pin_memory(),
+                "dB": torch.empty_like(hin["B"]), "dC": torch.empty_like(hin["C"]),
+                "dA": torch.empty(c["H"]).pin_memory(), "dD": torch.empty(c["H"]).pin_memory()}
+        for k in ("y", "dx", "dB", "dC"):
+            hout[k] = hout[k].pin_memory()
+        if c["z"]:
+            hout["dz"] = torch.empty_like(hin["x"]).pin_memory()
+        e2e_step = lambda: hb.run(hin, inp["A"], inp["D"], hout)
+        e2e_step()
+        e2e_steps = max(2, min(args.steps, 5))
+        ems = timed(e2e_step, e2e_steps, world, dev) / e2e_steps
+        h2d, d2h = hb.bytes_per_call()
+        e2e = {"value": tokens_job / (ems * 1e-3), "unit": "tokens/s", "ms_per_step": ems,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+        del hb, hin, hout
+
+    if rank != 0:
+        return
+    peak, peak_kind = peaks()
+    roof = None
+    if prof:
+        dom = max(prof.items(), key=lambda kv: kv[1][0] * kv[1][1])
+        name, (n_launch, avg_ms) = dom
+        bpt = kernel_bytes_per_token(name, c)
+        if bpt is not None:
+            ach = bpt * tokens_rank / (avg_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "peak_kind": peak_kind, "traffic": None, "avg_launch_ms": avg_ms,
+                    "algorithmic_bytes_per_launch": bpt * tokens_rank}
+    op_bytes = (fwd_bytes_per_token(c) + bwd_bytes_per_token(c)) * tokens_rank
+    op_ach = op_bytes / (ms_step * 1e-3) / 1e9
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        sample = 64 if args.workload == "cfg1" else 1
+        cores = os.cpu_count() or 1
+        tps, dt_s, Ls = cpu_fwd_bwd(c, sample, cores, iters=2)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"batch {sample} of {c['B']}, seqlen {Ls} of {c['L']}, fwd+bwd, chunked fp32 torch ops, {dt_s:.2f} s/iter"}
+    line = {"metric": "ssd_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if sp_mode and args.strong else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"{c['name']}: B{c['B']} L{c['L']} H{c['H']} P{c['P']} N{c['N']} G{c['G']} Q{c['Q']}"
+                                   f"{' z-gated' if c['z'] else ''} fwd+bwd per GPU" + (" (sequence sharded)" if sp_mode else ""),
+                       "algo": args.algo, "l2": f"inputs+outputs {op_bytes / 1e6:.0f} MB per step, larger than the 126 MB L2",
+                       "parallelism": "sequence-parallel" if sp_mode else f"batch-sharded x{world}, no collective"},
+            "roofline": roof,
+            "op_roofline": {"bound": "hbm", "achieved": op_ach, "peak": peak, "unit": "GB/s", "frac": op_ach / peak,
+                            "peak_kind": peak_kind, "algorithmic_bytes_per_step": op_bytes},
+            "kernels": {k: {"launches_per_step": v[0], "avg_ms": round(v[1], 5)} for k, v in prof.items()},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
+def run_decode(args, c, rank, world, local):
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib
+    from trading_bot_0_b200.host import HostStep
+    dev = torch.device("cuda", local)
+    S, H, P, N, G = c["B"], c["H"], c["P"], c["N"], c["G"]
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    ring = args.ring                                     # distinct pre-drawn steps held in HBM
+    state = 0.1 * torch.randn(S, H, P, N, generator=g, device=dev)
+    A = -torch.exp(torch.rand(H, generator=g, device=dev) * math.log(16.0))
+    D = torch.ones(H, device=dev)
+    u = torch.rand(H, generator=g, device=dev)
+    dt0 = torch.exp(math.log(1e-3) + u * math.log(100.0))
+    dt_bias = dt0 + torch.log(-torch.expm1(-dt0))
+    xs = torch.randn(ring, S, H, P, generator=g, device=dev).bfloat16()
+    dts = F.softplus(0.5 * torch.randn(ring, S, H, generator=g, device=dev) + dt_bias).bfloat16()
+    Bs = (torch.randn(ring, S, G, N, generator=g, device=dev) / math.sqrt(N)).bfloat16()
+    Cs = (torch.randn(ring, S, G, N, generator=g, device=dev) / math.sqrt(N)).bfloat16()
+    y = torch.empty(S, H, P, dtype=torch.bfloat16, device=dev)
+    st = T.StreamState(state)
+    k = [0]
+
+    def step():
+        i = k[0] % ring
+        k[0] += 1
+        st.step(xs[i], dts[i], A, Bs[i], Cs[i], D, y=y)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = _lib.launch_count()
+    ms = timed(step, args.steps, world, dev)
+    launches = _lib.launch_count() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms / args.steps
+    prof = kernel_profile(step, 20, dev)
+    hs = HostStep(state, G)
+    hx, hdt, hB, hC = (t[0].cpu().pin_memory() for t in (xs, dts, Bs, Cs))
+    hy = torch.empty(S, H, P, dtype=torch.bfloat16).pin_memory()
+    e2e_step = lambda: hs.step(hx, hdt, hB, hC, A, D, hy)
+    e2e_step()
+    ems = timed(e2e_step, args.steps, world, dev) / args.steps
+    if rank != 0:
+        return
+    peak, peak_kind = peaks()
+    name, (n_launch, avg_ms) = max(prof.items(), key=lambda kv: kv[1][0] * kv[1][1])
+    bytes_step = decode_bytes_per_stream(c) * S
+    ach = bytes_step / (avg_ms * 1e-3) / 1e9
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        cores = os.cpu_count() or 1
+        sample = 512
+        dt_s = cpu_decode(c, sample, cores, steps=16)
+        cpu = {"value": 1.0 / (dt_s * S / sample), "unit": "steps/s", "cores": cores, "kind": "port",
+               "sample": f"{sample} of {S} streams, 16 steps, time scaled by {S // sample}"}
+    h2d, d2h = hs.bytes_per_call()
+    line = {"metric": "ssd_decode_steps_per_s", "value": 1e3 / ms_step, "unit": "steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{c['name']}: {S} streams per GPU, H{H} P{P} N{N} G{G}, fp32 state, bf16 step vectors",
+                       "streams_total": S * world, "l2": f"state {S * H * P * N * 4 / 1e6:.0f} MB per GPU, larger than the 126 MB L2",
+                       "inputs": f"{ring} distinct pre-drawn steps cycled", "parallelism": f"stream-sharded x{world}, no collective"},
+            "roofline": {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_kind": peak_kind, "traffic": None, "avg_launch_ms": avg_ms,
+                         "algorithmic_bytes_per_launch": bytes_step},
+            "cpu_baseline": cpu,
+            "e2e": {"value": 1e3 / ems, "unit": "steps/s", "ms_per_step": ems, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(CFGS))
+    ap.add_argument("--algo", default="auto", choices=["auto", "fp32_cores", "tensor"])
+    ap.add_argument("--ring", type=int, default=64, help="cfg2: distinct pre-drawn steps kept in HBM")
+    ap.add_argument("--strong", action="store_true", help="cfg4: label the run strong scaling (fixed global L)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    c = CFGS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, c)
+        return
+    rank, world, local = dist_setup(args.gpus)
+    try:
+        if args.workload == "cfg2":
+            run_decode(args, c, rank, world, local)
+        else:
+            run_train(args, c, rank, world, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

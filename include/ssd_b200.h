@@ -202,6 +202,19 @@ SSD_API int32_t ssd_sp_prefix_state(const float* gathered_states, const float* g
  * this thread.  Mirrors `get_and_reset_last_err` (trading_bots/src/torch/cuda/graph.rs:107-118). */
 SSD_API const char* ssd_last_error(void);
 
+/*
+ * Tracing.  ssd_launch_count: kernels this library has launched in this process (all threads).
+ * ssd_profile_begin/end: between the two calls every kernel launched from THIS thread gets a
+ * CUDA event recorded behind it on its launch stream; _end synchronises on the last event and
+ * returns the number of entries written: newline-separated kernel names into `names` and the
+ * matching device durations in milliseconds into `ms`.  Not for use during stream capture.  The
+ * reference times at wall-clock granularity only (`Instant` around rollout/update,
+ * trading_bots/src/torch/train/rollout.rs:24,237); this is the kernel-level counterpart.
+ */
+SSD_API int64_t ssd_launch_count(void);
+SSD_API int32_t ssd_profile_begin(void* cuda_stream);
+SSD_API int32_t ssd_profile_end(char* names, size_t names_bytes, float* ms, int32_t max_entries);
+
 /* Library version and the SM architecture it was compiled for (100 for sm_100a). */
 SSD_API int32_t ssd_version(void);
 SSD_API int32_t ssd_compiled_arch(void);

@@ -20,7 +20,8 @@ STAGE_LOCAL, STAGE_TOTAL, STAGE_FINISH = 1, 2, 4
 EXPORTS = [
     "ssd_workspace_bytes", "ssd_forward", "ssd_backward", "ssd_forward_staged", "ssd_backward_staged",
     "ssd_state_update", "ssd_state_reset_rows", "ssd_sp_total_logdecay", "ssd_sp_prefix_state",
-    "ssd_last_error", "ssd_version", "ssd_compiled_arch",
+    "ssd_last_error", "ssd_version", "ssd_compiled_arch", "ssd_launch_count", "ssd_profile_begin",
+    "ssd_profile_end",
 ]
 
 
@@ -94,6 +95,12 @@ def load() -> C.CDLL:
     lib.ssd_sp_prefix_state.argtypes = [vp, vp, i32, i32, i32, i64, i64, vp, vp, vp]
     lib.ssd_last_error.restype = C.c_char_p
     lib.ssd_last_error.argtypes = []
+    lib.ssd_launch_count.restype = i64
+    lib.ssd_launch_count.argtypes = []
+    lib.ssd_profile_begin.restype = i32
+    lib.ssd_profile_begin.argtypes = [vp]
+    lib.ssd_profile_end.restype = i32
+    lib.ssd_profile_end.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), i32]
     lib.ssd_version.restype = i32
     lib.ssd_compiled_arch.restype = i32
     _lib = lib
@@ -103,3 +110,30 @@ def load() -> C.CDLL:
 def check(rc: int) -> None:
     if rc != 0:
         raise SsdError(rc, load().ssd_last_error().decode("utf-8", "replace"))
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(load().ssd_launch_count())
+
+
+class profile:
+    """Context manager: per-kernel device times (ms) of every library launch made inside it from
+    this thread.  `.entries` is a list of (kernel name, ms) in launch order."""
+
+    def __init__(self, stream_ptr: int):
+        self.stream_ptr = stream_ptr
+        self.entries = []
+
+    def __enter__(self):
+        check(load().ssd_profile_begin(C.c_void_p(self.stream_ptr)))
+        return self
+
+    def __exit__(self, *exc):
+        names = C.create_string_buffer(1 << 16)
+        ms = (C.c_float * 256)()
+        n = load().ssd_profile_end(names, len(names), ms, 256)
+        if n < 0:
+            check(n)
+        self.entries = list(zip(names.value.decode().split("\n")[:n], [float(ms[i]) for i in range(n)]))
+        return False

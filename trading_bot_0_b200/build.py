@@ -15,7 +15,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libssd_b200.so"
 SOURCES = ["ssd_api.cu", "ssd_simt.cu", "ssd_decode.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared", "-lcuda"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared"]
 
 
 def nvcc_path() -> str:

@@ -38,6 +38,11 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + __expf
 void set_error(const char* fmt, ...);
 void clear_error();
 
+// Bookkeeping after every kernel launch: counts it and, while a profile is open on this thread,
+// records an event behind it on the launch stream.
+void after_launch(const char* what, cudaStream_t s);
+
+// Uses the cudaStream_t named `s` in the enclosing scope.
 #define SSD_CUDA_CHECK_LAUNCH(what)                                              \
   do {                                                                           \
     cudaError_t e__ = cudaGetLastError();                                        \
@@ -45,6 +50,7 @@ void clear_error();
       ::ssd::set_error("%s: launch failed: %s", what, cudaGetErrorString(e__));  \
       return SSD_ERR_CUDA;                                                       \
     }                                                                            \
+    ::ssd::after_launch(what, s);                                                \
   } while (0)
 
 static inline int cdiv(int a, int b) { return (a + b - 1) / b; }

@@ -1,4 +1,5 @@
 // extern "C" entry points: argument validation, workspace layout, kernel-family dispatch.
+#include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -17,6 +18,29 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 void clear_error() { g_err[0] = 0; }
+
+// ---- launch counter and per-kernel event profile -------------------------------------------
+static std::atomic<long long> g_launches{0};
+constexpr int kMaxProf = 256;
+struct Profile {
+  bool on = false;
+  int n = 0;
+  cudaEvent_t ev[kMaxProf + 1];
+  const char* name[kMaxProf];
+};
+static thread_local Profile g_prof;
+
+void after_launch(const char* what, cudaStream_t s) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  Profile& p = g_prof;
+  if (p.on && p.n < kMaxProf) {
+    if (cudaEventCreate(&p.ev[p.n + 1]) == cudaSuccess) {
+      cudaEventRecord(p.ev[p.n + 1], s);
+      p.name[p.n] = what;
+      ++p.n;
+    }
+  }
+}
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -99,6 +123,46 @@ extern "C" {
 const char* ssd_last_error(void) { return g_err; }
 int32_t ssd_version(void) { return 1; }
 int32_t ssd_compiled_arch(void) { return 100; }
+int64_t ssd_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int32_t ssd_profile_begin(void* cuda_stream) {
+  clear_error();
+  Profile& p = g_prof;
+  if (p.on) { set_error("a profile is already open on this thread"); return SSD_ERR_UNSUPPORTED; }
+  if (cudaEventCreate(&p.ev[0]) != cudaSuccess) { set_error("cudaEventCreate failed"); return SSD_ERR_CUDA; }
+  cudaEventRecord(p.ev[0], (cudaStream_t)cuda_stream);
+  p.n = 0;
+  p.on = true;
+  return SSD_OK;
+}
+
+int32_t ssd_profile_end(char* names, size_t names_bytes, float* ms, int32_t max_entries) {
+  clear_error();
+  Profile& p = g_prof;
+  if (!p.on) { set_error("no profile is open on this thread"); return SSD_ERR_UNSUPPORTED; }
+  p.on = false;
+  int rc = SSD_OK;
+  if (p.n > 0 && cudaEventSynchronize(p.ev[p.n]) != cudaSuccess) { set_error("cudaEventSynchronize failed"); rc = SSD_ERR_CUDA; }
+  size_t off = 0;
+  int out = 0;
+  for (int i = 0; i < p.n; ++i) {
+    float t = 0.f;
+    if (rc == SSD_OK) cudaEventElapsedTime(&t, p.ev[i], p.ev[i + 1]);
+    if (i < max_entries && ms && names) {
+      const size_t len = strlen(p.name[i]);
+      if (off + len + 2 <= names_bytes) {
+        memcpy(names + off, p.name[i], len);
+        off += len;
+        names[off++] = '\n';
+        names[off] = 0;
+        ms[out++] = t;
+      }
+    }
+  }
+  for (int i = 0; i <= p.n; ++i) cudaEventDestroy(p.ev[i]);
+  p.n = 0;
+  return rc == SSD_OK ? out : rc;
+}
 
 size_t ssd_workspace_bytes(const SsdDims* dims, int32_t pass) {
   clear_error();
