@@ -16,6 +16,7 @@ struct Geo {
 
 // Workspace segments (offsets in bytes from the workspace base; 0-size segments unused).
 struct WsLayout {
+  size_t status;                                     // 256-byte status block (int32 code first)
   size_t cs, dtf, states, fin, cb;                   // forward
   size_t dstates, dyp, dcsp, ddtd, ddot, sdot, dapart, ddpart, dini;  // backward extras
   size_t total_fwd, total_bwd;

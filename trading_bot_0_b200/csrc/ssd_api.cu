@@ -97,6 +97,7 @@ static void make_layout(const Geo& g, bool has_z, WsLayout* w) {
   const size_t nbh = (size_t)g.B * g.nc * g.H * f;
   size_t o = 0;
   auto take = [&](size_t bytes) { size_t r = o; o += align256(bytes); return r; };
+  w->status = take(256);
   w->cs = take(nq); w->dtf = take(nq); w->states = take(nst); w->fin = take(nfin); w->cb = take(ncb);
   w->total_fwd = o;
   w->dstates = take(nst);
@@ -105,6 +106,15 @@ static void make_layout(const Geo& g, bool has_z, WsLayout* w) {
   w->sdot = take(nbh); w->dapart = take(nbh); w->ddpart = take(nbh);
   w->dini = take(nfin);
   w->total_bwd = o;
+}
+
+// Kernel-family choice: 1 = tensor cores, 0 = CUDA cores, <0 = error.
+static int pick_family(const Geo& g, const SsdDims* d) {
+  if (d->algo == SSD_ALGO_FP32_CORES) return 0;
+  const char* why = "";
+  if (tensor_supported(g, d->dtype, &why)) return 1;
+  if (d->algo == SSD_ALGO_TENSOR) { set_error("algo=TENSOR not possible for these dims: %s", why); return SSD_ERR_UNSUPPORTED; }
+  return 0;
 }
 
 static int check_ws(const void* ws, size_t have, size_t need) {
@@ -193,7 +203,9 @@ int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* works
   cudaStream_t s = (cudaStream_t)cuda_stream;
   SsdFwdPtrs q = *p;
   q.final_state = nullptr;  // kernels always leave the final state in the workspace; copied out below
-  rc = simt_forward(g, dims->dtype, q, (char*)workspace, w, s, stages);
+  const int fam = pick_family(g, dims);
+  if (fam < 0) return fam;
+  rc = run_forward(g, dims->dtype, fam == 1, q, (char*)workspace, w, s, stages);
   if (rc) return rc;
   if (p->final_state && (stages & (SSD_STAGE_TOTAL | SSD_STAGE_FINISH))) {
     cudaError_t e = cudaMemcpyAsync(p->final_state, (char*)workspace + w.fin,
@@ -227,7 +239,9 @@ int32_t ssd_backward_staged(const SsdDims* dims, const SsdBwdPtrs* p, void* work
   make_layout(g, dims->has_z != 0, &w);
   rc = check_ws(workspace, workspace_bytes, w.total_bwd);
   if (rc) return rc;
-  return simt_backward(g, dims->dtype, *p, (char*)workspace, w, (cudaStream_t)cuda_stream, stages);
+  const int fam = pick_family(g, dims);
+  if (fam < 0) return fam;
+  return run_backward(g, dims->dtype, fam == 1, *p, (char*)workspace, w, (cudaStream_t)cuda_stream, stages);
 }
 
 int32_t ssd_backward(const SsdDims* dims, const SsdBwdPtrs* p, void* workspace, size_t workspace_bytes,

@@ -620,8 +620,9 @@ __global__ void __launch_bounds__(NT) k_reduce_heads(int rows, int H, const floa
 // Host launchers
 // =============================================================================================
 template <typename T>
-static int fwd_stages_t(const Geo& g, const SsdFwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
-                        int stages) {
+static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                        int stages, bool need_cb) {
+  int* status = (int*)(ws + w.status);
   float* cs = (float*)(ws + w.cs);
   float* dtf = (float*)(ws + w.dtf);
   float* states = (float*)(ws + w.states);
@@ -630,23 +631,44 @@ static int fwd_stages_t(const Geo& g, const SsdFwdPtrs& p, char* ws, const WsLay
   const T* x = (const T*)p.x;
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   if (stages & SSD_STAGE_LOCAL) {
+    cudaMemsetAsync(status, 0, 256, s);
     k_cumsum<T><<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
-    DySrc<T> none{nullptr, nullptr, 0, 0};
-    k_chunk_state<T, 0><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, none, (const T*)p.Bm,
-                                                                       g.bsb, g.bsl, cs, dtf, states);
-    SSD_CUDA_CHECK_LAUNCH("chunk_state");
+    if (tc) {
+      int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, cs, dtf, states, status, s);
+      if (rc) return rc;
+    } else {
+      DySrc<T> none{nullptr, nullptr, 0, 0};
+      k_chunk_state<T, 0><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, none, (const T*)p.Bm,
+                                                                         g.bsb, g.bsl, cs, dtf, states);
+      SSD_CUDA_CHECK_LAUNCH("chunk_state");
+    }
   }
   if (stages & SSD_STAGE_TOTAL) {
-    k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, nullptr, fin, 0);
-    SSD_CUDA_CHECK_LAUNCH("state_total");
+    if (tc) {
+      int rc = tensor_state_passing(g, states, cs, nullptr, fin, 0, false, s);
+      if (rc) return rc;
+    } else {
+      k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, nullptr, fin, 0);
+      SSD_CUDA_CHECK_LAUNCH("state_total");
+    }
   }
   if (stages & SSD_STAGE_FINISH) {
-    k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, p.init_state, fin, 0);
-    SSD_CUDA_CHECK_LAUNCH("state_passing");
-    k_cb<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, (const T*)p.Bm, (const T*)p.Cm, cb);
-    SSD_CUDA_CHECK_LAUNCH("cb");
-    if (p.y) {
+    if (tc) {
+      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, 0, true, s);
+      if (rc) return rc;
+    } else {
+      k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, p.init_state, fin, 0);
+      SSD_CUDA_CHECK_LAUNCH("state_passing");
+    }
+    if (!tc || need_cb) {
+      k_cb<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, (const T*)p.Bm, (const T*)p.Cm, cb);
+      SSD_CUDA_CHECK_LAUNCH("cb");
+    }
+    if (p.y && tc) {
+      int rc = tensor_chunk_scan(g, p, cs, dtf, states, status, s);
+      if (rc) return rc;
+    } else if (p.y) {
       k_chunk_scan<T, 0><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
           g, x, (const T*)p.Cm, p.D, (const T*)p.z, cs, dtf, cb, states, (T*)p.y, nullptr, nullptr, nullptr,
           nullptr, nullptr);
@@ -656,15 +678,16 @@ static int fwd_stages_t(const Geo& g, const SsdFwdPtrs& p, char* ws, const WsLay
   return SSD_OK;
 }
 
-int simt_forward(const Geo& g, int dtype, const SsdFwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
-                 int stages) {
-  return dtype == SSD_BF16 ? fwd_stages_t<__nv_bfloat16>(g, p, ws, w, s, stages)
-                           : fwd_stages_t<float>(g, p, ws, w, s, stages);
+int run_forward(const Geo& g, int dtype, bool tc, const SsdFwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                int stages) {
+  return dtype == SSD_BF16 ? fwd_stages_t<__nv_bfloat16>(g, tc, p, ws, w, s, stages, false)
+                           : fwd_stages_t<float>(g, false, p, ws, w, s, stages, false);
 }
 
 template <typename T>
-static int bwd_stages_t(const Geo& g, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
                         int stages) {
+  int* status = (int*)(ws + w.status);
   float* cs = (float*)(ws + w.cs);
   float* dtf = (float*)(ws + w.dtf);
   float* states = (float*)(ws + w.states);
@@ -682,47 +705,75 @@ static int bwd_stages_t(const Geo& g, const SsdBwdPtrs& p, char* ws, const WsLay
   const T* x = (const T*)p.x;
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   DySrc<T> dys{p.z ? dyp : nullptr, (const T*)p.dy, g.ysb, g.ysl};
+  // tensor-core family: the pre-gate gradient is dy itself, or (gated) a dense bf16 copy in the workspace
+  const void* tc_dy = p.z ? (const void*)dyp : p.dy;
+  const bool tc_dense = p.z != nullptr;
   if (stages & SSD_STAGE_LOCAL) {
     if (!p.fwd_saved) {
       SsdFwdPtrs f{};
       f.x = p.x; f.dt = p.dt; f.A = p.A; f.Bm = p.Bm; f.Cm = p.Cm; f.D = p.D; f.z = p.z;
       f.init_state = p.init_state; f.y = nullptr; f.final_state = fin;
-      int rc = fwd_stages_t<T>(g, f, ws, w, s, SSD_STAGE_LOCAL | SSD_STAGE_FINISH);
+      int rc = fwd_stages_t<T>(g, tc, f, ws, w, s, SSD_STAGE_LOCAL | SSD_STAGE_FINISH, false);
       if (rc) return rc;
     }
     const size_t nq = (size_t)g.B * g.H * g.nc * g.Q * sizeof(float);
     cudaMemsetAsync(dcsp, 0, nq, s);
     cudaMemsetAsync(ddtd, 0, nq, s);
     cudaMemsetAsync(ddot, 0, nq, s);
-    // forward recompute with the backward epilogue: dz, pre-gate dy, dcsp, ddot
-    k_chunk_scan<T, 1><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
-        g, x, (const T*)p.Cm, p.D, (const T*)p.z, cs, dtf, cb, states, nullptr, (const T*)p.dy, dyp, (T*)p.dz,
-        dcsp, ddot);
-    SSD_CUDA_CHECK_LAUNCH("chunk_scan_bwd_epilogue");
-    k_chunk_state<T, 1><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, dys, (const T*)p.Cm,
-                                                                       g.csb, g.csl, cs, dtf, dst);
-    SSD_CUDA_CHECK_LAUNCH("dstates_local");
+    if (tc) {
+      int rc = tensor_scan_bwd(g, p, cs, dtf, states, dyp, dcsp, ddot, status, s);
+      if (rc) return rc;
+      rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
+                              tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, cs, dtf, dst, status, s);
+      if (rc) return rc;
+    } else {
+      // forward recompute with the backward epilogue: dz, pre-gate dy, dcsp, ddot
+      k_chunk_scan<T, 1><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
+          g, x, (const T*)p.Cm, p.D, (const T*)p.z, cs, dtf, cb, states, nullptr, (const T*)p.dy, dyp, (T*)p.dz,
+          dcsp, ddot);
+      SSD_CUDA_CHECK_LAUNCH("chunk_scan_bwd_epilogue");
+      k_chunk_state<T, 1><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, dys, (const T*)p.Cm,
+                                                                         g.csb, g.csl, cs, dtf, dst);
+      SSD_CUDA_CHECK_LAUNCH("dstates_local");
+    }
   }
   if (stages & SSD_STAGE_TOTAL) {
-    k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, nullptr, dini, 1);
-    SSD_CUDA_CHECK_LAUNCH("dstate_total");
+    if (tc) {
+      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, 1, false, s);
+      if (rc) return rc;
+    } else {
+      k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, nullptr, dini, 1);
+      SSD_CUDA_CHECK_LAUNCH("dstate_total");
+    }
   }
   if (stages & SSD_STAGE_FINISH) {
-    k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, p.dfinal_state, dini, 1);
-    SSD_CUDA_CHECK_LAUNCH("dstate_passing");
+    if (tc) {
+      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, 1, true, s);
+      if (rc) return rc;
+    } else {
+      k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, p.dfinal_state, dini, 1);
+      SSD_CUDA_CHECK_LAUNCH("dstate_passing");
+    }
     k_sdot<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, dst, states, fin, sdot);
     SSD_CUDA_CHECK_LAUNCH("sdot");
-    k_dx<T><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, p.D, dys, cs, dtf, cb, dst,
-                                                           (T*)p.dx, ddtd);
-    SSD_CUDA_CHECK_LAUNCH("dx");
-    k_dw<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, x, dys, cs, dtf, cb /* reused as wsum */);
-    SSD_CUDA_CHECK_LAUNCH("dw");
-    k_dbc<T, 0><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, g.bsb, g.bsl, dys, cs, dtf,
-                                                               cb, states, (T*)p.dC);
-    SSD_CUDA_CHECK_LAUNCH("dC");
-    k_dbc<T, 1><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Cm, g.csb, g.csl, dys, cs, dtf,
-                                                               cb, dst, (T*)p.dB);
-    SSD_CUDA_CHECK_LAUNCH("dB");
+    if (tc) {
+      int rc = tensor_dx(g, p, tc_dy, tc_dense, cs, dtf, dst, ddtd, status, s);
+      if (rc) return rc;
+      rc = tensor_dbc(g, p, tc_dy, tc_dense, cs, dtf, states, dst, status, s);
+      if (rc) return rc;
+    } else {
+      k_dx<T><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, p.D, dys, cs, dtf, cb, dst,
+                                                             (T*)p.dx, ddtd);
+      SSD_CUDA_CHECK_LAUNCH("dx");
+      k_dw<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, x, dys, cs, dtf, cb /* reused as wsum */);
+      SSD_CUDA_CHECK_LAUNCH("dw");
+      k_dbc<T, 0><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, g.bsb, g.bsl, dys, cs, dtf,
+                                                                 cb, states, (T*)p.dC);
+      SSD_CUDA_CHECK_LAUNCH("dC");
+      k_dbc<T, 1><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Cm, g.csb, g.csl, dys, cs, dtf,
+                                                                 cb, dst, (T*)p.dB);
+      SSD_CUDA_CHECK_LAUNCH("dB");
+    }
     k_ddt<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, p.ddt, dapart, ddpart);
     SSD_CUDA_CHECK_LAUNCH("ddt");
     k_reduce_heads<<<g.H, NT, 0, s>>>(g.B * g.nc, g.H, dapart, ddpart, p.dA, p.dD);
@@ -731,10 +782,10 @@ static int bwd_stages_t(const Geo& g, const SsdBwdPtrs& p, char* ws, const WsLay
   return SSD_OK;
 }
 
-int simt_backward(const Geo& g, int dtype, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
-                  int stages) {
-  return dtype == SSD_BF16 ? bwd_stages_t<__nv_bfloat16>(g, p, ws, w, s, stages)
-                           : bwd_stages_t<float>(g, p, ws, w, s, stages);
+int run_backward(const Geo& g, int dtype, bool tc, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
+                 int stages) {
+  return dtype == SSD_BF16 ? bwd_stages_t<__nv_bfloat16>(g, tc, p, ws, w, s, stages)
+                           : bwd_stages_t<float>(g, false, p, ws, w, s, stages);
 }
 
 }  // namespace ssd

@@ -1,0 +1,858 @@
+// bf16 tensor-core kernels (tcgen05.mma, accumulators in TMEM, operands fed by TMA) for the two
+// intra-chunk contractions of the SSD forward, chunk length 128.
+//
+//   k_state_tc : per (batch, chunk, group)   states[(h,p), n] = sum_l w[h,l] x[l,(h,p)] B[l,n]
+//                A = x tile, scaled in place in shared memory, read MN-major; B = B tile read
+//                MN-major; one 128 x N accumulator per 128 (h,p) rows.
+//   k_scan_tc  : per (batch, chunk, group)   G = C B^T once (128x128 in TMEM), then per head
+//                M_h = tril(G o exp(cs_i-cs_j) o dt_j) -> bf16 -> shared memory,
+//                Y = M_h X_h  (+)  exp(cs_i) * (C S_prev^T),  y = Y + D x, optional silu gate.
+//
+// Shared-memory tiles and descriptor conventions are described in umma.cuh.  Each CTA has 256
+// threads: thread t owns accumulator row (t % 128) and half (t / 128) of the columns.
+#include <mutex>
+
+#include "common.cuh"
+#include "ssd_internal.h"
+#include "umma.cuh"
+
+namespace ssd {
+namespace {
+
+using namespace umma;
+typedef __nv_bfloat16 bf16;
+
+constexpr int QT = 128;          // chunk length of the tensor-core path
+constexpr int TC_THREADS = 256;
+constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows x 64 bf16
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int WAIT_LIMIT = 4000000;
+
+// Bounded waits: after the first one gives up every later wait is skipped, so a broken
+// pipeline drains in bounded time instead of hanging; the status word tells the host.
+struct Waiter {
+  int* status;
+  bool dead;
+  __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
+    if (dead) return;
+    if (!mbar_wait(bar, parity, WAIT_LIMIT)) {
+      dead = true;
+      atomicExch(status, code);
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// chunk states (MODE 0: x, B, w = exp(cs_end-cs_l)*dt_l) and their backward twin (MODE 1: dy, C,
+// w = exp(cs_l)).  grid = (nc, G, B).
+template <int P, int N, int MODE>
+__global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
+                                                          const __grid_constant__ CUtensorMap tmB,
+                                                          const float* __restrict__ cs, const float* __restrict__ dtf,
+                                                          float* __restrict__ out, int* __restrict__ status) {
+  constexpr int NB = N / 64;       // 64-column boxes of the B/C tile
+  constexpr int HT = 128 / P;      // heads per 128-row accumulator
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sB = smem;                         // NB boxes
+  uint8_t* sX = smem + NB * BOX_BYTES;        // 2 buffers x 2 boxes
+  float* sW = (float*)(sX + 4 * BOX_BYTES);   // [HT][128]
+  __shared__ __align__(8) uint64_t bar_b, bar_x[2], bar_mma;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) s_abort = *(volatile int*)status;   // an earlier CTA gave up: drain the grid quickly
+  __syncthreads();
+  if (s_abort) return;
+  const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
+  const int row = tid & 127, half = tid >> 7;
+  if (tid == 0) {
+    mbar_init(&bar_b, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, N < 32 ? 32 : N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  Waiter w{status, false};
+
+  const int MT = g.hpg * P / 128;             // accumulator tiles in this group
+  const int col_base = grp * g.hpg * P;       // first (h,p) column of the group in x
+  if (tid == 0) {
+    mbar_expect_tx(&bar_b, NB * BOX_BYTES);
+    for (int kb = 0; kb < NB; ++kb) tma_load_3d(sB + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &bar_b);
+    mbar_expect_tx(&bar_x[0], 2 * BOX_BYTES);
+    tma_load_3d(sX, &tmX, col_base, c * QT, b, &bar_x[0]);
+    tma_load_3d(sX + BOX_BYTES, &tmX, col_base + 64, c * QT, b, &bar_x[0]);
+  }
+  uint32_t xphase[2] = {0, 0}, mphase = 0;
+  const uint32_t idesc = make_idesc(128, N, 1, 1);
+  for (int mt = 0; mt < MT; ++mt) {
+    const int buf = mt & 1;
+    uint8_t* xt = sX + buf * 2 * BOX_BYTES;
+    if (tid == 0 && mt + 1 < MT) {
+      uint8_t* nx = sX + (buf ^ 1) * 2 * BOX_BYTES;
+      mbar_expect_tx(&bar_x[buf ^ 1], 2 * BOX_BYTES);
+      tma_load_3d(nx, &tmX, col_base + (mt + 1) * 128, c * QT, b, &bar_x[buf ^ 1]);
+      tma_load_3d(nx + BOX_BYTES, &tmX, col_base + (mt + 1) * 128 + 64, c * QT, b, &bar_x[buf ^ 1]);
+    }
+    const int h0 = grp * g.hpg + mt * HT;
+    for (int i = tid; i < HT * 128; i += TC_THREADS) {
+      const int hl = i >> 7, l = i & 127;
+      const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
+      sW[i] = (MODE == 0) ? exp2f((cs[co + QT - 1] - cs[co + l]) * LOG2E) * dtf[co + l] : exp2f(cs[co + l] * LOG2E);
+    }
+    __syncthreads();
+    w.wait(&bar_x[buf], xphase[buf], 11);
+    xphase[buf] ^= 1;
+    // scale the tile in place: 2 boxes x 128 rows x 8 chunks of 16 bytes
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int idx = tid + r * TC_THREADS;
+      const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
+      const int lc = (pc ^ l) & 7;
+      const int hl = (box * 64 + lc * 8) / P;
+      const float wv = sW[hl * 128 + l];
+      const uint32_t a = smem_u32(xt + box * BOX_BYTES + l * 128 + pc * 16);
+      uint4 v = ld_shared_v4(a);
+      float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+      st_shared_v4(a, pack_bf16(f0.x * wv, f0.y * wv), pack_bf16(f1.x * wv, f1.y * wv),
+                   pack_bf16(f2.x * wv, f2.y * wv), pack_bf16(f3.x * wv, f3.y * wv));
+    }
+    fence_async_smem();
+    if (mt == 0) w.wait(&bar_b, 0, 12);
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t xa = smem_u32(xt), ba = smem_u32(sB);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        mma_bf16(tm, desc_sw128_mn(xa, ks * 16, 0, BOX_BYTES), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idesc, ks > 0);
+      mma_commit(&bar_mma);
+    }
+    w.wait(&bar_mma, mphase, 13);
+    mphase ^= 1;
+    tc_fence_after();
+    // epilogue: row = (head, p) of this tile, half of the N columns per thread
+    float* o = out + (((size_t)(b * g.nc + c) * g.H + h0) * P + row) * N + half * (N / 2);
+#pragma unroll
+    for (int q = 0; q < N / 64; ++q) {
+      float v[32];
+      tmem_ld32(tmem_addr(tm, (warp & 3) * 32, half * (N / 2) + q * 32), v);
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(o + q * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tm, N < 32 ? 32 : N);
+}
+
+// ---------------------------------------------------------------------------------------------
+// chunk_scan family.  grid = (nc, G, B).  G = C B^T (128x128, TMEM) once per CTA, then per head
+// the masked, decayed matrix M_h[i,j] = G[i,j] exp(cs_i-cs_j) dt_j (j <= i) goes to shared
+// memory as bf16 and feeds
+//   MODE 0 (forward)            Y  = M_h X_h   (+) exp(cs_i) C S_prev^T      -> y (+ D x, gate)
+//   MODE 1 (backward, recompute) the same Y, epilogue instead forms dz / pre-gate dy and the
+//                                row sums  dcsp[i] = sum_p dy*Y,  ddot[i] = sum_p dy*x
+//   MODE 2 (backward, dx)        U' = M_h^T dY_h (+) dt_j exp(cs_end-cs_j) B dS_end^T
+//                                dx = D dy + U',  ddtd[j] = sum_p x*U' / dt_j
+// "SV" below is the fp32 [64 x N] state block staged as bf16: S_prev (modes 0,1) or dS_end (2).
+template <int P, int N, int XBUF, int MODE>
+__global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
+                                                         const __grid_constant__ CUtensorMap tmDY,
+                                                         const __grid_constant__ CUtensorMap tmB,
+                                                         const __grid_constant__ CUtensorMap tmC,
+                                                         const float* __restrict__ cs, const float* __restrict__ dtf,
+                                                         const float* __restrict__ sv, const float* __restrict__ D,
+                                                         const bf16* __restrict__ z, bf16* __restrict__ y,
+                                                         const bf16* __restrict__ dy, bf16* __restrict__ dypb,
+                                                         bf16* __restrict__ dz, bf16* __restrict__ dx,
+                                                         float* __restrict__ rs0, float* __restrict__ rs1,
+                                                         int* __restrict__ status) {
+  constexpr int NB = N / 64;
+  constexpr int HB = 64 / P;                   // heads per 64-column box
+  constexpr int NBOX = (MODE == 0) ? 1 : 2;    // boxes per head block: x (and dy)
+  constexpr uint32_t TM_COLS = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sKeep = smem;                       // NB boxes kept for the whole CTA: C (modes 0,1) or B (mode 2)
+  uint8_t* sBM = sKeep + NB * BOX_BYTES;       // the other tile (NB boxes), later the 32 KB M_h tile
+  uint8_t* sX = sBM + 2 * BOX_BYTES;           // XBUF x NBOX boxes: x [, dy]
+  uint8_t* sS = sX + XBUF * NBOX * BOX_BYTES;  // 64 x N bf16, plain layout
+  float2* sCD = (float2*)(sS + 64 * N * 2);    // [HB][128] {cs*log2e, dt}
+  __shared__ __align__(8) uint64_t bar_cb, bar_x[2], bar_mma;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) s_abort = *(volatile int*)status;   // an earlier CTA gave up: drain the grid quickly
+  __syncthreads();
+  if (s_abort) return;
+  const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
+  const int row = tid & 127, half = tid >> 7;
+  if (tid == 0) {
+    mbar_init(&bar_cb, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tmG = tm, tmYd = tm + 128, tmYo = tm + 192;
+  Waiter w{status, false};
+
+  const int nblk = g.hpg / HB;
+  const int col_base = grp * g.hpg * P;
+  auto load_boxes = [&](int blk, int buf) {   // thread 0 only
+    uint8_t* dst = sX + buf * NBOX * BOX_BYTES;
+    mbar_expect_tx(&bar_x[buf], NBOX * BOX_BYTES);
+    tma_load_3d(dst, &tmX, col_base + blk * 64, c * QT, b, &bar_x[buf]);
+    if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col_base + blk * 64, c * QT, b, &bar_x[buf]);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
+    for (int kb = 0; kb < NB; ++kb) {
+      tma_load_3d(sKeep + kb * BOX_BYTES, (MODE == 2) ? &tmB : &tmC, grp * N + kb * 64, c * QT, b, &bar_cb);
+      tma_load_3d(sBM + kb * BOX_BYTES, (MODE == 2) ? &tmC : &tmB, grp * N + kb * 64, c * QT, b, &bar_cb);
+    }
+    load_boxes(0, 0);
+  }
+  uint32_t xphase[2] = {0, 0}, mphase = 0;
+  w.wait(&bar_cb, 0, 21);
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t idG = make_idesc(128, 128, 0, 0);
+    const uint32_t ca = smem_u32((MODE == 2) ? sBM : sKeep), ba = smem_u32((MODE == 2) ? sKeep : sBM);
+#pragma unroll
+    for (int kb = 0; kb < NB; ++kb)
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        mma_bf16(tmG, desc_sw128_k(ca + kb * BOX_BYTES, ks * 32), desc_sw128_k(ba + kb * BOX_BYTES, ks * 32), idG,
+                 (kb | ks) > 0);
+    mma_commit(&bar_mma);
+  }
+  w.wait(&bar_mma, mphase, 22);
+  mphase ^= 1;
+  tc_fence_after();
+
+  const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
+  const int t_row = c * QT + row;
+  for (int blk = 0; blk < nblk; ++blk) {
+    const int buf = (XBUF == 2) ? (blk & 1) : 0;
+    uint8_t* xt = sX + buf * NBOX * BOX_BYTES;          // x box
+    uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;         // dy box (modes 1, 2)
+    const int h0 = grp * g.hpg + blk * HB;
+    if (XBUF == 2 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1, buf ^ 1);
+    for (int i = tid; i < HB * 128; i += TC_THREADS) {
+      const int hl = i >> 7, l = i & 127;
+      const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
+      sCD[i] = make_float2(cs[co + l] * LOG2E, dtf[co + l]);
+    }
+    {  // state block of these heads: 64 rows x N fp32 -> bf16, plain layout (rows = 64)
+      const float* pv = sv + (((size_t)(b * g.nc + c) * g.H + h0) * P) * N;
+      for (int u = tid; u < 64 * (N / 8); u += TC_THREADS) {
+        const int r = u & 63, ch = u >> 6;
+        const float4 a = *reinterpret_cast<const float4*>(pv + (size_t)r * N + ch * 8);
+        const float4 bb = *reinterpret_cast<const float4*>(pv + (size_t)r * N + ch * 8 + 4);
+        st_shared_v4(smem_u32(sS) + plain_off(64, r, ch * 8), pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
+                     pack_bf16(bb.x, bb.y), pack_bf16(bb.z, bb.w));
+      }
+    }
+    __syncthreads();
+    for (int hl = 0; hl < HB; ++hl) {
+      // M_h: this thread does row `row`, columns [64*half, 64*half + 64)
+      const float csi = sCD[hl * 128 + row].x;
+      const uint32_t mrow = smem_u32(sBM);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int c0 = half * 64 + q * 32;
+        float v[32];
+        tmem_ld32(tmem_addr(tmG, (warp & 3) * 32, c0), v);
+#pragma unroll
+        for (int j8 = 0; j8 < 32; j8 += 8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const int j = c0 + j8 + k;
+            const float2 e0 = sCD[hl * 128 + j], e1 = sCD[hl * 128 + j + 1];
+            const float m0 = (j <= row) ? v[j8 + k] * exp2f(csi - e0.x) * e0.y : 0.f;
+            const float m1 = (j + 1 <= row) ? v[j8 + k + 1] * exp2f(csi - e1.x) * e1.y : 0.f;
+            pk[k >> 1] = pack_bf16(m0, m1);
+          }
+          st_shared_v4(mrow + plain_off(128, row, c0 + j8), pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+      fence_async_smem();
+      if (hl == 0) {
+        w.wait(&bar_x[buf], xphase[buf], 23);
+        xphase[buf] ^= 1;
+      }
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t ma = smem_u32(sBM), oa = smem_u32((MODE == 2) ? dyt : xt);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_bf16(tmYd + hl * P, (MODE == 2) ? desc_plain_mn(ma, 128, ks * 16, 0) : desc_plain_k(ma, 128, ks * 16),
+                   desc_sw128_mn(oa, ks * 16, hl * P * 2, 16), idY, ks > 0);
+        if (hl == 0) {
+          const uint32_t ka = smem_u32(sKeep), sa = smem_u32(sS);
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              mma_bf16(tmYo, desc_sw128_k(ka + kb * BOX_BYTES, ks * 32), desc_plain_k(sa, 64, kb * 64 + ks * 16), idO,
+                       (kb | ks) > 0);
+        }
+        mma_commit(&bar_mma);
+      }
+      w.wait(&bar_mma, mphase, 24);
+      mphase ^= 1;
+      tc_fence_after();
+    }
+    // epilogue for the HB heads of this block: this thread has columns [32*half, 32*half + 32) of the 64
+    {
+      float yd[32], yo[32];
+      tmem_ld32(tmem_addr(tmYd, (warp & 3) * 32, half * 32), yd);
+      tmem_ld32(tmem_addr(tmYo, (warp & 3) * 32, half * 32), yo);
+      const int hl = (half * 32) / P;                    // P in {32, 64}: one head per thread
+      const int h = h0 + hl;
+      const float2 cd = sCD[hl * 128 + row];
+      const float Dh = D ? __ldg(D + h) : 0.f;
+      const long long colo = (long long)h0 * P + half * 32;
+      const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
+      const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + colo;
+      // off-diagonal scale: exp(cs_i) for Y, dt_j exp(cs_end - cs_j) for U'
+      const float osc = (MODE == 2) ? cd.y * exp2f(sCD[hl * 128 + 127].x - cd.x) : exp2f(cd.x);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int k8 = 0; k8 < 32; k8 += 8) {
+        const int chunk = (half * 32 + k8) >> 3;
+        const uint4 xv = ld_shared_v4(smem_u32(xt) + sw128_off(row, chunk));
+        const float2 x0 = unpack_bf16(xv.x), x1 = unpack_bf16(xv.y), x2 = unpack_bf16(xv.z), x3 = unpack_bf16(xv.w);
+        const float xs[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = yd[k8 + k] + osc * yo[k8 + k];
+        float zs[8], dys[8];
+        if (z) {
+          const uint4 zv = *reinterpret_cast<const uint4*>(zp + k8);
+          const float2 z0 = unpack_bf16(zv.x), z1 = unpack_bf16(zv.y), z2 = unpack_bf16(zv.z), z3 = unpack_bf16(zv.w);
+          zs[0] = z0.x; zs[1] = z0.y; zs[2] = z1.x; zs[3] = z1.y; zs[4] = z2.x; zs[5] = z2.y; zs[6] = z3.x; zs[7] = z3.y;
+        }
+        if (MODE != 0) {
+          const uint4 dv = ld_shared_v4(smem_u32(dyt) + sw128_off(row, chunk));
+          const float2 d0 = unpack_bf16(dv.x), d1 = unpack_bf16(dv.y), d2 = unpack_bf16(dv.z), d3 = unpack_bf16(dv.w);
+          dys[0] = d0.x; dys[1] = d0.y; dys[2] = d1.x; dys[3] = d1.y; dys[4] = d2.x; dys[5] = d2.y; dys[6] = d3.x; dys[7] = d3.y;
+        }
+        float o[8];
+        if (MODE == 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            o[k] = acc[k] + Dh * xs[k];
+            if (z) o[k] *= zs[k] * sigmoidf_(zs[k]);
+          }
+          *reinterpret_cast<uint4*>(y + b * g.ysb + (long long)t_row * g.ysl + colo + k8) =
+              make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+        } else if (MODE == 1) {
+          float dp[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float dyv = dys[k];
+            if (z) {
+              const float sg = 1.f / (1.f + __expf(-zs[k]));
+              o[k] = dyv * (acc[k] + Dh * xs[k]) * sg * (1.f + zs[k] * (1.f - sg));   // dz
+              dyv *= zs[k] * sg;
+            }
+            dp[k] = dyv;
+            s0 = fmaf(dyv, acc[k], s0);
+            s1 = fmaf(dyv, xs[k], s1);
+          }
+          if (z) {
+            *reinterpret_cast<uint4*>(dz + dense + k8) =
+                make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+            *reinterpret_cast<uint4*>(dypb + dense + k8) =
+                make_uint4(pack_bf16(dp[0], dp[1]), pack_bf16(dp[2], dp[3]), pack_bf16(dp[4], dp[5]), pack_bf16(dp[6], dp[7]));
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            o[k] = acc[k] + Dh * dys[k];
+            s0 = fmaf(xs[k], acc[k], s0);
+          }
+          *reinterpret_cast<uint4*>(dx + dense + k8) =
+              make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+        }
+      }
+      if (MODE != 0) {
+        const size_t co = ((size_t)(b * g.H + h) * g.nc + c) * QT + row;
+        if (MODE == 1) {
+          atomicAdd(rs0 + co, s0);   // dcsp
+          atomicAdd(rs1 + co, s1);   // ddot
+        } else {
+          atomicAdd(rs0 + co, cd.y > 0.f ? s0 / cd.y : 0.f);   // ddtd
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (XBUF == 1 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1, 0);
+  }
+  if (warp == 1) tmem_dealloc(tm, TM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward, dB and dC.  grid = (nc, G, B).  Per head W_h = dY_h X_h^T (128x128, TMEM), masked and
+// decayed like M_h into W'_h (bf16, shared memory), then accumulated over the heads of the group
+//   dC[i,n] += W'_h B      (+ per head block)  (exp(cs_i) dY) S_prev
+//   dB[j,n] += W'_h^T C    (+ per head block)  (exp(cs_end-cs_j) dt_j X) dS_end
+template <int P, int N>
+__global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
+                                                        const __grid_constant__ CUtensorMap tmDY,
+                                                        const __grid_constant__ CUtensorMap tmB,
+                                                        const __grid_constant__ CUtensorMap tmC,
+                                                        const float* __restrict__ cs, const float* __restrict__ dtf,
+                                                        const float* __restrict__ prev, const float* __restrict__ dS,
+                                                        bf16* __restrict__ dB, bf16* __restrict__ dC,
+                                                        int* __restrict__ status) {
+  constexpr int NB = N / 64;
+  constexpr int HB = 64 / P;
+  constexpr uint32_t TM_COLS = (128 + 2 * N <= 256) ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sB = smem;                          // NB boxes
+  uint8_t* sC = sB + NB * BOX_BYTES;           // NB boxes
+  uint8_t* sM = sC + NB * BOX_BYTES;           // 32 KB W'_h tile, plain layout
+  uint8_t* sX = sM + 2 * BOX_BYTES;            // x box
+  uint8_t* sDY = sX + BOX_BYTES;               // dy box
+  uint8_t* sS = sM;                            // S_prev block, 64 x N bf16 plain: reuses the W' tile
+  uint8_t* sDS = sM + 64 * N * 2;              // dS_end block            (after the head loop)
+  float2* sCD = (float2*)(sDY + BOX_BYTES);    // [HB][128]
+  __shared__ __align__(8) uint64_t bar_cb, bar_x, bar_mma;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) s_abort = *(volatile int*)status;
+  __syncthreads();
+  if (s_abort) return;
+  const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
+  const int row = tid & 127, half = tid >> 7;
+  if (tid == 0) {
+    mbar_init(&bar_cb, 1); mbar_init(&bar_x, 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tmW = tm, tmDC = tm + 128, tmDB = tm + 128 + N;
+  Waiter w{status, false};
+
+  const int nblk = g.hpg / HB;
+  const int col_base = grp * g.hpg * P;
+  auto load_boxes = [&](int blk) {
+    mbar_expect_tx(&bar_x, 2 * BOX_BYTES);
+    tma_load_3d(sX, &tmX, col_base + blk * 64, c * QT, b, &bar_x);
+    tma_load_3d(sDY, &tmDY, col_base + blk * 64, c * QT, b, &bar_x);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
+    for (int kb = 0; kb < NB; ++kb) {
+      tma_load_3d(sB + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &bar_cb);
+      tma_load_3d(sC + kb * BOX_BYTES, &tmC, grp * N + kb * 64, c * QT, b, &bar_cb);
+    }
+    load_boxes(0);
+  }
+  uint32_t xphase = 0, mphase = 0;
+  const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
+  auto issue_w = [&](int hl) {   // thread 0: W = dY_h X_h^T, K = P
+    const uint32_t da = smem_u32(sDY), xa = smem_u32(sX);
+#pragma unroll
+    for (int ks = 0; ks < P / 16; ++ks)
+      mma_bf16(tmW, desc_sw128_k(da, hl * P * 2 + ks * 32), desc_sw128_k(xa, hl * P * 2 + ks * 32), idW, ks > 0);
+  };
+  w.wait(&bar_cb, 0, 31);
+  bool first = true;
+  for (int blk = 0; blk < nblk; ++blk) {
+    const int h0 = grp * g.hpg + blk * HB;
+    for (int i = tid; i < HB * 128; i += TC_THREADS) {
+      const int hl = i >> 7, l = i & 127;
+      const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
+      sCD[i] = make_float2(cs[co + l] * LOG2E, dtf[co + l]);
+    }
+    w.wait(&bar_x, xphase, 32);
+    xphase ^= 1;
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      issue_w(0);
+      mma_commit(&bar_mma);
+    }
+    w.wait(&bar_mma, mphase, 33);
+    mphase ^= 1;
+    tc_fence_after();
+    for (int hl = 0; hl < HB; ++hl) {
+      const float csi = sCD[hl * 128 + row].x;
+      const uint32_t mrow = smem_u32(sM);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int c0 = half * 64 + q * 32;
+        float v[32];
+        tmem_ld32(tmem_addr(tmW, (warp & 3) * 32, c0), v);
+#pragma unroll
+        for (int j8 = 0; j8 < 32; j8 += 8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const int j = c0 + j8 + k;
+            const float2 e0 = sCD[hl * 128 + j], e1 = sCD[hl * 128 + j + 1];
+            const float m0 = (j <= row) ? v[j8 + k] * exp2f(csi - e0.x) * e0.y : 0.f;
+            const float m1 = (j + 1 <= row) ? v[j8 + k + 1] * exp2f(csi - e1.x) * e1.y : 0.f;
+            pk[k >> 1] = pack_bf16(m0, m1);
+          }
+          st_shared_v4(mrow + plain_off(128, row, c0 + j8), pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t ma = smem_u32(sM), ba = smem_u32(sB), ca = smem_u32(sC);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          mma_bf16(tmDC, desc_plain_k(ma, 128, ks * 16), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idC, !first || ks > 0);
+          mma_bf16(tmDB, desc_plain_mn(ma, 128, ks * 16, 0), desc_sw128_mn(ca, ks * 16, 0, BOX_BYTES), idB, !first || ks > 0);
+        }
+        if (hl + 1 < HB) issue_w(hl + 1);
+        mma_commit(&bar_mma);
+      }
+      first = false;
+      w.wait(&bar_mma, mphase, 34);
+      mphase ^= 1;
+      tc_fence_after();
+    }
+    // state terms of this head block: stage S_prev and dS_end (fp32 -> bf16) over the W' tile, scale
+    // the dy box by exp(cs_i) and the x box by exp(cs_end - cs_j) dt_j in place, then one K = 64
+    // product each
+    {
+      const size_t so = (((size_t)(b * g.nc + c) * g.H + h0) * P) * N;
+      for (int u = tid; u < 2 * 64 * (N / 8); u += TC_THREADS) {
+        const int which = u / (64 * (N / 8)), uu = u % (64 * (N / 8));
+        const int r = uu & 63, ch = uu >> 6;
+        const float* pv = (which ? dS : prev) + so + (size_t)r * N + ch * 8;
+        const float4 a = *reinterpret_cast<const float4*>(pv);
+        const float4 bb = *reinterpret_cast<const float4*>(pv + 4);
+        st_shared_v4(smem_u32(which ? sDS : sS) + plain_off(64, r, ch * 8), pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
+                     pack_bf16(bb.x, bb.y), pack_bf16(bb.z, bb.w));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int idx = tid + r * TC_THREADS;
+      const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
+      const int hl = (((pc ^ l) & 7) * 8) / P;
+      const float2 cd = sCD[hl * 128 + l];
+      const float f = box ? exp2f(cd.x) : exp2f(sCD[hl * 128 + 127].x - cd.x) * cd.y;
+      const uint32_t a = smem_u32((box ? sDY : sX) + l * 128 + pc * 16);
+      uint4 v = ld_shared_v4(a);
+      float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+      st_shared_v4(a, pack_bf16(f0.x * f, f0.y * f), pack_bf16(f1.x * f, f1.y * f), pack_bf16(f2.x * f, f2.y * f),
+                   pack_bf16(f3.x * f, f3.y * f));
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t da = smem_u32(sDY), xa = smem_u32(sX), sa = smem_u32(sS), dsa = smem_u32(sDS);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        mma_bf16(tmDC, desc_sw128_k(da, ks * 32), desc_plain_mn(sa, 64, ks * 16, 0), idC, true);
+        mma_bf16(tmDB, desc_sw128_k(xa, ks * 32), desc_plain_mn(dsa, 64, ks * 16, 0), idC, true);
+      }
+      mma_commit(&bar_mma);
+    }
+    w.wait(&bar_mma, mphase, 35);
+    mphase ^= 1;
+    tc_fence_after();
+    __syncthreads();
+    if (tid == 0 && blk + 1 < nblk) load_boxes(blk + 1);
+  }
+  // epilogue: this thread writes N/2 columns of row `row` of dC and of dB
+  {
+    const size_t o = (((size_t)b * g.L + c * QT + row) * g.G + grp) * N + half * (N / 2);
+#pragma unroll
+    for (int q = 0; q < N / 64; ++q) {
+      float vc[32], vb[32];
+      tmem_ld32(tmem_addr(tmDC, (warp & 3) * 32, half * (N / 2) + q * 32), vc);
+      tmem_ld32(tmem_addr(tmDB, (warp & 3) * 32, half * (N / 2) + q * 32), vb);
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        *reinterpret_cast<uint4*>(dC + o + q * 32 + j) = make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]),
+                                                                   pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7]));
+        *reinterpret_cast<uint4*>(dB + o + q * 32 + j) = make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]),
+                                                                   pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tm, TM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Exclusive scan over chunks, 4 state elements per thread, decays staged in shared memory.
+template <bool WRITE>
+__global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restrict__ st, const float* __restrict__ cs,
+                                                          const float* __restrict__ init, float* __restrict__ last,
+                                                          int reverse) {
+  extern __shared__ float sdec[];  // [nc]
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int PN = g.P * g.N;
+  for (int c = threadIdx.x; c < g.nc; c += blockDim.x)
+    sdec[c] = expf(cs[((size_t)(b * g.H + h) * g.nc + c) * g.Q + g.Q - 1]);
+  __syncthreads();
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (e >= PN) return;
+  float4 run = init ? *reinterpret_cast<const float4*>(init + ((size_t)(b * g.H + h)) * PN + e)
+                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  const size_t cstride = (size_t)g.H * PN;
+  float* base = st + ((size_t)b * g.nc * g.H + h) * PN + e;
+  constexpr int U = 4;
+  for (int s0 = 0; s0 < g.nc; s0 += U) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int s = s0 + u;
+      if (s < g.nc) {
+        const int c = reverse ? g.nc - 1 - s : s;
+        v[u] = *reinterpret_cast<const float4*>(base + (size_t)c * cstride);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int s = s0 + u;
+      if (s < g.nc) {
+        const int c = reverse ? g.nc - 1 - s : s;
+        if (WRITE) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+        const float d = sdec[c];
+        run.x = fmaf(d, run.x, v[u].x); run.y = fmaf(d, run.y, v[u].y);
+        run.z = fmaf(d, run.z, v[u].z); run.w = fmaf(d, run.w, v[u].w);
+      }
+    }
+  }
+  if (last) *reinterpret_cast<float4*>(last + ((size_t)(b * g.H + h)) * PN + e) = run;
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeFn)p;
+  });
+  return fn;
+}
+
+// 3-D map over a [batch, seqlen, cols] bf16 tensor (cols dense), box = 64 cols x 128 rows, 128B swizzle.
+int make_seq_map(CUtensorMap* m, const void* ptr, long long cols, long long L, long long B, long long stride_l,
+                 long long stride_b, const char* what) {
+  EncodeFn enc = get_encode();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return SSD_ERR_CUDA; }
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)L, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)stride_l * 2, (cuuint64_t)stride_b * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r); return SSD_ERR_CUDA; }
+  return SSD_OK;
+}
+
+template <int P, int N>
+constexpr size_t state_smem() { return 1024 + (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (128 / P) * 128 * 4; }
+template <int P, int N, int XBUF, int MODE>
+constexpr size_t scan_smem() {
+  return 1024 + (N / 64) * BOX_BYTES + 2 * BOX_BYTES + XBUF * (MODE == 0 ? 1 : 2) * BOX_BYTES + 64 * N * 2 +
+         (64 / P) * 128 * 8;
+}
+template <int P, int N>
+constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * 128 * 8; }
+
+template <int P, int N, int MODE>
+int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* cs, const float* dtf,
+                 float* out, int* status, cudaStream_t s) {
+  auto k = k_state_tc<P, N, MODE>;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P, N>());
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, state_smem<P, N>(), s>>>(g, tx, tb, cs, dtf, out, status);
+  SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_state_tc" : "dstates_local_tc");
+  return SSD_OK;
+}
+
+struct ScanArgs {
+  const float *cs, *dtf, *sv, *D;
+  const void* z;
+  void* y;
+  const void* dy;
+  void *dypb, *dz, *dx;
+  float *rs0, *rs1;
+};
+
+template <int P, int N, int MODE>
+int launch_scan(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tdy, const CUtensorMap& tb,
+                const CUtensorMap& tc, const ScanArgs& a, int* status, cudaStream_t s) {
+  constexpr int XBUF = (MODE == 0 && N < 128) ? 2 : 1;
+  auto k = k_scan_tc<P, N, XBUF, MODE>;
+  constexpr size_t sm = scan_smem<P, N, XBUF, MODE>();
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, sm, s>>>(g, tx, tdy, tb, tc, a.cs, a.dtf, a.sv, a.D, (const bf16*)a.z, (bf16*)a.y,
+                                                 (const bf16*)a.dy, (bf16*)a.dypb, (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1,
+                                                 status);
+  SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_tc" : (MODE == 1 ? "chunk_scan_bwd_tc" : "dx_tc"));
+  return SSD_OK;
+}
+
+template <int P, int N>
+int launch_dbc(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tdy, const CUtensorMap& tb, const CUtensorMap& tc,
+               const float* cs, const float* dtf, const float* prev, const float* dS, void* dB, void* dC, int* status,
+               cudaStream_t s) {
+  auto k = k_dbc_tc<P, N>;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dbc_smem<P, N>());
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, dbc_smem<P, N>(), s>>>(g, tx, tdy, tb, tc, cs, dtf, prev, dS, (bf16*)dB, (bf16*)dC,
+                                                               status);
+  SSD_CUDA_CHECK_LAUNCH("dBdC_tc");
+  return SSD_OK;
+}
+
+struct SeqMaps {
+  CUtensorMap x, dy, b, c;
+};
+// dy may be NULL (forward); dy strides are the y strides of the geometry unless `dy_dense`.
+int make_maps(const Geo& g, const void* x, const void* dy, bool dy_dense, const void* Bm, const void* Cm, SeqMaps* m) {
+  const long long HP = (long long)g.H * g.P, GN = (long long)g.G * g.N;
+  int rc = make_seq_map(&m->x, x, HP, g.L, g.B, g.xsl, g.xsb, "x");
+  if (rc) return rc;
+  if (dy) {
+    rc = dy_dense ? make_seq_map(&m->dy, dy, HP, g.L, g.B, HP, HP * g.L, "dy") : make_seq_map(&m->dy, dy, HP, g.L, g.B, g.ysl, g.ysb, "dy");
+    if (rc) return rc;
+  } else {
+    m->dy = m->x;
+  }
+  rc = make_seq_map(&m->b, Bm, GN, g.L, g.B, g.bsl, g.bsb, "B");
+  if (rc) return rc;
+  return make_seq_map(&m->c, Cm, GN, g.L, g.B, g.csl, g.csb, "C");
+}
+
+}  // namespace
+
+bool tensor_supported(const Geo& g, int dtype, const char** why) {
+  auto no = [&](const char* m) { if (why) *why = m; return false; };
+  if (dtype != SSD_BF16) return no("tensor-core kernels need bf16 storage");
+  if (g.Q != QT) return no("tensor-core kernels need chunk == 128");
+  if (g.L % QT) return no("tensor-core kernels need seqlen % 128 == 0");
+  if (!((g.P == 32 || g.P == 64) && (g.N == 64 || g.N == 128))) return no("tensor-core kernels cover headdim in {32,64}, dstate in {64,128}");
+  if ((g.hpg * g.P) % 128) return no("heads_per_group * headdim must be a multiple of 128");
+  if ((g.xsl % 8) || (g.xsb % 8) || (g.bsl % 8) || (g.bsb % 8) || (g.csl % 8) || (g.csb % 8) || (g.ysl % 8) || (g.ysb % 8) ||
+      (g.zsl % 8) || (g.zsb % 8))
+    return no("strides must be multiples of 8 elements (16 bytes) for TMA");
+  return true;
+}
+
+int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, int reverse,
+                         bool write, cudaStream_t s) {
+  const int PN = g.P * g.N;
+  const dim3 grid(cdiv(PN / 4, 256), g.H, g.B);
+  const size_t sm = (size_t)g.nc * sizeof(float);
+  if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, reverse);
+  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, reverse);
+  SSD_CUDA_CHECK_LAUNCH(reverse ? (write ? "dstate_passing" : "dstate_total") : (write ? "state_passing" : "state_total"));
+  return SSD_OK;
+}
+
+#define DISPATCH_PN(CALL)                                                 \
+  if (g.P == 32 && g.N == 64) { CALL(32, 64) }                            \
+  else if (g.P == 32 && g.N == 128) { CALL(32, 128) }                     \
+  else if (g.P == 64 && g.N == 64) { CALL(64, 64) }                       \
+  else { CALL(64, 128) }
+
+// chunk states (mode 0: x, B) or local state gradients (mode 1: dy, C) on tensor cores
+int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc,
+                       long long bsb, long long bsl, const float* cs, const float* dtf, float* out, int* status,
+                       cudaStream_t s) {
+  CUtensorMap tx, tb;
+  int rc = make_seq_map(&tx, xdy, (long long)g.H * g.P, g.L, g.B, sl, sb, "x/dy");
+  if (rc) return rc;
+  rc = make_seq_map(&tb, bc, (long long)g.G * g.N, g.L, g.B, bsl, bsb, "B/C");
+  if (rc) return rc;
+#define CALL(PP, NN) return mode == 0 ? launch_state<PP, NN, 0>(g, tx, tb, cs, dtf, out, status, s) \
+                                      : launch_state<PP, NN, 1>(g, tx, tb, cs, dtf, out, status, s);
+  DISPATCH_PN(CALL)
+#undef CALL
+}
+
+int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* cs, const float* dtf, const float* prev,
+                      int* status, cudaStream_t s) {
+  SeqMaps m;
+  int rc = make_maps(g, p.x, nullptr, false, p.Bm, p.Cm, &m);
+  if (rc) return rc;
+  ScanArgs a{cs, dtf, prev, p.D, p.z, p.y, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+#define CALL(PP, NN) return launch_scan<PP, NN, 0>(g, m.x, m.dy, m.b, m.c, a, status, s);
+  DISPATCH_PN(CALL)
+#undef CALL
+}
+
+// backward, forward-recompute pass: dcsp, ddot, and for the gated case dz and the bf16 pre-gate dy
+int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* cs, const float* dtf, const float* prev,
+                    void* dypb, float* dcsp, float* ddot, int* status, cudaStream_t s) {
+  SeqMaps m;
+  int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, &m);
+  if (rc) return rc;
+  ScanArgs a{cs, dtf, prev, p.D, p.z, nullptr, p.dy, dypb, p.dz, nullptr, dcsp, ddot};
+#define CALL(PP, NN) return launch_scan<PP, NN, 1>(g, m.x, m.dy, m.b, m.c, a, status, s);
+  DISPATCH_PN(CALL)
+#undef CALL
+}
+
+// backward, dx and ddtd; `dyp` is the pre-gate gradient (dy itself, or the dense bf16 copy)
+int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* cs, const float* dtf,
+              const float* dS, float* ddtd, int* status, cudaStream_t s) {
+  SeqMaps m;
+  int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, &m);
+  if (rc) return rc;
+  ScanArgs a{cs, dtf, dS, p.D, nullptr, nullptr, dyp, nullptr, nullptr, p.dx, ddtd, nullptr};
+#define CALL(PP, NN) return launch_scan<PP, NN, 2>(g, m.x, m.dy, m.b, m.c, a, status, s);
+  DISPATCH_PN(CALL)
+#undef CALL
+}
+
+int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* cs, const float* dtf,
+               const float* prev, const float* dS, int* status, cudaStream_t s) {
+  SeqMaps m;
+  int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, &m);
+  if (rc) return rc;
+#define CALL(PP, NN) return launch_dbc<PP, NN>(g, m.x, m.dy, m.b, m.c, cs, dtf, prev, dS, p.dB, p.dC, status, s);
+  DISPATCH_PN(CALL)
+#undef CALL
+}
+
+}  // namespace ssd
