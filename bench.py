@@ -79,6 +79,10 @@ def kernel_bytes_per_token(name, c, e=2):
         "chunk_scan": (2 * hp + gn) * e + zb, "chunk_scan_bwd_epilogue": (2 * hp + gn) * e + 2 * zb,
         "dstates_local": (hp + gn) * e, "dx": (3 * hp + gn) * e, "dw": 2 * hp * e,
         "dC": (2 * gn + hp) * e, "dB": (2 * gn + hp) * e, "ddt": 4 * H, "sdot": st / 2,
+        # tensor-core kernels: each reads its operand tiles once and writes its outputs once
+        "chunk_state_tc": (hp + gn) * e, "dstates_local_tc": (hp + gn) * e,
+        "chunk_scan_tc": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_tc": (2 * hp + 2 * gn) * e + 2 * zb,
+        "dx_tc": (3 * hp + 2 * gn) * e, "dBdC_tc": (2 * hp + 4 * gn) * e,
     }
     return table.get(name)
 
@@ -310,7 +314,8 @@ def run_train(args, c, rank, world, local):
             T.backward(inp["dy"], inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"], z, chunk=c["Q"],
                        algo=args.algo, workspace=ws, fwd_saved=True, out=out)
 
-    for _ in range(max(3, args.warmup)):
+    nwarm = args.warmup if args.profile_mode else max(3, args.warmup)
+    for _ in range(nwarm):
         step()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -323,11 +328,11 @@ def run_train(args, c, rank, world, local):
     tokens_job = tokens_rank * world
     value = tokens_job / (ms_step * 1e-3)
 
-    prof = kernel_profile(step, 3, dev) if not (sp_mode and world > 1) else {}
+    prof = kernel_profile(step, 3, dev) if not (sp_mode and world > 1) and not args.profile_mode else {}
 
     # end to end through the host-buffer entry point: pinned host tensors in, pinned host tensors out
     e2e = None
-    if not sp_mode:
+    if not sp_mode and not args.no_e2e:
         hb = HostFwdBwd(c["B"], c["L"], c["H"], c["P"], c["N"], c["G"], c["Q"], torch.bfloat16, has_z=c["z"], device=dev,
                         algo=args.algo)
         hin = {k: inp[k].cpu().pin_memory() for k in ("x", "dt", "B", "C", "dy") + (("z",) if c["z"] else ())}
@@ -371,7 +376,7 @@ def run_train(args, c, rank, world, local):
         cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": f"batch {sample} of {c['B']}, seqlen {Ls} of {c['L']}, fwd+bwd, chunked fp32 torch ops, {dt_s:.2f} s/iter"}
     line = {"metric": "ssd_fwd_bwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "steps": args.steps, "warmup": nwarm, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if sp_mode and args.strong else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": f"{c['name']}: B{c['B']} L{c['L']} H{c['H']} P{c['P']} N{c['N']} G{c['G']} Q{c['Q']}"
@@ -413,7 +418,8 @@ def run_decode(args, c, rank, world, local):
         k[0] += 1
         st.step(xs[i], dts[i], A, Bs[i], Cs[i], D, y=y)
 
-    for _ in range(max(3, args.warmup)):
+    nwarm = args.warmup if args.profile_mode else max(3, args.warmup)
+    for _ in range(nwarm):
         step()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -423,6 +429,11 @@ def run_decode(args, c, rank, world, local):
     launches = _lib.launch_count() - n0
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms / args.steps
+    if args.profile_mode:
+        if rank == 0:
+            print(json.dumps({"metric": "ssd_decode_steps_per_s", "value": 1e3 / ms_step, "ms_per_step": ms_step,
+                              "profile_mode": True, "gpu_launches": int(launches)}), flush=True)
+        return
     prof = kernel_profile(step, 20, dev)
     hs = HostStep(state, G)
     hx, hdt, hB, hC = (t[0].cpu().pin_memory() for t in (xs, dts, Bs, Cs))
@@ -445,7 +456,7 @@ def run_decode(args, c, rank, world, local):
                "sample": f"{sample} of {S} streams, 16 steps, time scaled by {S // sample}"}
     h2d, d2h = hs.bytes_per_call()
     line = {"metric": "ssd_decode_steps_per_s", "value": 1e3 / ms_step, "unit": "steps/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "steps": args.steps, "warmup": nwarm, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{c['name']}: {S} streams per GPU, H{H} P{P} N{N} G{G}, fp32 state, bf16 step vectors",
                        "streams_total": S * world, "l2": f"state {S * H * P * N * 4 / 1e6:.0f} MB per GPU, larger than the 126 MB L2",
@@ -471,8 +482,16 @@ def main():
     ap.add_argument("--ring", type=int, default=64, help="cfg2: distinct pre-drawn steps kept in HBM")
     ap.add_argument("--strong", action="store_true", help="cfg4: label the run strong scaling (fixed global L)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch / stream count (profiling a small case)")
+    ap.add_argument("--profile-mode", action="store_true",
+                    help="for captures under a profiler: exactly --warmup warm-ups, no per-kernel event pass, no CPU/e2e legs")
     args = ap.parse_args()
-    c = CFGS[args.workload]
+    c = dict(CFGS[args.workload])
+    if args.batch:
+        c["B"] = args.batch
+    if args.profile_mode:
+        args.no_cpu = args.no_e2e = True
     if args.impl == "reference":
         run_reference(args, c)
         return

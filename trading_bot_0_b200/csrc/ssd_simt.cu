@@ -84,30 +84,57 @@ struct DySrc {
 
 // ---------------------------------------------------------------------------------------------
 // Stage 1: cs = inclusive within-chunk cumsum of dt*A (fp32), dtf = dt as fp32, both [B,H,nc,Q].
+// One block per (chunk, batch): thread q reads the H contiguous dt values of position q once and
+// the block scans 8 heads at a time with warp shuffles.
 template <typename T>
 __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ A,
                                                float* __restrict__ cs, float* __restrict__ dtf) {
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, q = threadIdx.x;
-  __shared__ float wsum[NT / 32];
+  constexpr int HG = 8;
+  const int c = blockIdx.x, b = blockIdx.y, q = threadIdx.x;
+  __shared__ float wsum[NT / 32][HG];
   const int t = c * g.Q + q;
-  float d = 0.f;
-  if (q < g.Q && t < g.L) d = ldf(dt + b * g.dtsb + t * g.dtsl + h);
-  float v = d * A[h];
+  const bool live = (q < g.Q) && (t < g.L);
   const int lane = q & 31, w = q >> 5;
+  const T* row = dt + b * g.dtsb + (long long)t * g.dtsl;
+  for (int h0 = 0; h0 < g.H; h0 += HG) {
+    float d[HG], v[HG];
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    float n = __shfl_up_sync(0xffffffffu, v, o);
-    if (lane >= o) v += n;
-  }
-  if (lane == 31) wsum[w] = v;
-  __syncthreads();
-  float base = 0.f;
-  for (int i = 0; i < w; ++i) base += wsum[i];
-  v += base;
-  if (q < g.Q) {
-    const size_t o = cs_idx(g, b, h, c) + q;
-    cs[o] = v;
-    dtf[o] = d;
+    for (int k = 0; k < HG; ++k) {
+      const int h = h0 + k;
+      d[k] = (live && h < g.H) ? ldf(row + h) : 0.f;
+      v[k] = (h < g.H) ? d[k] * A[h] : 0.f;
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) {
+        const float n = __shfl_up_sync(0xffffffffu, v[k], o);
+        if (lane >= o) v[k] += n;
+      }
+    }
+    if (lane == 31) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) wsum[w][k] = v[k];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < HG; ++k) {
+      float base = 0.f;
+      for (int i = 0; i < w; ++i) base += wsum[i][k];
+      v[k] += base;
+    }
+    if (q < g.Q) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) {
+        const int h = h0 + k;
+        if (h < g.H) {
+          const size_t o = cs_idx(g, b, h, c) + q;
+          cs[o] = v[k];
+          dtf[o] = d[k];
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -632,7 +659,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   if (stages & SSD_STAGE_LOCAL) {
     cudaMemsetAsync(status, 0, 256, s);
-    k_cumsum<T><<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf);
+    k_cumsum<T><<<dim3(g.nc, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
     if (tc) {
       int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, cs, dtf, states, status, s);
@@ -716,10 +743,12 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       int rc = fwd_stages_t<T>(g, tc, f, ws, w, s, SSD_STAGE_LOCAL | SSD_STAGE_FINISH, false);
       if (rc) return rc;
     }
-    const size_t nq = (size_t)g.B * g.H * g.nc * g.Q * sizeof(float);
-    cudaMemsetAsync(dcsp, 0, nq, s);
-    cudaMemsetAsync(ddtd, 0, nq, s);
-    cudaMemsetAsync(ddot, 0, nq, s);
+    if (!tc) {  // the CUDA-core kernels accumulate these row sums with atomics; the tensor-core ones store them
+      const size_t nq = (size_t)g.B * g.H * g.nc * g.Q * sizeof(float);
+      cudaMemsetAsync(dcsp, 0, nq, s);
+      cudaMemsetAsync(ddtd, 0, nq, s);
+      cudaMemsetAsync(ddot, 0, nq, s);
+    }
     if (tc) {
       int rc = tensor_scan_bwd(g, p, cs, dtf, states, dyp, dcsp, ddot, status, s);
       if (rc) return rc;

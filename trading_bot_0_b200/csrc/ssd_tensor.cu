@@ -9,7 +9,7 @@
 //                Y = M_h X_h  (+)  exp(cs_i) * (C S_prev^T),  y = Y + D x, optional silu gate.
 //
 // Shared-memory tiles and descriptor conventions are described in umma.cuh.  Each CTA has 256
-// threads: thread t owns accumulator row (t % 128) and half (t / 128) of the columns.
+// threads: thread t owns accumulator row (t % 128) and part (t / 128) of the columns.
 #include <mutex>
 
 #include "common.cuh"
@@ -23,7 +23,8 @@ using namespace umma;
 typedef __nv_bfloat16 bf16;
 
 constexpr int QT = 128;          // chunk length of the tensor-core path
-constexpr int TC_THREADS = 256;
+constexpr int TC_THREADS = 512;   // 16 warps: 4 per TMEM lane quarter
+constexpr int PARTS = TC_THREADS / 128;
 constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows x 64 bf16
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int WAIT_LIMIT = 4000000;
@@ -42,11 +43,75 @@ struct Waiter {
   }
 };
 
+
+// ---------------------------------------------------------------------------------------------
+// Decayed lower-triangular tile.  Source: a 128x128 fp32 accumulator in TMEM (C B^T or dY X^T).
+// Result: out[i,j] = src[i,j] * exp(cs_i - cs_j) * dt_j for j <= i, written as bf16 into a plain
+// 128x128 tile.  Work is done in 32x32 blocks: blocks above the diagonal are never touched (the
+// caller zero-fills them once with zero_upper_blocks), the 4 diagonal blocks evaluate one exp per
+// element, and blocks below the diagonal use the factorisation
+//     exp(cs_i - cs_j) dt_j = exp(cs_i - cs_r) * [exp(cs_r - cs_j) dt_j],   r = last column of the block,
+// whose second factor is a per-column table (`cf`) and whose exponents are both <= 0, so nothing
+// can overflow.  cd[j] = {cs_j * log2(e), dt_j}.  Thread = (row, part): one 32x32 block per thread and head.
+__device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float2* __restrict__ cd,
+                                                const float* __restrict__ cf, int row, int part, int warp,
+                                                uint32_t mtile) {
+  const int rb = warp & 3, cb = part;   // both warp-uniform
+  if (cb > rb) return;
+  const float csi = cd[row].x;
+  const int c0 = cb * 32;
+  float v[32];
+  tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
+  if (cb == rb) {
+#pragma unroll
+    for (int j8 = 0; j8 < 32; j8 += 8) {
+      uint32_t pk[4];
+#pragma unroll
+      for (int k = 0; k < 8; k += 2) {
+        const int j = c0 + j8 + k;
+        const float2 e0 = cd[j], e1 = cd[j + 1];
+        const float m0 = (j <= row) ? v[j8 + k] * ex2(csi - e0.x) * e0.y : 0.f;
+        const float m1 = (j + 1 <= row) ? v[j8 + k + 1] * ex2(csi - e1.x) * e1.y : 0.f;
+        pk[k >> 1] = pack_bf16(m0, m1);
+      }
+      st_shared_v4(mtile + plain_off(128, row, c0 + j8), pk[0], pk[1], pk[2], pk[3]);
+    }
+  } else {
+    const float rf = ex2(csi - cd[c0 + 31].x);
+#pragma unroll
+    for (int j8 = 0; j8 < 32; j8 += 8) {
+      const float4 f0 = *reinterpret_cast<const float4*>(cf + c0 + j8);
+      const float4 f1 = *reinterpret_cast<const float4*>(cf + c0 + j8 + 4);
+      st_shared_v4(mtile + plain_off(128, row, c0 + j8),
+                   pack_bf16(v[j8] * rf * f0.x, v[j8 + 1] * rf * f0.y), pack_bf16(v[j8 + 2] * rf * f0.z, v[j8 + 3] * rf * f0.w),
+                   pack_bf16(v[j8 + 4] * rf * f1.x, v[j8 + 5] * rf * f1.y), pack_bf16(v[j8 + 6] * rf * f1.z, v[j8 + 7] * rf * f1.w));
+    }
+  }
+}
+// zero the 32x32 blocks above the diagonal of a plain 128x128 tile (same thread mapping)
+__device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, uint32_t mtile) {
+  if (part <= (warp & 3)) return;
+#pragma unroll
+  for (int j8 = 0; j8 < 32; j8 += 8) st_shared_v4(mtile + plain_off(128, row, part * 32 + j8), 0u, 0u, 0u, 0u);
+}
+// per-head tables for decay_mask_tile: cd[l] = {cs_l*log2e, dt_l}, cf[l] = exp(cs_r(l) - cs_l) dt_l
+__device__ __forceinline__ void stage_decay_tables(const Geo& g, const float* __restrict__ cs,
+                                                   const float* __restrict__ dtf, int b, int c, int h0, int nheads,
+                                                   float2* cd, float* cf, int tid) {
+  for (int i = tid; i < nheads * 128; i += TC_THREADS) {
+    const int hl = i >> 7, l = i & 127;
+    const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
+    const float a = cs[co + l] * LOG2E, d = dtf[co + l];
+    cd[i] = make_float2(a, d);
+    cf[i] = ex2(cs[co + (l | 31)] * LOG2E - a) * d;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // chunk states (MODE 0: x, B, w = exp(cs_end-cs_l)*dt_l) and their backward twin (MODE 1: dy, C,
 // w = exp(cs_l)).  grid = (nc, G, B).
 template <int P, int N, int MODE>
-__global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
+__global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
                                                           const __grid_constant__ CUtensorMap tmB,
                                                           const float* __restrict__ cs, const float* __restrict__ dtf,
                                                           float* __restrict__ out, int* __restrict__ status) {
@@ -55,9 +120,10 @@ __global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sB = smem;                         // NB boxes
-  uint8_t* sX = smem + NB * BOX_BYTES;        // 2 buffers x 2 boxes
-  float* sW = (float*)(sX + 4 * BOX_BYTES);   // [HT][128]
-  __shared__ __align__(8) uint64_t bar_b, bar_x[2], bar_mma;
+  uint8_t* sX = smem + NB * BOX_BYTES;        // 2 boxes: the x tile, scaled in place (high bf16 part)
+  uint8_t* sL = sX + 2 * BOX_BYTES;           // 2 boxes: low bf16 part of the scaled tile
+  float* sW = (float*)(sL + 2 * BOX_BYTES);   // [HT][128]
+  __shared__ __align__(8) uint64_t bar_b, bar_x, bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -66,9 +132,9 @@ __global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_con
   __syncthreads();
   if (s_abort) return;
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
-  const int row = tid & 127, half = tid >> 7;
+  const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
-    mbar_init(&bar_b, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_b, 1); mbar_init(&bar_x, 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, N < 32 ? 32 : N);
@@ -80,46 +146,52 @@ __global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_con
 
   const int MT = g.hpg * P / 128;             // accumulator tiles in this group
   const int col_base = grp * g.hpg * P;       // first (h,p) column of the group in x
+  auto load_tile = [&](int mt) {              // thread 0 only
+    mbar_expect_tx(&bar_x, 2 * BOX_BYTES);
+    tma_load_3d(sX, &tmX, col_base + mt * 128, c * QT, b, &bar_x);
+    tma_load_3d(sX + BOX_BYTES, &tmX, col_base + mt * 128 + 64, c * QT, b, &bar_x);
+  };
   if (tid == 0) {
     mbar_expect_tx(&bar_b, NB * BOX_BYTES);
     for (int kb = 0; kb < NB; ++kb) tma_load_3d(sB + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &bar_b);
-    mbar_expect_tx(&bar_x[0], 2 * BOX_BYTES);
-    tma_load_3d(sX, &tmX, col_base, c * QT, b, &bar_x[0]);
-    tma_load_3d(sX + BOX_BYTES, &tmX, col_base + 64, c * QT, b, &bar_x[0]);
+    load_tile(0);
   }
-  uint32_t xphase[2] = {0, 0}, mphase = 0;
+  uint32_t xphase = 0, mphase = 0;
   const uint32_t idesc = make_idesc(128, N, 1, 1);
   for (int mt = 0; mt < MT; ++mt) {
-    const int buf = mt & 1;
-    uint8_t* xt = sX + buf * 2 * BOX_BYTES;
-    if (tid == 0 && mt + 1 < MT) {
-      uint8_t* nx = sX + (buf ^ 1) * 2 * BOX_BYTES;
-      mbar_expect_tx(&bar_x[buf ^ 1], 2 * BOX_BYTES);
-      tma_load_3d(nx, &tmX, col_base + (mt + 1) * 128, c * QT, b, &bar_x[buf ^ 1]);
-      tma_load_3d(nx + BOX_BYTES, &tmX, col_base + (mt + 1) * 128 + 64, c * QT, b, &bar_x[buf ^ 1]);
-    }
     const int h0 = grp * g.hpg + mt * HT;
     for (int i = tid; i < HT * 128; i += TC_THREADS) {
       const int hl = i >> 7, l = i & 127;
       const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
-      sW[i] = (MODE == 0) ? exp2f((cs[co + QT - 1] - cs[co + l]) * LOG2E) * dtf[co + l] : exp2f(cs[co + l] * LOG2E);
+      sW[i] = (MODE == 0) ? ex2((cs[co + QT - 1] - cs[co + l]) * LOG2E) * dtf[co + l] : ex2(cs[co + l] * LOG2E);
     }
     __syncthreads();
-    w.wait(&bar_x[buf], xphase[buf], 11);
-    xphase[buf] ^= 1;
-    // scale the tile in place: 2 boxes x 128 rows x 8 chunks of 16 bytes
+    w.wait(&bar_x, xphase, 11);
+    xphase ^= 1;
+    // scale the tile: 2 boxes x 128 rows x 8 chunks of 16 bytes.  The product w*x is split into a
+    // high and a low bf16 part (two MMAs) so the chunk states keep ~16 mantissa bits: they feed
+    // every later stage, and the per-chunk term of dA is a strongly cancelling sum over them.
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+    for (int r = 0; r < 2048 / TC_THREADS; ++r) {
       const int idx = tid + r * TC_THREADS;
       const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
       const int lc = (pc ^ l) & 7;
       const int hl = (box * 64 + lc * 8) / P;
       const float wv = sW[hl * 128 + l];
-      const uint32_t a = smem_u32(xt + box * BOX_BYTES + l * 128 + pc * 16);
-      uint4 v = ld_shared_v4(a);
-      float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-      st_shared_v4(a, pack_bf16(f0.x * wv, f0.y * wv), pack_bf16(f1.x * wv, f1.y * wv),
-                   pack_bf16(f2.x * wv, f2.y * wv), pack_bf16(f3.x * wv, f3.y * wv));
+      const uint32_t off = box * BOX_BYTES + l * 128 + pc * 16;
+      const uint32_t a = smem_u32(sX) + off;
+      const uint4 v = ld_shared_v4(a);
+      const float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+      const float f[8] = {f0.x * wv, f0.y * wv, f1.x * wv, f1.y * wv, f2.x * wv, f2.y * wv, f3.x * wv, f3.y * wv};
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        hi[k] = pack_bf16(f[2 * k], f[2 * k + 1]);
+        const float2 hf = unpack_bf16(hi[k]);
+        lo[k] = pack_bf16(f[2 * k] - hf.x, f[2 * k + 1] - hf.y);
+      }
+      st_shared_v4(a, hi[0], hi[1], hi[2], hi[3]);
+      st_shared_v4(smem_u32(sL) + off, lo[0], lo[1], lo[2], lo[3]);
     }
     fence_async_smem();
     if (mt == 0) w.wait(&bar_b, 0, 12);
@@ -127,24 +199,28 @@ __global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_con
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t xa = smem_u32(xt), ba = smem_u32(sB);
+      const uint32_t xa = smem_u32(sX), la = smem_u32(sL), ba = smem_u32(sB);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
         mma_bf16(tm, desc_sw128_mn(xa, ks * 16, 0, BOX_BYTES), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idesc, ks > 0);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        mma_bf16(tm, desc_sw128_mn(la, ks * 16, 0, BOX_BYTES), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idesc, true);
       mma_commit(&bar_mma);
     }
     w.wait(&bar_mma, mphase, 13);
     mphase ^= 1;
     tc_fence_after();
-    // epilogue: row = (head, p) of this tile, half of the N columns per thread
-    float* o = out + (((size_t)(b * g.nc + c) * g.H + h0) * P + row) * N + half * (N / 2);
+    if (tid == 0 && mt + 1 < MT) load_tile(mt + 1);   // the tile buffers are free again
+    // epilogue: row = (head, p) of this tile, N / PARTS columns per thread
+    float* o = out + (((size_t)(b * g.nc + c) * g.H + h0) * P + row) * N + part * (N / PARTS);
 #pragma unroll
-    for (int q = 0; q < N / 64; ++q) {
-      float v[32];
-      tmem_ld32(tmem_addr(tm, (warp & 3) * 32, half * (N / 2) + q * 32), v);
+    for (int q = 0; q < N / PARTS / 16; ++q) {
+      float v[16];
+      tmem_ld16(tmem_addr(tm, (warp & 3) * 32, part * (N / PARTS) + q * 16), v);
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(o + q * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(o + q * 16 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     }
     tc_fence_before();
     __syncthreads();
@@ -163,7 +239,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_state_tc(Geo g, const __grid_con
 //                                dx = D dy + U',  ddtd[j] = sum_p x*U' / dt_j
 // "SV" below is the fp32 [64 x N] state block staged as bf16: S_prev (modes 0,1) or dS_end (2).
 template <int P, int N, int XBUF, int MODE>
-__global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
+__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
                                                          const __grid_constant__ CUtensorMap tmDY,
                                                          const __grid_constant__ CUtensorMap tmB,
                                                          const __grid_constant__ CUtensorMap tmC,
@@ -185,6 +261,8 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
   uint8_t* sX = sBM + 2 * BOX_BYTES;           // XBUF x NBOX boxes: x [, dy]
   uint8_t* sS = sX + XBUF * NBOX * BOX_BYTES;  // 64 x N bf16, plain layout
   float2* sCD = (float2*)(sS + 64 * N * 2);    // [HB][128] {cs*log2e, dt}
+  float* sCF = (float*)(sCD + HB * 128);       // [HB][128] column factors of decay_mask_tile
+  float* sRed = sCF + HB * 128;                // [2][PARTS][128] partial row sums (modes 1, 2)
   __shared__ __align__(8) uint64_t bar_cb, bar_x[2], bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -194,7 +272,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
   __syncthreads();
   if (s_abort) return;
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
-  const int row = tid & 127, half = tid >> 7;
+  const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
     mbar_init(&bar_cb, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
@@ -240,6 +318,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
   w.wait(&bar_mma, mphase, 22);
   mphase ^= 1;
   tc_fence_after();
+  zero_upper_blocks(row, part, warp, smem_u32(sBM));   // the B/C tile is dead; M_h never writes these blocks
 
   const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
   const int t_row = c * QT + row;
@@ -249,11 +328,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
     uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;         // dy box (modes 1, 2)
     const int h0 = grp * g.hpg + blk * HB;
     if (XBUF == 2 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1, buf ^ 1);
-    for (int i = tid; i < HB * 128; i += TC_THREADS) {
-      const int hl = i >> 7, l = i & 127;
-      const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
-      sCD[i] = make_float2(cs[co + l] * LOG2E, dtf[co + l]);
-    }
+    stage_decay_tables(g, cs, dtf, b, c, h0, HB, sCD, sCF, tid);
     {  // state block of these heads: 64 rows x N fp32 -> bf16, plain layout (rows = 64)
       const float* pv = sv + (((size_t)(b * g.nc + c) * g.H + h0) * P) * N;
       for (int u = tid; u < 64 * (N / 8); u += TC_THREADS) {
@@ -266,28 +341,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
     }
     __syncthreads();
     for (int hl = 0; hl < HB; ++hl) {
-      // M_h: this thread does row `row`, columns [64*half, 64*half + 64)
-      const float csi = sCD[hl * 128 + row].x;
-      const uint32_t mrow = smem_u32(sBM);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int c0 = half * 64 + q * 32;
-        float v[32];
-        tmem_ld32(tmem_addr(tmG, (warp & 3) * 32, c0), v);
-#pragma unroll
-        for (int j8 = 0; j8 < 32; j8 += 8) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int k = 0; k < 8; k += 2) {
-            const int j = c0 + j8 + k;
-            const float2 e0 = sCD[hl * 128 + j], e1 = sCD[hl * 128 + j + 1];
-            const float m0 = (j <= row) ? v[j8 + k] * exp2f(csi - e0.x) * e0.y : 0.f;
-            const float m1 = (j + 1 <= row) ? v[j8 + k + 1] * exp2f(csi - e1.x) * e1.y : 0.f;
-            pk[k >> 1] = pack_bf16(m0, m1);
-          }
-          st_shared_v4(mrow + plain_off(128, row, c0 + j8), pk[0], pk[1], pk[2], pk[3]);
-        }
-      }
+      decay_mask_tile(tmG, sCD + hl * 128, sCF + hl * 128, row, part, warp, smem_u32(sBM));
       fence_async_smem();
       if (hl == 0) {
         w.wait(&bar_x[buf], xphase[buf], 23);
@@ -317,24 +371,24 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
       mphase ^= 1;
       tc_fence_after();
     }
-    // epilogue for the HB heads of this block: this thread has columns [32*half, 32*half + 32) of the 64
+    // epilogue for the HB heads of this block: this thread has 64/PARTS = 16 of the 64 columns
+    float s0 = 0.f, s1 = 0.f;
+    const int hl_e = (part * 16) / P;                    // head of this thread's columns
+    const int h_e = h0 + hl_e;
+    const float2 cd_e = sCD[hl_e * 128 + row];
     {
-      float yd[32], yo[32];
-      tmem_ld32(tmem_addr(tmYd, (warp & 3) * 32, half * 32), yd);
-      tmem_ld32(tmem_addr(tmYo, (warp & 3) * 32, half * 32), yo);
-      const int hl = (half * 32) / P;                    // P in {32, 64}: one head per thread
-      const int h = h0 + hl;
-      const float2 cd = sCD[hl * 128 + row];
-      const float Dh = D ? __ldg(D + h) : 0.f;
-      const long long colo = (long long)h0 * P + half * 32;
+      float yd[16], yo[16];
+      tmem_ld16(tmem_addr(tmYd, (warp & 3) * 32, part * 16), yd);
+      tmem_ld16(tmem_addr(tmYo, (warp & 3) * 32, part * 16), yo);
+      const float Dh = D ? __ldg(D + h_e) : 0.f;
+      const long long colo = (long long)h0 * P + part * 16;
       const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
       const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + colo;
       // off-diagonal scale: exp(cs_i) for Y, dt_j exp(cs_end - cs_j) for U'
-      const float osc = (MODE == 2) ? cd.y * exp2f(sCD[hl * 128 + 127].x - cd.x) : exp2f(cd.x);
-      float s0 = 0.f, s1 = 0.f;
+      const float osc = (MODE == 2) ? cd_e.y * ex2(sCD[hl_e * 128 + 127].x - cd_e.x) : ex2(cd_e.x);
 #pragma unroll
-      for (int k8 = 0; k8 < 32; k8 += 8) {
-        const int chunk = (half * 32 + k8) >> 3;
+      for (int k8 = 0; k8 < 16; k8 += 8) {
+        const int chunk = (part * 16 + k8) >> 3;
         const uint4 xv = ld_shared_v4(smem_u32(xt) + sw128_off(row, chunk));
         const float2 x0 = unpack_bf16(xv.x), x1 = unpack_bf16(xv.y), x2 = unpack_bf16(xv.z), x3 = unpack_bf16(xv.w);
         const float xs[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
@@ -391,18 +445,28 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
               make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
         }
       }
-      if (MODE != 0) {
-        const size_t co = ((size_t)(b * g.H + h) * g.nc + c) * QT + row;
-        if (MODE == 1) {
-          atomicAdd(rs0 + co, s0);   // dcsp
-          atomicAdd(rs1 + co, s1);   // ddot
-        } else {
-          atomicAdd(rs0 + co, cd.y > 0.f ? s0 / cd.y : 0.f);   // ddtd
-        }
+      if (MODE != 0) {   // row sums: P/16 threads share a (head, row); combine through shared memory
+        sRed[part * 128 + row] = s0;
+        if (MODE == 1) sRed[(PARTS + part) * 128 + row] = s1;
       }
     }
     tc_fence_before();
     __syncthreads();
+    if (MODE != 0 && (part % (P / 16)) == 0) {
+      float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+      for (int k = 0; k < P / 16; ++k) {
+        t0 += sRed[(part + k) * 128 + row];
+        if (MODE == 1) t1 += sRed[(PARTS + part + k) * 128 + row];
+      }
+      const size_t co = ((size_t)(b * g.H + h_e) * g.nc + c) * QT + row;
+      if (MODE == 1) {
+        rs0[co] = t0;   // dcsp
+        rs1[co] = t1;   // ddot
+      } else {
+        rs0[co] = cd_e.y > 0.f ? t0 / cd_e.y : 0.f;   // ddtd
+      }
+    }
     if (XBUF == 1 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1, 0);
   }
   if (warp == 1) tmem_dealloc(tm, TM_COLS);
@@ -414,7 +478,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_scan_tc(Geo g, const __grid_cons
 //   dC[i,n] += W'_h B      (+ per head block)  (exp(cs_i) dY) S_prev
 //   dB[j,n] += W'_h^T C    (+ per head block)  (exp(cs_end-cs_j) dt_j X) dS_end
 template <int P, int N>
-__global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
+__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
                                                         const __grid_constant__ CUtensorMap tmDY,
                                                         const __grid_constant__ CUtensorMap tmB,
                                                         const __grid_constant__ CUtensorMap tmC,
@@ -435,6 +499,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_const
   uint8_t* sS = sM;                            // S_prev block, 64 x N bf16 plain: reuses the W' tile
   uint8_t* sDS = sM + 64 * N * 2;              // dS_end block            (after the head loop)
   float2* sCD = (float2*)(sDY + BOX_BYTES);    // [HB][128]
+  float* sCF = (float*)(sCD + HB * 128);       // [HB][128]
   __shared__ __align__(8) uint64_t bar_cb, bar_x, bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -444,7 +509,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_const
   __syncthreads();
   if (s_abort) return;
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
-  const int row = tid & 127, half = tid >> 7;
+  const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
     mbar_init(&bar_cb, 1); mbar_init(&bar_x, 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
@@ -484,11 +549,8 @@ __global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_const
   bool first = true;
   for (int blk = 0; blk < nblk; ++blk) {
     const int h0 = grp * g.hpg + blk * HB;
-    for (int i = tid; i < HB * 128; i += TC_THREADS) {
-      const int hl = i >> 7, l = i & 127;
-      const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
-      sCD[i] = make_float2(cs[co + l] * LOG2E, dtf[co + l]);
-    }
+    stage_decay_tables(g, cs, dtf, b, c, h0, HB, sCD, sCF, tid);
+    zero_upper_blocks(row, part, warp, smem_u32(sM));   // the state blocks of the previous head block lived here
     w.wait(&bar_x, xphase, 32);
     xphase ^= 1;
     tc_fence_before();
@@ -502,27 +564,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_const
     mphase ^= 1;
     tc_fence_after();
     for (int hl = 0; hl < HB; ++hl) {
-      const float csi = sCD[hl * 128 + row].x;
-      const uint32_t mrow = smem_u32(sM);
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int c0 = half * 64 + q * 32;
-        float v[32];
-        tmem_ld32(tmem_addr(tmW, (warp & 3) * 32, c0), v);
-#pragma unroll
-        for (int j8 = 0; j8 < 32; j8 += 8) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int k = 0; k < 8; k += 2) {
-            const int j = c0 + j8 + k;
-            const float2 e0 = sCD[hl * 128 + j], e1 = sCD[hl * 128 + j + 1];
-            const float m0 = (j <= row) ? v[j8 + k] * exp2f(csi - e0.x) * e0.y : 0.f;
-            const float m1 = (j + 1 <= row) ? v[j8 + k + 1] * exp2f(csi - e1.x) * e1.y : 0.f;
-            pk[k >> 1] = pack_bf16(m0, m1);
-          }
-          st_shared_v4(mrow + plain_off(128, row, c0 + j8), pk[0], pk[1], pk[2], pk[3]);
-        }
-      }
+      decay_mask_tile(tmW, sCD + hl * 128, sCF + hl * 128, row, part, warp, smem_u32(sM));
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
@@ -558,12 +600,12 @@ __global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_const
       }
     }
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
+    for (int r = 0; r < 2048 / TC_THREADS; ++r) {
       const int idx = tid + r * TC_THREADS;
       const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
       const int hl = (((pc ^ l) & 7) * 8) / P;
       const float2 cd = sCD[hl * 128 + l];
-      const float f = box ? exp2f(cd.x) : exp2f(sCD[hl * 128 + 127].x - cd.x) * cd.y;
+      const float f = box ? ex2(cd.x) : ex2(sCD[hl * 128 + 127].x - cd.x) * cd.y;
       const uint32_t a = smem_u32((box ? sDY : sX) + l * 128 + pc * 16);
       uint4 v = ld_shared_v4(a);
       float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
@@ -589,19 +631,19 @@ __global__ void __launch_bounds__(TC_THREADS) k_dbc_tc(Geo g, const __grid_const
     __syncthreads();
     if (tid == 0 && blk + 1 < nblk) load_boxes(blk + 1);
   }
-  // epilogue: this thread writes N/2 columns of row `row` of dC and of dB
+  // epilogue: this thread writes N/PARTS columns of row `row` of dC and of dB
   {
-    const size_t o = (((size_t)b * g.L + c * QT + row) * g.G + grp) * N + half * (N / 2);
+    const size_t o = (((size_t)b * g.L + c * QT + row) * g.G + grp) * N + part * (N / PARTS);
 #pragma unroll
-    for (int q = 0; q < N / 64; ++q) {
-      float vc[32], vb[32];
-      tmem_ld32(tmem_addr(tmDC, (warp & 3) * 32, half * (N / 2) + q * 32), vc);
-      tmem_ld32(tmem_addr(tmDB, (warp & 3) * 32, half * (N / 2) + q * 32), vb);
+    for (int q = 0; q < N / PARTS / 16; ++q) {
+      float vc[16], vb[16];
+      tmem_ld16(tmem_addr(tmDC, (warp & 3) * 32, part * (N / PARTS) + q * 16), vc);
+      tmem_ld16(tmem_addr(tmDB, (warp & 3) * 32, part * (N / PARTS) + q * 16), vb);
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        *reinterpret_cast<uint4*>(dC + o + q * 32 + j) = make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]),
+      for (int j = 0; j < 16; j += 8) {
+        *reinterpret_cast<uint4*>(dC + o + q * 16 + j) = make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]),
                                                                    pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7]));
-        *reinterpret_cast<uint4*>(dB + o + q * 32 + j) = make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]),
+        *reinterpret_cast<uint4*>(dB + o + q * 16 + j) = make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]),
                                                                    pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7]));
       }
     }
@@ -694,10 +736,10 @@ constexpr size_t state_smem() { return 1024 + (N / 64) * BOX_BYTES + 4 * BOX_BYT
 template <int P, int N, int XBUF, int MODE>
 constexpr size_t scan_smem() {
   return 1024 + (N / 64) * BOX_BYTES + 2 * BOX_BYTES + XBUF * (MODE == 0 ? 1 : 2) * BOX_BYTES + 64 * N * 2 +
-         (64 / P) * 128 * 8;
+         (64 / P) * 128 * 12 + (MODE == 0 ? 0 : 2 * PARTS * 128 * 4);
 }
 template <int P, int N>
-constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * 128 * 8; }
+constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * 128 * 12; }
 
 template <int P, int N, int MODE>
 int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* cs, const float* dtf,
