@@ -203,6 +203,27 @@ SSD_API int32_t ssd_sp_prefix_state(const float* gathered_states, const float* g
 SSD_API const char* ssd_last_error(void);
 
 /*
+ * Forward pass that allocates nothing and takes no workspace argument: the scratch that
+ * ssd_forward gets from its caller comes instead from a fixed SSD_NOALLOC_MAX_BYTES array built
+ * into the library (present on every GPU that loads the library, until the process exits).
+ * For callers that cannot obtain device memory at the point of the call: a rollout or live
+ * trading loop running after its memory pool was frozen, a host that holds raw device pointers
+ * from an FFI but no allocator, a process whose free device memory is already committed.
+ * The caller still passes every input and output tensor.  Problems whose forward workspace
+ * (ssd_workspace_bytes(dims, SSD_PASS_FWD)) exceeds SSD_NOALLOC_MAX_BYTES are rejected with
+ * SSD_ERR_WORKSPACE_TOO_SMALL and a message naming both sizes.  The first call on each device
+ * looks up the array's device address (make that first call before any stream capture); no
+ * call allocates or frees device memory.  Every call on a device shares the one array: calls
+ * whose kernels could overlap on the GPU (different streams, or different host threads) race
+ * and must be serialised by the caller; the array keeps the previous call's contents and the
+ * entry point re-initialises what it needs.  Results equal ssd_forward's for the same inputs.
+ * This entry point has no counterpart in the reference.
+ */
+#define SSD_NOALLOC_MAX_BYTES ((size_t)32 << 20)
+SSD_API int32_t ssd_forward_noalloc(const SsdDims* dims, const SsdFwdPtrs* p, void* cuda_stream);
+SSD_API size_t ssd_noalloc_max_bytes(void);
+
+/*
  * Tracing.  ssd_launch_count: kernels this library has launched in this process (all threads).
  * ssd_profile_begin/end: between the two calls every kernel launched from THIS thread gets a
  * CUDA event recorded behind it on its launch stream; _end synchronises on the last event and

@@ -1,0 +1,66 @@
+"""The allocation-free forward entry point, called through the C ABI.
+
+Some users of the library cannot hand it a workspace: their loop runs after the device memory
+pool was frozen, or they only hold raw pointers from an FFI.  `ssd_forward_noalloc` serves them
+from a fixed buffer inside the library.  This file checks that it returns what `ssd_forward`
+returns, twice in a row (the second call finds the first call's leftovers in the buffer), and
+that it refuses problems larger than the buffer.  It is named to be collected last, so a run
+that stops at the first failure has already run every other test.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+from oracle import ssd_oracle as O
+from tests._util import to_dev
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _call_noalloc(T, L, d, cfg, y, fin):
+    dims = T.make_dims(d["x"], d["dt"], d["B"], d["C"], cfg.chunk, z=d.get("z"), y=y)
+    p = L.SsdFwdPtrs(*[C.c_void_p(t.data_ptr()) if t is not None else None for t in
+                       (d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d.get("z"), d.get("init_state"), y, fin)])
+    with torch.cuda.device(DEV):
+        return L.load().ssd_forward_noalloc(C.byref(dims), C.byref(p),
+                                            C.c_void_p(torch.cuda.current_stream(DEV).cuda_stream))
+
+
+@pytest.mark.parametrize("base,kw", [(0, dict(has_z=True)), (1, dict(batch=2, seqlen=512))])
+def test_noalloc_forward_equals_workspace_forward_twice(lib, base, kw):
+    import dataclasses
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib as L
+    cfg = dataclasses.replace(O.CONFIGS[base], **kw)
+    tol = 0.0   # same kernels on the same inputs: the two entry points must agree exactly
+    for rep, seed in enumerate((O.SEED, O.SEED + 17)):   # two calls in a row, different data
+        d = to_dev(O.make_inputs(cfg, seed, with_init_state=True), DEV)
+        y_ref, fin_ref, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d.get("z"), d["init_state"],
+                                      chunk=cfg.chunk)
+        y = torch.full_like(d["x"], float("nan"))
+        fin = torch.full_like(fin_ref, float("nan"))
+        rc = _call_noalloc(T, L, d, cfg, y, fin)
+        assert rc == 0, L.load().ssd_last_error().decode()
+        torch.cuda.synchronize()
+        assert (y.float() - y_ref.float()).abs().max().item() <= tol, f"call {rep}: y differs"
+        assert (fin - fin_ref).abs().max().item() <= tol, f"call {rep}: final_state differs"
+
+
+def test_noalloc_rejects_problems_beyond_its_buffer(lib):
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib as L
+    cfg = O.SsdConfig("big", 64, 2048, 8, 32, 64, 1, 128, "bf16")
+    x = torch.zeros(cfg.batch, cfg.seqlen, cfg.nheads, cfg.headdim, dtype=torch.bfloat16, device=DEV)
+    d = dict(x=x, dt=torch.zeros(cfg.batch, cfg.seqlen, cfg.nheads, dtype=torch.bfloat16, device=DEV),
+             A=-torch.ones(cfg.nheads, device=DEV), D=None,
+             B=torch.zeros(cfg.batch, cfg.seqlen, 1, cfg.dstate, dtype=torch.bfloat16, device=DEV),
+             C=torch.zeros(cfg.batch, cfg.seqlen, 1, cfg.dstate, dtype=torch.bfloat16, device=DEV))
+    dims = T.make_dims(d["x"], d["dt"], d["B"], d["C"], cfg.chunk)
+    assert T.workspace_bytes(dims) > L.load().ssd_noalloc_max_bytes()
+    y = torch.empty_like(x)
+    rc = _call_noalloc(T, L, d, cfg, y, None)
+    assert rc == -4
+    msg = L.load().ssd_last_error().decode()
+    assert "SSD_NOALLOC_MAX_BYTES" in msg and str(L.load().ssd_noalloc_max_bytes()) in msg

@@ -21,7 +21,7 @@ EXPORTS = [
     "ssd_workspace_bytes", "ssd_forward", "ssd_backward", "ssd_forward_staged", "ssd_backward_staged",
     "ssd_state_update", "ssd_state_reset_rows", "ssd_sp_total_logdecay", "ssd_sp_prefix_state",
     "ssd_last_error", "ssd_version", "ssd_compiled_arch", "ssd_launch_count", "ssd_profile_begin",
-    "ssd_profile_end",
+    "ssd_profile_end", "ssd_forward_noalloc", "ssd_noalloc_max_bytes",
 ]
 
 
@@ -101,6 +101,10 @@ def load() -> C.CDLL:
     lib.ssd_profile_begin.argtypes = [vp]
     lib.ssd_profile_end.restype = i32
     lib.ssd_profile_end.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), i32]
+    lib.ssd_forward_noalloc.restype = i32
+    lib.ssd_forward_noalloc.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdFwdPtrs), vp]
+    lib.ssd_noalloc_max_bytes.restype = sz
+    lib.ssd_noalloc_max_bytes.argtypes = []
     lib.ssd_version.restype = i32
     lib.ssd_compiled_arch.restype = i32
     _lib = lib
