@@ -58,6 +58,8 @@ typedef enum SsdAlgo { SSD_ALGO_AUTO = 0, SSD_ALGO_FP32_CORES = 1, SSD_ALGO_TENS
 /*
  * Problem geometry.  `dtype` is the storage type of x, dt, B, C, z, y and of dx, dB, dC, dz, dy;
  * A, D, states, ddt, dA, dD are always fp32.  All arithmetic accumulates in fp32.
+ * `chunk` (<= 256) is the evaluation schedule only: results do not depend on it.  The tensor-core
+ * family evaluates 128-long chunks; a chunk of 256 is run as two of them.
  * Strides are in ELEMENTS for the batch and sequence dims; the remaining dims are dense
  * (x/z/y/dy: [.., H, P]; dt: [.., H]; B/C: [.., G, N]).  A stride of 0 means "dense default".
  * This is how a narrowed / non-contiguous tch view is passed (the reference accepts those on

@@ -84,3 +84,24 @@ def test_tensor_request_on_unsupported_dims_is_an_error(lib):
     with pytest.raises(L.SsdError) as ei:
         T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=64, algo="tensor")
     assert ei.value.code == -3
+
+
+def test_chunk_256_runs_on_the_tensor_family_as_two_128_chunks(lib):
+    """The 130M-layer and long-sequence workloads ask for chunk 256; the result must not depend on it."""
+    import trading_bot_0_b200 as T
+    cfg = O.SsdConfig("tc256", 2, 512, 24, 64, 128, 1, 256, "bf16", True)
+    inp = O.make_inputs(cfg, with_init_state=True)
+    ref = oracle_all(inp)
+    d = to_dev(inp, DEV)
+    y, fin, ws = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d["z"], d["init_state"], chunk=256,
+                           algo="tensor", for_backward=True)
+    g = T.backward(d["dy"], d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d["z"], d["init_state"], chunk=256,
+                   algo="tensor", workspace=ws, fwd_saved=True, want_dinit=True)
+    torch.cuda.synchronize()
+    assert status_word(ws) == 0
+    assert_close("y", y, ref["y"], "bf16")
+    assert_close("final_state", fin, ref["final_state"], "bf16")
+    for k in GRADS + ("dD", "dz", "dinit"):
+        assert_close(k, g[k], ref[k], "bf16")
+    y128, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d["z"], d["init_state"], chunk=128, algo="tensor")
+    assert torch.equal(y, y128)

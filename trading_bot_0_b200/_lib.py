@@ -10,7 +10,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libssd_b200.so"
+import os
+
+# SSD_B200_LIB overrides the library location (e.g. to test a differently built copy).
+LIB_PATH = Path(os.environ.get("SSD_B200_LIB") or (Path(__file__).resolve().parent / "lib" / "libssd_b200.so"))
 
 SSD_F32, SSD_BF16 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1

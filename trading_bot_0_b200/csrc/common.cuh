@@ -6,6 +6,10 @@
 
 #include "../../include/ssd_b200.h"
 
+// floats per (batch, chunk, head) decay table written by the cumsum kernel for the tensor-core
+// family: [cs*log2e | dt | column factors | per-step decays], 128 each
+#define SSD_TAB_FLOATS 512
+
 namespace ssd {
 
 // Internal, fully-resolved geometry handed to every kernel by value.
@@ -18,6 +22,8 @@ struct Geo {
 struct WsLayout {
   size_t status;                                     // 256-byte status block (int32 code first)
   size_t cs, dtf, states, fin, cb;                   // forward
+  size_t tab, prev_bf;                               // forward, tensor-core family only (else empty)
+  size_t ds_bf;                                      // backward, tensor-core family only
   size_t dstates, dyp, dcsp, ddtd, ddot, sdot, dapart, ddpart, dini;  // backward extras
   size_t total_fwd, total_bwd;
 };

@@ -85,10 +85,19 @@ static int make_geo(const SsdDims* d, Geo* g) {
       return SSD_ERR_CUDA;
     }
   }
+  // The chunk length only schedules the evaluation; the operator's result does not depend on it.
+  // The tensor-core family works on 128-long chunks, so a requested chunk that is a larger
+  // multiple of 128 is evaluated as consecutive 128-long chunks when that family will run.
+  if (d->algo != SSD_ALGO_FP32_CORES && d->chunk > 128 && d->chunk % 128 == 0) {
+    Geo t = *g;
+    t.Q = 128;
+    t.nc = (t.L + 127) / 128;
+    if (tensor_supported(t, d->dtype, nullptr)) *g = t;
+  }
   return SSD_OK;
 }
 
-static void make_layout(const Geo& g, bool has_z, WsLayout* w) {
+static void make_layout(const Geo& g, bool has_z, bool tcfam, WsLayout* w) {
   const size_t f = sizeof(float);
   const size_t nq = (size_t)g.B * g.H * g.nc * g.Q * f;
   const size_t nst = (size_t)g.B * g.nc * g.H * g.P * g.N * f;
@@ -98,14 +107,22 @@ static void make_layout(const Geo& g, bool has_z, WsLayout* w) {
   size_t o = 0;
   auto take = [&](size_t bytes) { size_t r = o; o += align256(bytes); return r; };
   w->status = take(256);
-  w->cs = take(nq); w->dtf = take(nq); w->states = take(nst); w->fin = take(nfin); w->cb = take(ncb);
+  w->cs = take(nq); w->dtf = take(nq); w->states = take(nst); w->fin = take(nfin);
+  w->cb = take(tcfam ? 0 : ncb);   // C B^T stays on chip in the tensor-core family
+  w->tab = take(tcfam ? (size_t)g.B * g.nc * g.H * SSD_TAB_FLOATS * f : 0);
+  w->prev_bf = take(tcfam ? nst / 2 : 0);
   w->total_fwd = o;
   w->dstates = take(nst);
+  w->ds_bf = take(tcfam ? nst / 2 : 0);
   w->dyp = take(has_z ? (size_t)g.B * g.L * g.H * g.P * f : 0);
   w->dcsp = take(nq); w->ddtd = take(nq); w->ddot = take(nq);
   w->sdot = take(nbh); w->dapart = take(nbh); w->ddpart = take(nbh);
   w->dini = take(nfin);
   w->total_bwd = o;
+}
+
+static bool family_is_tensor(const Geo& g, const SsdDims* d) {
+  return d->algo != SSD_ALGO_FP32_CORES && tensor_supported(g, d->dtype, nullptr);
 }
 
 // Kernel-family choice: 1 = tensor cores, 0 = CUDA cores, <0 = error.
@@ -181,7 +198,7 @@ size_t ssd_workspace_bytes(const SsdDims* dims, int32_t pass) {
   if (dims) { d2 = *dims; d2.device = -1; }
   if (make_geo(dims ? &d2 : nullptr, &g)) return 0;
   WsLayout w;
-  make_layout(g, dims->has_z != 0, &w);
+  make_layout(g, dims->has_z != 0, family_is_tensor(g, dims), &w);
   return pass == SSD_PASS_BWD ? w.total_bwd : w.total_fwd;
 }
 
@@ -197,7 +214,7 @@ int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* works
   if ((p->z != nullptr) != (dims->has_z != 0)) { set_error("dims.has_z (%d) does not match the z pointer", dims->has_z); return SSD_ERR_BAD_SHAPE; }
   if (stages == 0 || (stages & ~(SSD_STAGE_LOCAL | SSD_STAGE_TOTAL | SSD_STAGE_FINISH))) { set_error("bad stage mask %d", stages); return SSD_ERR_BAD_SHAPE; }
   WsLayout w;
-  make_layout(g, dims->has_z != 0, &w);
+  make_layout(g, dims->has_z != 0, family_is_tensor(g, dims), &w);
   rc = check_ws(workspace, workspace_bytes, w.total_fwd);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)cuda_stream;
@@ -236,7 +253,7 @@ int32_t ssd_backward_staged(const SsdDims* dims, const SsdBwdPtrs* p, void* work
   if (p->z && !p->dz) { set_error("dz must be non-NULL when z is given"); return SSD_ERR_NULL_POINTER; }
   if (stages == 0 || (stages & ~(SSD_STAGE_LOCAL | SSD_STAGE_TOTAL | SSD_STAGE_FINISH))) { set_error("bad stage mask %d", stages); return SSD_ERR_BAD_SHAPE; }
   WsLayout w;
-  make_layout(g, dims->has_z != 0, &w);
+  make_layout(g, dims->has_z != 0, family_is_tensor(g, dims), &w);
   rc = check_ws(workspace, workspace_bytes, w.total_bwd);
   if (rc) return rc;
   const int fam = pick_family(g, dims);
@@ -302,7 +319,7 @@ int32_t ssd_sp_total_logdecay(const SsdDims* dims, const void* workspace, size_t
   if (rc) return rc;
   if (!out) { set_error("out is NULL"); return SSD_ERR_NULL_POINTER; }
   WsLayout w;
-  make_layout(g, dims->has_z != 0, &w);
+  make_layout(g, dims->has_z != 0, family_is_tensor(g, dims), &w);
   rc = check_ws(workspace, workspace_bytes, w.total_fwd);
   if (rc) return rc;
   return sp_total_logdecay(g, (const float*)((const char*)workspace + w.cs), out, (cudaStream_t)cuda_stream);

@@ -12,22 +12,21 @@ int run_forward(const Geo& g, int dtype, bool tc, const SsdFwdPtrs& p, char* ws,
 int run_backward(const Geo& g, int dtype, bool tc, const SsdBwdPtrs& p, char* ws, const WsLayout& w, cudaStream_t s,
                  int stages);
 
-// tensor-core (tcgen05) stages, bf16 storage, chunk 128
+// tensor-core (tcgen05) stages, bf16 storage, chunk 128.  `tab` = per-head decay tables written by
+// the cumsum kernel, `*_bf` = bf16 copies of the chunk-entry states written by the scan over chunks.
 bool tensor_supported(const Geo& g, int dtype, const char** why);
 int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc,
-                       long long bsb, long long bsl, const float* cs, const float* dtf, float* out, int* status,
-                       cudaStream_t s);
-int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, int reverse,
-                         bool write, cudaStream_t s);
-int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* cs, const float* dtf, const float* prev,
-                      int* status, cudaStream_t s);
-
-int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* cs, const float* dtf, const float* prev,
-                    void* dypb, float* dcsp, float* ddot, int* status, cudaStream_t s);
-int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* cs, const float* dtf,
-              const float* dS, float* ddtd, int* status, cudaStream_t s);
-int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* cs, const float* dtf,
-               const float* prev, const float* dS, int* status, cudaStream_t s);
+                       long long bsb, long long bsl, const float* tab, float* out, int* status, cudaStream_t s);
+int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, void* st_bf,
+                         int reverse, bool write, cudaStream_t s);
+int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const void* prev_bf, int* status,
+                      cudaStream_t s);
+int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, void* dypb, float* dcsp,
+                    float* ddot, int* status, cudaStream_t s);
+int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* ds_bf,
+              float* ddtd, int* status, cudaStream_t s);
+int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
+               const void* ds_bf, int* status, cudaStream_t s);
 
 int decode_step(const SsdStepDims& d, const SsdStepPtrs& p, cudaStream_t s);
 int reset_rows(float* state, long long row_elems, const long long* idx, long long count, long long streams,

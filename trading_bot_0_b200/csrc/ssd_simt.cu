@@ -88,7 +88,8 @@ struct DySrc {
 // the block scans 8 heads at a time with warp shuffles.
 template <typename T>
 __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ A,
-                                               float* __restrict__ cs, float* __restrict__ dtf) {
+                                               float* __restrict__ cs, float* __restrict__ dtf,
+                                               float* __restrict__ tab) {
   constexpr int HG = 8;
   const int c = blockIdx.x, b = blockIdx.y, q = threadIdx.x;
   __shared__ float wsum[NT / 32][HG];
@@ -123,14 +124,25 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
       for (int i = 0; i < w; ++i) base += wsum[i][k];
       v[k] += base;
     }
-    if (q < g.Q) {
+    {
 #pragma unroll
       for (int k = 0; k < HG; ++k) {
         const int h = h0 + k;
-        if (h < g.H) {
+        if (h < g.H && q < g.Q) {
           const size_t o = cs_idx(g, b, h, c) + q;
           cs[o] = v[k];
           dtf[o] = d[k];
+        }
+        // tensor-core family (chunk 128 only): the per-head decay table [cs*log2e | dt | exp(cs_r - cs) dt |
+        // exp(dt A)], r = last position of the 32-block (lane 31 of this warp)
+        const float vend = __shfl_sync(0xffffffffu, v[k], 31);
+        if (tab && h < g.H && q < g.Q) {
+          const float L2E = 1.4426950408889634f;
+          float* t = tab + ((size_t)(b * g.nc + c) * g.H + h) * SSD_TAB_FLOATS + q;
+          t[0] = v[k] * L2E;
+          t[128] = d[k];
+          t[256] = exp2f((vend - v[k]) * L2E) * d[k];
+          t[384] = expf(d[k] * A[h]);
         }
       }
     }
@@ -655,14 +667,16 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   float* states = (float*)(ws + w.states);
   float* cb = (float*)(ws + w.cb);
   float* fin = p.final_state ? p.final_state : (float*)(ws + w.fin);
+  float* tab = (float*)(ws + w.tab);
+  void* prev_bf = ws + w.prev_bf;
   const T* x = (const T*)p.x;
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   if (stages & SSD_STAGE_LOCAL) {
     cudaMemsetAsync(status, 0, 256, s);
-    k_cumsum<T><<<dim3(g.nc, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf);
+    k_cumsum<T><<<dim3(g.nc, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf, tc ? tab : nullptr);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
     if (tc) {
-      int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, cs, dtf, states, status, s);
+      int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, states, status, s);
       if (rc) return rc;
     } else {
       DySrc<T> none{nullptr, nullptr, 0, 0};
@@ -673,7 +687,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_TOTAL) {
     if (tc) {
-      int rc = tensor_state_passing(g, states, cs, nullptr, fin, 0, false, s);
+      int rc = tensor_state_passing(g, states, cs, nullptr, fin, nullptr, 0, false, s);
       if (rc) return rc;
     } else {
       k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, nullptr, fin, 0);
@@ -682,18 +696,18 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_FINISH) {
     if (tc) {
-      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, 0, true, s);
+      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, s);
       if (rc) return rc;
     } else {
       k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, p.init_state, fin, 0);
       SSD_CUDA_CHECK_LAUNCH("state_passing");
     }
-    if (!tc || need_cb) {
+    if (!tc) {
       k_cb<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, (const T*)p.Bm, (const T*)p.Cm, cb);
       SSD_CUDA_CHECK_LAUNCH("cb");
     }
     if (p.y && tc) {
-      int rc = tensor_chunk_scan(g, p, cs, dtf, states, status, s);
+      int rc = tensor_chunk_scan(g, p, tab, prev_bf, status, s);
       if (rc) return rc;
     } else if (p.y) {
       k_chunk_scan<T, 0><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
@@ -720,6 +734,9 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   float* states = (float*)(ws + w.states);
   float* cb = (float*)(ws + w.cb);
   float* fin = (float*)(ws + w.fin);
+  float* tab = (float*)(ws + w.tab);
+  void* prev_bf = ws + w.prev_bf;
+  void* ds_bf = ws + w.ds_bf;
   float* dst = (float*)(ws + w.dstates);
   float* dyp = (float*)(ws + w.dyp);
   float* dcsp = (float*)(ws + w.dcsp);
@@ -750,10 +767,10 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       cudaMemsetAsync(ddot, 0, nq, s);
     }
     if (tc) {
-      int rc = tensor_scan_bwd(g, p, cs, dtf, states, dyp, dcsp, ddot, status, s);
+      int rc = tensor_scan_bwd(g, p, tab, prev_bf, dyp, dcsp, ddot, status, s);
       if (rc) return rc;
       rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
-                              tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, cs, dtf, dst, status, s);
+                              tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, dst, status, s);
       if (rc) return rc;
     } else {
       // forward recompute with the backward epilogue: dz, pre-gate dy, dcsp, ddot
@@ -768,7 +785,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_TOTAL) {
     if (tc) {
-      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, 1, false, s);
+      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, nullptr, 1, false, s);
       if (rc) return rc;
     } else {
       k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, nullptr, dini, 1);
@@ -777,7 +794,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_FINISH) {
     if (tc) {
-      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, 1, true, s);
+      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, ds_bf, 1, true, s);
       if (rc) return rc;
     } else {
       k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, p.dfinal_state, dini, 1);
@@ -786,9 +803,9 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
     k_sdot<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, dst, states, fin, sdot);
     SSD_CUDA_CHECK_LAUNCH("sdot");
     if (tc) {
-      int rc = tensor_dx(g, p, tc_dy, tc_dense, cs, dtf, dst, ddtd, status, s);
+      int rc = tensor_dx(g, p, tc_dy, tc_dense, tab, ds_bf, ddtd, status, s);
       if (rc) return rc;
-      rc = tensor_dbc(g, p, tc_dy, tc_dense, cs, dtf, states, dst, status, s);
+      rc = tensor_dbc(g, p, tc_dy, tc_dense, tab, prev_bf, ds_bf, status, s);
       if (rc) return rc;
     } else {
       k_dx<T><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, p.D, dys, cs, dtf, cb, dst,

@@ -1,14 +1,20 @@
-// bf16 tensor-core kernels (tcgen05.mma, accumulators in TMEM, operands fed by TMA) for the two
-// intra-chunk contractions of the SSD forward, chunk length 128.
+// bf16 tensor-core kernels (tcgen05.mma, accumulators in TMEM, operands fed by TMA) for the
+// intra-chunk contractions of the SSD forward and backward, chunk length 128.
 //
 //   k_state_tc : per (batch, chunk, group)   states[(h,p), n] = sum_l w[h,l] x[l,(h,p)] B[l,n]
 //                A = x tile, scaled in place in shared memory, read MN-major; B = B tile read
 //                MN-major; one 128 x N accumulator per 128 (h,p) rows.
 //   k_scan_tc  : per (batch, chunk, group)   G = C B^T once (128x128 in TMEM), then per head
 //                M_h = tril(G o exp(cs_i-cs_j) o dt_j) -> bf16 -> shared memory,
-//                Y = M_h X_h  (+)  exp(cs_i) * (C S_prev^T),  y = Y + D x, optional silu gate.
+//                Y = M_h X_h  (+)  exp(cs_i) * (C S_prev^T);  three epilogues (forward, backward
+//                recompute, dx).
+//   k_dbc_tc   : per (batch, chunk, group)   W_h = dY_h X_h^T, masked/decayed like M_h, then
+//                dC += W'_h B, dB += W'_h^T C accumulated over heads in TMEM, plus state terms.
 //
-// Shared-memory tiles and descriptor conventions are described in umma.cuh.  Each CTA has 256
+// Everything a CTA reads arrives asynchronously: sequence tiles and the bf16 copies of the
+// chunk-entry states by TMA, the per-head decay tables (written by the cumsum kernel) by 1-D
+// bulk copies; the next head block's inputs are in flight while the current one is computed.
+// Shared-memory tiles and descriptor conventions are described in umma.cuh.  Each CTA has 512
 // threads: thread t owns accumulator row (t % 128) and part (t / 128) of the columns.
 #include <mutex>
 
@@ -22,11 +28,14 @@ namespace {
 using namespace umma;
 typedef __nv_bfloat16 bf16;
 
-constexpr int QT = 128;          // chunk length of the tensor-core path
-constexpr int TC_THREADS = 512;   // 16 warps: 4 per TMEM lane quarter
+constexpr int QT = 128;               // chunk length of the tensor-core path
+constexpr int TC_THREADS = 512;       // 16 warps: 4 per TMEM lane quarter
 constexpr int PARTS = TC_THREADS / 128;
-constexpr int BOX_BYTES = 128 * 128;  // one TMA box: 128 rows x 64 bf16
-constexpr float LOG2E = 1.4426950408889634f;
+constexpr int BOX_BYTES = 128 * 128;  // sequence TMA box: 128 rows x 64 bf16
+constexpr int SBOX_BYTES = 64 * 128;  // state TMA box: 64 (h,p) rows x 64 bf16
+constexpr int TAB = SSD_TAB_FLOATS;   // floats per (batch, chunk, head) decay table
+constexpr int TAB_BYTES = TAB * 4;
+constexpr int T_CS = 0, T_DT = 128, T_CF = 256, T_DS = 384;   // table sections, 128 floats each
 constexpr int WAIT_LIMIT = 4000000;
 
 // Bounded waits: after the first one gives up every later wait is skipped, so a broken
@@ -43,50 +52,45 @@ struct Waiter {
   }
 };
 
-
 // ---------------------------------------------------------------------------------------------
 // Decayed lower-triangular tile.  Source: a 128x128 fp32 accumulator in TMEM (C B^T or dY X^T).
 // Result: out[i,j] = src[i,j] * exp(cs_i - cs_j) * dt_j for j <= i, written as bf16 into a plain
-// 128x128 tile.  Work is done in 32x32 blocks: blocks above the diagonal are never touched (the
-// caller zero-fills them once with zero_upper_blocks), the 4 diagonal blocks evaluate one exp per
-// element, and blocks below the diagonal use the factorisation
-//     exp(cs_i - cs_j) dt_j = exp(cs_i - cs_r) * [exp(cs_r - cs_j) dt_j],   r = last column of the block,
-// whose second factor is a per-column table (`cf`) and whose exponents are both <= 0, so nothing
-// can overflow.  cd[j] = {cs_j * log2(e), dt_j}.  Thread = (row, part): one 32x32 block per thread and head.
-__device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float2* __restrict__ cd,
-                                                const float* __restrict__ cf, int row, int part, int warp,
-                                                uint32_t mtile) {
+// 128x128 tile, one 32x32 block per thread-and-head:
+//   * blocks above the diagonal are never touched (zero_upper_blocks fills them once);
+//   * blocks below use exp(cs_i - cs_j) dt_j = exp(cs_i - cs_r) * [exp(cs_r - cs_j) dt_j] with r the
+//     last column of the block: one ex2 per thread, the bracket is the per-column table T_CF, and
+//     both exponents are <= 0 so nothing can overflow;
+//   * diagonal blocks build the row right-to-left from the per-step decays (T_DS[j] = exp(dt_j A)):
+//     L[i,i] = 1, L[i,j] = L[i,j+1] * decay_{j+1}; one multiply per element and no ex2.
+// tab = this head's table: T_CS cs*log2(e), T_DT dt, T_CF column factors, T_DS per-step decays.
+__device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __restrict__ tab, int row, int part,
+                                                int warp, uint32_t mtile) {
   const int rb = warp & 3, cb = part;   // both warp-uniform
   if (cb > rb) return;
-  const float csi = cd[row].x;
   const int c0 = cb * 32;
   float v[32];
   tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
   if (cb == rb) {
+    float run = 0.f;
 #pragma unroll
-    for (int j8 = 0; j8 < 32; j8 += 8) {
-      uint32_t pk[4];
-#pragma unroll
-      for (int k = 0; k < 8; k += 2) {
-        const int j = c0 + j8 + k;
-        const float2 e0 = cd[j], e1 = cd[j + 1];
-        const float m0 = (j <= row) ? v[j8 + k] * ex2(csi - e0.x) * e0.y : 0.f;
-        const float m1 = (j + 1 <= row) ? v[j8 + k + 1] * ex2(csi - e1.x) * e1.y : 0.f;
-        pk[k >> 1] = pack_bf16(m0, m1);
-      }
-      st_shared_v4(mtile + plain_off(128, row, c0 + j8), pk[0], pk[1], pk[2], pk[3]);
+    for (int k = 31; k >= 0; --k) {
+      const int j = c0 + k;
+      const float dn = tab[T_DS + ((j + 1) & 127)];
+      run = (j == row) ? 1.f : run * dn;
+      v[k] = v[k] * run * tab[T_DT + j];
     }
   } else {
-    const float rf = ex2(csi - cd[c0 + 31].x);
+    const float rf = ex2(tab[T_CS + row] - tab[T_CS + c0 + 31]);
 #pragma unroll
-    for (int j8 = 0; j8 < 32; j8 += 8) {
-      const float4 f0 = *reinterpret_cast<const float4*>(cf + c0 + j8);
-      const float4 f1 = *reinterpret_cast<const float4*>(cf + c0 + j8 + 4);
-      st_shared_v4(mtile + plain_off(128, row, c0 + j8),
-                   pack_bf16(v[j8] * rf * f0.x, v[j8 + 1] * rf * f0.y), pack_bf16(v[j8 + 2] * rf * f0.z, v[j8 + 3] * rf * f0.w),
-                   pack_bf16(v[j8 + 4] * rf * f1.x, v[j8 + 5] * rf * f1.y), pack_bf16(v[j8 + 6] * rf * f1.z, v[j8 + 7] * rf * f1.w));
+    for (int k4 = 0; k4 < 32; k4 += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(tab + T_CF + c0 + k4);
+      v[k4] *= rf * f.x; v[k4 + 1] *= rf * f.y; v[k4 + 2] *= rf * f.z; v[k4 + 3] *= rf * f.w;
     }
   }
+#pragma unroll
+  for (int j8 = 0; j8 < 32; j8 += 8)
+    st_shared_v4(mtile + plain_off(128, row, c0 + j8), pack_bf16(v[j8], v[j8 + 1]), pack_bf16(v[j8 + 2], v[j8 + 3]),
+                 pack_bf16(v[j8 + 4], v[j8 + 5]), pack_bf16(v[j8 + 6], v[j8 + 7]));
 }
 // zero the 32x32 blocks above the diagonal of a plain 128x128 tile (same thread mapping)
 __device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, uint32_t mtile) {
@@ -94,17 +98,13 @@ __device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, u
 #pragma unroll
   for (int j8 = 0; j8 < 32; j8 += 8) st_shared_v4(mtile + plain_off(128, row, part * 32 + j8), 0u, 0u, 0u, 0u);
 }
-// per-head tables for decay_mask_tile: cd[l] = {cs_l*log2e, dt_l}, cf[l] = exp(cs_r(l) - cs_l) dt_l
-__device__ __forceinline__ void stage_decay_tables(const Geo& g, const float* __restrict__ cs,
-                                                   const float* __restrict__ dtf, int b, int c, int h0, int nheads,
-                                                   float2* cd, float* cf, int tid) {
-  for (int i = tid; i < nheads * 128; i += TC_THREADS) {
-    const int hl = i >> 7, l = i & 127;
-    const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
-    const float a = cs[co + l] * LOG2E, d = dtf[co + l];
-    cd[i] = make_float2(a, d);
-    cf[i] = ex2(cs[co + (l | 31)] * LOG2E - a) * d;
-  }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), d = unpack_bf16(v.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&o)[8]) {
+  return make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -112,17 +112,18 @@ __device__ __forceinline__ void stage_decay_tables(const Geo& g, const float* __
 // w = exp(cs_l)).  grid = (nc, G, B).
 template <int P, int N, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
-                                                          const __grid_constant__ CUtensorMap tmB,
-                                                          const float* __restrict__ cs, const float* __restrict__ dtf,
-                                                          float* __restrict__ out, int* __restrict__ status) {
+                                                             const __grid_constant__ CUtensorMap tmB,
+                                                             const float* __restrict__ tab, float* __restrict__ out,
+                                                             int* __restrict__ status) {
   constexpr int NB = N / 64;       // 64-column boxes of the B/C tile
   constexpr int HT = 128 / P;      // heads per 128-row accumulator
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sB = smem;                         // NB boxes
-  uint8_t* sX = smem + NB * BOX_BYTES;        // 2 boxes: the x tile, scaled in place (high bf16 part)
-  uint8_t* sL = sX + 2 * BOX_BYTES;           // 2 boxes: low bf16 part of the scaled tile
-  float* sW = (float*)(sL + 2 * BOX_BYTES);   // [HT][128]
+  uint8_t* sB = smem;                          // NB boxes
+  uint8_t* sX = smem + NB * BOX_BYTES;         // 2 boxes: the x tile, scaled in place (high bf16 part)
+  uint8_t* sL = sX + 2 * BOX_BYTES;            // 2 boxes: low bf16 part of the scaled tile
+  float* sTab = (float*)(sL + 2 * BOX_BYTES);  // [HT][TAB]
+  float* sW = sTab + HT * TAB;                 // [HT][128]
   __shared__ __align__(8) uint64_t bar_b, bar_x, bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -147,9 +148,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
   const int MT = g.hpg * P / 128;             // accumulator tiles in this group
   const int col_base = grp * g.hpg * P;       // first (h,p) column of the group in x
   auto load_tile = [&](int mt) {              // thread 0 only
-    mbar_expect_tx(&bar_x, 2 * BOX_BYTES);
+    mbar_expect_tx(&bar_x, 2 * BOX_BYTES + HT * TAB_BYTES);
     tma_load_3d(sX, &tmX, col_base + mt * 128, c * QT, b, &bar_x);
     tma_load_3d(sX + BOX_BYTES, &tmX, col_base + mt * 128 + 64, c * QT, b, &bar_x);
+    bulk_load(sTab, tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + mt * HT) * TAB, HT * TAB_BYTES, &bar_x);
   };
   if (tid == 0) {
     mbar_expect_tx(&bar_b, NB * BOX_BYTES);
@@ -160,14 +162,14 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
   const uint32_t idesc = make_idesc(128, N, 1, 1);
   for (int mt = 0; mt < MT; ++mt) {
     const int h0 = grp * g.hpg + mt * HT;
-    for (int i = tid; i < HT * 128; i += TC_THREADS) {
-      const int hl = i >> 7, l = i & 127;
-      const size_t co = ((size_t)(b * g.H + h0 + hl) * g.nc + c) * QT;
-      sW[i] = (MODE == 0) ? ex2((cs[co + QT - 1] - cs[co + l]) * LOG2E) * dtf[co + l] : ex2(cs[co + l] * LOG2E);
-    }
-    __syncthreads();
     w.wait(&bar_x, xphase, 11);
     xphase ^= 1;
+    for (int i = tid; i < HT * 128; i += TC_THREADS) {
+      const float* t = sTab + (i >> 7) * TAB;
+      const int l = i & 127;
+      sW[i] = (MODE == 0) ? ex2(t[T_CS + 127] - t[T_CS + l]) * t[T_DT + l] : ex2(t[T_CS + l]);
+    }
+    __syncthreads();
     // scale the tile: 2 boxes x 128 rows x 8 chunks of 16 bytes.  The product w*x is split into a
     // high and a low bf16 part (two MMAs) so the chunk states keep ~16 mantissa bits: they feed
     // every later stage, and the per-chunk term of dA is a strongly cancelling sum over them.
@@ -180,15 +182,15 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
       const float wv = sW[hl * 128 + l];
       const uint32_t off = box * BOX_BYTES + l * 128 + pc * 16;
       const uint32_t a = smem_u32(sX) + off;
-      const uint4 v = ld_shared_v4(a);
-      const float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-      const float f[8] = {f0.x * wv, f0.y * wv, f1.x * wv, f1.y * wv, f2.x * wv, f2.y * wv, f3.x * wv, f3.y * wv};
+      float f[8];
+      unpack8(ld_shared_v4(a), f);
       uint32_t hi[4], lo[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        hi[k] = pack_bf16(f[2 * k], f[2 * k + 1]);
+        const float f0 = f[2 * k] * wv, f1 = f[2 * k + 1] * wv;
+        hi[k] = pack_bf16(f0, f1);
         const float2 hf = unpack_bf16(hi[k]);
-        lo[k] = pack_bf16(f[2 * k] - hf.x, f[2 * k + 1] - hf.y);
+        lo[k] = pack_bf16(f0 - hf.x, f1 - hf.y);
       }
       st_shared_v4(a, hi[0], hi[1], hi[2], hi[3]);
       st_shared_v4(smem_u32(sL) + off, lo[0], lo[1], lo[2], lo[3]);
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
     w.wait(&bar_mma, mphase, 13);
     mphase ^= 1;
     tc_fence_after();
-    if (tid == 0 && mt + 1 < MT) load_tile(mt + 1);   // the tile buffers are free again
+    if (tid == 0 && mt + 1 < MT) load_tile(mt + 1);   // the tile buffers and the table are free again
     // epilogue: row = (head, p) of this tile, N / PARTS columns per thread
     float* o = out + (((size_t)(b * g.nc + c) * g.H + h0) * P + row) * N + part * (N / PARTS);
 #pragma unroll
@@ -237,33 +239,28 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
 //                                row sums  dcsp[i] = sum_p dy*Y,  ddot[i] = sum_p dy*x
 //   MODE 2 (backward, dx)        U' = M_h^T dY_h (+) dt_j exp(cs_end-cs_j) B dS_end^T
 //                                dx = D dy + U',  ddtd[j] = sum_p x*U' / dt_j
-// "SV" below is the fp32 [64 x N] state block staged as bf16: S_prev (modes 0,1) or dS_end (2).
-template <int P, int N, int XBUF, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
-                                                         const __grid_constant__ CUtensorMap tmDY,
-                                                         const __grid_constant__ CUtensorMap tmB,
-                                                         const __grid_constant__ CUtensorMap tmC,
-                                                         const float* __restrict__ cs, const float* __restrict__ dtf,
-                                                         const float* __restrict__ sv, const float* __restrict__ D,
-                                                         const bf16* __restrict__ z, bf16* __restrict__ y,
-                                                         const bf16* __restrict__ dy, bf16* __restrict__ dypb,
-                                                         bf16* __restrict__ dz, bf16* __restrict__ dx,
-                                                         float* __restrict__ rs0, float* __restrict__ rs1,
-                                                         int* __restrict__ status) {
+// The state block (tmS) is the bf16 copy of S_prev (modes 0,1) or dS_end (mode 2).
+// IBUF = 2: the inputs of head block k+1 load while block k computes; IBUF = 1: they are
+// requested as soon as block k's epilogue has copied what it needs into registers.
+template <int P, int N, int IBUF, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1)
+k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+          const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
+          const bf16* __restrict__ z, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
+          bf16* __restrict__ dx, float* __restrict__ rs0, float* __restrict__ rs1, int* __restrict__ status) {
   constexpr int NB = N / 64;
   constexpr int HB = 64 / P;                   // heads per 64-column box
-  constexpr int NBOX = (MODE == 0) ? 1 : 2;    // boxes per head block: x (and dy)
+  constexpr int NBOX = (MODE == 0) ? 1 : 2;    // sequence boxes per head block: x (and dy)
+  constexpr int IN_BYTES = NBOX * BOX_BYTES + NB * SBOX_BYTES + HB * TAB_BYTES;
   constexpr uint32_t TM_COLS = 256;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sKeep = smem;                       // NB boxes kept for the whole CTA: C (modes 0,1) or B (mode 2)
   uint8_t* sBM = sKeep + NB * BOX_BYTES;       // the other tile (NB boxes), later the 32 KB M_h tile
-  uint8_t* sX = sBM + 2 * BOX_BYTES;           // XBUF x NBOX boxes: x [, dy]
-  uint8_t* sS = sX + XBUF * NBOX * BOX_BYTES;  // 64 x N bf16, plain layout
-  float2* sCD = (float2*)(sS + 64 * N * 2);    // [HB][128] {cs*log2e, dt}
-  float* sCF = (float*)(sCD + HB * 128);       // [HB][128] column factors of decay_mask_tile
-  float* sRed = sCF + HB * 128;                // [2][PARTS][128] partial row sums (modes 1, 2)
-  __shared__ __align__(8) uint64_t bar_cb, bar_x[2], bar_mma;
+  uint8_t* sIn = sBM + 2 * BOX_BYTES;          // IBUF x {x [, dy], state boxes, tables}
+  float* sRed = (float*)(sIn + IBUF * IN_BYTES);  // [2][PARTS][128] partial row sums (modes 1, 2)
+  __shared__ __align__(8) uint64_t bar_cb, bar_in[2], bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -274,7 +271,7 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
   const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
-    mbar_init(&bar_cb, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_cb, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
@@ -287,11 +284,16 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
 
   const int nblk = g.hpg / HB;
   const int col_base = grp * g.hpg * P;
-  auto load_boxes = [&](int blk, int buf) {   // thread 0 only
-    uint8_t* dst = sX + buf * NBOX * BOX_BYTES;
-    mbar_expect_tx(&bar_x[buf], NBOX * BOX_BYTES);
-    tma_load_3d(dst, &tmX, col_base + blk * 64, c * QT, b, &bar_x[buf]);
-    if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col_base + blk * 64, c * QT, b, &bar_x[buf]);
+  auto load_block = [&](int blk, int ib) {    // thread 0 only
+    uint8_t* dst = sIn + ib * IN_BYTES;
+    const int h0 = grp * g.hpg + blk * HB;
+    mbar_expect_tx(&bar_in[ib], IN_BYTES);
+    tma_load_3d(dst, &tmX, col_base + blk * 64, c * QT, b, &bar_in[ib]);
+    if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col_base + blk * 64, c * QT, b, &bar_in[ib]);
+    for (int kb = 0; kb < NB; ++kb)
+      tma_load_3d(dst + NBOX * BOX_BYTES + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_in[ib]);
+    bulk_load(dst + NBOX * BOX_BYTES + NB * SBOX_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES,
+              &bar_in[ib]);
   };
   if (tid == 0) {
     mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
@@ -299,9 +301,10 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
       tma_load_3d(sKeep + kb * BOX_BYTES, (MODE == 2) ? &tmB : &tmC, grp * N + kb * 64, c * QT, b, &bar_cb);
       tma_load_3d(sBM + kb * BOX_BYTES, (MODE == 2) ? &tmC : &tmB, grp * N + kb * 64, c * QT, b, &bar_cb);
     }
-    load_boxes(0, 0);
+    load_block(0, 0);
+    if (IBUF == 2 && nblk > 1) load_block(1, 1);
   }
-  uint32_t xphase[2] = {0, 0}, mphase = 0;
+  uint32_t inphase[2] = {0, 0}, mphase = 0;
   w.wait(&bar_cb, 0, 21);
   if (tid == 0) {
     tc_fence_after();
@@ -322,31 +325,21 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
 
   const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
   const int t_row = c * QT + row;
+  const int hl_e = (part * 16) / P;            // head (inside the block) of this thread's epilogue columns
   for (int blk = 0; blk < nblk; ++blk) {
-    const int buf = (XBUF == 2) ? (blk & 1) : 0;
-    uint8_t* xt = sX + buf * NBOX * BOX_BYTES;          // x box
-    uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;         // dy box (modes 1, 2)
+    const int ib = (IBUF == 2) ? (blk & 1) : 0;
+    uint8_t* xt = sIn + ib * IN_BYTES;                    // x box
+    uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;           // dy box (modes 1, 2)
+    uint8_t* st = xt + NBOX * BOX_BYTES;                  // state boxes
+    const float* tb = (const float*)(st + NB * SBOX_BYTES);   // [HB][TAB]
     const int h0 = grp * g.hpg + blk * HB;
-    if (XBUF == 2 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1, buf ^ 1);
-    stage_decay_tables(g, cs, dtf, b, c, h0, HB, sCD, sCF, tid);
-    {  // state block of these heads: 64 rows x N fp32 -> bf16, plain layout (rows = 64)
-      const float* pv = sv + (((size_t)(b * g.nc + c) * g.H + h0) * P) * N;
-      for (int u = tid; u < 64 * (N / 8); u += TC_THREADS) {
-        const int r = u & 63, ch = u >> 6;
-        const float4 a = *reinterpret_cast<const float4*>(pv + (size_t)r * N + ch * 8);
-        const float4 bb = *reinterpret_cast<const float4*>(pv + (size_t)r * N + ch * 8 + 4);
-        st_shared_v4(smem_u32(sS) + plain_off(64, r, ch * 8), pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
-                     pack_bf16(bb.x, bb.y), pack_bf16(bb.z, bb.w));
-      }
-    }
-    __syncthreads();
+    const int h_e = h0 + hl_e;
+    const float Dh = D ? __ldg(D + h_e) : 0.f;            // requested now, used in the epilogue
+    w.wait(&bar_in[ib], inphase[ib], 23);
+    inphase[ib] ^= 1;
     for (int hl = 0; hl < HB; ++hl) {
-      decay_mask_tile(tmG, sCD + hl * 128, sCF + hl * 128, row, part, warp, smem_u32(sBM));
+      decay_mask_tile(tmG, tb + hl * TAB, row, part, warp, smem_u32(sBM));
       fence_async_smem();
-      if (hl == 0) {
-        w.wait(&bar_x[buf], xphase[buf], 23);
-        xphase[buf] ^= 1;
-      }
       tc_fence_before();
       __syncthreads();
       if (tid == 0) {
@@ -357,12 +350,12 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
           mma_bf16(tmYd + hl * P, (MODE == 2) ? desc_plain_mn(ma, 128, ks * 16, 0) : desc_plain_k(ma, 128, ks * 16),
                    desc_sw128_mn(oa, ks * 16, hl * P * 2, 16), idY, ks > 0);
         if (hl == 0) {
-          const uint32_t ka = smem_u32(sKeep), sa = smem_u32(sS);
+          const uint32_t ka = smem_u32(sKeep), sa = smem_u32(st);
 #pragma unroll
           for (int kb = 0; kb < NB; ++kb)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmYo, desc_sw128_k(ka + kb * BOX_BYTES, ks * 32), desc_plain_k(sa, 64, kb * 64 + ks * 16), idO,
+              mma_bf16(tmYo, desc_sw128_k(ka + kb * BOX_BYTES, ks * 32), desc_sw128_k(sa + kb * SBOX_BYTES, ks * 32), idO,
                        (kb | ks) > 0);
         }
         mma_commit(&bar_mma);
@@ -371,50 +364,45 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
       mphase ^= 1;
       tc_fence_after();
     }
-    // epilogue for the HB heads of this block: this thread has 64/PARTS = 16 of the 64 columns
+    // ---- epilogue for the HB heads of this block: this thread has 64/PARTS = 16 of the 64 columns.
+    // Copy what is needed from the input buffers into registers first, so the buffers can be refilled.
+    uint4 xv[2], dv[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      xv[q] = ld_shared_v4(smem_u32(xt) + sw128_off(row, part * 2 + q));
+      dv[q] = (MODE != 0) ? ld_shared_v4(smem_u32(dyt) + sw128_off(row, part * 2 + q)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const float cs_r = tb[hl_e * TAB + T_CS + row], dt_r = tb[hl_e * TAB + T_DT + row];
+    // off-diagonal scale: exp(cs_i) for Y, dt_j exp(cs_end - cs_j) for U'
+    const float osc = (MODE == 2) ? dt_r * ex2(tb[hl_e * TAB + T_CS + 127] - cs_r) : ex2(cs_r);
+    if (IBUF == 1) {
+      __syncthreads();
+      if (tid == 0 && blk + 1 < nblk) load_block(blk + 1, 0);
+    }
     float s0 = 0.f, s1 = 0.f;
-    const int hl_e = (part * 16) / P;                    // head of this thread's columns
-    const int h_e = h0 + hl_e;
-    const float2 cd_e = sCD[hl_e * 128 + row];
     {
       float yd[16], yo[16];
       tmem_ld16(tmem_addr(tmYd, (warp & 3) * 32, part * 16), yd);
       tmem_ld16(tmem_addr(tmYo, (warp & 3) * 32, part * 16), yo);
-      const float Dh = D ? __ldg(D + h_e) : 0.f;
       const long long colo = (long long)h0 * P + part * 16;
       const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
       const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + colo;
-      // off-diagonal scale: exp(cs_i) for Y, dt_j exp(cs_end - cs_j) for U'
-      const float osc = (MODE == 2) ? cd_e.y * ex2(sCD[hl_e * 128 + 127].x - cd_e.x) : ex2(cd_e.x);
 #pragma unroll
-      for (int k8 = 0; k8 < 16; k8 += 8) {
-        const int chunk = (part * 16 + k8) >> 3;
-        const uint4 xv = ld_shared_v4(smem_u32(xt) + sw128_off(row, chunk));
-        const float2 x0 = unpack_bf16(xv.x), x1 = unpack_bf16(xv.y), x2 = unpack_bf16(xv.z), x3 = unpack_bf16(xv.w);
-        const float xs[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
-        float acc[8];
+      for (int q = 0; q < 2; ++q) {
+        const int k8 = q * 8;
+        float xs[8], acc[8], zs[8], dys[8], o[8];
+        unpack8(xv[q], xs);
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = yd[k8 + k] + osc * yo[k8 + k];
-        float zs[8], dys[8];
-        if (z) {
-          const uint4 zv = *reinterpret_cast<const uint4*>(zp + k8);
-          const float2 z0 = unpack_bf16(zv.x), z1 = unpack_bf16(zv.y), z2 = unpack_bf16(zv.z), z3 = unpack_bf16(zv.w);
-          zs[0] = z0.x; zs[1] = z0.y; zs[2] = z1.x; zs[3] = z1.y; zs[4] = z2.x; zs[5] = z2.y; zs[6] = z3.x; zs[7] = z3.y;
-        }
-        if (MODE != 0) {
-          const uint4 dv = ld_shared_v4(smem_u32(dyt) + sw128_off(row, chunk));
-          const float2 d0 = unpack_bf16(dv.x), d1 = unpack_bf16(dv.y), d2 = unpack_bf16(dv.z), d3 = unpack_bf16(dv.w);
-          dys[0] = d0.x; dys[1] = d0.y; dys[2] = d1.x; dys[3] = d1.y; dys[4] = d2.x; dys[5] = d2.y; dys[6] = d3.x; dys[7] = d3.y;
-        }
-        float o[8];
+        if (z) unpack8(*reinterpret_cast<const uint4*>(zp + k8), zs);
+        if (MODE != 0) unpack8(dv[q], dys);
         if (MODE == 0) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             o[k] = acc[k] + Dh * xs[k];
             if (z) o[k] *= zs[k] * sigmoidf_(zs[k]);
           }
-          *reinterpret_cast<uint4*>(y + b * g.ysb + (long long)t_row * g.ysl + colo + k8) =
-              make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+          *reinterpret_cast<uint4*>(y + b * g.ysb + (long long)t_row * g.ysl + colo + k8) = pack8(o);
         } else if (MODE == 1) {
           float dp[8];
 #pragma unroll
@@ -430,10 +418,8 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
             s1 = fmaf(dyv, xs[k], s1);
           }
           if (z) {
-            *reinterpret_cast<uint4*>(dz + dense + k8) =
-                make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
-            *reinterpret_cast<uint4*>(dypb + dense + k8) =
-                make_uint4(pack_bf16(dp[0], dp[1]), pack_bf16(dp[2], dp[3]), pack_bf16(dp[4], dp[5]), pack_bf16(dp[6], dp[7]));
+            *reinterpret_cast<uint4*>(dz + dense + k8) = pack8(o);
+            *reinterpret_cast<uint4*>(dypb + dense + k8) = pack8(dp);
           }
         } else {
 #pragma unroll
@@ -441,8 +427,7 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
             o[k] = acc[k] + Dh * dys[k];
             s0 = fmaf(xs[k], acc[k], s0);
           }
-          *reinterpret_cast<uint4*>(dx + dense + k8) =
-              make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+          *reinterpret_cast<uint4*>(dx + dense + k8) = pack8(o);
         }
       }
       if (MODE != 0) {   // row sums: P/16 threads share a (head, row); combine through shared memory
@@ -464,10 +449,10 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
         rs0[co] = t0;   // dcsp
         rs1[co] = t1;   // ddot
       } else {
-        rs0[co] = cd_e.y > 0.f ? t0 / cd_e.y : 0.f;   // ddtd
+        rs0[co] = dt_r > 0.f ? t0 / dt_r : 0.f;   // ddtd
       }
     }
-    if (XBUF == 1 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1, 0);
+    if (IBUF == 2 && tid == 0 && blk + 2 < nblk) load_block(blk + 2, ib);
   }
   if (warp == 1) tmem_dealloc(tm, TM_COLS);
 }
@@ -478,14 +463,11 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_scan_tc(Geo g
 //   dC[i,n] += W'_h B      (+ per head block)  (exp(cs_i) dY) S_prev
 //   dB[j,n] += W'_h^T C    (+ per head block)  (exp(cs_end-cs_j) dt_j X) dS_end
 template <int P, int N>
-__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX,
-                                                        const __grid_constant__ CUtensorMap tmDY,
-                                                        const __grid_constant__ CUtensorMap tmB,
-                                                        const __grid_constant__ CUtensorMap tmC,
-                                                        const float* __restrict__ cs, const float* __restrict__ dtf,
-                                                        const float* __restrict__ prev, const float* __restrict__ dS,
-                                                        bf16* __restrict__ dB, bf16* __restrict__ dC,
-                                                        int* __restrict__ status) {
+__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1)
+k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+         const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmDS,
+         const float* __restrict__ tab, bf16* __restrict__ dB, bf16* __restrict__ dC, int* __restrict__ status) {
   constexpr int NB = N / 64;
   constexpr int HB = 64 / P;
   constexpr uint32_t TM_COLS = (128 + 2 * N <= 256) ? 256 : 512;
@@ -496,11 +478,10 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
   uint8_t* sM = sC + NB * BOX_BYTES;           // 32 KB W'_h tile, plain layout
   uint8_t* sX = sM + 2 * BOX_BYTES;            // x box
   uint8_t* sDY = sX + BOX_BYTES;               // dy box
-  uint8_t* sS = sM;                            // S_prev block, 64 x N bf16 plain: reuses the W' tile
-  uint8_t* sDS = sM + 64 * N * 2;              // dS_end block            (after the head loop)
-  float2* sCD = (float2*)(sDY + BOX_BYTES);    // [HB][128]
-  float* sCF = (float*)(sCD + HB * 128);       // [HB][128]
-  __shared__ __align__(8) uint64_t bar_cb, bar_x, bar_mma;
+  uint8_t* sS = sM;                            // S_prev boxes (NB x 8 KB): reuse the W' tile after the head loop
+  uint8_t* sDS = sM + NB * SBOX_BYTES;         // dS_end boxes
+  float* sTab = (float*)(sDY + BOX_BYTES);     // [HB][TAB]
+  __shared__ __align__(8) uint64_t bar_cb, bar_x, bar_s, bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -511,7 +492,7 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
   const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
-    mbar_init(&bar_cb, 1); mbar_init(&bar_x, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_cb, 1); mbar_init(&bar_x, 1); mbar_init(&bar_s, 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
@@ -524,10 +505,11 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
 
   const int nblk = g.hpg / HB;
   const int col_base = grp * g.hpg * P;
-  auto load_boxes = [&](int blk) {
-    mbar_expect_tx(&bar_x, 2 * BOX_BYTES);
+  auto load_boxes = [&](int blk) {             // thread 0 only
+    mbar_expect_tx(&bar_x, 2 * BOX_BYTES + HB * TAB_BYTES);
     tma_load_3d(sX, &tmX, col_base + blk * 64, c * QT, b, &bar_x);
     tma_load_3d(sDY, &tmDY, col_base + blk * 64, c * QT, b, &bar_x);
+    bulk_load(sTab, tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + blk * HB) * TAB, HB * TAB_BYTES, &bar_x);
   };
   if (tid == 0) {
     mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
@@ -537,7 +519,7 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
     }
     load_boxes(0);
   }
-  uint32_t xphase = 0, mphase = 0;
+  uint32_t xphase = 0, sphase = 0, mphase = 0;
   const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
   auto issue_w = [&](int hl) {   // thread 0: W = dY_h X_h^T, K = P
     const uint32_t da = smem_u32(sDY), xa = smem_u32(sX);
@@ -549,8 +531,7 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
   bool first = true;
   for (int blk = 0; blk < nblk; ++blk) {
     const int h0 = grp * g.hpg + blk * HB;
-    stage_decay_tables(g, cs, dtf, b, c, h0, HB, sCD, sCF, tid);
-    zero_upper_blocks(row, part, warp, smem_u32(sM));   // the state blocks of the previous head block lived here
+    zero_upper_blocks(row, part, warp, smem_u32(sM));   // the state boxes of the previous head block lived here
     w.wait(&bar_x, xphase, 32);
     xphase ^= 1;
     tc_fence_before();
@@ -564,7 +545,7 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
     mphase ^= 1;
     tc_fence_after();
     for (int hl = 0; hl < HB; ++hl) {
-      decay_mask_tile(tmW, sCD + hl * 128, sCF + hl * 128, row, part, warp, smem_u32(sM));
+      decay_mask_tile(tmW, sTab + hl * TAB, row, part, warp, smem_u32(sM));
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
@@ -584,35 +565,33 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
       mphase ^= 1;
       tc_fence_after();
     }
-    // state terms of this head block: stage S_prev and dS_end (fp32 -> bf16) over the W' tile, scale
-    // the dy box by exp(cs_i) and the x box by exp(cs_end - cs_j) dt_j in place, then one K = 64
-    // product each
-    {
-      const size_t so = (((size_t)(b * g.nc + c) * g.H + h0) * P) * N;
-      for (int u = tid; u < 2 * 64 * (N / 8); u += TC_THREADS) {
-        const int which = u / (64 * (N / 8)), uu = u % (64 * (N / 8));
-        const int r = uu & 63, ch = uu >> 6;
-        const float* pv = (which ? dS : prev) + so + (size_t)r * N + ch * 8;
-        const float4 a = *reinterpret_cast<const float4*>(pv);
-        const float4 bb = *reinterpret_cast<const float4*>(pv + 4);
-        st_shared_v4(smem_u32(which ? sDS : sS) + plain_off(64, r, ch * 8), pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
-                     pack_bf16(bb.x, bb.y), pack_bf16(bb.z, bb.w));
+    // state terms of this head block: fetch the bf16 S_prev and dS_end boxes over the W' tile (its
+    // last readers have completed), scale the dy box by exp(cs_i) and the x box by
+    // exp(cs_end - cs_j) dt_j in place meanwhile, then one K = 64 product each
+    if (tid == 0) {
+      mbar_expect_tx(&bar_s, 2 * NB * SBOX_BYTES);
+      for (int kb = 0; kb < NB; ++kb) {
+        tma_load_3d(sS + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_s);
+        tma_load_3d(sDS + kb * SBOX_BYTES, &tmDS, kb * 64, h0 * P, b * g.nc + c, &bar_s);
       }
     }
 #pragma unroll
     for (int r = 0; r < 2048 / TC_THREADS; ++r) {
       const int idx = tid + r * TC_THREADS;
       const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
-      const int hl = (((pc ^ l) & 7) * 8) / P;
-      const float2 cd = sCD[hl * 128 + l];
-      const float f = box ? ex2(cd.x) : ex2(sCD[hl * 128 + 127].x - cd.x) * cd.y;
+      const float* t = sTab + ((((pc ^ l) & 7) * 8) / P) * TAB;
+      const float f = box ? ex2(t[T_CS + l]) : ex2(t[T_CS + 127] - t[T_CS + l]) * t[T_DT + l];
       const uint32_t a = smem_u32((box ? sDY : sX) + l * 128 + pc * 16);
-      uint4 v = ld_shared_v4(a);
-      float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-      st_shared_v4(a, pack_bf16(f0.x * f, f0.y * f), pack_bf16(f1.x * f, f1.y * f), pack_bf16(f2.x * f, f2.y * f),
-                   pack_bf16(f3.x * f, f3.y * f));
+      float v[8];
+      unpack8(ld_shared_v4(a), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] *= f;
+      const uint4 o = pack8(v);
+      st_shared_v4(a, o.x, o.y, o.z, o.w);
     }
     fence_async_smem();
+    w.wait(&bar_s, sphase, 36);
+    sphase ^= 1;
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
@@ -620,8 +599,8 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
       const uint32_t da = smem_u32(sDY), xa = smem_u32(sX), sa = smem_u32(sS), dsa = smem_u32(sDS);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        mma_bf16(tmDC, desc_sw128_k(da, ks * 32), desc_plain_mn(sa, 64, ks * 16, 0), idC, true);
-        mma_bf16(tmDB, desc_sw128_k(xa, ks * 32), desc_plain_mn(dsa, 64, ks * 16, 0), idC, true);
+        mma_bf16(tmDC, desc_sw128_k(da, ks * 32), desc_sw128_mn(sa, ks * 16, 0, SBOX_BYTES), idC, true);
+        mma_bf16(tmDB, desc_sw128_k(xa, ks * 32), desc_sw128_mn(dsa, ks * 16, 0, SBOX_BYTES), idC, true);
       }
       mma_commit(&bar_mma);
     }
@@ -655,10 +634,11 @@ __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1) k_dbc_tc(Geo g,
 
 // ---------------------------------------------------------------------------------------------
 // Exclusive scan over chunks, 4 state elements per thread, decays staged in shared memory.
+// Optionally also writes the bf16 copy of the chunk-entry states that the tensor kernels load.
 template <bool WRITE>
 __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restrict__ st, const float* __restrict__ cs,
                                                           const float* __restrict__ init, float* __restrict__ last,
-                                                          int reverse) {
+                                                          bf16* __restrict__ st_bf, int reverse) {
   extern __shared__ float sdec[];  // [nc]
   const int h = blockIdx.y, b = blockIdx.z;
   const int PN = g.P * g.N;
@@ -670,7 +650,8 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
   float4 run = init ? *reinterpret_cast<const float4*>(init + ((size_t)(b * g.H + h)) * PN + e)
                     : make_float4(0.f, 0.f, 0.f, 0.f);
   const size_t cstride = (size_t)g.H * PN;
-  float* base = st + ((size_t)b * g.nc * g.H + h) * PN + e;
+  const size_t boff = ((size_t)b * g.nc * g.H + h) * PN + e;
+  float* base = st + boff;
   constexpr int U = 4;
   for (int s0 = 0; s0 < g.nc; s0 += U) {
     float4 v[U];
@@ -687,7 +668,12 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
       const int s = s0 + u;
       if (s < g.nc) {
         const int c = reverse ? g.nc - 1 - s : s;
-        if (WRITE) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+        if (WRITE) {
+          *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+          if (st_bf)
+            *reinterpret_cast<uint2*>(st_bf + boff + (size_t)c * cstride) =
+                make_uint2(pack_bf16(run.x, run.y), pack_bf16(run.z, run.w));
+        }
         const float d = sdec[c];
         run.x = fmaf(d, run.x, v[u].x); run.y = fmaf(d, run.y, v[u].y);
         run.z = fmaf(d, run.z, v[u].z); run.w = fmaf(d, run.w, v[u].w);
@@ -715,14 +701,14 @@ EncodeFn get_encode() {
   return fn;
 }
 
-// 3-D map over a [batch, seqlen, cols] bf16 tensor (cols dense), box = 64 cols x 128 rows, 128B swizzle.
-int make_seq_map(CUtensorMap* m, const void* ptr, long long cols, long long L, long long B, long long stride_l,
-                 long long stride_b, const char* what) {
+// 3-D bf16 map, 128B swizzle: dims (fastest first) {d0, d1, d2}, strides in ELEMENTS, box {64, box1, 1}.
+int make_map3(CUtensorMap* m, const void* ptr, long long d0, long long d1, long long d2, long long s1, long long s2,
+              int box1, const char* what) {
   EncodeFn enc = get_encode();
   if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return SSD_ERR_CUDA; }
-  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)L, (cuuint64_t)B};
-  cuuint64_t strides[2] = {(cuuint64_t)stride_l * 2, (cuuint64_t)stride_b * 2};
-  cuuint32_t box[3] = {64, 128, 1};
+  cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)d2};
+  cuuint64_t strides[2] = {(cuuint64_t)s1 * 2, (cuuint64_t)s2 * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box1, 1};
   cuuint32_t es[3] = {1, 1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -730,79 +716,99 @@ int make_seq_map(CUtensorMap* m, const void* ptr, long long cols, long long L, l
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r); return SSD_ERR_CUDA; }
   return SSD_OK;
 }
+// [batch, seqlen, cols] sequence tensor: box = 64 cols x 128 rows
+int make_seq_map(CUtensorMap* m, const void* ptr, long long cols, long long L, long long B, long long stride_l,
+                 long long stride_b, const char* what) {
+  return make_map3(m, ptr, cols, L, B, stride_l, stride_b, 128, what);
+}
+// dense [B*nc, H*P, N] bf16 chunk states: box = 64 cols (n) x 64 rows ((h,p))
+int make_state_map(CUtensorMap* m, const Geo& g, const void* ptr, const char* what) {
+  return make_map3(m, ptr, g.N, (long long)g.H * g.P, (long long)g.B * g.nc, g.N, (long long)g.H * g.P * g.N, 64, what);
+}
 
 template <int P, int N>
-constexpr size_t state_smem() { return 1024 + (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (128 / P) * 128 * 4; }
-template <int P, int N, int XBUF, int MODE>
+constexpr size_t state_smem() { return 1024 + (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (128 / P) * (TAB_BYTES + 512); }
+template <int P, int N, int IBUF, int MODE>
 constexpr size_t scan_smem() {
-  return 1024 + (N / 64) * BOX_BYTES + 2 * BOX_BYTES + XBUF * (MODE == 0 ? 1 : 2) * BOX_BYTES + 64 * N * 2 +
-         (64 / P) * 128 * 12 + (MODE == 0 ? 0 : 2 * PARTS * 128 * 4);
+  return 1024 + (N / 64) * BOX_BYTES + 2 * BOX_BYTES +
+         IBUF * ((MODE == 0 ? 1 : 2) * BOX_BYTES + (N / 64) * SBOX_BYTES + (64 / P) * TAB_BYTES) +
+         (MODE == 0 ? 0 : 2 * PARTS * 128 * 4);
 }
 template <int P, int N>
-constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * 128 * 12; }
+constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * TAB_BYTES; }
 
 template <int P, int N, int MODE>
-int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* cs, const float* dtf,
-                 float* out, int* status, cudaStream_t s) {
+int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* tab, float* out, int* status,
+                 cudaStream_t s) {
   auto k = k_state_tc<P, N, MODE>;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P, N>());
-  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, state_smem<P, N>(), s>>>(g, tx, tb, cs, dtf, out, status);
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, state_smem<P, N>(), s>>>(g, tx, tb, tab, out, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_state_tc" : "dstates_local_tc");
   return SSD_OK;
 }
 
 struct ScanArgs {
-  const float *cs, *dtf, *sv, *D;
+  const float *tab, *D;
   const void* z;
-  void* y;
-  const void* dy;
-  void *dypb, *dz, *dx;
+  void *y, *dypb, *dz, *dx;
   float *rs0, *rs1;
+};
+struct SeqMaps {
+  CUtensorMap x, dy, b, c, s, ds;
 };
 
 template <int P, int N, int MODE>
-int launch_scan(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tdy, const CUtensorMap& tb,
-                const CUtensorMap& tc, const ScanArgs& a, int* status, cudaStream_t s) {
-  constexpr int XBUF = (MODE == 0 && N < 128) ? 2 : 1;
-  auto k = k_scan_tc<P, N, XBUF, MODE>;
-  constexpr size_t sm = scan_smem<P, N, XBUF, MODE>();
+int launch_scan(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const ScanArgs& a, int* status, cudaStream_t s) {
+  constexpr int IBUF = (MODE == 0 && N < 128) ? 2 : 1;
+  auto k = k_scan_tc<P, N, IBUF, MODE>;
+  constexpr size_t sm = scan_smem<P, N, IBUF, MODE>();
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, sm, s>>>(g, tx, tdy, tb, tc, a.cs, a.dtf, a.sv, a.D, (const bf16*)a.z, (bf16*)a.y,
-                                                 (const bf16*)a.dy, (bf16*)a.dypb, (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1,
-                                                 status);
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y,
+                                                 (bf16*)a.dypb, (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_tc" : (MODE == 1 ? "chunk_scan_bwd_tc" : "dx_tc"));
   return SSD_OK;
 }
 
 template <int P, int N>
-int launch_dbc(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tdy, const CUtensorMap& tb, const CUtensorMap& tc,
-               const float* cs, const float* dtf, const float* prev, const float* dS, void* dB, void* dC, int* status,
-               cudaStream_t s) {
+int launch_dbc(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
   auto k = k_dbc_tc<P, N>;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dbc_smem<P, N>());
-  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, dbc_smem<P, N>(), s>>>(g, tx, tdy, tb, tc, cs, dtf, prev, dS, (bf16*)dB, (bf16*)dC,
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, dbc_smem<P, N>(), s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, (bf16*)dB, (bf16*)dC,
                                                                status);
   SSD_CUDA_CHECK_LAUNCH("dBdC_tc");
   return SSD_OK;
 }
 
-struct SeqMaps {
-  CUtensorMap x, dy, b, c;
-};
 // dy may be NULL (forward); dy strides are the y strides of the geometry unless `dy_dense`.
-int make_maps(const Geo& g, const void* x, const void* dy, bool dy_dense, const void* Bm, const void* Cm, SeqMaps* m) {
+int make_maps(const Geo& g, const void* x, const void* dy, bool dy_dense, const void* Bm, const void* Cm,
+              const void* s_bf, const void* ds_bf, SeqMaps* m) {
   const long long HP = (long long)g.H * g.P, GN = (long long)g.G * g.N;
   int rc = make_seq_map(&m->x, x, HP, g.L, g.B, g.xsl, g.xsb, "x");
   if (rc) return rc;
   if (dy) {
-    rc = dy_dense ? make_seq_map(&m->dy, dy, HP, g.L, g.B, HP, HP * g.L, "dy") : make_seq_map(&m->dy, dy, HP, g.L, g.B, g.ysl, g.ysb, "dy");
+    rc = dy_dense ? make_seq_map(&m->dy, dy, HP, g.L, g.B, HP, HP * g.L, "dy")
+                  : make_seq_map(&m->dy, dy, HP, g.L, g.B, g.ysl, g.ysb, "dy");
     if (rc) return rc;
   } else {
     m->dy = m->x;
   }
   rc = make_seq_map(&m->b, Bm, GN, g.L, g.B, g.bsl, g.bsb, "B");
   if (rc) return rc;
-  return make_seq_map(&m->c, Cm, GN, g.L, g.B, g.csl, g.csb, "C");
+  rc = make_seq_map(&m->c, Cm, GN, g.L, g.B, g.csl, g.csb, "C");
+  if (rc) return rc;
+  if (s_bf) {
+    rc = make_state_map(&m->s, g, s_bf, "states");
+    if (rc) return rc;
+  } else {
+    m->s = m->x;
+  }
+  if (ds_bf) {
+    rc = make_state_map(&m->ds, g, ds_bf, "dstates");
+    if (rc) return rc;
+  } else {
+    m->ds = m->s;
+  }
+  return SSD_OK;
 }
 
 }  // namespace
@@ -810,7 +816,7 @@ int make_maps(const Geo& g, const void* x, const void* dy, bool dy_dense, const 
 bool tensor_supported(const Geo& g, int dtype, const char** why) {
   auto no = [&](const char* m) { if (why) *why = m; return false; };
   if (dtype != SSD_BF16) return no("tensor-core kernels need bf16 storage");
-  if (g.Q != QT) return no("tensor-core kernels need chunk == 128");
+  if (g.Q != QT) return no("tensor-core kernels need chunk == 128 (or a multiple of it)");
   if (g.L % QT) return no("tensor-core kernels need seqlen % 128 == 0");
   if (!((g.P == 32 || g.P == 64) && (g.N == 64 || g.N == 128))) return no("tensor-core kernels cover headdim in {32,64}, dstate in {64,128}");
   if ((g.hpg * g.P) % 128) return no("heads_per_group * headdim must be a multiple of 128");
@@ -820,13 +826,13 @@ bool tensor_supported(const Geo& g, int dtype, const char** why) {
   return true;
 }
 
-int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, int reverse,
-                         bool write, cudaStream_t s) {
+int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, void* st_bf,
+                         int reverse, bool write, cudaStream_t s) {
   const int PN = g.P * g.N;
   const dim3 grid(cdiv(PN / 4, 256), g.H, g.B);
   const size_t sm = (size_t)g.nc * sizeof(float);
-  if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, reverse);
-  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, reverse);
+  if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse);
+  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, nullptr, reverse);
   SSD_CUDA_CHECK_LAUNCH(reverse ? (write ? "dstate_passing" : "dstate_total") : (write ? "state_passing" : "state_total"));
   return SSD_OK;
 }
@@ -839,60 +845,59 @@ int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* 
 
 // chunk states (mode 0: x, B) or local state gradients (mode 1: dy, C) on tensor cores
 int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc,
-                       long long bsb, long long bsl, const float* cs, const float* dtf, float* out, int* status,
-                       cudaStream_t s) {
+                       long long bsb, long long bsl, const float* tab, float* out, int* status, cudaStream_t s) {
   CUtensorMap tx, tb;
   int rc = make_seq_map(&tx, xdy, (long long)g.H * g.P, g.L, g.B, sl, sb, "x/dy");
   if (rc) return rc;
   rc = make_seq_map(&tb, bc, (long long)g.G * g.N, g.L, g.B, bsl, bsb, "B/C");
   if (rc) return rc;
-#define CALL(PP, NN) return mode == 0 ? launch_state<PP, NN, 0>(g, tx, tb, cs, dtf, out, status, s) \
-                                      : launch_state<PP, NN, 1>(g, tx, tb, cs, dtf, out, status, s);
+#define CALL(PP, NN) return mode == 0 ? launch_state<PP, NN, 0>(g, tx, tb, tab, out, status, s) \
+                                      : launch_state<PP, NN, 1>(g, tx, tb, tab, out, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
 }
 
-int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* cs, const float* dtf, const float* prev,
-                      int* status, cudaStream_t s) {
+int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const void* prev_bf, int* status,
+                      cudaStream_t s) {
   SeqMaps m;
-  int rc = make_maps(g, p.x, nullptr, false, p.Bm, p.Cm, &m);
+  int rc = make_maps(g, p.x, nullptr, false, p.Bm, p.Cm, prev_bf, nullptr, &m);
   if (rc) return rc;
-  ScanArgs a{cs, dtf, prev, p.D, p.z, p.y, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-#define CALL(PP, NN) return launch_scan<PP, NN, 0>(g, m.x, m.dy, m.b, m.c, a, status, s);
+  ScanArgs a{tab, p.D, p.z, p.y, nullptr, nullptr, nullptr, nullptr, nullptr};
+#define CALL(PP, NN) return launch_scan<PP, NN, 0>(g, m, m.s, a, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
 }
 
 // backward, forward-recompute pass: dcsp, ddot, and for the gated case dz and the bf16 pre-gate dy
-int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* cs, const float* dtf, const float* prev,
-                    void* dypb, float* dcsp, float* ddot, int* status, cudaStream_t s) {
+int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, void* dypb, float* dcsp,
+                    float* ddot, int* status, cudaStream_t s) {
   SeqMaps m;
-  int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, &m);
+  int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, prev_bf, nullptr, &m);
   if (rc) return rc;
-  ScanArgs a{cs, dtf, prev, p.D, p.z, nullptr, p.dy, dypb, p.dz, nullptr, dcsp, ddot};
-#define CALL(PP, NN) return launch_scan<PP, NN, 1>(g, m.x, m.dy, m.b, m.c, a, status, s);
+  ScanArgs a{tab, p.D, p.z, nullptr, dypb, p.dz, nullptr, dcsp, ddot};
+#define CALL(PP, NN) return launch_scan<PP, NN, 1>(g, m, m.s, a, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
 }
 
 // backward, dx and ddtd; `dyp` is the pre-gate gradient (dy itself, or the dense bf16 copy)
-int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* cs, const float* dtf,
-              const float* dS, float* ddtd, int* status, cudaStream_t s) {
+int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* ds_bf,
+              float* ddtd, int* status, cudaStream_t s) {
   SeqMaps m;
-  int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, &m);
+  int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, nullptr, ds_bf, &m);
   if (rc) return rc;
-  ScanArgs a{cs, dtf, dS, p.D, nullptr, nullptr, dyp, nullptr, nullptr, p.dx, ddtd, nullptr};
-#define CALL(PP, NN) return launch_scan<PP, NN, 2>(g, m.x, m.dy, m.b, m.c, a, status, s);
+  ScanArgs a{tab, p.D, nullptr, nullptr, nullptr, nullptr, p.dx, ddtd, nullptr};
+#define CALL(PP, NN) return launch_scan<PP, NN, 2>(g, m, m.ds, a, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
 }
 
-int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* cs, const float* dtf,
-               const float* prev, const float* dS, int* status, cudaStream_t s) {
+int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
+               const void* ds_bf, int* status, cudaStream_t s) {
   SeqMaps m;
-  int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, &m);
+  int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, prev_bf, ds_bf, &m);
   if (rc) return rc;
-#define CALL(PP, NN) return launch_dbc<PP, NN>(g, m.x, m.dy, m.b, m.c, cs, dtf, prev, dS, p.dB, p.dC, status, s);
+#define CALL(PP, NN) return launch_dbc<PP, NN>(g, m, tab, p.dB, p.dC, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
 }
