@@ -116,7 +116,8 @@ static void make_layout(const Geo& g, bool has_z, bool tcfam, WsLayout* w) {
   w->ds_bf = take(tcfam ? nst / 2 : 0);
   w->dyp = take(has_z ? (size_t)g.B * g.L * g.H * g.P * f : 0);
   w->dcsp = take(nq); w->ddtd = take(nq); w->ddot = take(nq);
-  w->sdot = take(nbh); w->dapart = take(nbh); w->ddpart = take(nbh);
+  w->sdot = take(nbh * (tcfam ? 64 : 1));   // tensor family: up to 64 warp-partial sums per entry
+  w->dapart = take(nbh); w->ddpart = take(nbh);
   w->dini = take(nfin);
   w->total_bwd = o;
 }

@@ -583,47 +583,88 @@ __global__ void __launch_bounds__(NT) k_sdot(Geo g, const float* __restrict__ dS
 
 // ---------------------------------------------------------------------------------------------
 // Backward: da_k = sum_{i>=k in chunk}(dcsp_i - dt_i*ddtd_i) + sdot ; ddt_k = ddtd_k + A*da_k ;
-// per-chunk partial sums for dA (= sum dt*da) and dD (= sum ddot).
+// per-chunk partial sums for dA (= sum dt*da) and dD (= sum ddot).  One block per (chunk, batch),
+// 8 heads at a time; sdot arrives as `nw` partial sums per (batch, chunk, head), added in fixed order.
 __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, const float* __restrict__ dtf,
                                             const float* __restrict__ dcsp, const float* __restrict__ ddtd,
-                                            const float* __restrict__ ddot, const float* __restrict__ sdot,
+                                            const float* __restrict__ ddot, const float* __restrict__ sdot, int nw,
                                             float* __restrict__ ddt, float* __restrict__ dapart,
                                             float* __restrict__ ddpart) {
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, q = threadIdx.x;
-  __shared__ float wsum[NT / 32], red1[NT / 32], red2[NT / 32];
-  const size_t co = cs_idx(g, b, h, c);
-  // reverse the chunk so an inclusive prefix scan yields the suffix sum
-  const int qr = g.Q - 1 - q;
+  constexpr int HG = 8;
+  const int c = blockIdx.x, b = blockIdx.y, q = threadIdx.x;
+  __shared__ float wsum[NT / 32][HG], red1[NT / 32][HG], red2[NT / 32][HG], ssd[HG];
+  const int qr = g.Q - 1 - q;   // reversed position: an inclusive prefix scan over q is a suffix sum over qr
   const bool ok = (q < g.Q);
-  const float d = ok ? dtf[co + qr] : 0.f;
-  const float dd = ok ? ddtd[co + qr] : 0.f;
-  float v = ok ? dcsp[co + qr] - d * dd : 0.f;
   const int lane = q & 31, w = q >> 5;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    float n = __shfl_up_sync(0xffffffffu, v, o);
-    if (lane >= o) v += n;
-  }
-  if (lane == 31) wsum[w] = v;
-  __syncthreads();
-  float base = 0.f;
-  for (int i = 0; i < w; ++i) base += wsum[i];
-  const float da = v + base + sdot[(size_t)(b * g.nc + c) * g.H + h];
   const int t = c * g.Q + qr;
-  if (ok && t < g.L) ddt[((size_t)b * g.L + t) * g.H + h] = dd + A[h] * da;
-  float s1 = ok ? d * da : 0.f, s2 = ok ? ddot[co + qr] : 0.f;
+  for (int h0 = 0; h0 < g.H; h0 += HG) {
+    if (q < HG) {
+      float s = 0.f;
+      if (h0 + q < g.H) {
+        const float* sp = sdot + ((size_t)(b * g.nc + c) * g.H + h0 + q) * nw;
+        for (int i = 0; i < nw; ++i) s += sp[i];
+      }
+      ssd[q] = s;
+    }
+    float d[HG], dd[HG], v[HG], s2[HG];
 #pragma unroll
-  for (int o = 16; o; o >>= 1) {
-    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-  }
-  if (lane == 0) { red1[w] = s1; red2[w] = s2; }
-  __syncthreads();
-  if (q == 0) {
-    float a1 = 0.f, a2 = 0.f;
-    for (int i = 0; i < NT / 32; ++i) { a1 += red1[i]; a2 += red2[i]; }
-    dapart[(size_t)(b * g.nc + c) * g.H + h] = a1;
-    ddpart[(size_t)(b * g.nc + c) * g.H + h] = a2;
+    for (int k = 0; k < HG; ++k) {
+      const int h = h0 + k;
+      const bool live = ok && h < g.H;
+      const size_t o = live ? cs_idx(g, b, h, c) + qr : 0;
+      d[k] = live ? dtf[o] : 0.f;
+      dd[k] = live ? ddtd[o] : 0.f;
+      v[k] = live ? dcsp[o] - d[k] * dd[k] : 0.f;
+      s2[k] = live ? ddot[o] : 0.f;
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) {
+        const float n = __shfl_up_sync(0xffffffffu, v[k], o);
+        if (lane >= o) v[k] += n;
+      }
+    }
+    if (lane == 31) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) wsum[w][k] = v[k];
+    }
+    __syncthreads();
+    float s1[HG];
+#pragma unroll
+    for (int k = 0; k < HG; ++k) {
+      float base = 0.f;
+      for (int i = 0; i < w; ++i) base += wsum[i][k];
+      const float da = v[k] + base + ssd[k];
+      s1[k] = ok ? d[k] * da : 0.f;
+      v[k] = dd[k] + ((h0 + k < g.H) ? A[h0 + k] : 0.f) * da;   // ddt of this position
+    }
+    if (ok && t < g.L) {
+      float* o = ddt + ((size_t)b * g.L + t) * g.H + h0;
+#pragma unroll
+      for (int k = 0; k < HG; ++k)
+        if (h0 + k < g.H) o[k] = v[k];
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) {
+        s1[k] += __shfl_xor_sync(0xffffffffu, s1[k], o);
+        s2[k] += __shfl_xor_sync(0xffffffffu, s2[k], o);
+      }
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int k = 0; k < HG; ++k) { red1[w][k] = s1[k]; red2[w][k] = s2[k]; }
+    }
+    __syncthreads();
+    if (q < HG && h0 + q < g.H) {
+      float a1 = 0.f, a2 = 0.f;
+      for (int i = 0; i < NT / 32; ++i) { a1 += red1[i][q]; a2 += red2[i][q]; }
+      dapart[(size_t)(b * g.nc + c) * g.H + h0 + q] = a1;
+      ddpart[(size_t)(b * g.nc + c) * g.H + h0 + q] = a2;
+    }
+    __syncthreads();
   }
 }
 
@@ -687,7 +728,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_TOTAL) {
     if (tc) {
-      int rc = tensor_state_passing(g, states, cs, nullptr, fin, nullptr, 0, false, s);
+      int rc = tensor_state_passing(g, states, cs, nullptr, fin, nullptr, 0, false, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
       k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, nullptr, fin, 0);
@@ -696,7 +737,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_FINISH) {
     if (tc) {
-      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, s);
+      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
       k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, p.init_state, fin, 0);
@@ -785,23 +826,25 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_TOTAL) {
     if (tc) {
-      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, nullptr, 1, false, s);
+      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, nullptr, 1, false, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
       k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, nullptr, dini, 1);
       SSD_CUDA_CHECK_LAUNCH("dstate_total");
     }
   }
+  int sdot_nw = 1;
   if (stages & SSD_STAGE_FINISH) {
     if (tc) {
-      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, ds_bf, 1, true, s);
+      // the reverse scan also leaves the warp-partial sums of <dS_end, S_end> per chunk
+      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, ds_bf, 1, true, states, fin, sdot, &sdot_nw, s);
       if (rc) return rc;
     } else {
       k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, p.dfinal_state, dini, 1);
       SSD_CUDA_CHECK_LAUNCH("dstate_passing");
+      k_sdot<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, dst, states, fin, sdot);
+      SSD_CUDA_CHECK_LAUNCH("sdot");
     }
-    k_sdot<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, dst, states, fin, sdot);
-    SSD_CUDA_CHECK_LAUNCH("sdot");
     if (tc) {
       int rc = tensor_dx(g, p, tc_dy, tc_dense, tab, ds_bf, ddtd, status, s);
       if (rc) return rc;
@@ -820,7 +863,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
                                                                  cb, dst, (T*)p.dB);
       SSD_CUDA_CHECK_LAUNCH("dB");
     }
-    k_ddt<<<dim3(g.nc, g.H, g.B), NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, p.ddt, dapart, ddpart);
+    k_ddt<<<dim3(g.nc, g.B), NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, sdot_nw, p.ddt, dapart, ddpart);
     SSD_CUDA_CHECK_LAUNCH("ddt");
     k_reduce_heads<<<g.H, NT, 0, s>>>(g.B * g.nc, g.H, dapart, ddpart, p.dA, p.dD);
     SSD_CUDA_CHECK_LAUNCH("reduce_heads");

@@ -160,6 +160,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
   }
   uint32_t xphase = 0, mphase = 0;
   const uint32_t idesc = make_idesc(128, N, 1, 1);
+  const uint64_t dX0 = desc_sw128_mn(smem_u32(sX), 0, 0, BOX_BYTES), dL0 = desc_sw128_mn(smem_u32(sL), 0, 0, BOX_BYTES),
+                 dB0 = desc_sw128_mn(smem_u32(sB), 0, 0, BOX_BYTES);
   for (int mt = 0; mt < MT; ++mt) {
     const int h0 = grp * g.hpg + mt * HT;
     w.wait(&bar_x, xphase, 11);
@@ -201,13 +203,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t xa = smem_u32(sX), la = smem_u32(sL), ba = smem_u32(sB);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        mma_bf16(tm, desc_sw128_mn(xa, ks * 16, 0, BOX_BYTES), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idesc, ks > 0);
+        mma_bf16(tm, desc_adv(dX0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, ks > 0);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks)
-        mma_bf16(tm, desc_sw128_mn(la, ks * 16, 0, BOX_BYTES), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idesc, true);
+        mma_bf16(tm, desc_adv(dL0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
       mma_commit(&bar_mma);
     }
     w.wait(&bar_mma, mphase, 13);
@@ -309,13 +310,12 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   if (tid == 0) {
     tc_fence_after();
     const uint32_t idG = make_idesc(128, 128, 0, 0);
-    const uint32_t ca = smem_u32((MODE == 2) ? sBM : sKeep), ba = smem_u32((MODE == 2) ? sKeep : sBM);
+    const uint64_t dc = desc_sw128_k(smem_u32((MODE == 2) ? sBM : sKeep), 0), db = desc_sw128_k(smem_u32((MODE == 2) ? sKeep : sBM), 0);
 #pragma unroll
     for (int kb = 0; kb < NB; ++kb)
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        mma_bf16(tmG, desc_sw128_k(ca + kb * BOX_BYTES, ks * 32), desc_sw128_k(ba + kb * BOX_BYTES, ks * 32), idG,
-                 (kb | ks) > 0);
+        mma_bf16(tmG, desc_adv(dc, kb * BOX_BYTES + ks * 32), desc_adv(db, kb * BOX_BYTES + ks * 32), idG, (kb | ks) > 0);
     mma_commit(&bar_mma);
   }
   w.wait(&bar_mma, mphase, 22);
@@ -324,6 +324,10 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   zero_upper_blocks(row, part, warp, smem_u32(sBM));   // the B/C tile is dead; M_h never writes these blocks
 
   const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
+  // descriptors of the tiles that never move (only thread 0 uses them)
+  const uint64_t dM0 = (MODE == 2) ? desc_plain_mn(smem_u32(sBM), 128, 0, 0) : desc_plain_k(smem_u32(sBM), 128, 0);
+  constexpr uint32_t M_STEP = (MODE == 2) ? 256 : 4096;   // bytes per K step of 16 in the M_h tile
+  const uint64_t dK0 = desc_sw128_k(smem_u32(sKeep), 0);
   const int t_row = c * QT + row;
   const int hl_e = (part * 16) / P;            // head (inside the block) of this thread's epilogue columns
   for (int blk = 0; blk < nblk; ++blk) {
@@ -344,18 +348,17 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       __syncthreads();
       if (tid == 0) {
         tc_fence_after();
-        const uint32_t ma = smem_u32(sBM), oa = smem_u32((MODE == 2) ? dyt : xt);
+        const uint64_t dO0 = desc_sw128_mn(smem_u32((MODE == 2) ? dyt : xt), 0, hl * P * 2, 16);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          mma_bf16(tmYd + hl * P, (MODE == 2) ? desc_plain_mn(ma, 128, ks * 16, 0) : desc_plain_k(ma, 128, ks * 16),
-                   desc_sw128_mn(oa, ks * 16, hl * P * 2, 16), idY, ks > 0);
+          mma_bf16(tmYd + hl * P, desc_adv(dM0, ks * M_STEP), desc_adv(dO0, ks * 2048), idY, ks > 0);
         if (hl == 0) {
-          const uint32_t ka = smem_u32(sKeep), sa = smem_u32(st);
+          const uint64_t dS0 = desc_sw128_k(smem_u32(st), 0);
 #pragma unroll
           for (int kb = 0; kb < NB; ++kb)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmYo, desc_sw128_k(ka + kb * BOX_BYTES, ks * 32), desc_sw128_k(sa + kb * SBOX_BYTES, ks * 32), idO,
+              mma_bf16(tmYo, desc_adv(dK0, kb * BOX_BYTES + ks * 32), desc_adv(dS0, kb * SBOX_BYTES + ks * 32), idO,
                        (kb | ks) > 0);
         }
         mma_commit(&bar_mma);
@@ -521,11 +524,14 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   }
   uint32_t xphase = 0, sphase = 0, mphase = 0;
   const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
+  const uint64_t dDY0 = desc_sw128_k(smem_u32(sDY), 0), dX0 = desc_sw128_k(smem_u32(sX), 0);
+  const uint64_t dMk0 = desc_plain_k(smem_u32(sM), 128, 0), dMt0 = desc_plain_mn(smem_u32(sM), 128, 0, 0);
+  const uint64_t dBm0 = desc_sw128_mn(smem_u32(sB), 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(smem_u32(sC), 0, 0, BOX_BYTES);
+  const uint64_t dSm0 = desc_sw128_mn(smem_u32(sS), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sDS), 0, 0, SBOX_BYTES);
   auto issue_w = [&](int hl) {   // thread 0: W = dY_h X_h^T, K = P
-    const uint32_t da = smem_u32(sDY), xa = smem_u32(sX);
 #pragma unroll
     for (int ks = 0; ks < P / 16; ++ks)
-      mma_bf16(tmW, desc_sw128_k(da, hl * P * 2 + ks * 32), desc_sw128_k(xa, hl * P * 2 + ks * 32), idW, ks > 0);
+      mma_bf16(tmW, desc_adv(dDY0, hl * P * 2 + ks * 32), desc_adv(dX0, hl * P * 2 + ks * 32), idW, ks > 0);
   };
   w.wait(&bar_cb, 0, 31);
   bool first = true;
@@ -551,11 +557,10 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       __syncthreads();
       if (tid == 0) {
         tc_fence_after();
-        const uint32_t ma = smem_u32(sM), ba = smem_u32(sB), ca = smem_u32(sC);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          mma_bf16(tmDC, desc_plain_k(ma, 128, ks * 16), desc_sw128_mn(ba, ks * 16, 0, BOX_BYTES), idC, !first || ks > 0);
-          mma_bf16(tmDB, desc_plain_mn(ma, 128, ks * 16, 0), desc_sw128_mn(ca, ks * 16, 0, BOX_BYTES), idB, !first || ks > 0);
+          mma_bf16(tmDC, desc_adv(dMk0, ks * 4096), desc_adv(dBm0, ks * 2048), idC, !first || ks > 0);
+          mma_bf16(tmDB, desc_adv(dMt0, ks * 256), desc_adv(dCm0, ks * 2048), idB, !first || ks > 0);
         }
         if (hl + 1 < HB) issue_w(hl + 1);
         mma_commit(&bar_mma);
@@ -596,11 +601,10 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t da = smem_u32(sDY), xa = smem_u32(sX), sa = smem_u32(sS), dsa = smem_u32(sDS);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        mma_bf16(tmDC, desc_sw128_k(da, ks * 32), desc_sw128_mn(sa, ks * 16, 0, SBOX_BYTES), idC, true);
-        mma_bf16(tmDB, desc_sw128_k(xa, ks * 32), desc_sw128_mn(dsa, ks * 16, 0, SBOX_BYTES), idC, true);
+        mma_bf16(tmDC, desc_adv(dDY0, ks * 32), desc_adv(dSm0, ks * 2048), idC, true);
+        mma_bf16(tmDB, desc_adv(dX0, ks * 32), desc_adv(dDSm0, ks * 2048), idC, true);
       }
       mma_commit(&bar_mma);
     }
@@ -635,10 +639,15 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // ---------------------------------------------------------------------------------------------
 // Exclusive scan over chunks, 4 state elements per thread, decays staged in shared memory.
 // Optionally also writes the bf16 copy of the chunk-entry states that the tensor kernels load.
+// The reverse scan (state gradient) can also emit, per chunk, this block's warp-partial sums of
+// <dS_end_c, S_end_c> (S_end_c = forward state entering chunk c+1, or the final state), which is
+// the per-chunk term of the dt*A gradient: `sdot` [B, nc, H, gridDim.x * 8].
 template <bool WRITE>
 __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restrict__ st, const float* __restrict__ cs,
                                                           const float* __restrict__ init, float* __restrict__ last,
-                                                          bf16* __restrict__ st_bf, int reverse) {
+                                                          bf16* __restrict__ st_bf, int reverse,
+                                                          const float* __restrict__ fwd_prev,
+                                                          const float* __restrict__ fwd_fin, float* __restrict__ sdot) {
   extern __shared__ float sdec[];  // [nc]
   const int h = blockIdx.y, b = blockIdx.z;
   const int PN = g.P * g.N;
@@ -646,33 +655,45 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
     sdec[c] = expf(cs[((size_t)(b * g.H + h) * g.nc + c) * g.Q + g.Q - 1]);
   __syncthreads();
   const int e = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  if (e >= PN) return;
-  float4 run = init ? *reinterpret_cast<const float4*>(init + ((size_t)(b * g.H + h)) * PN + e)
-                    : make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool valid = e < PN;
+  const int eo = valid ? e : 0;
+  float4 run = (init && valid) ? *reinterpret_cast<const float4*>(init + ((size_t)(b * g.H + h)) * PN + eo)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
   const size_t cstride = (size_t)g.H * PN;
-  const size_t boff = ((size_t)b * g.nc * g.H + h) * PN + e;
+  const size_t boff = ((size_t)b * g.nc * g.H + h) * PN + eo;
   float* base = st + boff;
+  const int nw = gridDim.x * 8, wslot = blockIdx.x * 8 + (threadIdx.x >> 5);
   constexpr int U = 4;
   for (int s0 = 0; s0 < g.nc; s0 += U) {
-    float4 v[U];
+    float4 v[U], se[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int s = s0 + u;
-      if (s < g.nc) {
+      v[u] = se[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s < g.nc && valid) {
         const int c = reverse ? g.nc - 1 - s : s;
         v[u] = *reinterpret_cast<const float4*>(base + (size_t)c * cstride);
+        if (sdot)
+          se[u] = (c + 1 < g.nc) ? *reinterpret_cast<const float4*>(fwd_prev + boff + (size_t)(c + 1) * cstride)
+                                 : *reinterpret_cast<const float4*>(fwd_fin + ((size_t)(b * g.H + h)) * PN + eo);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int s = s0 + u;
-      if (s < g.nc) {
+      if (s < g.nc) {   // block-uniform
         const int c = reverse ? g.nc - 1 - s : s;
-        if (WRITE) {
+        if (WRITE && valid) {
           *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
           if (st_bf)
             *reinterpret_cast<uint2*>(st_bf + boff + (size_t)c * cstride) =
                 make_uint2(pack_bf16(run.x, run.y), pack_bf16(run.z, run.w));
+        }
+        if (sdot) {
+          float d = run.x * se[u].x + run.y * se[u].y + run.z * se[u].z + run.w * se[u].w;
+#pragma unroll
+          for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          if ((threadIdx.x & 31) == 0) sdot[((size_t)(b * g.nc + c) * g.H + h) * nw + wslot] = d;
         }
         const float d = sdec[c];
         run.x = fmaf(d, run.x, v[u].x); run.y = fmaf(d, run.y, v[u].y);
@@ -680,7 +701,7 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
       }
     }
   }
-  if (last) *reinterpret_cast<float4*>(last + ((size_t)(b * g.H + h)) * PN + e) = run;
+  if (last && valid) *reinterpret_cast<float4*>(last + ((size_t)(b * g.H + h)) * PN + eo) = run;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -827,12 +848,14 @@ bool tensor_supported(const Geo& g, int dtype, const char** why) {
 }
 
 int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, void* st_bf,
-                         int reverse, bool write, cudaStream_t s) {
+                         int reverse, bool write, const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw,
+                         cudaStream_t s) {
   const int PN = g.P * g.N;
   const dim3 grid(cdiv(PN / 4, 256), g.H, g.B);
   const size_t sm = (size_t)g.nc * sizeof(float);
-  if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse);
-  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, nullptr, reverse);
+  if (sdot_nw) *sdot_nw = (int)grid.x * 8;
+  if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse, fwd_prev, fwd_fin, sdot);
+  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, nullptr, reverse, nullptr, nullptr, nullptr);
   SSD_CUDA_CHECK_LAUNCH(reverse ? (write ? "dstate_passing" : "dstate_total") : (write ? "state_passing" : "state_total"));
   return SSD_OK;
 }

@@ -143,6 +143,11 @@ __device__ __forceinline__ uint64_t desc_plain_k(uint32_t tile, uint32_t rows, u
 __device__ __forceinline__ uint64_t desc_plain_mn(uint32_t tile, uint32_t rows, uint32_t k0, uint32_t mn0) {
   return make_desc(tile + k0 * 16 + (mn0 >> 3) * rows * 16, 128, rows * 16, LAYOUT_NONE);
 }
+// Advance the start address of a descriptor by `bytes` (a multiple of 16).  Shared-memory addresses
+// stay below 256 KB, so the 14-bit address field never carries into its neighbours.  Building a
+// descriptor costs a chain of dependent integer ops in the single issuing thread; loops over K
+// steps should build the first one and add to it.
+__device__ __forceinline__ uint64_t desc_adv(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 // byte offset of (row, col) in a plain tile; col multiple of 8 addresses one 16-byte chunk
 __device__ __forceinline__ uint32_t plain_off(uint32_t rows, uint32_t row, uint32_t col) {
   return (col >> 3) * rows * 16 + row * 16 + (col & 7) * 2;
