@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
           dtf[o] = d[k];
         }
         // tensor-core family (chunk 128 only): the per-head decay table [cs*log2e | dt | exp(cs_r - cs) dt |
-        // exp(dt A)], r = last position of the 32-block (lane 31 of this warp)
+        // exp(dt_{l+1} A)], r = last position of the 32-block (lane 31 of this warp)
         const float vend = __shfl_sync(0xffffffffu, v[k], 31);
         if (tab && h < g.H && q < g.Q) {
           const float L2E = 1.4426950408889634f;
@@ -142,7 +142,8 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
           t[0] = v[k] * L2E;
           t[128] = d[k];
           t[256] = exp2f((vend - v[k]) * L2E) * d[k];
-          t[384] = expf(d[k] * A[h]);
+          if (q > 0) t[384 - 1] = expf(d[k] * A[h]);   // section 3, entry l = decay of step l+1
+          if (q == 0) t[384 + 127] = 1.f;
         }
       }
     }

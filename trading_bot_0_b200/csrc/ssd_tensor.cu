@@ -16,6 +16,9 @@
 // bulk copies; the next head block's inputs are in flight while the current one is computed.
 // Shared-memory tiles and descriptor conventions are described in umma.cuh.  Each CTA has 512
 // threads: thread t owns accumulator row (t % 128) and part (t / 128) of the columns.
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -36,67 +39,96 @@ constexpr int SBOX_BYTES = 64 * 128;  // state TMA box: 64 (h,p) rows x 64 bf16
 constexpr int TAB = SSD_TAB_FLOATS;   // floats per (batch, chunk, head) decay table
 constexpr int TAB_BYTES = TAB * 4;
 constexpr int T_CS = 0, T_DT = 128, T_CF = 256, T_DS = 384;   // table sections, 128 floats each
-constexpr int WAIT_LIMIT = 4000000;
 
 // Bounded waits: after the first one gives up every later wait is skipped, so a broken
 // pipeline drains in bounded time instead of hanging; the status word tells the host.
 struct Waiter {
   int* status;
   bool dead;
+#ifdef SSD_WS_DEBUG
+  long long acc[26] = {0};
+#endif
   __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
     if (dead) return;
-    if (!mbar_wait(bar, parity, WAIT_LIMIT)) {
+#ifdef SSD_WS_DEBUG
+    const long long t0 = clock64();
+#endif
+    if (!mbar_wait(bar, parity)) {
       dead = true;
       atomicExch(status, code);
     }
+#ifdef SSD_WS_DEBUG
+    if (code >= 41 && code < 57) acc[code - 41] += clock64() - t0;
+#endif
   }
+#ifdef SSD_WS_DEBUG
+  // one lane per warp adds its waiting time per wait site to the 64-bit counters behind the status word
+  __device__ __forceinline__ void flush(long long total) {
+    unsigned long long* d = (unsigned long long*)(status + 8);
+    for (int i = 0; i < 26; ++i) if (i != 15 && acc[i]) atomicAdd(d + i, (unsigned long long)acc[i]);
+    atomicAdd(d + 15, (unsigned long long)total);
+  }
+#endif
 };
 
 // ---------------------------------------------------------------------------------------------
 // Decayed lower-triangular tile.  Source: a 128x128 fp32 accumulator in TMEM (C B^T or dY X^T).
 // Result: out[i,j] = src[i,j] * exp(cs_i - cs_j) * dt_j for j <= i, written as bf16 into a plain
-// 128x128 tile, one 32x32 block per thread-and-head:
+// 128x128 tile.  The tile is cut into 32x32 blocks; the four warps that share a TMEM lane quarter
+// (= a block row) each take an 8-column slice of every block at or below the diagonal, so the work
+// of a block row is spread over its four warps and every dependent chain is 8 long:
 //   * blocks above the diagonal are never touched (zero_upper_blocks fills them once);
 //   * blocks below use exp(cs_i - cs_j) dt_j = exp(cs_i - cs_r) * [exp(cs_r - cs_j) dt_j] with r the
-//     last column of the block: one ex2 per thread, the bracket is the per-column table T_CF, and
+//     last column of the block: one ex2 per block, the bracket is the per-column table T_CF, and
 //     both exponents are <= 0 so nothing can overflow;
-//   * diagonal blocks build the row right-to-left from the per-step decays (T_DS[j] = exp(dt_j A)):
-//     L[i,i] = 1, L[i,j] = L[i,j+1] * decay_{j+1}; one multiply per element and no ex2.
-// tab = this head's table: T_CS cs*log2(e), T_DT dt, T_CF column factors, T_DS per-step decays.
+//   * in the diagonal block a slice starts from L[i, je] (je = its last column; exp(cs_i - cs_je) for
+//     rows at or below je, 0 above) and walks left with the per-step decays,
+//     L[i,j] = L[i,j+1] * decay_{j+1}, restarting at 1 on the diagonal.
+// tab = this head's table: T_CS cs*log2(e), T_DT dt, T_CF column factors, T_DS[j] = exp(dt_{j+1} A).
 __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __restrict__ tab, int row, int part,
                                                 int warp, uint32_t mtile) {
-  const int rb = warp & 3, cb = part;   // both warp-uniform
-  if (cb > rb) return;
-  const int c0 = cb * 32;
-  float v[32];
-  tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
-  if (cb == rb) {
-    float run = 0.f;
+  const int rb = warp & 3;                 // block row of this warp (warp-uniform)
+  const float csi = tab[T_CS + row];
+  uint32_t raw[4][8];
 #pragma unroll
-    for (int k = 31; k >= 0; --k) {
-      const int j = c0 + k;
-      const float dn = tab[T_DS + ((j + 1) & 127)];
-      run = (j == row) ? 1.f : run * dn;
-      v[k] = v[k] * run * tab[T_DT + j];
-    }
-  } else {
-    const float rf = ex2(tab[T_CS + row] - tab[T_CS + c0 + 31]);
+  for (int cb = 0; cb < 4; ++cb)
+    if (cb <= rb) tmem_ld8_issue(tmem_addr(tm_src, rb * 32, cb * 32 + part * 8), raw[cb]);
+  tmem_ld_wait();
 #pragma unroll
-    for (int k4 = 0; k4 < 32; k4 += 4) {
-      const float4 f = *reinterpret_cast<const float4*>(tab + T_CF + c0 + k4);
-      v[k4] *= rf * f.x; v[k4 + 1] *= rf * f.y; v[k4 + 2] *= rf * f.z; v[k4 + 3] *= rf * f.w;
+  for (int cb = 0; cb < 4; ++cb) {
+    if (cb > rb) continue;
+    const int c0 = cb * 32 + part * 8;
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(raw[cb][k]);
+    if (cb < rb) {
+      const float rf = ex2(csi - tab[T_CS + cb * 32 + 31]);
+      const float4 f0 = *reinterpret_cast<const float4*>(tab + T_CF + c0), f1 = *reinterpret_cast<const float4*>(tab + T_CF + c0 + 4);
+      v[0] *= rf * f0.x; v[1] *= rf * f0.y; v[2] *= rf * f0.z; v[3] *= rf * f0.w;
+      v[4] *= rf * f1.x; v[5] *= rf * f1.y; v[6] *= rf * f1.z; v[7] *= rf * f1.w;
+    } else {
+      const int je = c0 + 7;
+      const float4 d0 = *reinterpret_cast<const float4*>(tab + T_DS + c0), d1 = *reinterpret_cast<const float4*>(tab + T_DS + c0 + 4);
+      const float4 t0 = *reinterpret_cast<const float4*>(tab + T_DT + c0), t1 = *reinterpret_cast<const float4*>(tab + T_DT + c0 + 4);
+      const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};   // ds[k] = decay of step c0+k+1
+      const float dt[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+      float run = (row >= je) ? ex2(csi - tab[T_CS + je]) : 0.f;
+      v[7] *= run * dt[7];
+#pragma unroll
+      for (int k = 6; k >= 0; --k) {
+        run = (c0 + k == row) ? 1.f : run * ds[k];
+        v[k] *= run * dt[k];
+      }
     }
+    st_shared_v4(mtile + plain_off(128, row, c0), pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
+                 pack_bf16(v[6], v[7]));
   }
-#pragma unroll
-  for (int j8 = 0; j8 < 32; j8 += 8)
-    st_shared_v4(mtile + plain_off(128, row, c0 + j8), pack_bf16(v[j8], v[j8 + 1]), pack_bf16(v[j8 + 2], v[j8 + 3]),
-                 pack_bf16(v[j8 + 4], v[j8 + 5]), pack_bf16(v[j8 + 6], v[j8 + 7]));
 }
 // zero the 32x32 blocks above the diagonal of a plain 128x128 tile (same thread mapping)
 __device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, uint32_t mtile) {
-  if (part <= (warp & 3)) return;
 #pragma unroll
-  for (int j8 = 0; j8 < 32; j8 += 8) st_shared_v4(mtile + plain_off(128, row, part * 32 + j8), 0u, 0u, 0u, 0u);
+  for (int cb = 1; cb < 4; ++cb)
+    if (cb > (warp & 3)) st_shared_v4(mtile + plain_off(128, row, cb * 32 + part * 8), 0u, 0u, 0u, 0u);
 }
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -157,6 +189,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
     mbar_expect_tx(&bar_b, NB * BOX_BYTES);
     for (int kb = 0; kb < NB; ++kb) tma_load_3d(sB + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &bar_b);
     load_tile(0);
+    for (int mt = 1; mt < MT; ++mt) {   // later tiles: start them towards L2 now
+      tma_prefetch_3d(&tmX, col_base + mt * 128, c * QT, b);
+      tma_prefetch_3d(&tmX, col_base + mt * 128 + 64, c * QT, b);
+      bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + mt * HT) * TAB, HT * TAB_BYTES);
+    }
   }
   uint32_t xphase = 0, mphase = 0;
   const uint32_t idesc = make_idesc(128, N, 1, 1);
@@ -304,6 +341,13 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
     load_block(0, 0);
     if (IBUF == 2 && nblk > 1) load_block(1, 1);
+    for (int blk = IBUF; blk < nblk; ++blk) {   // later blocks: start them towards L2 now
+      const int h0 = grp * g.hpg + blk * HB;
+      tma_prefetch_3d(&tmX, col_base + blk * 64, c * QT, b);
+      if (NBOX == 2) tma_prefetch_3d(&tmDY, col_base + blk * 64, c * QT, b);
+      for (int kb = 0; kb < NB; ++kb) tma_prefetch_3d(&tmS, kb * 64, h0 * P, b * g.nc + c);
+      bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
+    }
   }
   uint32_t inphase[2] = {0, 0}, mphase = 0;
   w.wait(&bar_cb, 0, 21);
@@ -521,6 +565,18 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tma_load_3d(sC + kb * BOX_BYTES, &tmC, grp * N + kb * 64, c * QT, b, &bar_cb);
     }
     load_boxes(0);
+    for (int blk = 0; blk < nblk; ++blk) {   // everything this CTA will load later: start it towards L2 now
+      const int h0 = grp * g.hpg + blk * HB;
+      if (blk > 0) {
+        tma_prefetch_3d(&tmX, col_base + blk * 64, c * QT, b);
+        tma_prefetch_3d(&tmDY, col_base + blk * 64, c * QT, b);
+        bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
+      }
+      for (int kb = 0; kb < NB; ++kb) {
+        tma_prefetch_3d(&tmS, kb * 64, h0 * P, b * g.nc + c);
+        tma_prefetch_3d(&tmDS, kb * 64, h0 * P, b * g.nc + c);
+      }
+    }
   }
   uint32_t xphase = 0, sphase = 0, mphase = 0;
   const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
@@ -634,6 +690,372 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tm, TM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Persistent, warp-specialised version of the chunk_scan family for dstate 64: one CTA per SM walks
+// over (batch, chunk, group) tiles and keeps every stage busy at once:
+//   warp 16 lane 0    TMA producer: C/B tiles (2 slots) and per-head-block inputs (2 slots)
+//   warp 17 lane 0    MMA issuer:   G = C B^T of the NEXT tile early, then per head Y/U' and the state term
+//   warps 0-15        decay pass:   G (TMEM) -> M_h (ring of NM shared-memory tiles)
+//   warps 20-27       epilogue:     accumulators (2 TMEM slots) -> global, overlapped with the next block
+// Hand-offs are mbarriers: *_full arrive by TMA bytes / tcgen05.commit / one lane per producer warp,
+// *_empty by tcgen05.commit or one lane per consumer warp.  Slot use n (0,1,2,...) waits `full` with
+// parity n&1 and `empty` with parity (n&1)^1 (a fresh barrier passes a wait on parity 1).
+// TMEM: G x2 (256 columns) + {Y, Y_off} x2 (256 columns) = 512.  Same math and operand layouts as
+// k_scan_tc; MODE as there.
+constexpr int WS_THREADS = 28 * 32;
+constexpr int WS_SCALE_WARPS = 16, WS_EPI_WARPS = 8;
+
+template <int P, int MODE>
+struct WsCfg {
+  static constexpr int N = 64, NB = 1, HB = 64 / P;
+  static constexpr int NBOX = (MODE == 0) ? 1 : 2;
+  static constexpr int NM = (MODE == 0) ? 3 : 2;                    // M_h ring depth
+  static constexpr int CB_BYTES = 2 * BOX_BYTES;                     // keep + other tile
+  static constexpr int IN_BYTES = NBOX * BOX_BYTES + SBOX_BYTES;      // x [, dy] box + state box
+  static constexpr int TB_BYTES = HB * TAB_BYTES;                     // decay tables of one head block
+  static constexpr int NT = 4;                                        // table ring depth
+  static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
+  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + NT * TB_BYTES + RED_BYTES;
+};
+
+struct WsBars {
+  uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], acc_full[2], acc_empty[2];
+  uint64_t m_full[3], m_empty[3], tab_full[4], tab_empty[4], done;
+};
+
+template <int P, int MODE>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+          const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
+          const bf16* __restrict__ z, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
+          bf16* __restrict__ dx, float* __restrict__ rs0, float* __restrict__ rs1, int* __restrict__ status) {
+  using Cfg = WsCfg<P, MODE>;
+  constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sCB = smem;                                   // 2 x {keep tile, other tile}
+  uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
+  uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x [, dy], state box}
+  uint8_t* sTab = sIn + 2 * Cfg::IN_BYTES;               // NT x decay tables of a head block (they run further ahead)
+  float* sRed = (float*)(sTab + Cfg::NT * Cfg::TB_BYTES);   // [2][256] (P = 64 row-sum exchange)
+  __shared__ __align__(8) WsBars bars;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) s_abort = *(volatile int*)status;
+  __syncthreads();
+  if (s_abort) return;
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 1);
+      mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], WS_SCALE_WARPS);
+      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 1 + WS_EPI_WARPS);
+      mbar_init(&bars.acc_full[i], 1); mbar_init(&bars.acc_empty[i], WS_EPI_WARPS);
+    }
+    for (int i = 0; i < 3; ++i) { mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS + WS_EPI_WARPS); }
+    mbar_init(&bars.done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 17) tmem_alloc(&tmem_slot, 512);
+  // the blocks above the diagonal of every M_h ring tile are zero for the whole kernel
+  if (tid < 512) {
+    for (int i = 0; i < NM; ++i) zero_upper_blocks(tid & 127, tid >> 7, warp, smem_u32(sM + i * 2 * BOX_BYTES));
+    fence_async_smem();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  Waiter w{status, false};
+#ifdef SSD_WS_DEBUG
+  const long long t_start = clock64();
+#endif
+
+  const int nblk = g.hpg / HB;
+  const int ntiles = g.B * g.G * g.nc;
+  const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // >= 1 by launch
+  auto tile_coords = [&](int t, int& b, int& grp, int& c) {
+    const int u = blockIdx.x + t * gridDim.x;
+    c = u % g.nc;
+    const int r = u / g.nc;
+    grp = r % g.G;
+    b = r / g.G;
+  };
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      auto load_cb = [&](int t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        const int cs_ = t & 1;
+        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
+        uint8_t* keep = sCB + cs_ * Cfg::CB_BYTES;
+        mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
+        tma_load_3d(keep, (MODE == 2) ? &tmB : &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
+        tma_load_3d(keep + BOX_BYTES, (MODE == 2) ? &tmC : &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
+      };
+      auto prefetch_tile = [&](int t) {   // all per-block inputs of tile t towards L2
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        for (int blk = 0; blk < nblk; ++blk) {
+          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
+          tma_prefetch_3d(&tmX, col, c * QT, b);
+          if (NBOX == 2) tma_prefetch_3d(&tmDY, col, c * QT, b);
+          tma_prefetch_3d(&tmS, 0, h0 * P, b * g.nc + c);
+          bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
+        }
+      };
+      const int total_blocks = my_tiles * nblk;
+      auto load_tab = [&](int kg) {        // tables of global block kg: they run two blocks ahead of the boxes
+        if (kg >= total_blocks) return;
+        int b, grp, c;
+        tile_coords(kg / nblk, b, grp, c);
+        const int h0 = grp * g.hpg + (kg % nblk) * HB, ts = kg % Cfg::NT;
+        w.wait(&bars.tab_empty[ts], ((kg / Cfg::NT) & 1) ^ 1, 49);
+        mbar_expect_tx(&bars.tab_full[ts], Cfg::TB_BYTES);
+        bulk_load(sTab + ts * Cfg::TB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, Cfg::TB_BYTES, &bars.tab_full[ts]);
+      };
+      int kb = 0;
+      load_cb(0);
+      prefetch_tile(0);
+      load_tab(0);
+      load_tab(1);
+      for (int t = 0; t < my_tiles; ++t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        if (t + 1 < my_tiles) prefetch_tile(t + 1);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          load_tab(kb + 2);
+          const int ib = kb & 1;
+          w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
+          uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
+          const int h0 = grp * g.hpg + blk * HB;
+          const int col = grp * g.hpg * P + blk * 64;
+          mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
+          tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
+          if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
+          tma_load_3d(dst + NBOX * BOX_BYTES, &tmS, 0, h0 * P, b * g.nc + c, &bars.in_full[ib]);
+          // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
+          // the next G while this tile is still being worked on
+          if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idG = make_idesc(128, 128, 0, 0);
+      const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
+      constexpr uint32_t M_STEP = (MODE == 2) ? 256 : 4096;
+      auto issue_g = [&](int t) {
+        const int s_ = t & 1;
+        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43);
+        w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
+        tc_fence_after();
+        const uint32_t keep = smem_u32(sCB + s_ * Cfg::CB_BYTES), other = keep + BOX_BYTES;
+        const uint64_t dc = desc_sw128_k((MODE == 2) ? other : keep, 0), db = desc_sw128_k((MODE == 2) ? keep : other, 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, ks > 0);
+        mma_commit(&bars.g_full[s_]);
+      };
+      issue_g(0);
+      int kb = 0, kh = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        const uint64_t dK0 = desc_sw128_k(smem_u32(sCB + (t & 1) * Cfg::CB_BYTES), 0);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          const int ib = kb & 1, ab = kb & 1;
+          const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
+          const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
+          w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
+          w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46);
+          for (int hl = 0; hl < HB; ++hl, ++kh) {
+            const int ms = kh % NM;
+            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            tc_fence_after();
+            const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
+            const uint64_t dM0 = (MODE == 2) ? desc_plain_mn(mt, 128, 0, 0) : desc_plain_k(mt, 128, 0);
+            const uint64_t dO0 = desc_sw128_mn(inb + ((MODE == 2) ? BOX_BYTES : 0), 0, hl * P * 2, 16);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_bf16(tmYd + hl * P, desc_adv(dM0, ks * M_STEP), desc_adv(dO0, ks * 2048), idY, ks > 0);
+            if (hl == 0) {
+              const uint64_t dS0 = desc_sw128_k(inb + NBOX * BOX_BYTES, 0);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) mma_bf16(tmYo, desc_adv(dK0, ks * 32), desc_adv(dS0, ks * 32), idO, ks > 0);
+            }
+            mma_commit(&bars.m_empty[ms]);
+          }
+          mma_commit(&bars.in_empty[ib]);
+          if (blk == nblk - 1) mma_commit(&bars.cb_empty[t & 1]);
+          mma_commit(&bars.acc_full[ab]);
+          if (blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
+        }
+      }
+      mma_commit(&bars.done);
+      w.wait(&bars.done, 0, 48);
+    }
+  } else if (warp < WS_SCALE_WARPS) {
+    // ------------------------------------------------------------------ decay pass warps
+    const int row = tid & 127, part = tid >> 7;
+    int kb = 0, kh = 0;
+    for (int t = 0; t < my_tiles; ++t) {
+      const int gs = t & 1;
+      w.wait(&bars.g_full[gs], (t >> 1) & 1, 51);
+      tc_fence_after();
+      for (int blk = 0; blk < nblk; ++blk, ++kb) {
+        const int ts = kb % Cfg::NT;
+        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES);
+        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 52);
+        for (int hl = 0; hl < HB; ++hl, ++kh) {
+          const int ms = kh % NM;
+          w.wait(&bars.m_empty[ms], ((kh / NM) & 1) ^ 1, 53);
+#ifdef SSD_WS_DEBUG
+          const long long f00 = clock64();
+#endif
+          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
+#ifdef SSD_WS_DEBUG
+          const long long f0 = clock64();
+          w.acc[16 + (warp & 3)] += f0 - f00;
+#endif
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.m_full[ms]);
+#ifdef SSD_WS_DEBUG
+          w.acc[(part == (warp & 3)) ? 22 : (part < (warp & 3) ? 23 : 24)] += clock64() - f0;
+#endif
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.g_empty[gs]);
+    }
+  } else if (warp >= 20) {
+    // ------------------------------------------------------------------ epilogue warps
+    const int ew = warp - 20;
+    const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
+    const int hl_e = (half * 32) / P;
+    int kb = 0;
+    for (int t = 0; t < my_tiles; ++t) {
+      int b, grp, c;
+      tile_coords(t, b, grp, c);
+      const int t_row = c * QT + row;
+      for (int blk = 0; blk < nblk; ++blk, ++kb) {
+        const int ib = kb & 1, ab = kb & 1;
+        uint8_t* xt = sIn + ib * Cfg::IN_BYTES;
+        uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;
+        const int ts = kb % Cfg::NT;
+        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES) + hl_e * TAB;
+        const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
+        const int h0 = grp * g.hpg + blk * HB, h_e = h0 + hl_e;
+        const float Dh = D ? __ldg(D + h_e) : 0.f;
+        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 56);
+        const float cs_r = tb[T_CS + row], dt_r = tb[T_DT + row];
+        const float osc = (MODE == 2) ? dt_r * ex2(tb[T_CS + 127] - cs_r) : ex2(cs_r);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
+        w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
+        w.wait(&bars.acc_full[ab], (kb >> 1) & 1, 55);
+        tc_fence_after();
+        const long long colo = (long long)h0 * P + half * 32;
+        const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
+        const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + colo;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int h16 = 0; h16 < 2; ++h16) {
+          // pull this 16-column slice out of shared memory and TMEM; after the second slice the input
+          // slot and the accumulator slot are handed back before the arithmetic and the stores
+          uint4 xv[2], dv[2];
+          float yd[16], yo[16];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            xv[q] = ld_shared_v4(smem_u32(xt) + sw128_off(row, half * 4 + h16 * 2 + q));
+            dv[q] = (MODE != 0) ? ld_shared_v4(smem_u32(dyt) + sw128_off(row, half * 4 + h16 * 2 + q)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+          tmem_ld16(tmem_addr(tmYd, (ew & 3) * 32, half * 32 + h16 * 16), yd);
+          tmem_ld16(tmem_addr(tmYo, (ew & 3) * 32, half * 32 + h16 * 16), yo);
+          if (h16 == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&bars.acc_empty[ab]); mbar_arrive(&bars.in_empty[ib]); }
+          }
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int k8 = h16 * 16 + q * 8;
+            float xs[8], zs[8], dys[8], o[8], acc[8];
+            unpack8(xv[q], xs);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = yd[q * 8 + k] + osc * yo[q * 8 + k];
+            if (z) unpack8(*reinterpret_cast<const uint4*>(zp + k8), zs);
+            if (MODE != 0) unpack8(dv[q], dys);
+            if (MODE == 0) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                o[k] = acc[k] + Dh * xs[k];
+                if (z) o[k] *= zs[k] * sigmoidf_(zs[k]);
+              }
+              *reinterpret_cast<uint4*>(y + b * g.ysb + (long long)t_row * g.ysl + colo + k8) = pack8(o);
+            } else if (MODE == 1) {
+              float dp[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                float dyv = dys[k];
+                if (z) {
+                  const float sg = 1.f / (1.f + __expf(-zs[k]));
+                  o[k] = dyv * (acc[k] + Dh * xs[k]) * sg * (1.f + zs[k] * (1.f - sg));   // dz
+                  dyv *= zs[k] * sg;
+                }
+                dp[k] = dyv;
+                s0 = fmaf(dyv, acc[k], s0);
+                s1 = fmaf(dyv, xs[k], s1);
+              }
+              if (z) {
+                *reinterpret_cast<uint4*>(dz + dense + k8) = pack8(o);
+                *reinterpret_cast<uint4*>(dypb + dense + k8) = pack8(dp);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                o[k] = acc[k] + Dh * dys[k];
+                s0 = fmaf(xs[k], acc[k], s0);
+              }
+              *reinterpret_cast<uint4*>(dx + dense + k8) = pack8(o);
+            }
+          }
+        }
+        if (MODE != 0) {
+          if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // previous block's exchange fully read
+            if (half == 1) { sRed[row] = s0; sRed[256 + row] = s1; }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (half == 0) { s0 += sRed[row]; s1 += sRed[256 + row]; }
+          }
+          if (P == 32 || half == 0) {
+            const size_t co = ((size_t)(b * g.H + h_e) * g.nc + c) * QT + row;
+            if (MODE == 1) {
+              rs0[co] = s0;   // dcsp
+              rs1[co] = s1;   // ddot
+            } else {
+              rs0[co] = dt_r > 0.f ? s0 / dt_r : 0.f;   // ddtd
+            }
+          }
+        }
+      }
+    }
+  }
+#ifdef SSD_WS_DEBUG
+  if (lane == 0) w.flush(warp == 17 ? clock64() - t_start : 0);
+#endif
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 17) tmem_dealloc(tm, 512);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -778,8 +1200,41 @@ struct SeqMaps {
   CUtensorMap x, dy, b, c, s, ds;
 };
 
+// SSD_B200_SCAN=classic selects the one-tile-per-CTA kernels for every shape (default: the
+// persistent warp-specialised kernel where it applies, i.e. dstate 64).
+bool use_ws_scan() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SSD_B200_SCAN");
+    v = (e && strcmp(e, "classic") == 0) ? 0 : 1;
+  }
+  return v == 1;
+}
+int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 132;
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev] > 0 ? n[dev] : 132;
+}
+
+template <int P, int MODE>
+int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const ScanArgs& a, int* status, cudaStream_t s) {
+  auto k = k_scan_ws<P, MODE>;
+  constexpr size_t sm = WsCfg<P, MODE>::SMEM;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  const int ntiles = g.B * g.G * g.nc;
+  const int grid = ntiles < sm_count() ? ntiles : sm_count();
+  k<<<grid, WS_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
+                                 (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1, status);
+  SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_ws" : (MODE == 1 ? "chunk_scan_bwd_ws" : "dx_ws"));
+  return SSD_OK;
+}
+
 template <int P, int N, int MODE>
 int launch_scan(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const ScanArgs& a, int* status, cudaStream_t s) {
+  if (N == 64 && use_ws_scan()) return launch_scan_ws<P, MODE>(g, m, ts, a, status, s);
   constexpr int IBUF = (MODE == 0 && N < 128) ? 2 : 1;
   auto k = k_scan_tc<P, N, IBUF, MODE>;
   constexpr size_t sm = scan_smem<P, N, IBUF, MODE>();
