@@ -26,6 +26,9 @@ int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const v
                     float* ddot, int* status, cudaStream_t s);
 int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* ds_bf,
               float* ddtd, int* status, cudaStream_t s);
+bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p);
+int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, const void* ds_bf,
+                      float* dcsp, float* ddot, float* ddtd, int* status, cudaStream_t s);
 int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
                const void* ds_bf, int* status, cudaStream_t s);
 

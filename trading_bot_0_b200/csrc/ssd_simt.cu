@@ -809,7 +809,8 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       cudaMemsetAsync(ddot, 0, nq, s);
     }
     if (tc) {
-      int rc = tensor_scan_bwd(g, p, tab, prev_bf, dyp, dcsp, ddot, status, s);
+      // ungated, dstate 64: the recompute pass is folded into the dx kernel of the FINISH stage
+      int rc = tensor_bwd_merged_applies(g, p) ? SSD_OK : tensor_scan_bwd(g, p, tab, prev_bf, dyp, dcsp, ddot, status, s);
       if (rc) return rc;
       rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
                               tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, dst, status, s);
@@ -847,7 +848,8 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       SSD_CUDA_CHECK_LAUNCH("sdot");
     }
     if (tc) {
-      int rc = tensor_dx(g, p, tc_dy, tc_dense, tab, ds_bf, ddtd, status, s);
+      int rc = tensor_bwd_merged_applies(g, p) ? tensor_bwd_merged(g, p, tab, prev_bf, ds_bf, dcsp, ddot, ddtd, status, s)
+                                                : tensor_dx(g, p, tc_dy, tc_dense, tab, ds_bf, ddtd, status, s);
       if (rc) return rc;
       rc = tensor_dbc(g, p, tc_dy, tc_dense, tab, prev_bf, ds_bf, status, s);
       if (rc) return rc;

@@ -1059,6 +1059,327 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Backward chunk_scan, ungated case, dstate 64: the recompute pass (dcsp, ddot) and the dx pass of
+// k_scan_ws share G and every M_h, so this kernel does both from one decay pass per head:
+//   Y  = M_h X_h    (+) exp(cs_i) C S_prev^T                   -> dcsp[i] = sum_p dy*Y, ddot[i] = sum_p dy*x
+//   U' = M_h^T dY_h (+) dt_j exp(cs_end-cs_j) B dS_end^T       -> dx = D dy + U', ddtd[j] = sum_p x*U' / dt_j
+// Same roles, rings and parities as k_scan_ws.  TMEM: G x2 (256) + {Y, Y_off, U, U_off} (256, one
+// slot: the epilogue hands it back as soon as it has read it).  The two state boxes (S_prev, dS_end)
+// have a buffer of their own that is refilled while the second head of a block is worked on.
+template <int P>
+struct BwCfg {
+  static constexpr int N = 64, HB = 64 / P, NM = 2, NT = 4;
+  static constexpr int CB_BYTES = 2 * BOX_BYTES;             // C tile, B tile
+  static constexpr int IN_BYTES = 2 * BOX_BYTES;             // x box, dy box
+  static constexpr int ST_BYTES = 2 * SBOX_BYTES;            // S_prev box, dS_end box
+  static constexpr int TB_BYTES = HB * TAB_BYTES;
+  static constexpr int RED_BYTES = (P == 64) ? 3 * 256 * 4 : 0;
+  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + ST_BYTES + NT * TB_BYTES + RED_BYTES;
+};
+
+struct BwBars {
+  uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], m_full[2], m_empty[2];
+  uint64_t tab_full[4], tab_empty[4], st_full, st_empty, acc_full, acc_empty, done;
+};
+
+template <int P>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+         const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmDS,
+         const float* __restrict__ tab, const float* __restrict__ D, bf16* __restrict__ dx, float* __restrict__ dcsp,
+         float* __restrict__ ddot, float* __restrict__ ddtd, int* __restrict__ status) {
+  using Cfg = BwCfg<P>;
+  constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sCB = smem;                                   // 2 x {C tile, B tile}
+  uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
+  uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x box, dy box}
+  uint8_t* sSt = sIn + 2 * Cfg::IN_BYTES;                // S_prev box, dS_end box
+  uint8_t* sTab = sSt + Cfg::ST_BYTES;                   // NT x decay tables of a head block
+  float* sRed = (float*)(sTab + Cfg::NT * Cfg::TB_BYTES);
+  __shared__ __align__(8) BwBars bars;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) s_abort = *(volatile int*)status;
+  __syncthreads();
+  if (s_abort) return;
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 1);
+      mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], WS_SCALE_WARPS);
+      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 1 + WS_EPI_WARPS);
+      mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS + WS_EPI_WARPS); }
+    mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 1);
+    mbar_init(&bars.acc_full, 1); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
+    mbar_init(&bars.done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 17) tmem_alloc(&tmem_slot, 512);
+  if (tid < 512) {
+    for (int i = 0; i < NM; ++i) zero_upper_blocks(tid & 127, tid >> 7, warp, smem_u32(sM + i * 2 * BOX_BYTES));
+    fence_async_smem();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tmYd = tm + 256, tmYo = tm + 320, tmUd = tm + 384, tmUo = tm + 448;
+  Waiter w{status, false};
+
+  const int nblk = g.hpg / HB;
+  const int ntiles = g.B * g.G * g.nc;
+  const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto tile_coords = [&](int t, int& b, int& grp, int& c) {
+    const int u = blockIdx.x + t * gridDim.x;
+    c = u % g.nc;
+    const int r = u / g.nc;
+    grp = r % g.G;
+    b = r / g.G;
+  };
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      auto load_cb = [&](int t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        const int cs_ = t & 1;
+        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
+        uint8_t* dst = sCB + cs_ * Cfg::CB_BYTES;
+        mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
+        tma_load_3d(dst, &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
+        tma_load_3d(dst + BOX_BYTES, &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
+      };
+      auto prefetch_tile = [&](int t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        for (int blk = 0; blk < nblk; ++blk) {
+          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
+          tma_prefetch_3d(&tmX, col, c * QT, b);
+          tma_prefetch_3d(&tmDY, col, c * QT, b);
+          tma_prefetch_3d(&tmS, 0, h0 * P, b * g.nc + c);
+          tma_prefetch_3d(&tmDS, 0, h0 * P, b * g.nc + c);
+          bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
+        }
+      };
+      const int total_blocks = my_tiles * nblk;
+      auto load_tab = [&](int kg) {
+        if (kg >= total_blocks) return;
+        int b, grp, c;
+        tile_coords(kg / nblk, b, grp, c);
+        const int h0 = grp * g.hpg + (kg % nblk) * HB, ts = kg % Cfg::NT;
+        w.wait(&bars.tab_empty[ts], ((kg / Cfg::NT) & 1) ^ 1, 49);
+        mbar_expect_tx(&bars.tab_full[ts], Cfg::TB_BYTES);
+        bulk_load(sTab + ts * Cfg::TB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, Cfg::TB_BYTES, &bars.tab_full[ts]);
+      };
+      int kb = 0;
+      load_cb(0);
+      prefetch_tile(0);
+      load_tab(0);
+      load_tab(1);
+      for (int t = 0; t < my_tiles; ++t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        if (t + 1 < my_tiles) prefetch_tile(t + 1);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          load_tab(kb + 2);
+          const int ib = kb & 1;
+          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
+          w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
+          uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
+          mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
+          tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
+          tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
+          w.wait(&bars.st_empty, (kb & 1) ^ 1, 50);
+          mbar_expect_tx(&bars.st_full, Cfg::ST_BYTES);
+          tma_load_3d(sSt, &tmS, 0, h0 * P, b * g.nc + c, &bars.st_full);
+          tma_load_3d(sSt + SBOX_BYTES, &tmDS, 0, h0 * P, b * g.nc + c, &bars.st_full);
+          if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idG = make_idesc(128, 128, 0, 0);
+      const uint32_t idY = make_idesc(128, P, 0, 1), idU = make_idesc(128, P, 1, 1), idO = make_idesc(128, 64, 0, 0);
+      auto issue_g = [&](int t) {
+        const int s_ = t & 1;
+        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43);
+        w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
+        tc_fence_after();
+        const uint32_t ct = smem_u32(sCB + s_ * Cfg::CB_BYTES);
+        const uint64_t dc = desc_sw128_k(ct, 0), db = desc_sw128_k(ct + BOX_BYTES, 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, ks > 0);
+        mma_commit(&bars.g_full[s_]);
+      };
+      issue_g(0);
+      const uint64_t dS0 = desc_sw128_k(smem_u32(sSt), 0), dDS0 = desc_sw128_k(smem_u32(sSt + SBOX_BYTES), 0);
+      int kb = 0, kh = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        const uint32_t ct = smem_u32(sCB + (t & 1) * Cfg::CB_BYTES);
+        const uint64_t dC0 = desc_sw128_k(ct, 0), dB0 = desc_sw128_k(ct + BOX_BYTES, 0);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          const int ib = kb & 1;
+          const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
+          w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
+          w.wait(&bars.st_full, kb & 1, 57);
+          w.wait(&bars.acc_empty, (kb & 1) ^ 1, 46);
+          for (int hl = 0; hl < HB; ++hl, ++kh) {
+            const int ms = kh % NM;
+            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            tc_fence_after();
+            const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
+            const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
+            const uint64_t dX0 = desc_sw128_mn(inb, 0, hl * P * 2, 16), dY0 = desc_sw128_mn(inb + BOX_BYTES, 0, hl * P * 2, 16);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              mma_bf16(tmYd + hl * P, desc_adv(dMk, ks * 4096), desc_adv(dX0, ks * 2048), idY, ks > 0);
+              mma_bf16(tmUd + hl * P, desc_adv(dMt, ks * 256), desc_adv(dY0, ks * 2048), idU, ks > 0);
+            }
+            if (hl == 0) {
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                mma_bf16(tmYo, desc_adv(dC0, ks * 32), desc_adv(dS0, ks * 32), idO, ks > 0);
+                mma_bf16(tmUo, desc_adv(dB0, ks * 32), desc_adv(dDS0, ks * 32), idO, ks > 0);
+              }
+              mma_commit(&bars.st_empty);
+            }
+            mma_commit(&bars.m_empty[ms]);
+          }
+          mma_commit(&bars.in_empty[ib]);
+          if (blk == nblk - 1) mma_commit(&bars.cb_empty[t & 1]);
+          mma_commit(&bars.acc_full);
+          if (blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
+        }
+      }
+      mma_commit(&bars.done);
+      w.wait(&bars.done, 0, 48);
+    }
+  } else if (warp < WS_SCALE_WARPS) {
+    // ------------------------------------------------------------------ decay pass warps
+    const int row = tid & 127, part = tid >> 7;
+    int kb = 0, kh = 0;
+    for (int t = 0; t < my_tiles; ++t) {
+      const int gs = t & 1;
+      w.wait(&bars.g_full[gs], (t >> 1) & 1, 51);
+      tc_fence_after();
+      for (int blk = 0; blk < nblk; ++blk, ++kb) {
+        const int ts = kb % Cfg::NT;
+        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES);
+        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 52);
+        for (int hl = 0; hl < HB; ++hl, ++kh) {
+          const int ms = kh % NM;
+          w.wait(&bars.m_empty[ms], ((kh / NM) & 1) ^ 1, 53);
+          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.m_full[ms]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.g_empty[gs]);
+    }
+  } else if (warp >= 20) {
+    // ------------------------------------------------------------------ epilogue warps
+    const int ew = warp - 20;
+    const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
+    const int hl_e = (half * 32) / P;
+    int kb = 0;
+    for (int t = 0; t < my_tiles; ++t) {
+      int b, grp, c;
+      tile_coords(t, b, grp, c);
+      const int t_row = c * QT + row;
+      for (int blk = 0; blk < nblk; ++blk, ++kb) {
+        const int ib = kb & 1, ts = kb % Cfg::NT;
+        const uint32_t xt = smem_u32(sIn + ib * Cfg::IN_BYTES), dyt = xt + BOX_BYTES;
+        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES) + hl_e * TAB;
+        const int h0 = grp * g.hpg + blk * HB, h_e = h0 + hl_e;
+        const float Dh = D ? __ldg(D + h_e) : 0.f;
+        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 56);
+        const float cs_r = tb[T_CS + row], dt_r = tb[T_DT + row];
+        const float osc_y = ex2(cs_r), osc_u = dt_r * ex2(tb[T_CS + 127] - cs_r);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
+        w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
+        w.wait(&bars.acc_full, kb & 1, 55);
+        tc_fence_after();
+        const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + (size_t)h0 * P + half * 32;
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) {          // ph 0,1: Y slices; ph 2,3: U' slices (16 columns each)
+          const int h16 = ph & 1;
+          const bool upass = ph >= 2;
+          uint4 xv[2], dv[2];
+          float a16[16], o16[16];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            xv[q] = ld_shared_v4(xt + sw128_off(row, half * 4 + h16 * 2 + q));
+            dv[q] = ld_shared_v4(dyt + sw128_off(row, half * 4 + h16 * 2 + q));
+          }
+          tmem_ld16(tmem_addr(upass ? tmUd : tmYd, (ew & 3) * 32, half * 32 + h16 * 16), a16);
+          tmem_ld16(tmem_addr(upass ? tmUo : tmYo, (ew & 3) * 32, half * 32 + h16 * 16), o16);
+          if (ph == 3) {   // everything read: hand the accumulators and the input slot back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&bars.acc_empty); mbar_arrive(&bars.in_empty[ib]); }
+          }
+          const float osc = upass ? osc_u : osc_y;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            float xs[8], dys[8];
+            unpack8(xv[q], xs);
+            unpack8(dv[q], dys);
+            if (!upass) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const float acc = a16[q * 8 + k] + osc * o16[q * 8 + k];
+                s0 = fmaf(dys[k], acc, s0);
+                s1 = fmaf(dys[k], xs[k], s1);
+              }
+            } else {
+              float o[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const float acc = a16[q * 8 + k] + osc * o16[q * 8 + k];
+                o[k] = acc + Dh * dys[k];
+                s2 = fmaf(xs[k], acc, s2);
+              }
+              *reinterpret_cast<uint4*>(dx + dense + h16 * 16 + q * 8) = pack8(o);
+            }
+          }
+        }
+        if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          if (half == 1) { sRed[row] = s0; sRed[256 + row] = s1; sRed[512 + row] = s2; }
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          if (half == 0) { s0 += sRed[row]; s1 += sRed[256 + row]; s2 += sRed[512 + row]; }
+        }
+        if (P == 32 || half == 0) {
+          const size_t co = ((size_t)(b * g.H + h_e) * g.nc + c) * QT + row;
+          dcsp[co] = s0;
+          ddot[co] = s1;
+          ddtd[co] = dt_r > 0.f ? s2 / dt_r : 0.f;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 17) tmem_dealloc(tm, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Exclusive scan over chunks, 4 state elements per thread, decays staged in shared memory.
 // Optionally also writes the bf16 copy of the chunk-entry states that the tensor kernels load.
 // The reverse scan (state gradient) can also emit, per chunk, this block's warp-partial sums of
@@ -1245,6 +1566,19 @@ int launch_scan(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const Sca
   return SSD_OK;
 }
 
+template <int P>
+int launch_bwd_ws(const Geo& g, const SeqMaps& m, const float* tab, const float* D, void* dx, float* dcsp, float* ddot,
+                  float* ddtd, int* status, cudaStream_t s) {
+  auto k = k_bwd_ws<P>;
+  constexpr size_t sm = BwCfg<P>::SMEM;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  const int ntiles = g.B * g.G * g.nc;
+  const int grid = ntiles < sm_count() ? ntiles : sm_count();
+  k<<<grid, WS_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, D, (bf16*)dx, dcsp, ddot, ddtd, status);
+  SSD_CUDA_CHECK_LAUNCH("scan_bwd_dx_ws");
+  return SSD_OK;
+}
+
 template <int P, int N>
 int launch_dbc(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
   auto k = k_dbc_tc<P, N>;
@@ -1368,6 +1702,17 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
 #define CALL(PP, NN) return launch_scan<PP, NN, 2>(g, m, m.ds, a, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
+}
+
+// ungated backward with dstate 64: recompute pass and dx pass in one kernel (false if not applicable)
+bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p) { return g.N == 64 && !p.z && use_ws_scan(); }
+int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, const void* ds_bf,
+                      float* dcsp, float* ddot, float* ddtd, int* status, cudaStream_t s) {
+  SeqMaps m;
+  int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, prev_bf, ds_bf, &m);
+  if (rc) return rc;
+  if (g.P == 32) return launch_bwd_ws<32>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
+  return launch_bwd_ws<64>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
 }
 
 int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
