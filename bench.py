@@ -84,7 +84,7 @@ def kernel_bytes_per_token(name, c, e=2):
         "chunk_scan_tc": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_tc": (2 * hp + 2 * gn) * e + 2 * zb,
         "dx_tc": (3 * hp + 2 * gn) * e, "dBdC_tc": (2 * hp + 4 * gn) * e,
         "chunk_scan_ws": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_ws": (2 * hp + 2 * gn) * e + 2 * zb,
-        "dx_ws": (3 * hp + 2 * gn) * e, "scan_bwd_dx_ws": (3 * hp + 2 * gn) * e,
+        "dx_ws": (3 * hp + 2 * gn) * e, "scan_bwd_dx_ws": (3 * hp + 2 * gn) * e, "dBdC_ws": (2 * hp + 4 * gn) * e,
     }
     return table.get(name)
 

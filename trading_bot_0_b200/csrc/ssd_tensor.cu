@@ -86,14 +86,21 @@ struct Waiter {
 //     L[i,j] = L[i,j+1] * decay_{j+1}, restarting at 1 on the diagonal.
 // tab = this head's table: T_CS cs*log2(e), T_DT dt, T_CF column factors, T_DS[j] = exp(dt_{j+1} A).
 __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __restrict__ tab, int row, int part,
-                                                int warp, uint32_t mtile) {
+                                                int warp, uint32_t mtile, long long* dbg = nullptr) {
   const int rb = warp & 3;                 // block row of this warp (warp-uniform)
+#ifdef SSD_WS_DEBUG
+  const long long q0 = clock64();
+#endif
   const float csi = tab[T_CS + row];
   uint32_t raw[4][8];
 #pragma unroll
   for (int cb = 0; cb < 4; ++cb)
     if (cb <= rb) tmem_ld8_issue(tmem_addr(tm_src, rb * 32, cb * 32 + part * 8), raw[cb]);
   tmem_ld_wait();
+#ifdef SSD_WS_DEBUG
+  const long long q1 = clock64();
+  long long q2 = q1;
+#endif
 #pragma unroll
   for (int cb = 0; cb < 4; ++cb) {
     if (cb > rb) continue;
@@ -120,9 +127,16 @@ __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __
         v[k] *= run * dt[k];
       }
     }
+#ifdef SSD_WS_DEBUG
+    if (cb == rb) q2 = clock64();
+#endif
     st_shared_v4(mtile + plain_off(128, row, c0), pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
                  pack_bf16(v[6], v[7]));
   }
+#ifdef SSD_WS_DEBUG
+  if (dbg && rb == 0) { const long long q3 = clock64(); dbg[20] += q1 - q0; dbg[21] += q2 - q1; dbg[22] += q3 - q2; }
+  if (dbg && rb == 3) { const long long q3 = clock64(); dbg[23] += q1 - q0; dbg[24] += q2 - q1; dbg[25] += q3 - q2; }
+#endif
 }
 // zero the 32x32 blocks above the diagonal of a plain 128x128 tile (same thread mapping)
 __device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, uint32_t mtile) {
@@ -918,17 +932,17 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #ifdef SSD_WS_DEBUG
           const long long f00 = clock64();
 #endif
-          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
 #ifdef SSD_WS_DEBUG
+          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES), w.acc);
           const long long f0 = clock64();
           w.acc[16 + (warp & 3)] += f0 - f00;
+#else
+          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
 #endif
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars.m_full[ms]);
-#ifdef SSD_WS_DEBUG
-          w.acc[(part == (warp & 3)) ? 22 : (part < (warp & 3) ? 23 : 24)] += clock64() - f0;
-#endif
+
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
@@ -1380,6 +1394,296 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------------------------
+// Backward dB / dC, dstate 64, persistent and warp-specialised like k_scan_ws.  Per head
+//   W_h = dY_h X_h^T (K = P) into one of two TMEM slots -> decay pass -> W'_h (ring of 2 tiles) ->
+//   dC += W'_h B, dB += W'_h^T C;
+// per head block, once its raw x / dy boxes are no longer needed by a W product, the decay warps scale
+// them in place (dy by exp(cs_i), x by exp(cs_end-cs_j) dt_j) and one K = 64 product each adds the state
+// terms dC += dY' S_prev, dB += X' dS_end.  dC / dB stay in TMEM for the whole tile (one slot).
+template <int P>
+struct DbCfg {
+  static constexpr int N = 64, HB = 64 / P, NM = 2, NT = 4;
+  static constexpr int CB_BYTES = 2 * BOX_BYTES;             // B tile, C tile
+  static constexpr int IN_BYTES = 2 * BOX_BYTES;             // x box, dy box
+  static constexpr int ST_BYTES = 2 * SBOX_BYTES;            // S_prev box, dS_end box
+  static constexpr int TB_BYTES = HB * TAB_BYTES;
+  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + ST_BYTES + NT * TB_BYTES;
+};
+
+struct DbBars {
+  uint64_t cb_full[2], cb_empty[2], in_full[2], in_empty[2], w_full[2], w_empty[2], m_full[2], m_empty[2];
+  uint64_t tab_full[4], tab_empty[4], st_full, st_empty, wraw_done[2], sc_full[2], acc_full, acc_empty, done;
+};
+
+template <int P>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+         const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmDS,
+         const float* __restrict__ tab, bf16* __restrict__ dB, bf16* __restrict__ dC, int* __restrict__ status) {
+  using Cfg = DbCfg<P>;
+  constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sCB = smem;                                   // 2 x {B tile, C tile}
+  uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB W'_h tiles
+  uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x box, dy box}
+  uint8_t* sSt = sIn + 2 * Cfg::IN_BYTES;                // S_prev box, dS_end box
+  uint8_t* sTab = sSt + Cfg::ST_BYTES;                   // NT x decay tables of a head block
+  __shared__ __align__(8) DbBars bars;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) s_abort = *(volatile int*)status;
+  __syncthreads();
+  if (s_abort) return;
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 1);
+      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 1);
+      mbar_init(&bars.w_full[i], 1); mbar_init(&bars.w_empty[i], WS_SCALE_WARPS);
+      mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS); }
+    mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars.wraw_done[i], 1); mbar_init(&bars.sc_full[i], WS_SCALE_WARPS); }
+    mbar_init(&bars.acc_full, 1); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
+    mbar_init(&bars.done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 17) tmem_alloc(&tmem_slot, 512);
+  if (tid < 512) {
+    for (int i = 0; i < NM; ++i) zero_upper_blocks(tid & 127, tid >> 7, warp, smem_u32(sM + i * 2 * BOX_BYTES));
+    fence_async_smem();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tmDC = tm + 256, tmDB = tm + 320;
+  Waiter w{status, false};
+
+  const int nblk = g.hpg / HB;
+  const int ntiles = g.B * g.G * g.nc;
+  const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto tile_coords = [&](int t, int& b, int& grp, int& c) {
+    const int u = blockIdx.x + t * gridDim.x;
+    c = u % g.nc;
+    const int r = u / g.nc;
+    grp = r % g.G;
+    b = r / g.G;
+  };
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      auto load_cb = [&](int t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        const int cs_ = t & 1;
+        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
+        uint8_t* dst = sCB + cs_ * Cfg::CB_BYTES;
+        mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
+        tma_load_3d(dst, &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
+        tma_load_3d(dst + BOX_BYTES, &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
+      };
+      auto prefetch_tile = [&](int t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        for (int blk = 0; blk < nblk; ++blk) {
+          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
+          tma_prefetch_3d(&tmX, col, c * QT, b);
+          tma_prefetch_3d(&tmDY, col, c * QT, b);
+          tma_prefetch_3d(&tmS, 0, h0 * P, b * g.nc + c);
+          tma_prefetch_3d(&tmDS, 0, h0 * P, b * g.nc + c);
+          bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
+        }
+      };
+      const int total_blocks = my_tiles * nblk;
+      auto load_tab = [&](int kg) {
+        if (kg >= total_blocks) return;
+        int b, grp, c;
+        tile_coords(kg / nblk, b, grp, c);
+        const int h0 = grp * g.hpg + (kg % nblk) * HB, ts = kg % Cfg::NT;
+        w.wait(&bars.tab_empty[ts], ((kg / Cfg::NT) & 1) ^ 1, 49);
+        mbar_expect_tx(&bars.tab_full[ts], Cfg::TB_BYTES);
+        bulk_load(sTab + ts * Cfg::TB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, Cfg::TB_BYTES, &bars.tab_full[ts]);
+      };
+      int kb = 0;
+      load_cb(0);
+      prefetch_tile(0);
+      load_tab(0);
+      load_tab(1);
+      for (int t = 0; t < my_tiles; ++t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        if (t + 1 < my_tiles) prefetch_tile(t + 1);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          load_tab(kb + 2);
+          const int ib = kb & 1;
+          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
+          w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
+          uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
+          mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
+          tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
+          tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
+          w.wait(&bars.st_empty, (kb & 1) ^ 1, 50);
+          mbar_expect_tx(&bars.st_full, Cfg::ST_BYTES);
+          tma_load_3d(sSt, &tmS, 0, h0 * P, b * g.nc + c, &bars.st_full);
+          tma_load_3d(sSt + SBOX_BYTES, &tmDS, 0, h0 * P, b * g.nc + c, &bars.st_full);
+          if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
+      const uint64_t dSm0 = desc_sw128_mn(smem_u32(sSt), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sSt + SBOX_BYTES), 0, 0, SBOX_BYTES);
+      const int total_blocks = my_tiles * nblk;
+      int kw = 0;   // W products issued so far (global head counter of the W stage)
+      auto issue_w_block = [&](int kg) {   // all W products of global block kg
+        if (kg >= total_blocks) return;
+        const int ib = kg & 1;
+        w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45);
+        tc_fence_after();
+        const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
+        const uint64_t dX0 = desc_sw128_k(inb, 0), dDY0 = desc_sw128_k(inb + BOX_BYTES, 0);
+        for (int hl = 0; hl < HB; ++hl, ++kw) {
+          const int ws = kw & 1;
+          w.wait(&bars.w_empty[ws], ((kw >> 1) & 1) ^ 1, 58);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < P / 16; ++ks)
+            mma_bf16(tm + ws * 128, desc_adv(dDY0, hl * P * 2 + ks * 32), desc_adv(dX0, hl * P * 2 + ks * 32), idW, ks > 0);
+          mma_commit(&bars.w_full[ws]);
+        }
+        mma_commit(&bars.wraw_done[kg & 1]);   // the raw boxes of this block have been read by every W product
+      };
+      issue_w_block(0);
+      int kb = 0, kh = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43);
+        w.wait(&bars.acc_empty, (t & 1) ^ 1, 46);
+        tc_fence_after();
+        const uint32_t ct = smem_u32(sCB + (t & 1) * Cfg::CB_BYTES);
+        const uint64_t dBm0 = desc_sw128_mn(ct, 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(ct + BOX_BYTES, 0, 0, BOX_BYTES);
+        bool first = true;
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          const int ib = kb & 1;
+          const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
+          for (int hl = 0; hl < HB; ++hl, ++kh) {
+            const int ms = kh % NM;
+            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            tc_fence_after();
+            const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
+            const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              mma_bf16(tmDC, desc_adv(dMk, ks * 4096), desc_adv(dBm0, ks * 2048), idC, !first || ks > 0);
+              mma_bf16(tmDB, desc_adv(dMt, ks * 256), desc_adv(dCm0, ks * 2048), idB, !first || ks > 0);
+            }
+            first = false;
+            mma_commit(&bars.m_empty[ms]);
+          }
+          // the next block's W products go out before this block's state terms, so the decay warps
+          // find their next input ready when they come back from scaling this block's boxes
+          issue_w_block(kb + 1);
+          w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59);
+          w.wait(&bars.st_full, kb & 1, 57);
+          tc_fence_after();
+          {
+            const uint64_t dXk = desc_sw128_k(inb, 0), dDYk = desc_sw128_k(inb + BOX_BYTES, 0);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              mma_bf16(tmDC, desc_adv(dDYk, ks * 32), desc_adv(dSm0, ks * 2048), idC, true);
+              mma_bf16(tmDB, desc_adv(dXk, ks * 32), desc_adv(dDSm0, ks * 2048), idC, true);
+            }
+          }
+          mma_commit(&bars.st_empty);
+          mma_commit(&bars.in_empty[ib]);
+        }
+        mma_commit(&bars.cb_empty[t & 1]);
+        mma_commit(&bars.acc_full);
+      }
+      mma_commit(&bars.done);
+      w.wait(&bars.done, 0, 48);
+    }
+  } else if (warp < WS_SCALE_WARPS) {
+    // ------------------------------------------------------------------ decay pass warps
+    const int row = tid & 127, part = tid >> 7;
+    int kb = 0, kh = 0;
+    for (int t = 0; t < my_tiles; ++t) {
+      for (int blk = 0; blk < nblk; ++blk, ++kb) {
+        const int ts = kb % Cfg::NT, ib = kb & 1;
+        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES);
+        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 52);
+        for (int hl = 0; hl < HB; ++hl, ++kh) {
+          const int ms = kh % NM, ws = kh & 1;
+          w.wait(&bars.w_full[ws], (kh >> 1) & 1, 51);
+          w.wait(&bars.m_empty[ms], ((kh / NM) & 1) ^ 1, 53);
+          tc_fence_after();
+          decay_mask_tile(tm + ws * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
+          fence_async_smem();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { mbar_arrive(&bars.m_full[ms]); mbar_arrive(&bars.w_empty[ws]); }
+        }
+        // scale this block's boxes in place for the state terms (x: box 0, dy: box 1)
+        w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
+        w.wait(&bars.wraw_done[kb & 1], (kb >> 1) & 1, 55);
+        uint8_t* xb = sIn + ib * Cfg::IN_BYTES;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int idx = tid + r * 512;
+          const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
+          const float* tt = tb + ((((pc ^ l) & 7) * 8) / P) * TAB;
+          const float f = box ? ex2(tt[T_CS + l]) : ex2(tt[T_CS + 127] - tt[T_CS + l]) * tt[T_DT + l];
+          const uint32_t a = smem_u32(xb + box * BOX_BYTES + l * 128 + pc * 16);
+          float v[8];
+          unpack8(ld_shared_v4(a), v);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] *= f;
+          const uint4 o = pack8(v);
+          st_shared_v4(a, o.x, o.y, o.z, o.w);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&bars.sc_full[kb & 1]); mbar_arrive(&bars.tab_empty[ts]); }
+      }
+    }
+  } else if (warp >= 20) {
+    // ------------------------------------------------------------------ epilogue warps: dC, dB of a finished tile
+    const int ew = warp - 20;
+    const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the 64 columns
+    for (int t = 0; t < my_tiles; ++t) {
+      int b, grp, c;
+      tile_coords(t, b, grp, c);
+      w.wait(&bars.acc_full, t & 1, 56);
+      tc_fence_after();
+      float vc[32], vb[32];
+      tmem_ld32(tmem_addr(tmDC, (ew & 3) * 32, half * 32), vc);
+      tmem_ld32(tmem_addr(tmDB, (ew & 3) * 32, half * 32), vb);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.acc_empty);
+      const size_t o = (((size_t)b * g.L + c * QT + row) * g.G + grp) * N + half * 32;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        *reinterpret_cast<uint4*>(dC + o + j) = make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]),
+                                                          pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7]));
+        *reinterpret_cast<uint4*>(dB + o + j) = make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]),
+                                                          pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 17) tmem_dealloc(tm, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Exclusive scan over chunks, 4 state elements per thread, decays staged in shared memory.
 // Optionally also writes the bf16 copy of the chunk-entry states that the tensor kernels load.
 // The reverse scan (state gradient) can also emit, per chunk, this block's warp-partial sums of
@@ -1579,8 +1883,21 @@ int launch_bwd_ws(const Geo& g, const SeqMaps& m, const float* tab, const float*
   return SSD_OK;
 }
 
+template <int P>
+int launch_dbc_ws(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
+  auto k = k_dbc_ws<P>;
+  constexpr size_t sm = DbCfg<P>::SMEM;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  const int ntiles = g.B * g.G * g.nc;
+  const int grid = ntiles < sm_count() ? ntiles : sm_count();
+  k<<<grid, WS_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, (bf16*)dB, (bf16*)dC, status);
+  SSD_CUDA_CHECK_LAUNCH("dBdC_ws");
+  return SSD_OK;
+}
+
 template <int P, int N>
 int launch_dbc(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
+  if (N == 64 && use_ws_scan()) return launch_dbc_ws<P>(g, m, tab, dB, dC, status, s);
   auto k = k_dbc_tc<P, N>;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dbc_smem<P, N>());
   k<<<dim3(g.nc, g.G, g.B), TC_THREADS, dbc_smem<P, N>(), s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, (bf16*)dB, (bf16*)dC,
