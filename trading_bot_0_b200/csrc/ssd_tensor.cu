@@ -145,6 +145,42 @@ __device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, u
     if (cb > (warp & 3)) st_shared_v4(mtile + plain_off(128, row, cb * 32 + part * 8), 0u, 0u, 0u, 0u);
 }
 
+// Variant used by the one-tile-per-CTA kernels (all 16 warps meet at a CTA barrier per head anyway):
+// one whole 32x32 block per thread-and-head, thread = (row, part = block column).
+__device__ __forceinline__ void decay_mask_block(uint32_t tm_src, const float* __restrict__ tab, int row, int part,
+                                                 int warp, uint32_t mtile) {
+  const int rb = warp & 3, cb = part;   // both warp-uniform
+  if (cb > rb) return;
+  const int c0 = cb * 32;
+  float v[32];
+  tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
+  if (cb == rb) {
+    float run = 0.f;
+#pragma unroll
+    for (int k = 31; k >= 0; --k) {
+      const int j = c0 + k;
+      run = (j == row) ? 1.f : run * tab[T_DS + j];   // T_DS[j] = decay of step j+1
+      v[k] = v[k] * run * tab[T_DT + j];
+    }
+  } else {
+    const float rf = ex2(tab[T_CS + row] - tab[T_CS + c0 + 31]);
+#pragma unroll
+    for (int k4 = 0; k4 < 32; k4 += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(tab + T_CF + c0 + k4);
+      v[k4] *= rf * f.x; v[k4 + 1] *= rf * f.y; v[k4 + 2] *= rf * f.z; v[k4 + 3] *= rf * f.w;
+    }
+  }
+#pragma unroll
+  for (int j8 = 0; j8 < 32; j8 += 8)
+    st_shared_v4(mtile + plain_off(128, row, c0 + j8), pack_bf16(v[j8], v[j8 + 1]), pack_bf16(v[j8 + 2], v[j8 + 3]),
+                 pack_bf16(v[j8 + 4], v[j8 + 5]), pack_bf16(v[j8 + 6], v[j8 + 7]));
+}
+__device__ __forceinline__ void zero_upper_block(int row, int part, int warp, uint32_t mtile) {
+  if (part <= (warp & 3)) return;
+#pragma unroll
+  for (int j8 = 0; j8 < 32; j8 += 8) st_shared_v4(mtile + plain_off(128, row, part * 32 + j8), 0u, 0u, 0u, 0u);
+}
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), d = unpack_bf16(v.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
@@ -379,7 +415,7 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   w.wait(&bar_mma, mphase, 22);
   mphase ^= 1;
   tc_fence_after();
-  zero_upper_blocks(row, part, warp, smem_u32(sBM));   // the B/C tile is dead; M_h never writes these blocks
+  zero_upper_block(row, part, warp, smem_u32(sBM));   // the B/C tile is dead; M_h never writes these blocks
 
   const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
   // descriptors of the tiles that never move (only thread 0 uses them)
@@ -400,7 +436,7 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     w.wait(&bar_in[ib], inphase[ib], 23);
     inphase[ib] ^= 1;
     for (int hl = 0; hl < HB; ++hl) {
-      decay_mask_tile(tmG, tb + hl * TAB, row, part, warp, smem_u32(sBM));
+      decay_mask_block(tmG, tb + hl * TAB, row, part, warp, smem_u32(sBM));
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
@@ -607,7 +643,7 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   bool first = true;
   for (int blk = 0; blk < nblk; ++blk) {
     const int h0 = grp * g.hpg + blk * HB;
-    zero_upper_blocks(row, part, warp, smem_u32(sM));   // the state boxes of the previous head block lived here
+    zero_upper_block(row, part, warp, smem_u32(sM));   // the state boxes of the previous head block lived here
     w.wait(&bar_x, xphase, 32);
     xphase ^= 1;
     tc_fence_before();
@@ -621,7 +657,7 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     mphase ^= 1;
     tc_fence_after();
     for (int hl = 0; hl < HB; ++hl) {
-      decay_mask_tile(tmW, sTab + hl * TAB, row, part, warp, smem_u32(sM));
+      decay_mask_block(tmW, sTab + hl * TAB, row, part, warp, smem_u32(sM));
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
