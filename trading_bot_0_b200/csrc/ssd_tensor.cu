@@ -46,7 +46,10 @@ struct Waiter {
   int* status;
   bool dead;
 #ifdef SSD_WS_DEBUG
-  long long acc[26] = {0};
+  unsigned long long* dbg;   // counters in shared memory: [code - 41] waiting cycles per wait site, 16.. free use
+  __device__ __forceinline__ void add(int idx, long long cycles) {
+    if (dbg && (threadIdx.x & 31) == 0) atomicAdd(dbg + idx, (unsigned long long)cycles);
+  }
 #endif
   __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
     if (dead) return;
@@ -58,17 +61,9 @@ struct Waiter {
       atomicExch(status, code);
     }
 #ifdef SSD_WS_DEBUG
-    if (code >= 41 && code < 57) acc[code - 41] += clock64() - t0;
+    if (code >= 41 && code < 57) add(code - 41, clock64() - t0);
 #endif
   }
-#ifdef SSD_WS_DEBUG
-  // one lane per warp adds its waiting time per wait site to the 64-bit counters behind the status word
-  __device__ __forceinline__ void flush(long long total) {
-    unsigned long long* d = (unsigned long long*)(status + 8);
-    for (int i = 0; i < 26; ++i) if (i != 15 && acc[i]) atomicAdd(d + i, (unsigned long long)acc[i]);
-    atomicAdd(d + 15, (unsigned long long)total);
-  }
-#endif
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -86,21 +81,14 @@ struct Waiter {
 //     L[i,j] = L[i,j+1] * decay_{j+1}, restarting at 1 on the diagonal.
 // tab = this head's table: T_CS cs*log2(e), T_DT dt, T_CF column factors, T_DS[j] = exp(dt_{j+1} A).
 __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __restrict__ tab, int row, int part,
-                                                int warp, uint32_t mtile, long long* dbg = nullptr) {
+                                                int warp, uint32_t mtile) {
   const int rb = warp & 3;                 // block row of this warp (warp-uniform)
-#ifdef SSD_WS_DEBUG
-  const long long q0 = clock64();
-#endif
   const float csi = tab[T_CS + row];
   uint32_t raw[4][8];
 #pragma unroll
   for (int cb = 0; cb < 4; ++cb)
     if (cb <= rb) tmem_ld8_issue(tmem_addr(tm_src, rb * 32, cb * 32 + part * 8), raw[cb]);
   tmem_ld_wait();
-#ifdef SSD_WS_DEBUG
-  const long long q1 = clock64();
-  long long q2 = q1;
-#endif
 #pragma unroll
   for (int cb = 0; cb < 4; ++cb) {
     if (cb > rb) continue;
@@ -127,22 +115,124 @@ __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __
         v[k] *= run * dt[k];
       }
     }
-#ifdef SSD_WS_DEBUG
-    if (cb == rb) q2 = clock64();
-#endif
     st_shared_v4(mtile + plain_off(128, row, c0), pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
                  pack_bf16(v[6], v[7]));
   }
-#ifdef SSD_WS_DEBUG
-  if (dbg && rb == 0) { const long long q3 = clock64(); dbg[20] += q1 - q0; dbg[21] += q2 - q1; dbg[22] += q3 - q2; }
-  if (dbg && rb == 3) { const long long q3 = clock64(); dbg[23] += q1 - q0; dbg[24] += q2 - q1; dbg[25] += q3 - q2; }
-#endif
 }
 // zero the 32x32 blocks above the diagonal of a plain 128x128 tile (same thread mapping)
 __device__ __forceinline__ void zero_upper_blocks(int row, int part, int warp, uint32_t mtile) {
 #pragma unroll
   for (int cb = 1; cb < 4; ++cb)
     if (cb > (warp & 3)) st_shared_v4(mtile + plain_off(128, row, cb * 32 + part * 8), 0u, 0u, 0u, 0u);
+}
+
+// Whole-row variant for the persistent kernels.  A group of four warps (one per TMEM lane quarter)
+// owns one head at a time and different groups work on different heads, so the latency of one group's
+// TMEM loads, table loads and stores hides behind another group's arithmetic.  Thread = accumulator
+// row; it walks the 32x32 blocks of its block row left to right (blocks below the diagonal first, the
+// diagonal block last) with the next block's TMEM load in flight while the current one is scaled,
+// converted and stored.  Same factorisation as decay_mask_tile.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait_2x16(uint32_t (&r)[16], uint32_t (&q)[16]) {
+  // the registers are operands so that no use of them can be scheduled above the wait
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(q[0]),
+                 "+r"(q[1]), "+r"(q[2]), "+r"(q[3]), "+r"(q[4]), "+r"(q[5]), "+r"(q[6]), "+r"(q[7]), "+r"(q[8]),
+                 "+r"(q[9]), "+r"(q[10]), "+r"(q[11]), "+r"(q[12]), "+r"(q[13]), "+r"(q[14]), "+r"(q[15])
+               :: "memory");
+}
+// 16 columns of a block below the diagonal: out[k] = raw[k] * rf * cf[k]
+__device__ __forceinline__ void decay_off_half(const uint32_t (&raw)[16], float rf, const float* __restrict__ cf, uint32_t dst) {
+#pragma unroll
+  for (int j8 = 0; j8 < 16; j8 += 8) {
+    const float4 f0 = *reinterpret_cast<const float4*>(cf + j8), f1 = *reinterpret_cast<const float4*>(cf + j8 + 4);
+    const float v0 = __uint_as_float(raw[j8]) * f0.x * rf, v1 = __uint_as_float(raw[j8 + 1]) * f0.y * rf;
+    const float v2 = __uint_as_float(raw[j8 + 2]) * f0.z * rf, v3 = __uint_as_float(raw[j8 + 3]) * f0.w * rf;
+    const float v4 = __uint_as_float(raw[j8 + 4]) * f1.x * rf, v5 = __uint_as_float(raw[j8 + 5]) * f1.y * rf;
+    const float v6 = __uint_as_float(raw[j8 + 6]) * f1.z * rf, v7 = __uint_as_float(raw[j8 + 7]) * f1.w * rf;
+    st_shared_v4(dst + (j8 >> 3) * 2048, pack_bf16(v0, v1), pack_bf16(v2, v3), pack_bf16(v4, v5), pack_bf16(v6, v7));
+  }
+}
+// 16 columns (starting at column c0) of the diagonal block: two independent 8-column walks
+__device__ __forceinline__ void decay_diag_half(const uint32_t (&raw)[16], const float* __restrict__ tab, int c0, int row,
+                                                float csi, uint32_t dst) {
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const int cs0 = c0 + 8 * s, je = cs0 + 7;
+    const float4 d0 = *reinterpret_cast<const float4*>(tab + T_DS + cs0), d1 = *reinterpret_cast<const float4*>(tab + T_DS + cs0 + 4);
+    const float4 t0 = *reinterpret_cast<const float4*>(tab + T_DT + cs0), t1 = *reinterpret_cast<const float4*>(tab + T_DT + cs0 + 4);
+    const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};   // ds[k] = decay of step cs0+k+1
+    const float dt[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+    float v[8];
+    float run = (row >= je) ? ex2(csi - tab[T_CS + je]) : 0.f;
+    v[7] = __uint_as_float(raw[8 * s + 7]) * (run * dt[7]);
+#pragma unroll
+    for (int k = 6; k >= 0; --k) {
+      run = (cs0 + k == row) ? 1.f : run * ds[k];
+      v[k] = __uint_as_float(raw[8 * s + k]) * (run * dt[k]);
+    }
+    st_shared_v4(dst + s * 2048, pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+  }
+}
+// rb: block row of the warp (warp-uniform); tm_row: TMEM address of (first lane of this warp's quarter, first
+// source column); mrow: shared-memory address of this row's first 16 bytes in the plain 128x128 bf16 tile.
+// One compact loop body for every block row (the code has to stay resident in the instruction cache while
+// several groups run through it at different places); the two 16-column halves of the next block are
+// requested as soon as the registers of the current ones are free.
+template <int NCH>
+__device__ __forceinline__ void decay_row(int rb, int ch, uint32_t tm_row, const float* __restrict__ tab, int row, uint32_t mrow) {
+  const float csi = tab[T_CS + row];
+  if (NCH == 1) {
+    uint32_t a[16], b[16];
+    tmem_ld16_issue(tm_row, a);
+    tmem_ld16_issue(tm_row + 16, b);
+#pragma unroll 1
+    for (int cb = 0; cb < rb; ++cb) {
+      const float rf = ex2(csi - tab[T_CS + cb * 32 + 31]);
+      const float* cf = tab + T_CF + cb * 32;
+      const uint32_t dst = mrow + cb * 4 * 2048;
+      tmem_ld_wait_2x16(a, b);
+      decay_off_half(a, rf, cf, dst);
+      tmem_ld16_issue(tm_row + (cb + 1) * 32, a);
+      decay_off_half(b, rf, cf + 16, dst + 2 * 2048);
+      tmem_ld16_issue(tm_row + (cb + 1) * 32 + 16, b);
+    }
+    tmem_ld_wait_2x16(a, b);
+    decay_diag_half(a, tab, rb * 32, row, csi, mrow + rb * 4 * 2048);
+    decay_diag_half(b, tab, rb * 32 + 16, row, csi, mrow + rb * 4 * 2048 + 2 * 2048);
+  } else {
+    // two threads per row: this one owns columns [16 ch, 16 ch + 16) of every block; two register sets so that
+    // the load of the next block flies while the current one is worked on
+    uint32_t a[16], b[16];
+    const uint32_t tmc = tm_row + ch * 16;
+    const uint32_t mr = mrow + ch * 2 * 2048;
+    tmem_ld16_issue(tmc, a);
+    int cb = 0;
+#pragma unroll 1
+    for (; cb + 1 < rb; cb += 2) {
+      tmem_ld16_issue(tmc + (cb + 1) * 32, b);
+      tmem_ld_wait_2x16(a, b);
+      decay_off_half(a, ex2(csi - tab[T_CS + cb * 32 + 31]), tab + T_CF + cb * 32 + ch * 16, mr + cb * 4 * 2048);
+      tmem_ld16_issue(tmc + (cb + 2) * 32, a);
+      decay_off_half(b, ex2(csi - tab[T_CS + cb * 32 + 63]), tab + T_CF + cb * 32 + 32 + ch * 16, mr + (cb + 1) * 4 * 2048);
+    }
+    if (cb < rb) {   // one more block below the diagonal, then the diagonal block
+      tmem_ld16_issue(tmc + (cb + 1) * 32, b);
+      tmem_ld_wait_2x16(a, b);
+      decay_off_half(a, ex2(csi - tab[T_CS + cb * 32 + 31]), tab + T_CF + cb * 32 + ch * 16, mr + cb * 4 * 2048);
+      decay_diag_half(b, tab, rb * 32 + ch * 16, row, csi, mr + rb * 4 * 2048);
+    } else {
+      tmem_ld_wait_2x16(a, b);
+      decay_diag_half(a, tab, rb * 32 + ch * 16, row, csi, mr + rb * 4 * 2048);
+    }
+  }
 }
 
 // Variant used by the one-tile-per-CTA kernels (all 16 warps meet at a CTA barrier per head anyway):
@@ -754,6 +844,21 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // parity n&1 and `empty` with parity (n&1)^1 (a fresh barrier passes a wait on parity 1).
 // TMEM: G x2 (256 columns) + {Y, Y_off} x2 (256 columns) = 512.  Same math and operand layouts as
 // k_scan_tc; MODE as there.
+// Light per-role profiling of the persistent kernels (-DWS_PROF): register accumulators in one lane per role,
+// added to the 64-bit counters behind the status word when the role ends.
+#ifdef WS_PROF
+#define PROF_DECL(n) long long pw[n] = {0}; const long long p_start = clock64();
+#define PW(i, stmt) { const long long p0_ = clock64(); stmt; pw[i] += clock64() - p0_; }
+#define PROF_T(name) const long long name = clock64();
+#define PROF_ADD(i, name) pw[i] += clock64() - name;
+#define PROF_FLUSH(base, n, cond) if (cond) { pw[(n) - 1] = clock64() - p_start; for (int i_ = 0; i_ < (n); ++i_) atomicAdd((unsigned long long*)(status + 8) + (base) + i_, (unsigned long long)pw[i_]); }
+#else
+#define PROF_DECL(n)
+#define PW(i, stmt) { stmt; }
+#define PROF_T(name)
+#define PROF_ADD(i, name)
+#define PROF_FLUSH(base, n, cond)
+#endif
 constexpr int WS_THREADS = 28 * 32;
 constexpr int WS_SCALE_WARPS = 16, WS_EPI_WARPS = 8;
 
@@ -761,36 +866,46 @@ template <int P, int MODE>
 struct WsCfg {
   static constexpr int N = 64, NB = 1, HB = 64 / P;
   static constexpr int NBOX = (MODE == 0) ? 1 : 2;
-  static constexpr int NM = (MODE == 0) ? 3 : 2;                    // M_h ring depth
+  static constexpr int NM = (MODE == 0) ? 3 : 2;                    // M_h ring depth = decay groups
   static constexpr int CB_BYTES = 2 * BOX_BYTES;                     // keep + other tile
   static constexpr int IN_BYTES = NBOX * BOX_BYTES + SBOX_BYTES;      // x [, dy] box + state box
   static constexpr int TB_BYTES = HB * TAB_BYTES;                     // decay tables of one head block
-  static constexpr int NT = 4;                                        // table ring depth
+  static constexpr int NTH = 4 * HB;                                  // table ring depth (one 2 KB table per head)
   static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
-  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + NT * TB_BYTES + RED_BYTES;
+  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + NTH * TAB_BYTES + RED_BYTES;
+  // warp roles: NM groups of four decay warps, then {producer, MMA issuer, 2 idle}, then 8 epilogue warps
+  // two MMA issuer warps (one per head of a head block) on the two least loaded schedulers, then the producer
+  static constexpr int NCH = 1;                                       // threads per row of the decay pass
+  static constexpr int DW = 4 * NCH * NM, W_MMA = DW, W_PROD = DW + 2, W_EPI = DW + 4;
+  static constexpr int NI = HB;                                       // active issuers: warps W_MMA .. W_MMA + NI - 1
+  static constexpr int THREADS = (DW + 4 + WS_EPI_WARPS) * 32;
+  // registers per thread after re-balancing (launch share: 80 at 768 threads, 96 at 640)
+  static constexpr int R_DECAY = (THREADS == 768) ? 88 : (THREADS == 640 ? 128 : (MODE == 0 ? 80 : 72)),
+                       R_SPECIAL = (THREADS > 768) ? 48 : 56,
+                       R_EPI = (THREADS > 768) ? (MODE == 0 ? 64 : 72) : ((MODE == 0) ? 72 : 80);
 };
 
 struct WsBars {
   uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], acc_full[2], acc_empty[2];
-  uint64_t m_full[3], m_empty[3], tab_full[4], tab_empty[4], done;
+  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], done;
 };
 
 template <int P, int MODE>
-__global__ void __launch_bounds__(WS_THREADS, 1)
+__global__ void __launch_bounds__(WsCfg<P, MODE>::THREADS, 1)
 k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
           const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
           const bf16* __restrict__ z, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
           bf16* __restrict__ dx, float* __restrict__ rs0, float* __restrict__ rs1, int* __restrict__ status) {
   using Cfg = WsCfg<P, MODE>;
-  constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM;
+  constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM, NTH = Cfg::NTH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sCB = smem;                                   // 2 x {keep tile, other tile}
   uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
   uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x [, dy], state box}
-  uint8_t* sTab = sIn + 2 * Cfg::IN_BYTES;               // NT x decay tables of a head block (they run further ahead)
-  float* sRed = (float*)(sTab + Cfg::NT * Cfg::TB_BYTES);   // [2][256] (P = 64 row-sum exchange)
+  uint8_t* sTab = sIn + 2 * Cfg::IN_BYTES;               // NTH x decay table of one head (they run further ahead)
+  float* sRed = (float*)(sTab + NTH * TAB_BYTES);          // [2][256] (P = 64 row-sum exchange)
   __shared__ __align__(8) WsBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -801,17 +916,18 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   if (s_abort) return;
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 1);
-      mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], WS_SCALE_WARPS);
-      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 1 + WS_EPI_WARPS);
-      mbar_init(&bars.acc_full[i], 1); mbar_init(&bars.acc_empty[i], WS_EPI_WARPS);
+      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], Cfg::NI);
+      mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], Cfg::DW);
+      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], Cfg::NI + WS_EPI_WARPS);
+      mbar_init(&bars.acc_full[i], Cfg::NI); mbar_init(&bars.acc_empty[i], WS_EPI_WARPS);
     }
-    for (int i = 0; i < 3; ++i) { mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 1); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS + WS_EPI_WARPS); }
-    mbar_init(&bars.done, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&bars.m_full[i], 4 * Cfg::NCH); mbar_init(&bars.m_empty[i], 1); }
+    // a head's table is read by the warps of its decay group and by the epilogue warps of its columns
+    for (int i = 0; i < NTH; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], 4 * Cfg::NCH + WS_EPI_WARPS / HB); }
+    mbar_init(&bars.done, Cfg::NI);
     mbar_fence_init();
   }
-  if (warp == 17) tmem_alloc(&tmem_slot, 512);
+  if (warp == Cfg::W_MMA) tmem_alloc(&tmem_slot, 512);
   // the blocks above the diagonal of every M_h ring tile are zero for the whole kernel
   if (tid < 512) {
     for (int i = 0; i < NM; ++i) zero_upper_blocks(tid & 127, tid >> 7, warp, smem_u32(sM + i * 2 * BOX_BYTES));
@@ -822,9 +938,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   tc_fence_after();
   const uint32_t tm = tmem_slot;
   Waiter w{status, false};
-#ifdef SSD_WS_DEBUG
-  const long long t_start = clock64();
-#endif
 
   const int nblk = g.hpg / HB;
   const int ntiles = g.B * g.G * g.nc;
@@ -837,53 +950,45 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     b = r / g.G;
   };
 
-  if (warp == 16) {
+  if (warp >= Cfg::DW && warp < Cfg::W_EPI) reg_dec<Cfg::R_SPECIAL>();
+  if (warp == Cfg::W_PROD) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      PROF_DECL(4)
       auto load_cb = [&](int t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
         const int cs_ = t & 1;
-        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
+        PW(0, w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41));
         uint8_t* keep = sCB + cs_ * Cfg::CB_BYTES;
         mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
         tma_load_3d(keep, (MODE == 2) ? &tmB : &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
         tma_load_3d(keep + BOX_BYTES, (MODE == 2) ? &tmC : &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
       };
-      auto prefetch_tile = [&](int t) {   // all per-block inputs of tile t towards L2
-        int b, grp, c;
-        tile_coords(t, b, grp, c);
-        for (int blk = 0; blk < nblk; ++blk) {
-          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
-          tma_prefetch_3d(&tmX, col, c * QT, b);
-          if (NBOX == 2) tma_prefetch_3d(&tmDY, col, c * QT, b);
-          tma_prefetch_3d(&tmS, 0, h0 * P, b * g.nc + c);
-          bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
-        }
-      };
       const int total_blocks = my_tiles * nblk;
-      auto load_tab = [&](int kg) {        // tables of global block kg: they run two blocks ahead of the boxes
+      auto load_tab = [&](int kg) {        // tables of the heads of global block kg: they run two blocks ahead of the boxes
         if (kg >= total_blocks) return;
         int b, grp, c;
         tile_coords(kg / nblk, b, grp, c);
-        const int h0 = grp * g.hpg + (kg % nblk) * HB, ts = kg % Cfg::NT;
-        w.wait(&bars.tab_empty[ts], ((kg / Cfg::NT) & 1) ^ 1, 49);
-        mbar_expect_tx(&bars.tab_full[ts], Cfg::TB_BYTES);
-        bulk_load(sTab + ts * Cfg::TB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, Cfg::TB_BYTES, &bars.tab_full[ts]);
+        const int h0 = grp * g.hpg + (kg % nblk) * HB;
+        for (int hl = 0; hl < HB; ++hl) {
+          const int kh = kg * HB + hl, ts = kh % NTH;
+          PW(1, w.wait(&bars.tab_empty[ts], ((kh / NTH) & 1) ^ 1, 49));
+          mbar_expect_tx(&bars.tab_full[ts], TAB_BYTES);
+          bulk_load(sTab + ts * TAB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0 + hl) * TAB, TAB_BYTES, &bars.tab_full[ts]);
+        }
       };
       int kb = 0;
       load_cb(0);
-      prefetch_tile(0);
       load_tab(0);
       load_tab(1);
       for (int t = 0; t < my_tiles; ++t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
-        if (t + 1 < my_tiles) prefetch_tile(t + 1);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           load_tab(kb + 2);
           const int ib = kb & 1;
-          w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
+          PW(2, w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42));
           uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
           const int h0 = grp * g.hpg + blk * HB;
           const int col = grp * g.hpg * P + blk * 64;
@@ -894,27 +999,42 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
           // the next G while this tile is still being worked on
           if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+#ifdef WS_PF_STREAM   // one block of the next tile per block of this one
+          if (t + 1 < my_tiles) {
+            int b2, grp2, c2;
+            tile_coords(t + 1, b2, grp2, c2);
+            tma_prefetch_3d(&tmX, grp2 * g.hpg * P + blk * 64, c2 * QT, b2);
+            if (NBOX == 2) tma_prefetch_3d(&tmDY, grp2 * g.hpg * P + blk * 64, c2 * QT, b2);
+#if WS_PF_STREAM > 1
+            tma_prefetch_3d(&tmS, 0, (grp2 * g.hpg + blk * HB) * P, b2 * g.nc + c2);
+#endif
+          }
+#endif
         }
       }
+      PROF_FLUSH(0, 4, true)
     }
-  } else if (warp == 17) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= Cfg::W_MMA && warp < Cfg::W_MMA + Cfg::NI) {
+    // ------------------------------------------------------------------ MMA issuers: issuer mi takes head mi of every
+    // head block; issuer 0 also forms G and the state term.  A commit only tracks the MMAs of its own thread, so the
+    // block-level barriers expect one arrival per issuer.
+    const int mi = warp - Cfg::W_MMA;
     if (lane == 0) {
+      PROF_DECL(6)
       const uint32_t idG = make_idesc(128, 128, 0, 0);
       const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
       constexpr uint32_t M_STEP = (MODE == 2) ? 256 : 4096;
       auto issue_g = [&](int t) {
         const int s_ = t & 1;
-        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43);
-        w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
+        PW(0, w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43); w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44));
         tc_fence_after();
         const uint32_t keep = smem_u32(sCB + s_ * Cfg::CB_BYTES), other = keep + BOX_BYTES;
         const uint64_t dc = desc_sw128_k((MODE == 2) ? other : keep, 0), db = desc_sw128_k((MODE == 2) ? keep : other, 0);
-#pragma unroll
+#pragma unroll 1
         for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, ks > 0);
         mma_commit(&bars.g_full[s_]);
       };
-      issue_g(0);
+      if (mi == 0) issue_g(0);
       int kb = 0, kh = 0;
       for (int t = 0; t < my_tiles; ++t) {
         const uint64_t dK0 = desc_sw128_k(smem_u32(sCB + (t & 1) * Cfg::CB_BYTES), 0);
@@ -922,77 +1042,71 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const int ib = kb & 1, ab = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
           const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
-          w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
-          w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46);
+          PW(1, w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45));
+          PW(2, w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46));
           for (int hl = 0; hl < HB; ++hl, ++kh) {
+            if (hl != mi) continue;
             const int ms = kh % NM;
-            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            PW(3, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
+            PROF_T(ph0)
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             const uint64_t dM0 = (MODE == 2) ? desc_plain_mn(mt, 128, 0, 0) : desc_plain_k(mt, 128, 0);
             const uint64_t dO0 = desc_sw128_mn(inb + ((MODE == 2) ? BOX_BYTES : 0), 0, hl * P * 2, 16);
-#pragma unroll
+#pragma unroll 1
             for (int ks = 0; ks < 8; ++ks)
               mma_bf16(tmYd + hl * P, desc_adv(dM0, ks * M_STEP), desc_adv(dO0, ks * 2048), idY, ks > 0);
             if (hl == 0) {
               const uint64_t dS0 = desc_sw128_k(inb + NBOX * BOX_BYTES, 0);
-#pragma unroll
+#pragma unroll 1
               for (int ks = 0; ks < 4; ++ks) mma_bf16(tmYo, desc_adv(dK0, ks * 32), desc_adv(dS0, ks * 32), idO, ks > 0);
             }
             mma_commit(&bars.m_empty[ms]);
+            PROF_ADD(4, ph0)
           }
           mma_commit(&bars.in_empty[ib]);
           if (blk == nblk - 1) mma_commit(&bars.cb_empty[t & 1]);
           mma_commit(&bars.acc_full[ab]);
-          if (blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
+          if (mi == 0 && blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
         }
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
+      PROF_FLUSH(4 + 6 * mi, 6, true)
     }
-  } else if (warp < WS_SCALE_WARPS) {
-    // ------------------------------------------------------------------ decay pass warps
-    const int row = tid & 127, part = tid >> 7;
-    int kb = 0, kh = 0;
+  } else if (warp < Cfg::DW) {
+    // ------------------------------------------------------------------ decay pass: group wg owns heads kh = wg (mod NM)
+    reg_inc<Cfg::R_DECAY>();
+    const int wg = warp / (4 * Cfg::NCH), ch = (warp >> 2) % Cfg::NCH, rb = warp & 3, row = rb * 32 + lane;
+    const uint32_t mrow = smem_u32(sM + wg * 2 * BOX_BYTES) + row * 16;
+    int kh = 0;
+    PROF_DECL(6)
     for (int t = 0; t < my_tiles; ++t) {
       const int gs = t & 1;
-      w.wait(&bars.g_full[gs], (t >> 1) & 1, 51);
+      PW(0, w.wait(&bars.g_full[gs], (t >> 1) & 1, 51));
       tc_fence_after();
-      for (int blk = 0; blk < nblk; ++blk, ++kb) {
-        const int ts = kb % Cfg::NT;
-        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES);
-        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 52);
-        for (int hl = 0; hl < HB; ++hl, ++kh) {
-          const int ms = kh % NM;
-          w.wait(&bars.m_empty[ms], ((kh / NM) & 1) ^ 1, 53);
-#ifdef SSD_WS_DEBUG
-          const long long f00 = clock64();
-#endif
-#ifdef SSD_WS_DEBUG
-          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES), w.acc);
-          const long long f0 = clock64();
-          w.acc[16 + (warp & 3)] += f0 - f00;
-#else
-          decay_mask_tile(tm + gs * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
-#endif
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars.m_full[ms]);
-
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
+      const uint32_t tm_row = tmem_addr(tm + gs * 128, rb * 32, 0);
+      for (int hh = 0; hh < nblk * HB; ++hh, ++kh) {
+        if (kh % NM != wg) continue;
+        const int ts = kh % NTH;
+        PW(1, w.wait(&bars.tab_full[ts], (kh / NTH) & 1, 52));
+        PW(2, w.wait(&bars.m_empty[wg], ((kh / NM) & 1) ^ 1, 53));
+        PW(3, decay_row<Cfg::NCH>(rb, ch, tm_row, (const float*)(sTab + ts * TAB_BYTES), row, mrow));
+        PW(4, fence_async_smem(); __syncwarp(); if (lane == 0) { mbar_arrive(&bars.m_full[wg]); mbar_arrive(&bars.tab_empty[ts]); });
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.g_empty[gs]);
     }
-  } else if (warp >= 20) {
+    PROF_FLUSH(16, 6, lane == 0 && rb == 3 && wg == 0)
+  } else if (warp >= Cfg::W_EPI) {
     // ------------------------------------------------------------------ epilogue warps
-    const int ew = warp - 20;
+    reg_dec<Cfg::R_EPI>();
+    const int ew = warp - Cfg::W_EPI;
     const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
     const int hl_e = (half * 32) / P;
     int kb = 0;
+    PROF_DECL(6)
     for (int t = 0; t < my_tiles; ++t) {
       int b, grp, c;
       tile_coords(t, b, grp, c);
@@ -1001,18 +1115,19 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const int ib = kb & 1, ab = kb & 1;
         uint8_t* xt = sIn + ib * Cfg::IN_BYTES;
         uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;
-        const int ts = kb % Cfg::NT;
-        const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES) + hl_e * TAB;
+        const int khe = kb * HB + hl_e, ts = khe % NTH;
+        const float* tb = (const float*)(sTab + ts * TAB_BYTES);
         const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
         const int h0 = grp * g.hpg + blk * HB, h_e = h0 + hl_e;
         const float Dh = D ? __ldg(D + h_e) : 0.f;
-        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 56);
+        PW(0, w.wait(&bars.tab_full[ts], (khe / NTH) & 1, 56));
         const float cs_r = tb[T_CS + row], dt_r = tb[T_DT + row];
         const float osc = (MODE == 2) ? dt_r * ex2(tb[T_CS + 127] - cs_r) : ex2(cs_r);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
-        w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
-        w.wait(&bars.acc_full[ab], (kb >> 1) & 1, 55);
+        PW(1, w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54));
+        PW(2, w.wait(&bars.acc_full[ab], (kb >> 1) & 1, 55));
+        PROF_T(pe0)
         tc_fence_after();
         const long long colo = (long long)h0 * P + half * 32;
         const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
@@ -1036,6 +1151,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             __syncwarp();
             if (lane == 0) { mbar_arrive(&bars.acc_empty[ab]); mbar_arrive(&bars.in_empty[ib]); }
           }
+          uint4 ov[2];
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             const int k8 = h16 * 16 + q * 8;
@@ -1051,7 +1167,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 o[k] = acc[k] + Dh * xs[k];
                 if (z) o[k] *= zs[k] * sigmoidf_(zs[k]);
               }
-              *reinterpret_cast<uint4*>(y + b * g.ysb + (long long)t_row * g.ysl + colo + k8) = pack8(o);
+              ov[q] = pack8(o);
             } else if (MODE == 1) {
               float dp[8];
 #pragma unroll
@@ -1076,10 +1192,13 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 o[k] = acc[k] + Dh * dys[k];
                 s0 = fmaf(xs[k], acc[k], s0);
               }
-              *reinterpret_cast<uint4*>(dx + dense + k8) = pack8(o);
+              ov[q] = pack8(o);
             }
           }
+          if (MODE == 0) st_global_32B(y + b * g.ysb + (long long)t_row * g.ysl + colo + h16 * 16, ov[0], ov[1]);
+          if (MODE == 2) st_global_32B(dx + dense + h16 * 16, ov[0], ov[1]);
         }
+        PROF_ADD(3, pe0)
         if (MODE != 0) {
           if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
             asm volatile("bar.sync 1, 256;" ::: "memory");   // previous block's exchange fully read
@@ -1099,13 +1218,11 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
       }
     }
+    PROF_FLUSH(22, 6, lane == 0 && ew == 3)
   }
-#ifdef SSD_WS_DEBUG
-  if (lane == 0) w.flush(warp == 17 ? clock64() - t_start : 0);
-#endif
   tc_fence_before();
   __syncthreads();
-  if (warp == 17) tmem_dealloc(tm, 512);
+  if (warp == Cfg::W_MMA) tmem_dealloc(tm, 512);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1193,6 +1310,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     b = r / g.G;
   };
 
+  // the single-thread roles give registers back, the epilogue (widest live set) takes them
   if (warp == 16) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -1206,18 +1324,6 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         tma_load_3d(dst, &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
         tma_load_3d(dst + BOX_BYTES, &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
       };
-      auto prefetch_tile = [&](int t) {
-        int b, grp, c;
-        tile_coords(t, b, grp, c);
-        for (int blk = 0; blk < nblk; ++blk) {
-          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
-          tma_prefetch_3d(&tmX, col, c * QT, b);
-          tma_prefetch_3d(&tmDY, col, c * QT, b);
-          tma_prefetch_3d(&tmS, 0, h0 * P, b * g.nc + c);
-          tma_prefetch_3d(&tmDS, 0, h0 * P, b * g.nc + c);
-          bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
-        }
-      };
       const int total_blocks = my_tiles * nblk;
       auto load_tab = [&](int kg) {
         if (kg >= total_blocks) return;
@@ -1230,13 +1336,11 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       };
       int kb = 0;
       load_cb(0);
-      prefetch_tile(0);
       load_tab(0);
       load_tab(1);
       for (int t = 0; t < my_tiles; ++t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
-        if (t + 1 < my_tiles) prefetch_tile(t + 1);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           load_tab(kb + 2);
           const int ib = kb & 1;
@@ -1257,12 +1361,13 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   } else if (warp == 17) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      PROF_DECL(2)
       const uint32_t idG = make_idesc(128, 128, 0, 0);
       const uint32_t idY = make_idesc(128, P, 0, 1), idU = make_idesc(128, P, 1, 1), idO = make_idesc(128, 64, 0, 0);
       auto issue_g = [&](int t) {
         const int s_ = t & 1;
-        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43);
-        w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
+        PW(0, w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43));
+        PW(0, w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44));
         tc_fence_after();
         const uint32_t ct = smem_u32(sCB + s_ * Cfg::CB_BYTES);
         const uint64_t dc = desc_sw128_k(ct, 0), db = desc_sw128_k(ct + BOX_BYTES, 0);
@@ -1279,12 +1384,12 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           const int ib = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
-          w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
-          w.wait(&bars.st_full, kb & 1, 57);
-          w.wait(&bars.acc_empty, (kb & 1) ^ 1, 46);
+          PW(0, w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45));
+          PW(0, w.wait(&bars.st_full, kb & 1, 57));
+          PW(0, w.wait(&bars.acc_empty, (kb & 1) ^ 1, 46));
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             const int ms = kh % NM;
-            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            PW(0, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
@@ -1312,9 +1417,11 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
+      PROF_FLUSH(0, 2, true)
     }
   } else if (warp < WS_SCALE_WARPS) {
-    // ------------------------------------------------------------------ decay pass warps
+    // ------------------------------------------------------------------ decay pass warps (they hand registers to the epilogue)
+    reg_dec<64>();
     const int row = tid & 127, part = tid >> 7;
     int kb = 0, kh = 0;
     for (int t = 0; t < my_tiles; ++t) {
@@ -1342,6 +1449,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     }
   } else if (warp >= 20) {
     // ------------------------------------------------------------------ epilogue warps
+    reg_inc<88>();
     const int ew = warp - 20;
     const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
     const int hl_e = (half * 32) / P;
@@ -1385,6 +1493,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             if (lane == 0) { mbar_arrive(&bars.acc_empty); mbar_arrive(&bars.in_empty[ib]); }
           }
           const float osc = upass ? osc_u : osc_y;
+          uint4 ov[2];
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
             float xs[8], dys[8];
@@ -1405,9 +1514,10 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
                 o[k] = acc + Dh * dys[k];
                 s2 = fmaf(xs[k], acc, s2);
               }
-              *reinterpret_cast<uint4*>(dx + dense + h16 * 16 + q * 8) = pack8(o);
+              ov[q] = pack8(o);
             }
           }
+          if (upass) st_global_32B(dx + dense + h16 * 16, ov[0], ov[1]);
         }
         if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
           asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -1524,18 +1634,6 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         tma_load_3d(dst, &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
         tma_load_3d(dst + BOX_BYTES, &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
       };
-      auto prefetch_tile = [&](int t) {
-        int b, grp, c;
-        tile_coords(t, b, grp, c);
-        for (int blk = 0; blk < nblk; ++blk) {
-          const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
-          tma_prefetch_3d(&tmX, col, c * QT, b);
-          tma_prefetch_3d(&tmDY, col, c * QT, b);
-          tma_prefetch_3d(&tmS, 0, h0 * P, b * g.nc + c);
-          tma_prefetch_3d(&tmDS, 0, h0 * P, b * g.nc + c);
-          bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
-        }
-      };
       const int total_blocks = my_tiles * nblk;
       auto load_tab = [&](int kg) {
         if (kg >= total_blocks) return;
@@ -1548,13 +1646,11 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       };
       int kb = 0;
       load_cb(0);
-      prefetch_tile(0);
       load_tab(0);
       load_tab(1);
       for (int t = 0; t < my_tiles; ++t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
-        if (t + 1 < my_tiles) prefetch_tile(t + 1);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           load_tab(kb + 2);
           const int ib = kb & 1;
@@ -1575,6 +1671,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   } else if (warp == 17) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      PROF_DECL(2)
       const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
       const uint64_t dSm0 = desc_sw128_mn(smem_u32(sSt), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sSt + SBOX_BYTES), 0, 0, SBOX_BYTES);
       const int total_blocks = my_tiles * nblk;
@@ -1582,13 +1679,13 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       auto issue_w_block = [&](int kg) {   // all W products of global block kg
         if (kg >= total_blocks) return;
         const int ib = kg & 1;
-        w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45);
+        PW(0, w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45));
         tc_fence_after();
         const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
         const uint64_t dX0 = desc_sw128_k(inb, 0), dDY0 = desc_sw128_k(inb + BOX_BYTES, 0);
         for (int hl = 0; hl < HB; ++hl, ++kw) {
           const int ws = kw & 1;
-          w.wait(&bars.w_empty[ws], ((kw >> 1) & 1) ^ 1, 58);
+          PW(0, w.wait(&bars.w_empty[ws], ((kw >> 1) & 1) ^ 1, 58));
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < P / 16; ++ks)
@@ -1600,8 +1697,8 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       issue_w_block(0);
       int kb = 0, kh = 0;
       for (int t = 0; t < my_tiles; ++t) {
-        w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43);
-        w.wait(&bars.acc_empty, (t & 1) ^ 1, 46);
+        PW(0, w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43));
+        PW(0, w.wait(&bars.acc_empty, (t & 1) ^ 1, 46));
         tc_fence_after();
         const uint32_t ct = smem_u32(sCB + (t & 1) * Cfg::CB_BYTES);
         const uint64_t dBm0 = desc_sw128_mn(ct, 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(ct + BOX_BYTES, 0, 0, BOX_BYTES);
@@ -1611,7 +1708,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             const int ms = kh % NM;
-            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            PW(0, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
@@ -1626,8 +1723,8 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           // the next block's W products go out before this block's state terms, so the decay warps
           // find their next input ready when they come back from scaling this block's boxes
           issue_w_block(kb + 1);
-          w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59);
-          w.wait(&bars.st_full, kb & 1, 57);
+          PW(0, w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59));
+          PW(0, w.wait(&bars.st_full, kb & 1, 57));
           tc_fence_after();
           {
             const uint64_t dXk = desc_sw128_k(inb, 0), dDYk = desc_sw128_k(inb + BOX_BYTES, 0);
@@ -1645,6 +1742,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
+      PROF_FLUSH(2, 2, true)
     }
   } else if (warp < WS_SCALE_WARPS) {
     // ------------------------------------------------------------------ decay pass warps
@@ -1706,11 +1804,13 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       if (lane == 0) mbar_arrive(&bars.acc_empty);
       const size_t o = (((size_t)b * g.L + c * QT + row) * g.G + grp) * N + half * 32;
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        *reinterpret_cast<uint4*>(dC + o + j) = make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]),
-                                                          pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7]));
-        *reinterpret_cast<uint4*>(dB + o + j) = make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]),
-                                                          pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7]));
+      for (int j = 0; j < 32; j += 16) {
+        st_global_32B(dC + o + j,
+                      make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]), pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7])),
+                      make_uint4(pack_bf16(vc[j + 8], vc[j + 9]), pack_bf16(vc[j + 10], vc[j + 11]), pack_bf16(vc[j + 12], vc[j + 13]), pack_bf16(vc[j + 14], vc[j + 15])));
+        st_global_32B(dB + o + j,
+                      make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]), pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7])),
+                      make_uint4(pack_bf16(vb[j + 8], vb[j + 9]), pack_bf16(vb[j + 10], vb[j + 11]), pack_bf16(vb[j + 12], vb[j + 13]), pack_bf16(vb[j + 14], vb[j + 15])));
       }
     }
   }
@@ -1887,7 +1987,7 @@ int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const 
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int ntiles = g.B * g.G * g.nc;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  k<<<grid, WS_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
+  k<<<grid, WsCfg<P, MODE>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
                                  (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_ws" : (MODE == 1 ? "chunk_scan_bwd_ws" : "dx_ws"));
   return SSD_OK;
