@@ -399,8 +399,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
       float v[16];
       tmem_ld16(tmem_addr(tm, (warp & 3) * 32, part * (N / PARTS) + q * 16), v);
 #pragma unroll
-      for (int j = 0; j < 16; j += 4)
-        *reinterpret_cast<float4*>(o + q * 16 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      for (int j = 0; j < 16; j += 8)
+        st_global_32B(o + q * 16 + j, make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3])),
+                      make_uint4(__float_as_uint(v[j + 4]), __float_as_uint(v[j + 5]), __float_as_uint(v[j + 6]), __float_as_uint(v[j + 7])));
     }
     tc_fence_before();
     __syncthreads();
@@ -574,6 +575,7 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const long long colo = (long long)h0 * P + part * 16;
       const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
       const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + colo;
+      uint4 ov[2];
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         const int k8 = q * 8;
@@ -589,7 +591,7 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             o[k] = acc[k] + Dh * xs[k];
             if (z) o[k] *= zs[k] * sigmoidf_(zs[k]);
           }
-          *reinterpret_cast<uint4*>(y + b * g.ysb + (long long)t_row * g.ysl + colo + k8) = pack8(o);
+          ov[q] = pack8(o);
         } else if (MODE == 1) {
           float dp[8];
 #pragma unroll
@@ -614,9 +616,11 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             o[k] = acc[k] + Dh * dys[k];
             s0 = fmaf(xs[k], acc[k], s0);
           }
-          *reinterpret_cast<uint4*>(dx + dense + k8) = pack8(o);
+          ov[q] = pack8(o);
         }
       }
+      if (MODE == 0) st_global_32B(y + b * g.ysb + (long long)t_row * g.ysl + colo, ov[0], ov[1]);
+      if (MODE == 2) st_global_32B(dx + dense, ov[0], ov[1]);
       if (MODE != 0) {   // row sums: P/16 threads share a (head, row); combine through shared memory
         sRed[part * 128 + row] = s0;
         if (MODE == 1) sRed[(PARTS + part) * 128 + row] = s1;
@@ -818,13 +822,12 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       float vc[16], vb[16];
       tmem_ld16(tmem_addr(tmDC, (warp & 3) * 32, part * (N / PARTS) + q * 16), vc);
       tmem_ld16(tmem_addr(tmDB, (warp & 3) * 32, part * (N / PARTS) + q * 16), vb);
-#pragma unroll
-      for (int j = 0; j < 16; j += 8) {
-        *reinterpret_cast<uint4*>(dC + o + q * 16 + j) = make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]),
-                                                                   pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7]));
-        *reinterpret_cast<uint4*>(dB + o + q * 16 + j) = make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]),
-                                                                   pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7]));
-      }
+      st_global_32B(dC + o + q * 16,
+                    make_uint4(pack_bf16(vc[0], vc[1]), pack_bf16(vc[2], vc[3]), pack_bf16(vc[4], vc[5]), pack_bf16(vc[6], vc[7])),
+                    make_uint4(pack_bf16(vc[8], vc[9]), pack_bf16(vc[10], vc[11]), pack_bf16(vc[12], vc[13]), pack_bf16(vc[14], vc[15])));
+      st_global_32B(dB + o + q * 16,
+                    make_uint4(pack_bf16(vb[0], vb[1]), pack_bf16(vb[2], vb[3]), pack_bf16(vb[4], vb[5]), pack_bf16(vb[6], vb[7])),
+                    make_uint4(pack_bf16(vb[8], vb[9]), pack_bf16(vb[10], vb[11]), pack_bf16(vb[12], vb[13]), pack_bf16(vb[14], vb[15])));
     }
   }
   tc_fence_before();
