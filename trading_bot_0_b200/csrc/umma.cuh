@@ -43,8 +43,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 // Bounded wait on a phase parity.  Each try_wait may suspend the thread (up to the hint, in ns) until
 // the phase completes, so waiting warps stay off the issue slots; the bound is in elapsed clock
-// cycles (about 0.2 s), not in polls.  Returns false when the bound ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long max_cycles = 400000000LL) {
+// cycles, not in polls: about 2 s, because a profiler pass that instruments every instruction can
+// slow a kernel a thousandfold and must not be mistaken for a broken pipeline.  Returns false when
+// the bound ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long max_cycles = 4000000000LL) {
   const uint32_t a = smem_u32(bar);
   long long t0 = 0;
   for (int i = 0;; ++i) {
