@@ -89,6 +89,25 @@ def kernel_bytes_per_token(name, c, e=2):
     return table.get(name)
 
 
+def kernel_traffic_bytes_per_token(name, c, e=2):
+    """DRAM bytes per token a tensor-family kernel moves at full size: the reads are `dram__bytes_read.sum` of an ncu
+    capture of the same kernels at batch 128 (profiles/tensor_kernels_cfg1_batch128_ncu_full.md; they equal operand
+    tiles + bf16 state boxes + decay tables, each once, and grow in proportion to the token count); the writes are the
+    kernel's output bytes, because the writes of the small capture partly stay in L2.  None where nothing was measured
+    for this shape."""
+    if (c["H"], c["P"], c["N"], c["G"], c["Q"], bool(c["z"])) != (8, 32, 64, 1, 128, False) or e != 2:
+        return None
+    hp, gn, H = c["H"] * c["P"], c["G"] * c["N"], c["H"]
+    st32 = H * c["P"] * c["N"] * 4 / c["Q"]          # fp32 chunk states, bytes per token, one way
+    measured_reads = {"chunk_state_tc": 768.0, "dstates_local_tc": 768.0, "chunk_scan_ws": 1152.6,
+                      "scan_bwd_dx_ws": 1920.2, "dBdC_ws": 1920.2}
+    writes = {"chunk_state_tc": st32, "dstates_local_tc": st32, "chunk_scan_ws": hp * e,
+              "scan_bwd_dx_ws": hp * e + 3 * 4 * H, "dBdC_ws": 2 * gn * e}
+    if name not in measured_reads:
+        return None
+    return measured_reads[name] + writes[name]
+
+
 # ---- synthetic inputs --------------------------------------------------------------------------
 def make_inputs(c, device, seed, dtype=torch.bfloat16, batch=None, seqlen=None):
     """The workload's value distributions, drawn with a seeded generator on `device`."""
@@ -365,8 +384,9 @@ def run_train(args, c, rank, world, local):
         bpt = kernel_bytes_per_token(name, c)
         if bpt is not None:
             ach = bpt * tokens_rank / (avg_ms * 1e-3) / 1e9
+            tpt = kernel_traffic_bytes_per_token(name, c)
             roof = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "peak_kind": peak_kind, "traffic": None, "avg_launch_ms": avg_ms,
+                    "peak_kind": peak_kind, "traffic": None if tpt is None else tpt * tokens_rank, "avg_launch_ms": avg_ms,
                     "algorithmic_bytes_per_launch": bpt * tokens_rank}
     op_bytes = (fwd_bytes_per_token(c) + bwd_bytes_per_token(c)) * tokens_rank
     op_ach = op_bytes / (ms_step * 1e-3) / 1e9
