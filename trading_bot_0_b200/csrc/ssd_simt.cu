@@ -599,13 +599,15 @@ __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, 
   const int lane = q & 31, w = q >> 5;
   const int t = c * g.Q + qr;
   for (int h0 = 0; h0 < g.H; h0 += HG) {
-    if (q < HG) {
+    if (w < HG) {   // warp w adds the partial sums of head h0 + w (fixed order: lane-strided, then a butterfly)
       float s = 0.f;
-      if (h0 + q < g.H) {
-        const float* sp = sdot + ((size_t)(b * g.nc + c) * g.H + h0 + q) * nw;
-        for (int i = 0; i < nw; ++i) s += sp[i];
+      if (h0 + w < g.H) {
+        const float* sp = sdot + ((size_t)(b * g.nc + c) * g.H + h0 + w) * nw;
+        for (int i = lane; i < nw; i += 32) s += sp[i];
       }
-      ssd[q] = s;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0) ssd[w] = s;
     }
     float d[HG], dd[HG], v[HG], s2[HG];
 #pragma unroll
@@ -642,9 +644,14 @@ __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, 
     }
     if (ok && t < g.L) {
       float* o = ddt + ((size_t)b * g.L + t) * g.H + h0;
+      if (h0 + HG <= g.H && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+        reinterpret_cast<float4*>(o)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(o)[1] = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
 #pragma unroll
-      for (int k = 0; k < HG; ++k)
-        if (h0 + k < g.H) o[k] = v[k];
+        for (int k = 0; k < HG; ++k)
+          if (h0 + k < g.H) o[k] = v[k];
+      }
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
