@@ -94,3 +94,26 @@ def test_mid_rollout_stream_reset(lib):
     assert torch.equal(y[idx], yf[idx])
     st.reset()
     assert st.state.abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("groups,graph", [(1, False), (3, True), (8, True)])
+def test_host_step_groups_match_oracle(lib, groups, graph):
+    """The host-buffer rollout step (pinned staging buffers, streams cut into row groups that overlap on three CUDA
+    streams, the step replayed from a CUDA graph) gives the oracle's outputs and state, whatever the number of groups
+    (33 streams: ragged last group)."""
+    from trading_bot_0_b200.host import HostStep
+    cfg = O.SsdConfig("dec", 33, 1, 8, 32, 64, 1, 1, "bf16")
+    steps = 6
+    inp = O.make_decode_inputs(cfg, steps)
+    ref_y, ref_S = oracle_steps(inp, steps)
+    d = to_dev(inp, DEV)
+    state = d["state"].clone()
+    hs = HostStep(state, cfg.ngroups, groups=groups, graph=graph)
+    ys = []
+    for t in range(steps):
+        hs.load_inputs(inp["x"][t], inp["dt"][t], inp["B"][t], inp["C"][t])
+        hs.step(d["A"], d["D"])
+        torch.cuda.synchronize()
+        ys.append(hs.hy.clone())
+    assert_close("y", torch.stack(ys).to(DEV), ref_y, "bf16")
+    assert_close("state", state, ref_S, "bf16")

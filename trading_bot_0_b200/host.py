@@ -110,27 +110,86 @@ class HostFwdBwd:
 
 
 class HostStep:
-    """Streamed-rollout step with the per-step vectors in pinned host memory and the state
-    resident on the device: copies x, dt, B, C in, runs the state update, copies y out."""
+    """Streamed-rollout step with the per-step vectors in pinned host memory and the state resident on
+    the device: one call copies x, dt, B, C in, runs the state update and copies y out.
 
-    def __init__(self, state: torch.Tensor, ngroups: int, dtype=torch.bfloat16):
+    The object owns the pinned staging buffers: the caller writes the step's vectors into `hx`, `hdt`,
+    `hB`, `hC` (views of ONE packed pinned buffer, one packed row per stream, so a group of streams moves
+    with a single copy) and reads the result from `hy`.  The streams (environments) are cut into `groups`
+    row ranges that flow through three CUDA streams (host->device copies, kernels, device->host copies),
+    the way a rollout double-buffers groups of environments: while one group's kernel runs, the next
+    group's inputs arrive and the previous group's outputs leave.  After one eager step the whole step is
+    captured into a CUDA graph and replayed, so a step costs one launch on the host
+    (trading_bots/src/torch/train/rollout.rs:209-235 is the per-step loop this stands in for).
+    `step` returns after enqueueing on the caller's current stream."""
+
+    def __init__(self, state: torch.Tensor, ngroups: int, dtype=torch.bfloat16, groups: int = 8, graph: bool = True):
         S, H, P, N = state.shape
         dev = state.device
-        self.state = state
-        self.x = torch.empty(S, H, P, dtype=dtype, device=dev)
-        self.dt = torch.empty(S, H, dtype=dtype, device=dev)
-        self.Bm = torch.empty(S, ngroups, N, dtype=dtype, device=dev)
-        self.Cm = torch.empty(S, ngroups, N, dtype=dtype, device=dev)
+        self.state, self.dev = state, dev
+        hp, gn = H * P, ngroups * N
+        up = lambda n: (n + 7) // 8 * 8                      # every segment of a packed row starts 16-byte aligned
+        o_dt, o_b, o_c = up(hp), up(hp) + up(H), up(hp) + up(H) + up(gn)
+        self.row = o_c + up(gn)
+        self.host_in = torch.zeros(S, self.row, dtype=dtype).pin_memory()
+        self.dev_in = torch.zeros(S, self.row, dtype=dtype, device=dev)
+        cut = lambda buf: (buf[:, :hp].unflatten(1, (H, P)), buf[:, o_dt:o_dt + H],
+                           buf[:, o_b:o_b + gn].unflatten(1, (ngroups, N)),
+                           buf[:, o_c:o_c + gn].unflatten(1, (ngroups, N)))
+        self.hx, self.hdt, self.hB, self.hC = cut(self.host_in)
+        self.x, self.dt, self.Bm, self.Cm = cut(self.dev_in)
         self.y = torch.empty(S, H, P, dtype=dtype, device=dev)
+        self.hy = torch.empty(S, H, P, dtype=dtype).pin_memory()
+        groups = max(1, min(groups, S))
+        per = (S + groups - 1) // groups
+        self.ranges = [(lo, min(S, lo + per)) for lo in range(0, S, per)]
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.ev_in = [torch.cuda.Event() for _ in self.ranges]
+        self.ev_run = [torch.cuda.Event() for _ in self.ranges]
+        self.use_graph, self._graph, self._calls, self._params = graph, None, 0, None
 
     def bytes_per_call(self):
-        h2d = sum(t.numel() * t.element_size() for t in (self.x, self.dt, self.Bm, self.Cm))
-        return h2d, self.y.numel() * self.y.element_size()
+        """(host->device, device->host) bytes one step moves, counted from the buffers copied."""
+        return self.host_in.numel() * self.host_in.element_size(), self.hy.numel() * self.hy.element_size()
 
-    def step(self, hx, hdt, hB, hC, A, D, hy) -> None:
-        self.x.copy_(hx, non_blocking=True)
-        self.dt.copy_(hdt, non_blocking=True)
-        self.Bm.copy_(hB, non_blocking=True)
-        self.Cm.copy_(hC, non_blocking=True)
-        ssd.state_update(self.state, self.x, self.dt, A, self.Bm, self.Cm, D, y=self.y)
-        hy.copy_(self.y, non_blocking=True)
+    def load_inputs(self, hx, hdt, hB, hC) -> None:
+        """Convenience for callers whose vectors live elsewhere on the host: copy them into the staging views."""
+        self.hx.copy_(hx)
+        self.hdt.copy_(hdt)
+        self.hB.copy_(hB)
+        self.hC.copy_(hC)
+
+    def _enqueue(self, root, A, D) -> None:
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_stream(root)
+        for gi, (lo, hi) in enumerate(self.ranges):
+            with torch.cuda.stream(self.s_in):
+                self.dev_in[lo:hi].copy_(self.host_in[lo:hi], non_blocking=True)
+                self.ev_in[gi].record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.ev_in[gi])
+                ssd.state_update(self.state[lo:hi], self.x[lo:hi], self.dt[lo:hi], A, self.Bm[lo:hi], self.Cm[lo:hi], D,
+                                 y=self.y[lo:hi])
+                self.ev_run[gi].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_run[gi])
+                self.hy[lo:hi].copy_(self.y[lo:hi], non_blocking=True)
+        for s in (self.s_in, self.s_run, self.s_out):
+            root.wait_stream(s)
+
+    def step(self, A, D) -> None:
+        cur = torch.cuda.current_stream(self.dev)
+        self._calls += 1
+        if not self.use_graph or self._calls == 1:          # first step eagerly (also warms everything up)
+            self._enqueue(cur, A, D)
+            return
+        key = (A.data_ptr(), D.data_ptr() if D is not None else 0)
+        if self._graph is None or self._params != key:
+            g = torch.cuda.CUDAGraph()
+            cap = torch.cuda.Stream(self.dev)
+            cap.wait_stream(cur)
+            with torch.cuda.graph(g, stream=cap):
+                self._enqueue(cap, A, D)
+            cur.wait_stream(cap)
+            self._graph, self._params, self._keep = g, key, (A, D)
+        self._graph.replay()
