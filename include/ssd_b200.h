@@ -16,6 +16,7 @@
  * ssd_last_error().
  *
  * Operator (per batch b, head h with group g = h*ngroups/nheads, time t, state S [P x N]):
+ *     dt[b,t,h] = act(dt_in[b,t,h] + dt_bias[h])   act = softplus if dims.dt_softplus else identity; dt_bias optional
  *     a_t = exp(dt[b,t,h] * A[h])
  *     S_t = a_t * S_{t-1} + dt[b,t,h] * x[b,t,h,:] (outer) B[b,t,g,:]
  *     y_t = S_t . C[b,t,g,:] + D[h] * x[b,t,h,:]          (then y_t *= silu(z_t) if z given)
@@ -71,7 +72,8 @@ typedef struct SsdDims {
   int32_t algo;      /* SsdAlgo  */
   int32_t device;    /* CUDA ordinal the pointers live on; -1 = do not check */
   int32_t has_z;     /* 1 if a z gate is passed (sizes the backward workspace) */
-  int32_t reserved;
+  int32_t dt_softplus; /* 1: the step size is softplus(dt + dt_bias), fused into the cumsum kernel and its backward
+                          (the activation a Mamba-2 layer applies just before the scan); 0: dt + dt_bias as given */
   int64_t x_stride_b, x_stride_l;
   int64_t dt_stride_b, dt_stride_l;
   int64_t b_stride_b, b_stride_l;
@@ -83,7 +85,7 @@ typedef struct SsdDims {
 /* Forward operands.  Optional pointers may be NULL. */
 typedef struct SsdFwdPtrs {
   const void* x;           /* [B,L,H,P]  dtype */
-  const void* dt;          /* [B,L,H]    dtype  (already positive: softplus stays with the caller) */
+  const void* dt;          /* [B,L,H]    dtype  (positive after the optional bias / softplus) */
   const float* A;          /* [H]        fp32, negative */
   const void* Bm;          /* [B,L,G,N]  dtype */
   const void* Cm;          /* [B,L,G,N]  dtype */
@@ -92,6 +94,7 @@ typedef struct SsdFwdPtrs {
   const float* init_state; /* [B,H,P,N]  fp32, optional */
   void* y;                 /* [B,L,H,P]  dtype, out */
   float* final_state;      /* [B,H,P,N]  fp32, out, optional */
+  const float* dt_bias;    /* [H]        fp32, optional: added to dt before the activation */
 } SsdFwdPtrs;
 
 /* Backward operands: the forward inputs again, the incoming gradients, the outputs. */
@@ -111,6 +114,9 @@ typedef struct SsdBwdPtrs {
   int32_t fwd_saved;         /* 1: `workspace` is the buffer ssd_forward ran in for these same
                                 inputs (its chunk cumsums and chunk-entry states are reused);
                                 0: recompute them */
+  const float* dt_bias;      /* [H] fp32, optional, as in the forward */
+  float* ddt_bias;           /* [H] fp32, out, required iff dt_bias given.  With dt_bias / dt_softplus, `ddt` is the
+                                gradient w.r.t. the dt that was passed in (before bias and activation). */
 } SsdBwdPtrs;
 
 /* Single-timestep recurrence for streamed rollout (in place on `state`). */
@@ -118,7 +124,7 @@ typedef struct SsdStepDims {
   int32_t streams, nheads, headdim, dstate, ngroups;
   int32_t dtype;        /* SsdDtype of x, dt, B, C, z, y; state is always fp32 */
   int32_t device;       /* -1 = do not check */
-  int32_t reserved;
+  int32_t dt_softplus;  /* as in SsdDims */
   int64_t x_stride_s;   /* elements between streams; 0 = dense */
   int64_t dt_stride_s, b_stride_s, c_stride_s, z_stride_s, y_stride_s;
 } SsdStepDims;
@@ -133,6 +139,7 @@ typedef struct SsdStepPtrs {
   const float* D;      /* [H], optional */
   const void* z;       /* [S,H,P], optional */
   void* y;             /* [S,H,P], out */
+  const float* dt_bias;/* [H] fp32, optional */
 } SsdStepPtrs;
 
 /* Bytes of workspace ssd_forward / ssd_backward need for `dims` (0 on invalid dims, with the
@@ -224,6 +231,60 @@ SSD_API const char* ssd_last_error(void);
 #define SSD_NOALLOC_MAX_BYTES ((size_t)32 << 20)
 SSD_API int32_t ssd_forward_noalloc(const SsdDims* dims, const SsdFwdPtrs* p, void* cuda_stream);
 SSD_API size_t ssd_noalloc_max_bytes(void);
+
+/*
+ * The two bandwidth-bound operators either side of the scan in a Mamba-2 layer (the step-size activation
+ * softplus(dt + dt_bias) and the gate y * silu(z) are inside the scan itself, see SsdDims / SsdFwdPtrs):
+ *
+ *   before: out[b,t,c] = act(bias[c] + sum_k weight[c,k] * in[b, t-width+1+k, c])   causal, depthwise, zero history;
+ *           the layer runs it over the concatenated (x | B | C) channels and hands the three channel ranges of `out`
+ *           to ssd_forward as strided views.  The reference has the same 3-tap causal depthwise convolution on its
+ *           q/k/v (trading_bots/src/torch/model/blocks/gqa.rs:148-178).
+ *   after : out[r,:] = in[r,:] * rsqrt(mean(in[r,:]^2) + eps) * weight   over the H*P features of a token; weight is
+ *           optional (the reference's RMS norm has no gain, trading_bots/src/torch/model/rmsnorm.rs:16-19).
+ *
+ * Storage dtype bf16 or fp32, arithmetic fp32; weight, bias, rstd and their gradients fp32.  Strides in ELEMENTS,
+ * multiples of 16 bytes; channels / width multiples of 8.  The backward calls recompute what they need from the
+ * forward INPUT; the conv backward takes the incoming gradient as up to three channel segments so that the scan's
+ * dx, dB, dC tensors are consumed where they lie.  Reductions over tokens use a fixed summation order.
+ */
+typedef struct SsdConvDims {
+  int32_t batch, seqlen, channels, width;   /* width = taps, 2..4 */
+  int32_t dtype;                            /* SsdDtype of in, out and their gradients */
+  int32_t device;                           /* -1 = do not check */
+  int32_t activation;                       /* 0 identity, 1 silu */
+  int32_t reserved;
+  int64_t in_stride_b, in_stride_l, out_stride_b, out_stride_l;
+} SsdConvDims;
+
+typedef struct SsdConvGrad {                /* one channel segment of the gradient w.r.t. `out` */
+  const void* ptr;                          /* [B, L, channels] with the strides below */
+  int32_t channels, reserved;
+  int64_t stride_b, stride_l;
+} SsdConvGrad;
+
+typedef struct SsdNormDims {
+  int64_t rows;                             /* batch * seqlen */
+  int32_t width;                            /* features per row, <= 2048 */
+  int32_t dtype, device;
+  float eps;
+  int64_t in_stride_row, out_stride_row;
+} SsdNormDims;
+
+SSD_API size_t ssd_conv1d_workspace_bytes(const SsdConvDims* dims);   /* backward only */
+SSD_API int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float* weight /* [C,width] */,
+                                   const float* bias /* [C], optional */, void* out, void* cuda_stream);
+SSD_API int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float* weight, const float* bias,
+                                    const SsdConvGrad* dout, int32_t ndout, void* din, int64_t din_stride_b,
+                                    int64_t din_stride_l, float* dweight, float* dbias /* optional */, void* workspace,
+                                    size_t workspace_bytes, void* cuda_stream);
+SSD_API size_t ssd_rmsnorm_workspace_bytes(const SsdNormDims* dims);  /* backward with a weight only */
+SSD_API int32_t ssd_rmsnorm_forward(const SsdNormDims* dims, const void* in, const float* weight /* optional */, void* out,
+                                    float* rstd /* [rows], optional, kept for the backward */, void* cuda_stream);
+SSD_API int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, const float* weight, const float* rstd,
+                                     const void* dout, int64_t dout_stride_row, void* din, int64_t din_stride_row,
+                                     float* dweight /* iff weight */, void* workspace, size_t workspace_bytes,
+                                     void* cuda_stream);
 
 /*
  * Tracing.  ssd_launch_count: kernels this library has launched in this process (all threads).

@@ -102,6 +102,63 @@ def make_inputs(cfg: SsdConfig, seed: int = SEED, *, batch=None, seqlen=None, wi
     return out
 
 
+def dt_preactivation(dt_raw, dt_bias=None, softplus=False, dtype=torch.float64):
+    """Step size a Mamba-2 layer feeds the scan: act(dt_raw + dt_bias), act = softplus or identity, and its
+    derivative w.r.t. dt_raw (sigmoid for softplus).  The operator definition in the workload text takes the step
+    size after this; the fused form takes dt_raw and the per-head bias."""
+    v = dt_raw.to(dtype)
+    if dt_bias is not None:
+        v = v + dt_bias.to(dtype)
+    if softplus:
+        return F.softplus(v, threshold=20.0), torch.where(v <= 20.0, torch.sigmoid(v), torch.ones_like(v))
+    return v, torch.ones_like(v)
+
+
+def causal_conv1d_ref(inp, weight, bias=None, activation=True, dtype=torch.float64):
+    """out[b,t,c] = act(bias[c] + sum_k weight[c,k] * inp[b, t-K+1+k, c]) with zero history; act = silu or identity.
+    The depthwise causal convolution a Mamba-2 layer runs over its (x | B | C) channels (differentiable)."""
+    x = inp.to(dtype)
+    Bn, L, Cn = x.shape
+    K = weight.shape[1]
+    xp = F.pad(x, (0, 0, K - 1, 0))
+    out = torch.zeros(Bn, L, Cn, dtype=dtype)
+    for k in range(K):
+        out = out + xp[:, k:k + L, :] * weight.to(dtype)[:, k]
+    if bias is not None:
+        out = out + bias.to(dtype)
+    return F.silu(out) if activation else out
+
+
+def rmsnorm_ref(inp, weight=None, eps=1e-5, dtype=torch.float64):
+    """inp * rsqrt(mean(inp^2, last dim) + eps) * weight (differentiable)."""
+    x = inp.to(dtype)
+    out = x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return out if weight is None else out * weight.to(dtype)
+
+
+def _round_through(t, storage):
+    """Round to the storage dtype of a tensor that crosses an operator boundary, with a straight-through gradient."""
+    return t if storage is None else t + (t.detach().to(storage).to(t.dtype) - t.detach())
+
+
+def mamba2_mixer_core_ref(xBC, dt_raw, z, conv_weight, conv_bias, dt_bias, A, D, norm_weight, *, nheads, headdim, dstate,
+                          ngroups, eps=1e-5, init_state=None, dtype=torch.float64, storage=None):
+    """conv + silu -> split -> SSD with softplus(dt + dt_bias) and the silu(z) gate -> RMS norm, one timestep at a time
+    for the scan (differentiable ground truth of the fused composition).  `storage` (e.g. torch.bfloat16) rounds the two
+    tensors that cross operator boundaries in the forward pass (the conv output and the scan output), so that a
+    comparison measures the operators and not the quantisation of what they hand to each other."""
+    Bn, L, _ = xBC.shape
+    hp, gn = nheads * headdim, ngroups * dstate
+    u = _round_through(causal_conv1d_ref(xBC, conv_weight, conv_bias, True, dtype), storage)
+    x = u[..., :hp].reshape(Bn, L, nheads, headdim)
+    Bm = u[..., hp:hp + gn].reshape(Bn, L, ngroups, dstate)
+    Cm = u[..., hp + gn:].reshape(Bn, L, ngroups, dstate)
+    dt = F.softplus(dt_raw.to(dtype) + dt_bias.to(dtype), threshold=20.0)
+    y, S = ssd_sequential(x, dt, A.to(dtype), Bm, Cm, None if D is None else D.to(dtype), None if z is None else z.to(dtype),
+                          init_state, dtype=dtype)
+    return rmsnorm_ref(_round_through(y, storage).reshape(Bn, L, hp), norm_weight, eps, dtype), S
+
+
 def make_decode_inputs(cfg: SsdConfig, steps: int, seed: int = SEED, *, streams=None):
     """Per-step fresh draws for the streamed-rollout workload: state ~ N(0, 0.1)."""
     g = torch.Generator(device="cpu").manual_seed(seed)

@@ -27,10 +27,10 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_sizes_match_header(lib):
     from trading_bot_0_b200 import _lib
     assert C.sizeof(_lib.SsdDims) == 12 * 4 + 12 * 8
-    assert C.sizeof(_lib.SsdFwdPtrs) == 10 * 8
-    assert C.sizeof(_lib.SsdBwdPtrs) == 18 * 8 + 8
+    assert C.sizeof(_lib.SsdFwdPtrs) == 11 * 8
+    assert C.sizeof(_lib.SsdBwdPtrs) == 18 * 8 + 8 + 2 * 8
     assert C.sizeof(_lib.SsdStepDims) == 8 * 4 + 6 * 8
-    assert C.sizeof(_lib.SsdStepPtrs) == 9 * 8
+    assert C.sizeof(_lib.SsdStepPtrs) == 10 * 8
 
 
 def _dims(**kw):

@@ -85,3 +85,22 @@ def test_golden_fixture_reproduces():
                              inp["z"], inp["init_state"], dfin, dtype=torch.float64, chunk=CFG.chunk)
     for k, v in a.items():
         assert rel_err(v, torch.from_numpy(g["ref_" + k])) < 1e-10, k
+
+
+def test_prepost_references_match_torch_ops():
+    """The conv / norm / step-size references restate torch's own operators (fp64)."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 19, 16, generator=g, dtype=torch.float64)
+    w = torch.randn(16, 4, generator=g, dtype=torch.float64)
+    b = torch.randn(16, generator=g, dtype=torch.float64)
+    want = F.silu(F.conv1d(F.pad(x.transpose(1, 2), (3, 0)), w[:, None, :], b, groups=16).transpose(1, 2))
+    assert (O.causal_conv1d_ref(x, w, b, True) - want).abs().max() < 1e-12
+    n = O.rmsnorm_ref(x, b, 1e-5)
+    assert (n - F.rms_norm(x, (16,), b, 1e-5)).abs().max() < 1e-12
+    raw = torch.randn(3, 5, 4, generator=g, dtype=torch.float64).requires_grad_(True)
+    bias = torch.randn(4, generator=g, dtype=torch.float64)
+    dt, dact = O.dt_preactivation(raw, bias, True)
+    dt.sum().backward()
+    assert (raw.grad - dact).abs().max() < 1e-12
+    assert (dt - F.softplus(raw + bias)).abs().max() < 1e-12

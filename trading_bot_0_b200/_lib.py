@@ -25,36 +25,56 @@ EXPORTS = [
     "ssd_state_update", "ssd_state_reset_rows", "ssd_sp_total_logdecay", "ssd_sp_prefix_state",
     "ssd_last_error", "ssd_version", "ssd_compiled_arch", "ssd_launch_count", "ssd_profile_begin",
     "ssd_profile_end", "ssd_forward_noalloc", "ssd_noalloc_max_bytes",
+    "ssd_conv1d_workspace_bytes", "ssd_conv1d_forward", "ssd_conv1d_backward",
+    "ssd_rmsnorm_workspace_bytes", "ssd_rmsnorm_forward", "ssd_rmsnorm_backward",
 ]
 
 
 class SsdDims(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("batch", "seqlen", "nheads", "headdim", "dstate", "ngroups", "chunk",
-                                         "dtype", "algo", "device", "has_z", "reserved")] + \
+                                         "dtype", "algo", "device", "has_z", "dt_softplus")] + \
                [(n, C.c_int64) for n in ("x_stride_b", "x_stride_l", "dt_stride_b", "dt_stride_l",
                                          "b_stride_b", "b_stride_l", "c_stride_b", "c_stride_l",
                                          "z_stride_b", "z_stride_l", "y_stride_b", "y_stride_l")]
 
 
 class SsdFwdPtrs(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("x", "dt", "A", "Bm", "Cm", "D", "z", "init_state", "y", "final_state")]
+    _fields_ = [(n, C.c_void_p) for n in ("x", "dt", "A", "Bm", "Cm", "D", "z", "init_state", "y", "final_state",
+                                          "dt_bias")]
 
 
 class SsdBwdPtrs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("x", "dt", "A", "Bm", "Cm", "D", "z", "init_state", "dy",
                                           "dfinal_state", "dx", "ddt", "dA", "dB", "dC", "dD", "dz",
-                                          "dinit_state")] + [("fwd_saved", C.c_int32)]
+                                          "dinit_state")] + [("fwd_saved", C.c_int32), ("dt_bias", C.c_void_p),
+                                                           ("ddt_bias", C.c_void_p)]
 
 
 class SsdStepDims(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("streams", "nheads", "headdim", "dstate", "ngroups", "dtype", "device",
-                                         "reserved")] + \
+                                         "dt_softplus")] + \
                [(n, C.c_int64) for n in ("x_stride_s", "dt_stride_s", "b_stride_s", "c_stride_s", "z_stride_s",
                                          "y_stride_s")]
 
 
 class SsdStepPtrs(C.Structure):
-    _fields_ = [(n, C.c_void_p) for n in ("state", "x", "dt", "A", "Bm", "Cm", "D", "z", "y")]
+    _fields_ = [(n, C.c_void_p) for n in ("state", "x", "dt", "A", "Bm", "Cm", "D", "z", "y", "dt_bias")]
+
+
+class SsdConvDims(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("batch", "seqlen", "channels", "width", "dtype", "device", "activation",
+                                         "reserved")] + \
+               [(n, C.c_int64) for n in ("in_stride_b", "in_stride_l", "out_stride_b", "out_stride_l")]
+
+
+class SsdConvGrad(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("channels", C.c_int32), ("reserved", C.c_int32), ("stride_b", C.c_int64),
+                ("stride_l", C.c_int64)]
+
+
+class SsdNormDims(C.Structure):
+    _fields_ = [("rows", C.c_int64), ("width", C.c_int32), ("dtype", C.c_int32), ("device", C.c_int32), ("eps", C.c_float),
+                ("in_stride_row", C.c_int64), ("out_stride_row", C.c_int64)]
 
 
 class SsdError(RuntimeError):
@@ -108,6 +128,19 @@ def load() -> C.CDLL:
     lib.ssd_forward_noalloc.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdFwdPtrs), vp]
     lib.ssd_noalloc_max_bytes.restype = sz
     lib.ssd_noalloc_max_bytes.argtypes = []
+    lib.ssd_conv1d_workspace_bytes.restype = sz
+    lib.ssd_conv1d_workspace_bytes.argtypes = [C.POINTER(SsdConvDims)]
+    lib.ssd_conv1d_forward.restype = i32
+    lib.ssd_conv1d_forward.argtypes = [C.POINTER(SsdConvDims), vp, vp, vp, vp, vp]
+    lib.ssd_conv1d_backward.restype = i32
+    lib.ssd_conv1d_backward.argtypes = [C.POINTER(SsdConvDims), vp, vp, vp, C.POINTER(SsdConvGrad), i32, vp, i64, i64, vp, vp,
+                                        vp, sz, vp]
+    lib.ssd_rmsnorm_workspace_bytes.restype = sz
+    lib.ssd_rmsnorm_workspace_bytes.argtypes = [C.POINTER(SsdNormDims)]
+    lib.ssd_rmsnorm_forward.restype = i32
+    lib.ssd_rmsnorm_forward.argtypes = [C.POINTER(SsdNormDims), vp, vp, vp, vp, vp]
+    lib.ssd_rmsnorm_backward.restype = i32
+    lib.ssd_rmsnorm_backward.argtypes = [C.POINTER(SsdNormDims), vp, vp, vp, vp, i64, vp, i64, vp, vp, sz, vp]
     lib.ssd_version.restype = i32
     lib.ssd_compiled_arch.restype = i32
     _lib = lib

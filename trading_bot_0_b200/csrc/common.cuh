@@ -16,7 +16,15 @@ namespace ssd {
 struct Geo {
   int B, L, H, P, N, G, Q, nc, hpg;  // hpg = heads per group
   long long xsb, xsl, dtsb, dtsl, bsb, bsl, csb, csl, zsb, zsl, ysb, ysl;
+  int dt_softplus;                     // step size = softplus(dt + dt_bias) instead of dt + dt_bias
 };
+
+// The step-size pre-activation of a Mamba-2 layer, fused where dt is first read.  Above 20 softplus is the
+// identity in fp32 (same cut-off as torch.nn.functional.softplus).
+__device__ __forceinline__ float dt_activation(float raw, float bias, int softplus) {
+  const float v = raw + bias;
+  return (softplus && v <= 20.f) ? log1pf(expf(v)) : v;
+}
 
 // Workspace segments (offsets in bytes from the workspace base; 0-size segments unused).
 struct WsLayout {

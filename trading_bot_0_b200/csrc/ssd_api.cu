@@ -62,6 +62,7 @@ static int make_geo(const SsdDims* d, Geo* g) {
   if (d->algo < SSD_ALGO_AUTO || d->algo > SSD_ALGO_TENSOR) { set_error("unknown algo %d", d->algo); return SSD_ERR_UNSUPPORTED; }
   g->B = d->batch; g->L = d->seqlen; g->H = d->nheads; g->P = d->headdim; g->N = d->dstate; g->G = d->ngroups;
   g->Q = d->chunk; g->nc = (d->seqlen + d->chunk - 1) / d->chunk; g->hpg = d->nheads / d->ngroups;
+  g->dt_softplus = d->dt_softplus != 0;
   if ((long long)g->nc * g->H > 65535 || g->B > 65535) {
     set_error("grid limits: nchunks*nheads (%lld) and batch (%d) must each be <= 65535", (long long)g->nc * g->H, g->B);
     return SSD_ERR_UNSUPPORTED;
@@ -149,7 +150,7 @@ using namespace ssd;
 extern "C" {
 
 const char* ssd_last_error(void) { return g_err; }
-int32_t ssd_version(void) { return 1; }
+int32_t ssd_version(void) { return 2; }
 int32_t ssd_compiled_arch(void) { return 100; }
 int64_t ssd_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -249,6 +250,7 @@ int32_t ssd_backward_staged(const SsdDims* dims, const SsdBwdPtrs* p, void* work
   if (stages & SSD_STAGE_FINISH) {
     if (!p->dx || !p->ddt || !p->dA || !p->dB || !p->dC) { set_error("dx, ddt, dA, dB, dC must be non-NULL"); return SSD_ERR_NULL_POINTER; }
     if (p->D && !p->dD) { set_error("dD must be non-NULL when D is given"); return SSD_ERR_NULL_POINTER; }
+    if (p->dt_bias && !p->ddt_bias) { set_error("ddt_bias must be non-NULL when dt_bias is given"); return SSD_ERR_NULL_POINTER; }
   }
   if ((p->z != nullptr) != (dims->has_z != 0)) { set_error("dims.has_z (%d) does not match the z pointer", dims->has_z); return SSD_ERR_BAD_SHAPE; }
   if (p->z && !p->dz) { set_error("dz must be non-NULL when z is given"); return SSD_ERR_NULL_POINTER; }

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(DEC_THREADS) k_state_update(SsdStepDims d, Ssd
   const int P = d.headdim;
 
   const T* xs = (const T*)p.x + s * d.x_stride_s + (long long)h * P;
-  const float dtv = ldf((const T*)p.dt + s * d.dt_stride_s + h);
+  const float dtv = dt_activation(ldf((const T*)p.dt + s * d.dt_stride_s + h), p.dt_bias ? __ldg(p.dt_bias + h) : 0.f, d.dt_softplus);
   const float a = expf(dtv * __ldg(p.A + h));
   const float Dh = p.D ? __ldg(p.D + h) : 0.f;
   const T* Bp = (const T*)p.Bm + s * d.b_stride_s + (long long)grp * N;
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(DEC_THREADS) k_state_update_generic(SsdStepDim
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int P = d.headdim, N = d.dstate;
   const T* xs = (const T*)p.x + s * d.x_stride_s + (long long)h * P;
-  const float dtv = ldf((const T*)p.dt + s * d.dt_stride_s + h);
+  const float dtv = dt_activation(ldf((const T*)p.dt + s * d.dt_stride_s + h), p.dt_bias ? __ldg(p.dt_bias + h) : 0.f, d.dt_softplus);
   const float a = expf(dtv * __ldg(p.A + h));
   const float Dh = p.D ? __ldg(p.D + h) : 0.f;
   const T* Bp = (const T*)p.Bm + s * d.b_stride_s + (long long)grp * N;

@@ -1,0 +1,520 @@
+// The two bandwidth-bound operators either side of the scan in a Mamba-2 layer:
+//   before:  out = act(causal depthwise conv1d(in) + bias) over the (x | B | C) channels, act = silu or identity
+//   after :  out = in * rsqrt(mean(in^2) + eps) * weight   (RMS norm of the gated scan output, weight optional)
+// each with its backward.  Every tensor is read once and written once (the conv backward re-reads a
+// (width-1)-row halo per 64-token tile); arithmetic is fp32, storage bf16 or fp32, 16-byte accesses.
+// Reductions over tokens (dweight, dbias) are two-stage with a fixed summation order.
+//
+// The step-size activation softplus(dt + dt_bias) and the gate y*silu(z) need no kernel here: they are
+// evaluated inside the scan's own kernels.
+#include "common.cuh"
+#include "ssd_internal.h"
+
+namespace ssd {
+namespace {
+
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+constexpr int CONV_THREADS = 128;   // 128 channel vectors (8 channels each) per block
+constexpr int CONV_TL = 64;         // tokens per tile
+
+// ---------------------------------------------------------------------------------------------
+// conv forward: thread = 8 channels, walks a tile of tokens keeping the last K-1 input rows in registers.
+// grid = (tiles, channel blocks, batch).
+template <typename T, int K>
+__global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const T* __restrict__ in,
+                                                           const float* __restrict__ weight, const float* __restrict__ bias,
+                                                           T* __restrict__ out) {
+  const int cv = blockIdx.y * CONV_THREADS + threadIdx.x;
+  const int c0 = cv * 8;
+  if (c0 >= d.channels) return;
+  const int b = blockIdx.z, t0 = blockIdx.x * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
+  float w[8][K], bs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) w[j][k] = __ldg(weight + (size_t)(c0 + j) * K + k);
+    bs[j] = bias ? __ldg(bias + c0 + j) : 0.f;
+  }
+  const T* ip = in + (long long)b * d.in_stride_b + c0;
+  T* op = out + (long long)b * d.out_stride_b + c0;
+  float win[K][8];   // win[k] = input row t - (K-1) + k
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) {
+    const int t = t0 - (K - 1) + k;
+    if (t >= 0) load8<T>(ip + (long long)t * d.in_stride_l, win[k]);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) win[k][j] = 0.f;
+    }
+  }
+  for (int t = t0; t < t1; ++t) {
+    load8<T>(ip + (long long)t * d.in_stride_l, win[K - 1]);
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a = bs[j];
+#pragma unroll
+      for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+      o[j] = d.activation ? a * sigmoidf_(a) : a;
+    }
+    store8<T>(op + (long long)t * d.out_stride_l, o);
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// conv backward.  Streaming forward in time over a tile: at step s the pre-activation of row s is recomputed from
+// the input window, dpre[s] = dout[s] * act'(pre[s]) enters a second window, and
+//   din[s-K+1] = sum_j w[K-1-j] * dpre[s-K+1+j]          (complete once dpre[s] is known)
+//   dweight[k] += dpre[s] * in[s-K+1+k],  dbias += dpre[s]   (rows s of this tile only).
+// dout arrives as up to three channel segments (the scan's dx, dB, dC tensors).  Each block walks the (batch, tile)
+// pairs y, y+gridDim.x, ... and leaves one partial sum per block; k_conv_reduce adds them in block order.
+struct ConvSegs {
+  const void* ptr[3];
+  int c_begin[3];           // first channel of the segment; segment i covers [c_begin[i], c_begin[i+1])
+  long long stride_b[3], stride_l[3];
+  int n;
+};
+
+template <typename T, int K>
+__global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, const T* __restrict__ in,
+                                                           const float* __restrict__ weight, const float* __restrict__ bias,
+                                                           ConvSegs segs, T* __restrict__ din, long long din_stride_b,
+                                                           long long din_stride_l, float* __restrict__ partial) {
+  const int cv = blockIdx.y * CONV_THREADS + threadIdx.x;
+  const int c0 = cv * 8;
+  if (c0 >= d.channels) return;
+  float w[8][K], bs[8], dw[8][K], db[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) { w[j][k] = __ldg(weight + (size_t)(c0 + j) * K + k); dw[j][k] = 0.f; }
+    bs[j] = bias ? __ldg(bias + c0 + j) : 0.f;
+    db[j] = 0.f;
+  }
+  int si = 0;
+  for (int i = 1; i < segs.n; ++i) if (c0 >= segs.c_begin[i]) si = i;
+  const T* dop = (const T*)segs.ptr[si] + (c0 - segs.c_begin[si]);
+  const long long dosb = segs.stride_b[si], dosl = segs.stride_l[si];
+
+  const int ntile = (d.seqlen + CONV_TL - 1) / CONV_TL;
+  for (int pair = blockIdx.x; pair < d.batch * ntile; pair += gridDim.x) {
+    const int b = pair / ntile, t0 = (pair - b * ntile) * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
+    const T* ip = in + (long long)b * d.in_stride_b + c0;
+    float win[K][8], dpw[K][8];   // win[k] = in[s-K+1+k], dpw[k] = dpre[s-K+1+k]
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { win[k][j] = 0.f; dpw[k][j] = 0.f; }
+    const int s_end = min(t1 + K - 1, d.seqlen + K - 1);
+    for (int s = t0 - (K - 1); s < s_end; ++s) {
+      // shift both windows, then bring in row s
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { win[k][j] = win[k + 1][j]; dpw[k][j] = dpw[k + 1][j]; }
+      if (s >= 0 && s < d.seqlen) load8<T>(ip + (long long)s * d.in_stride_l, win[K - 1]);
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) win[K - 1][j] = 0.f;
+      }
+      if (s >= t0 && s < d.seqlen) {
+        float go[8];
+        load8<T>(dop + (long long)b * dosb + (long long)s * dosl, go);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float a = bs[j];
+#pragma unroll
+          for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+          float g = go[j];
+          if (d.activation) {
+            const float sg = sigmoidf_(a);
+            g *= sg * (1.f + a * (1.f - sg));
+          }
+          dpw[K - 1][j] = g;
+          if (s < t1) {   // each row's weight / bias gradient is counted by exactly one tile
+            db[j] += g;
+#pragma unroll
+            for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dpw[K - 1][j] = 0.f;
+      }
+      const int t = s - (K - 1);
+      if (t >= t0 && t < t1) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float a = 0.f;
+#pragma unroll
+          for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dpw[q][j], a);
+          o[j] = a;
+        }
+        store8<T>(din + (long long)b * din_stride_b + (long long)t * din_stride_l + c0, o);
+      }
+    }
+  }
+  float* pp = partial + ((size_t)blockIdx.x * d.channels + c0) * (K + 1);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) pp[j * (K + 1) + k] = dw[j][k];
+    pp[j * (K + 1) + K] = db[j];
+  }
+}
+
+// dweight[c,k] / dbias[c] = sum over blocks of the partials, in block order
+__global__ void k_conv_reduce(int nblk, int channels, int K, const float* __restrict__ partial, float* __restrict__ dweight,
+                              float* __restrict__ dbias) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= channels * (K + 1)) return;
+  float a = 0.f;
+  for (int r = 0; r < nblk; ++r) a += partial[(size_t)r * channels * (K + 1) + i];
+  const int c = i / (K + 1), k = i - c * (K + 1);
+  if (k < K) dweight[(size_t)c * K + k] = a;
+  else if (dbias) dbias[c] = a;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm.  One warp per row; a lane owns the 8-element vectors v, v+32, ... of the row.
+constexpr int NORM_THREADS = 128, NORM_MAXV = 8;   // rows of up to 2048 elements stay in registers (NV = vectors per lane)
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_fwd(SsdNormDims d, const T* __restrict__ in,
+                                                              const float* __restrict__ weight, T* __restrict__ out,
+                                                              float* __restrict__ rstd) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (NORM_THREADS / 32) + (threadIdx.x >> 5);
+  if (row >= d.rows) return;
+  const int nv = d.width / 8;
+  const T* ip = in + row * d.in_stride_row;
+  T* op = out + row * d.out_stride_row;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + 32 * i;
+    if (vi < nv) {
+      load8<T>(ip + vi * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = rsqrtf(ss / (float)d.width + d.eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + 32 * i;
+    if (vi < nv) {
+      float o[8], wv[8];
+      if (weight) load8<float>(weight + vi * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * (weight ? wv[j] : 1.f);
+      store8<T>(op + vi * 8, o);
+    }
+  }
+}
+
+// backward: n = in * rstd, dn = dout * weight, din = rstd * (dn - n * mean(dn * n)), dweight += dout * n.
+// Warps walk rows with a grid stride; a block leaves one dweight partial row.
+template <typename T, int NV>
+__global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_bwd(SsdNormDims d, const T* __restrict__ in,
+                                                              const float* __restrict__ weight, const float* __restrict__ rstd,
+                                                              const T* __restrict__ dout, long long dout_stride_row,
+                                                              T* __restrict__ din, long long din_stride_row,
+                                                              float* __restrict__ partial) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nv = d.width / 8;
+  float wv[NV][8], dwv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { wv[i][j] = 1.f; dwv[i][j] = 0.f; }
+    if (weight && vi < nv) load8<float>(weight + vi * 8, wv[i]);
+  }
+  const long long wstride = (long long)gridDim.x * (NORM_THREADS / 32);
+  for (long long row = (long long)blockIdx.x * (NORM_THREADS / 32) + warp; row < d.rows; row += wstride) {
+    const float r = rstd[row];
+    float n[NV][8], dn[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + 32 * i;
+      if (vi < nv) {
+        float x[8], g[8];
+        load8<T>(in + row * d.in_stride_row + vi * 8, x);
+        load8<T>(dout + row * dout_stride_row + vi * 8, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          n[i][j] = x[j] * r;
+          dn[i][j] = g[j] * wv[i][j];
+          dwv[i][j] = fmaf(g[j], n[i][j], dwv[i][j]);
+          dot = fmaf(dn[i][j], n[i][j], dot);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float m = dot / (float)d.width;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int vi = lane + 32 * i;
+      if (vi < nv) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = r * (dn[i][j] - n[i][j] * m);
+        store8<T>(din + row * din_stride_row + vi * 8, o);
+      }
+    }
+  }
+  if (!partial) return;
+  // the four warps of the block add their weight-gradient rows in warp order, through shared memory
+  __shared__ float sred[NORM_THREADS / 32][32 * 8 + 1];
+  for (int i = 0; i < NV; ++i) {   // block-uniform trip count
+    if (i * 32 >= nv) break;
+    const int vi = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sred[warp][lane * 8 + j] = dwv[i][j];
+    __syncthreads();
+    if (warp == 0 && vi < nv) {
+      float* pp = partial + (size_t)blockIdx.x * d.width + vi * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float a = 0.f;
+        for (int ww = 0; ww < NORM_THREADS / 32; ++ww) a += sred[ww][lane * 8 + j];
+        pp[j] = a;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void k_norm_reduce(int nblk, int width, const float* __restrict__ partial, float* __restrict__ dweight) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= width) return;
+  float a = 0.f;
+  for (int r = 0; r < nblk; ++r) a += partial[(size_t)r * width + i];
+  dweight[i] = a;
+}
+
+int conv_blocks(const SsdConvDims* d) {
+  const int ntile = (d->seqlen + CONV_TL - 1) / CONV_TL;
+  const long long pairs = (long long)d->batch * ntile;
+  return (int)(pairs < 296 ? pairs : 296);
+}
+int norm_blocks(const SsdNormDims* d) {
+  const long long need = (d->rows + NORM_THREADS / 32 - 1) / (NORM_THREADS / 32);
+  return (int)(need < 592 ? need : 592);
+}
+
+int check_conv(const SsdConvDims* d) {
+  if (!d) { set_error("dims is NULL"); return SSD_ERR_NULL_POINTER; }
+  if (d->batch <= 0 || d->seqlen <= 0 || d->channels <= 0) { set_error("conv1d: batch, seqlen and channels must be positive"); return SSD_ERR_BAD_SHAPE; }
+  if (d->width < 2 || d->width > 4) { set_error("conv1d: width %d not supported (2..4)", d->width); return SSD_ERR_UNSUPPORTED; }
+  if (d->channels % 8) { set_error("conv1d: channels (%d) must be a multiple of 8", d->channels); return SSD_ERR_UNSUPPORTED; }
+  if (d->dtype != SSD_F32 && d->dtype != SSD_BF16) { set_error("conv1d: unknown dtype %d", d->dtype); return SSD_ERR_UNSUPPORTED; }
+  if (d->batch > 65535) { set_error("conv1d: batch must be <= 65535"); return SSD_ERR_BAD_SHAPE; }
+  const int es = d->dtype == SSD_BF16 ? 2 : 4;
+  const long long strides[4] = {d->in_stride_b, d->in_stride_l, d->out_stride_b, d->out_stride_l};
+  for (long long st : strides)
+    if (st < 0 || (st * es) % 16) { set_error("conv1d: strides must be non-negative multiples of 16 bytes"); return SSD_ERR_BAD_ALIGNMENT; }
+  if (d->in_stride_l < d->channels || d->out_stride_l < d->channels) { set_error("conv1d: row strides smaller than the channel count"); return SSD_ERR_BAD_SHAPE; }
+  return SSD_OK;
+}
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+}  // namespace ssd
+
+using namespace ssd;
+
+extern "C" {
+
+size_t ssd_conv1d_workspace_bytes(const SsdConvDims* dims) {
+  clear_error();
+  if (check_conv(dims)) return 0;
+  return (size_t)conv_blocks(dims) * dims->channels * (dims->width + 1) * sizeof(float);
+}
+
+int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float* weight, const float* bias, void* out,
+                           void* cuda_stream) {
+  clear_error();
+  int rc = check_conv(dims);
+  if (rc) return rc;
+  if (!in || !weight || !out) { set_error("conv1d: in / weight / out is NULL"); return SSD_ERR_NULL_POINTER; }
+  if (!aligned16(in) || !aligned16(out)) { set_error("conv1d: in and out must be 16-byte aligned"); return SSD_ERR_BAD_ALIGNMENT; }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const dim3 grid((dims->seqlen + CONV_TL - 1) / CONV_TL, (dims->channels / 8 + CONV_THREADS - 1) / CONV_THREADS, dims->batch);
+#define CONV_FWD(T, K) k_conv_fwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, (const T*)in, weight, bias, (T*)out)
+  if (dims->dtype == SSD_BF16) {
+    if (dims->width == 4) CONV_FWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_FWD(__nv_bfloat16, 3); else CONV_FWD(__nv_bfloat16, 2);
+  } else {
+    if (dims->width == 4) CONV_FWD(float, 4); else if (dims->width == 3) CONV_FWD(float, 3); else CONV_FWD(float, 2);
+  }
+#undef CONV_FWD
+  SSD_CUDA_CHECK_LAUNCH("conv1d_fwd");
+  return SSD_OK;
+}
+
+int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float* weight, const float* bias,
+                            const SsdConvGrad* dout, int32_t ndout, void* din, int64_t din_stride_b, int64_t din_stride_l,
+                            float* dweight, float* dbias, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  clear_error();
+  int rc = check_conv(dims);
+  if (rc) return rc;
+  if (!in || !weight || !dout || !din || !dweight || !workspace) { set_error("conv1d backward: a required pointer is NULL"); return SSD_ERR_NULL_POINTER; }
+  if (ndout < 1 || ndout > 3) { set_error("conv1d backward: 1 to 3 gradient segments, got %d", ndout); return SSD_ERR_BAD_SHAPE; }
+  const int es = dims->dtype == SSD_BF16 ? 2 : 4;
+  ConvSegs segs;
+  segs.n = ndout;
+  int c = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (i < ndout) {
+      if (!dout[i].ptr || !aligned16(dout[i].ptr)) { set_error("conv1d backward: gradient segment %d is NULL or not 16-byte aligned", i); return SSD_ERR_BAD_ALIGNMENT; }
+      if (dout[i].channels <= 0 || dout[i].channels % 8 || dout[i].stride_l < dout[i].channels ||
+          (dout[i].stride_b * es) % 16 || (dout[i].stride_l * es) % 16) {
+        set_error("conv1d backward: gradient segment %d: channels must be a positive multiple of 8, strides multiples of 16 bytes", i);
+        return SSD_ERR_BAD_SHAPE;
+      }
+      segs.ptr[i] = dout[i].ptr; segs.c_begin[i] = c; segs.stride_b[i] = dout[i].stride_b; segs.stride_l[i] = dout[i].stride_l;
+      c += dout[i].channels;
+    } else {
+      segs.ptr[i] = nullptr; segs.c_begin[i] = 0x7fffffff; segs.stride_b[i] = 0; segs.stride_l[i] = 0;
+    }
+  }
+  if (c != dims->channels) { set_error("conv1d backward: gradient segments cover %d channels, expected %d", c, dims->channels); return SSD_ERR_BAD_SHAPE; }
+  if (!aligned16(in) || !aligned16(din) || din_stride_l < dims->channels || (din_stride_b * es) % 16 || (din_stride_l * es) % 16) {
+    set_error("conv1d backward: in / din must be 16-byte aligned with strides that are multiples of 16 bytes");
+    return SSD_ERR_BAD_ALIGNMENT;
+  }
+  const int nblk = conv_blocks(dims);
+  const size_t need = (size_t)nblk * dims->channels * (dims->width + 1) * sizeof(float);
+  if (workspace_bytes < need) { set_error("conv1d backward: workspace too small: %zu < %zu", workspace_bytes, need); return SSD_ERR_WORKSPACE_TOO_SMALL; }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const dim3 grid(nblk, (dims->channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
+  float* partial = (float*)workspace;
+#define CONV_BWD(T, K) k_conv_bwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial)
+  if (dims->dtype == SSD_BF16) {
+    if (dims->width == 4) CONV_BWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_BWD(__nv_bfloat16, 3); else CONV_BWD(__nv_bfloat16, 2);
+  } else {
+    if (dims->width == 4) CONV_BWD(float, 4); else if (dims->width == 3) CONV_BWD(float, 3); else CONV_BWD(float, 2);
+  }
+#undef CONV_BWD
+  SSD_CUDA_CHECK_LAUNCH("conv1d_bwd");
+  const int n = dims->channels * (dims->width + 1);
+  k_conv_reduce<<<(n + 255) / 256, 256, 0, s>>>(nblk, dims->channels, dims->width, partial, dweight, dbias);
+  SSD_CUDA_CHECK_LAUNCH("conv1d_reduce");
+  return SSD_OK;
+}
+
+static int check_norm(const SsdNormDims* d) {
+  if (!d) { set_error("dims is NULL"); return SSD_ERR_NULL_POINTER; }
+  if (d->rows <= 0 || d->width <= 0) { set_error("rmsnorm: rows and width must be positive"); return SSD_ERR_BAD_SHAPE; }
+  if (d->width % 8 || d->width > NORM_MAXV * 256) { set_error("rmsnorm: width (%d) must be a multiple of 8, at most %d", d->width, NORM_MAXV * 256); return SSD_ERR_UNSUPPORTED; }
+  if (d->dtype != SSD_F32 && d->dtype != SSD_BF16) { set_error("rmsnorm: unknown dtype %d", d->dtype); return SSD_ERR_UNSUPPORTED; }
+  const int es = d->dtype == SSD_BF16 ? 2 : 4;
+  if (d->in_stride_row < d->width || d->out_stride_row < d->width || (d->in_stride_row * es) % 16 || (d->out_stride_row * es) % 16) {
+    set_error("rmsnorm: row strides must cover the width and be multiples of 16 bytes");
+    return SSD_ERR_BAD_ALIGNMENT;
+  }
+  return SSD_OK;
+}
+
+size_t ssd_rmsnorm_workspace_bytes(const SsdNormDims* dims) {
+  clear_error();
+  if (check_norm(dims)) return 0;
+  return (size_t)norm_blocks(dims) * dims->width * sizeof(float);
+}
+
+int32_t ssd_rmsnorm_forward(const SsdNormDims* dims, const void* in, const float* weight, void* out, float* rstd,
+                            void* cuda_stream) {
+  clear_error();
+  int rc = check_norm(dims);
+  if (rc) return rc;
+  if (!in || !out) { set_error("rmsnorm: in / out is NULL"); return SSD_ERR_NULL_POINTER; }
+  if (!aligned16(in) || !aligned16(out) || (weight && !aligned16(weight))) { set_error("rmsnorm: pointers must be 16-byte aligned"); return SSD_ERR_BAD_ALIGNMENT; }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const long long nb = (dims->rows + NORM_THREADS / 32 - 1) / (NORM_THREADS / 32);
+  const int nvl = (dims->width / 8 + 31) / 32;   // vectors per lane
+#define NORM_FWD(T, NV) k_rmsnorm_fwd<T, NV><<<(unsigned)nb, NORM_THREADS, 0, s>>>(*dims, (const T*)in, weight, (T*)out, rstd)
+#define NORM_FWD_T(T) do { if (nvl <= 1) NORM_FWD(T, 1); else if (nvl <= 2) NORM_FWD(T, 2); else if (nvl <= 4) NORM_FWD(T, 4); else NORM_FWD(T, 8); } while (0)
+  if (dims->dtype == SSD_BF16) NORM_FWD_T(__nv_bfloat16); else NORM_FWD_T(float);
+#undef NORM_FWD_T
+#undef NORM_FWD
+  SSD_CUDA_CHECK_LAUNCH("rmsnorm_fwd");
+  return SSD_OK;
+}
+
+int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, const float* weight, const float* rstd,
+                             const void* dout, int64_t dout_stride_row, void* din, int64_t din_stride_row, float* dweight,
+                             void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  clear_error();
+  int rc = check_norm(dims);
+  if (rc) return rc;
+  if (!in || !rstd || !dout || !din) { set_error("rmsnorm backward: a required pointer is NULL"); return SSD_ERR_NULL_POINTER; }
+  if ((weight != nullptr) != (dweight != nullptr)) { set_error("rmsnorm backward: dweight must be given iff weight is"); return SSD_ERR_NULL_POINTER; }
+  const int es = dims->dtype == SSD_BF16 ? 2 : 4;
+  if (!aligned16(in) || !aligned16(dout) || !aligned16(din) || dout_stride_row < dims->width || din_stride_row < dims->width ||
+      (dout_stride_row * es) % 16 || (din_stride_row * es) % 16) {
+    set_error("rmsnorm backward: pointers must be 16-byte aligned, strides multiples of 16 bytes");
+    return SSD_ERR_BAD_ALIGNMENT;
+  }
+  const int nblk = norm_blocks(dims);
+  float* partial = nullptr;
+  if (dweight) {
+    const size_t need = (size_t)nblk * dims->width * sizeof(float);
+    if (!workspace || workspace_bytes < need) { set_error("rmsnorm backward: workspace too small: %zu < %zu", workspace_bytes, need); return SSD_ERR_WORKSPACE_TOO_SMALL; }
+    partial = (float*)workspace;
+  }
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  const int nvl = (dims->width / 8 + 31) / 32;
+#define NORM_BWD(T, NV) k_rmsnorm_bwd<T, NV><<<nblk, NORM_THREADS, 0, s>>>(*dims, (const T*)in, weight, rstd, (const T*)dout, dout_stride_row, (T*)din, din_stride_row, partial)
+#define NORM_BWD_T(T) do { if (nvl <= 1) NORM_BWD(T, 1); else if (nvl <= 2) NORM_BWD(T, 2); else if (nvl <= 4) NORM_BWD(T, 4); else NORM_BWD(T, 8); } while (0)
+  if (dims->dtype == SSD_BF16) NORM_BWD_T(__nv_bfloat16); else NORM_BWD_T(float);
+#undef NORM_BWD_T
+#undef NORM_BWD
+  SSD_CUDA_CHECK_LAUNCH("rmsnorm_bwd");
+  if (dweight) {
+    k_norm_reduce<<<(dims->width + 255) / 256, 256, 0, s>>>(nblk, dims->width, partial, dweight);
+    SSD_CUDA_CHECK_LAUNCH("rmsnorm_reduce");
+  }
+  return SSD_OK;
+}
+
+}  // extern "C"

@@ -83,13 +83,14 @@ struct DySrc {
 };
 
 // ---------------------------------------------------------------------------------------------
-// Stage 1: cs = inclusive within-chunk cumsum of dt*A (fp32), dtf = dt as fp32, both [B,H,nc,Q].
+// Stage 1: cs = inclusive within-chunk cumsum of dt*A (fp32), dtf = dt as fp32, both [B,H,nc,Q]; dt here is the
+// step size after the optional bias / softplus, which every later stage reads from dtf or the decay tables.
 // One block per (chunk, batch): thread q reads the H contiguous dt values of position q once and
 // the block scans 8 heads at a time with warp shuffles.
 template <typename T>
-__global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ A,
-                                               float* __restrict__ cs, float* __restrict__ dtf,
-                                               float* __restrict__ tab) {
+__global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ dt_bias,
+                                               const float* __restrict__ A, float* __restrict__ cs,
+                                               float* __restrict__ dtf, float* __restrict__ tab) {
   constexpr int HG = 8;
   const int c = blockIdx.x, b = blockIdx.y, q = threadIdx.x;
   __shared__ float wsum[NT / 32][HG];
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
 #pragma unroll
     for (int k = 0; k < HG; ++k) {
       const int h = h0 + k;
-      d[k] = (live && h < g.H) ? ldf(row + h) : 0.f;
+      d[k] = (live && h < g.H) ? dt_activation(ldf(row + h), dt_bias ? dt_bias[h] : 0.f, g.dt_softplus) : 0.f;
       v[k] = (h < g.H) ? d[k] * A[h] : 0.f;
     }
 #pragma unroll
@@ -583,7 +584,8 @@ __global__ void __launch_bounds__(NT) k_sdot(Geo g, const float* __restrict__ dS
 }
 
 // ---------------------------------------------------------------------------------------------
-// Backward: da_k = sum_{i>=k in chunk}(dcsp_i - dt_i*ddtd_i) + sdot ; ddt_k = ddtd_k + A*da_k ;
+// Backward: da_k = sum_{i>=k in chunk}(dcsp_i - dt_i*ddtd_i) + sdot ; ddt_k = ddtd_k + A*da_k (times the derivative
+// of the step-size activation when dt_softplus is set) ;
 // per-chunk partial sums for dA (= sum dt*da) and dD (= sum ddot).  One block per (chunk, batch),
 // 8 heads at a time; sdot arrives as `nw` partial sums per (batch, chunk, head), added in fixed order.
 __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, const float* __restrict__ dtf,
@@ -640,7 +642,9 @@ __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, 
       for (int i = 0; i < w; ++i) base += wsum[i][k];
       const float da = v[k] + base + ssd[k];
       s1[k] = ok ? d[k] * da : 0.f;
-      v[k] = dd[k] + ((h0 + k < g.H) ? A[h0 + k] : 0.f) * da;   // ddt of this position
+      v[k] = dd[k] + ((h0 + k < g.H) ? A[h0 + k] : 0.f) * da;   // gradient w.r.t. the step size of this position
+      // ... and through softplus to the dt that was passed in: softplus'(r) = sigmoid(r) = 1 - exp(-softplus(r))
+      if (g.dt_softplus) v[k] *= 1.f - __expf(-d[k]);
     }
     if (ok && t < g.L) {
       float* o = ddt + ((size_t)b * g.L + t) * g.H + h0;
@@ -673,6 +677,23 @@ __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, 
       ddpart[(size_t)(b * g.nc + c) * g.H + h0 + q] = a2;
     }
     __syncthreads();
+  }
+}
+
+// ddt_bias[h] = sum over (b,t) of ddt[b,t,h].  One block per head, fixed summation order.
+__global__ void __launch_bounds__(NT) k_sum_ddt(long long rows, int H, const float* __restrict__ ddt, float* __restrict__ out) {
+  const int h = blockIdx.x;
+  float a = 0.f;
+  for (long long r = threadIdx.x; r < rows; r += NT) a += ddt[r * H + h];
+  __shared__ float r1[NT / 32];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+  if ((threadIdx.x & 31) == 0) r1[threadIdx.x >> 5] = a;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < NT / 32; ++i) t += r1[i];
+    out[h] = t;
   }
 }
 
@@ -722,7 +743,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   if (stages & SSD_STAGE_LOCAL) {
     cudaMemsetAsync(status, 0, 256, s);
-    k_cumsum<T><<<dim3(g.nc, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.A, cs, dtf, tc ? tab : nullptr);
+    k_cumsum<T><<<dim3(g.nc, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
     if (tc) {
       int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, states, status, s);
@@ -804,7 +825,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   if (stages & SSD_STAGE_LOCAL) {
     if (!p.fwd_saved) {
       SsdFwdPtrs f{};
-      f.x = p.x; f.dt = p.dt; f.A = p.A; f.Bm = p.Bm; f.Cm = p.Cm; f.D = p.D; f.z = p.z;
+      f.x = p.x; f.dt = p.dt; f.A = p.A; f.Bm = p.Bm; f.Cm = p.Cm; f.D = p.D; f.z = p.z; f.dt_bias = p.dt_bias;
       f.init_state = p.init_state; f.y = nullptr; f.final_state = fin;
       int rc = fwd_stages_t<T>(g, tc, f, ws, w, s, SSD_STAGE_LOCAL | SSD_STAGE_FINISH, false);
       if (rc) return rc;
@@ -877,6 +898,10 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
     SSD_CUDA_CHECK_LAUNCH("ddt");
     k_reduce_heads<<<g.H, NT, 0, s>>>(g.B * g.nc, g.H, dapart, ddpart, p.dA, p.dD);
     SSD_CUDA_CHECK_LAUNCH("reduce_heads");
+    if (p.ddt_bias) {
+      k_sum_ddt<<<g.H, NT, 0, s>>>((long long)g.B * g.L, g.H, p.ddt, p.ddt_bias);
+      SSD_CUDA_CHECK_LAUNCH("sum_ddt");
+    }
   }
   return SSD_OK;
 }

@@ -49,7 +49,7 @@ def _check_dense_f32(name, t, shape, device):
     _need(t.device == device and t.is_contiguous(), f"{name}: must be a contiguous tensor on {device}")
 
 
-def make_dims(x, dt, Bm, Cm, chunk, *, z=None, y=None, algo="auto") -> L.SsdDims:
+def make_dims(x, dt, Bm, Cm, chunk, *, z=None, y=None, algo="auto", dt_softplus=False) -> L.SsdDims:
     """Validate the sequence operands and fill the geometry struct."""
     _need(x.is_cuda, "x must be a CUDA tensor (there is no CPU path)")
     _need(x.dim() == 4, "x must be [batch, seqlen, nheads, headdim]")
@@ -68,6 +68,7 @@ def make_dims(x, dt, Bm, Cm, chunk, *, z=None, y=None, algo="auto") -> L.SsdDims
     d.batch, d.seqlen, d.nheads, d.headdim, d.dstate, d.ngroups, d.chunk = Bn, Ln, H, P, N, G, chunk
     d.dtype, d.algo, d.device = _DT[x.dtype], ALGOS[algo], dev.index if dev.index is not None else torch.cuda.current_device()
     d.has_z = 0 if z is None else 1
+    d.dt_softplus = 1 if dt_softplus else 0
     d.x_stride_b, d.x_stride_l = x.stride(0), x.stride(1)
     d.dt_stride_b, d.dt_stride_l = dt.stride(0), dt.stride(1)
     d.b_stride_b, d.b_stride_l = Bm.stride(0), Bm.stride(1)
@@ -93,17 +94,21 @@ def alloc_workspace(dims: L.SsdDims, device, backward: bool = False) -> torch.Te
 
 
 def forward(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk, algo="auto", workspace=None,
-            y=None, final_state=None, return_final_state=True, for_backward=False, stages=None):
-    """y, final_state, workspace = SSD(x, dt, A, B, C, D, z, init_state)."""
+            y=None, final_state=None, return_final_state=True, for_backward=False, stages=None,
+            dt_bias=None, dt_softplus=False):
+    """y, final_state, workspace = SSD(x, dt, A, B, C, D, z, init_state).  With `dt_bias` / `dt_softplus` the step
+    size is act(dt + dt_bias), evaluated inside the cumsum kernel (the pre-activation of a Mamba-2 layer)."""
     lib = L.load()
     dev = x.device
     if y is None:
         y = torch.empty_like(x, memory_format=torch.contiguous_format)
-    d = make_dims(x, dt, Bm, Cm, chunk, z=z, y=y, algo=algo)
+    d = make_dims(x, dt, Bm, Cm, chunk, z=z, y=y, algo=algo, dt_softplus=dt_softplus)
     H, P, N = d.nheads, d.headdim, d.dstate
     _check_dense_f32("A", A, (H,), dev)
     if D is not None:
         _check_dense_f32("D", D, (H,), dev)
+    if dt_bias is not None:
+        _check_dense_f32("dt_bias", dt_bias, (H,), dev)
     if init_state is not None:
         _check_dense_f32("init_state", init_state, (d.batch, H, P, N), dev)
     if final_state is None and return_final_state:
@@ -113,7 +118,7 @@ def forward(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk, algo="a
     if workspace is None:
         workspace = alloc_workspace(d, dev, backward=for_backward)
     p = L.SsdFwdPtrs(_ptr(x), _ptr(dt), _ptr(A), _ptr(Bm), _ptr(Cm), _ptr(D), _ptr(z), _ptr(init_state),
-                     _ptr(y), _ptr(final_state))
+                     _ptr(y), _ptr(final_state), _ptr(dt_bias))
     with torch.cuda.device(dev):
         if stages is None:
             rc = lib.ssd_forward(C.byref(d), C.byref(p), _ptr(workspace), workspace.numel(), _stream(dev))
@@ -124,11 +129,13 @@ def forward(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk, algo="a
 
 
 def backward(dy, x, dt, A, Bm, Cm, D=None, z=None, init_state=None, dfinal_state=None, *, chunk, algo="auto",
-             workspace=None, fwd_saved=False, want_dinit=False, stages=None, out=None):
-    """Gradients of `forward`.  Returns a dict with dx, ddt, dA, dB, dC, dD, dz, dinit."""
+             workspace=None, fwd_saved=False, want_dinit=False, stages=None, out=None, dt_bias=None,
+             dt_softplus=False):
+    """Gradients of `forward`.  Returns a dict with dx, ddt, dA, dB, dC, dD, dz, dinit (and ddt_bias when dt_bias is
+    given; ddt is then the gradient w.r.t. the dt passed in, before bias and activation)."""
     lib = L.load()
     dev = x.device
-    d = make_dims(x, dt, Bm, Cm, chunk, z=z, y=dy, algo=algo)
+    d = make_dims(x, dt, Bm, Cm, chunk, z=z, y=dy, algo=algo, dt_softplus=dt_softplus)
     Bn, Ln, H, P, N, G = d.batch, d.seqlen, d.nheads, d.headdim, d.dstate, d.ngroups
     _check_dense_f32("A", A, (H,), dev)
     if D is not None:
@@ -149,13 +156,16 @@ def backward(dy, x, dt, A, Bm, Cm, D=None, z=None, init_state=None, dfinal_state
         o.setdefault("dz", torch.empty(Bn, Ln, H, P, dtype=x.dtype, device=dev))
     if want_dinit or init_state is not None:
         o.setdefault("dinit", torch.empty(Bn, H, P, N, dtype=torch.float32, device=dev))
+    if dt_bias is not None:
+        _check_dense_f32("dt_bias", dt_bias, (H,), dev)
+        o.setdefault("ddt_bias", torch.empty(H, dtype=torch.float32, device=dev))
     if workspace is None:
         _need(not fwd_saved, "fwd_saved=True needs the workspace the forward ran in")
         workspace = alloc_workspace(d, dev, backward=True)
     p = L.SsdBwdPtrs(_ptr(x), _ptr(dt), _ptr(A), _ptr(Bm), _ptr(Cm), _ptr(D), _ptr(z), _ptr(init_state),
                      _ptr(dy), _ptr(dfinal_state), _ptr(o["dx"]), _ptr(o["ddt"]), _ptr(o["dA"]), _ptr(o["dB"]),
                      _ptr(o["dC"]), _ptr(o.get("dD")), _ptr(o.get("dz")), _ptr(o.get("dinit")),
-                     1 if fwd_saved else 0)
+                     1 if fwd_saved else 0, _ptr(dt_bias), _ptr(o.get("ddt_bias")))
     with torch.cuda.device(dev):
         if stages is None:
             rc = lib.ssd_backward(C.byref(d), C.byref(p), _ptr(workspace), workspace.numel(), _stream(dev))
@@ -166,8 +176,9 @@ def backward(dy, x, dt, A, Bm, Cm, D=None, z=None, init_state=None, dfinal_state
     return o
 
 
-def state_update(state, x, dt, A, Bm, Cm, D=None, z=None, *, y=None):
-    """One timestep over all streams, IN PLACE on `state` [S,H,P,N] fp32.  Returns y [S,H,P]."""
+def state_update(state, x, dt, A, Bm, Cm, D=None, z=None, *, y=None, dt_bias=None, dt_softplus=False):
+    """One timestep over all streams, IN PLACE on `state` [S,H,P,N] fp32.  Returns y [S,H,P].  The step size is
+    act(dt + dt_bias) as in `forward`."""
     lib = L.load()
     _need(state.is_cuda, "state must be a CUDA tensor (there is no CPU path)")
     dev = state.device
@@ -189,12 +200,16 @@ def state_update(state, x, dt, A, Bm, Cm, D=None, z=None, *, y=None):
     d = L.SsdStepDims()
     d.streams, d.nheads, d.headdim, d.dstate, d.ngroups = S, H, P, N, G
     d.dtype, d.device = _DT[x.dtype], dev.index if dev.index is not None else torch.cuda.current_device()
+    d.dt_softplus = 1 if dt_softplus else 0
+    if dt_bias is not None:
+        _check_dense_f32("dt_bias", dt_bias, (H,), dev)
     d.x_stride_s, d.dt_stride_s, d.b_stride_s, d.c_stride_s, d.y_stride_s = (
         x.stride(0), dt.stride(0), Bm.stride(0), Cm.stride(0), y.stride(0))
     if z is not None:
         _need(tuple(z.shape) == (S, H, P) and z.dtype == x.dtype and z.device == dev, "z: expected x's shape/dtype/device")
         d.z_stride_s = z.stride(0)
-    p = L.SsdStepPtrs(_ptr(state), _ptr(x), _ptr(dt), _ptr(A), _ptr(Bm), _ptr(Cm), _ptr(D), _ptr(z), _ptr(y))
+    p = L.SsdStepPtrs(_ptr(state), _ptr(x), _ptr(dt), _ptr(A), _ptr(Bm), _ptr(Cm), _ptr(D), _ptr(z), _ptr(y),
+                      _ptr(dt_bias))
     with torch.cuda.device(dev):
         L.check(lib.ssd_state_update(C.byref(d), C.byref(p), _stream(dev)))
     return y
@@ -202,24 +217,27 @@ def state_update(state, x, dt, A, Bm, Cm, D=None, z=None, *, y=None):
 
 class _SsdScan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dt, A, Bm, Cm, D, z, init_state, chunk, algo):
-        y, fin, ws = forward(x, dt, A, Bm, Cm, D, z, init_state, chunk=chunk, algo=algo, for_backward=True)
-        ctx.save_for_backward(x, dt, A, Bm, Cm, D, z, init_state, ws)
-        ctx.chunk, ctx.algo = chunk, algo
+    def forward(ctx, x, dt, A, Bm, Cm, D, z, init_state, chunk, algo, dt_bias, dt_softplus):
+        y, fin, ws = forward(x, dt, A, Bm, Cm, D, z, init_state, chunk=chunk, algo=algo, for_backward=True,
+                             dt_bias=dt_bias, dt_softplus=dt_softplus)
+        ctx.save_for_backward(x, dt, A, Bm, Cm, D, z, init_state, ws, dt_bias)
+        ctx.chunk, ctx.algo, ctx.dt_softplus = chunk, algo, dt_softplus
         return y, fin
 
     @staticmethod
     def backward(ctx, dy, dfin):
-        x, dt, A, Bm, Cm, D, z, init_state, ws = ctx.saved_tensors
+        x, dt, A, Bm, Cm, D, z, init_state, ws, dt_bias = ctx.saved_tensors
         if dy.stride(-1) != 1 or dy.stride(2) != dy.shape[3]:
             dy = dy.contiguous()
         g = backward(dy, x, dt, A, Bm, Cm, D, z, init_state,
                      None if dfin is None else dfin.contiguous(), chunk=ctx.chunk, algo=ctx.algo,
-                     workspace=ws, fwd_saved=True, want_dinit=init_state is not None)
+                     workspace=ws, fwd_saved=True, want_dinit=init_state is not None, dt_bias=dt_bias,
+                     dt_softplus=ctx.dt_softplus)
         return (g["dx"], g["ddt"].to(dt.dtype), g["dA"], g["dB"], g["dC"], g.get("dD"), g.get("dz"),
-                g.get("dinit"), None, None)
+                g.get("dinit"), None, None, g.get("ddt_bias"), None)
 
 
-def ssd_scan(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk=128, algo="auto"):
+def ssd_scan(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk=128, algo="auto", dt_bias=None,
+             dt_softplus=False):
     """Differentiable SSD: returns (y, final_state)."""
-    return _SsdScan.apply(x, dt, A, Bm, Cm, D, z, init_state, chunk, algo)
+    return _SsdScan.apply(x, dt, A, Bm, Cm, D, z, init_state, chunk, algo, dt_bias, dt_softplus)
