@@ -498,13 +498,80 @@ def run_decode(args, c, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
+def run_mixer_ops(args, c, rank, world, local):
+    """The bandwidth-bound operators either side of the scan (conv1d + silu over the x|B|C channels, RMS norm of the gated
+    output), forward and backward, at the cfg1 layer shapes.  A step = the four kernels once over the whole batch."""
+    import trading_bot_0_b200  # noqa: F401  (fails loudly without the CUDA library)
+    from trading_bot_0_b200 import _lib, prepost as PP
+    dev = torch.device("cuda", local)
+    B, L, H, P, N, G = c["B"], c["L"], c["H"], c["P"], c["N"], c["G"]
+    hp, gn = H * P, G * N
+    Cn = hp + 2 * gn
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    r = lambda *s: torch.randn(*s, generator=g, device=dev)
+    xBC, dout_c = r(B, L, Cn).bfloat16(), r(B, L, Cn).bfloat16()
+    cw, cb = r(Cn, 4) / 2, 0.1 * r(Cn)
+    yg, dout_n, nw = r(B, L, hp).bfloat16(), r(B, L, hp).bfloat16(), 1.0 + 0.1 * r(hp)
+    segs = [t.contiguous() for t in dout_c.split((hp, gn, gn), dim=2)]
+    _, rstd = PP.rmsnorm_forward(yg, nw)
+    ops = {"conv1d_fwd": (lambda: PP.conv1d_forward(xBC, cw, cb), 2 * Cn * 2),
+           "conv1d_bwd": (lambda: PP.conv1d_backward(xBC, cw, cb, segs), 3 * Cn * 2),
+           "rmsnorm_fwd": (lambda: PP.rmsnorm_forward(yg, nw), 2 * hp * 2 + 4),
+           "rmsnorm_bwd": (lambda: PP.rmsnorm_backward(yg, nw, rstd, dout_n), 3 * hp * 2 + 4)}
+    step = lambda: [f() for f, _ in ops.values()]
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = _lib.launch_count()
+    ms_step = timed(step, args.steps, world, dev) / args.steps
+    launches = _lib.launch_count() - n0
+    clocks = sampler.stop() if rank == 0 else None
+    per = {k: timed(f, args.steps, world, dev) / args.steps for k, (f, _) in ops.items()}
+    if rank != 0:
+        return
+    peak, peak_kind = peaks()
+    tokens = B * L
+    kern = {k: {"avg_ms": per[k], "algorithmic_bytes_per_token": ops[k][1],
+                "achieved_GBps": ops[k][1] * tokens / (per[k] * 1e-3) / 1e9,
+                "frac": ops[k][1] * tokens / (per[k] * 1e-3) / 1e9 / peak} for k in ops}
+    dom = max(per, key=per.get)
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        import time as _t
+        from oracle import ssd_oracle as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        sb = 16
+        hx, hy = xBC[:sb].float().cpu(), yg[:sb].float().cpu()
+        hw, hb, hn = cw.cpu(), cb.cpu(), nw.cpu()
+        t0 = _t.perf_counter()
+        for t_, fn in ((hx, lambda a: O.causal_conv1d_ref(a, hw, hb, True, torch.float32)), (hy, lambda a: O.rmsnorm_ref(a, hn, 1e-5, torch.float32))):
+            a = t_.clone().requires_grad_(True)
+            fn(a).sum().backward()
+        dt_s = _t.perf_counter() - t0
+        cpu = {"value": sb * L / dt_s, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"batch {sb} of {B}, the four operators through torch CPU ops in fp32, {dt_s:.2f} s"}
+    line = {"metric": "mixer_pre_post_ops_tokens_per_s", "value": world * tokens / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"mixer_ops at cfg1 shapes: B{B} L{L}, conv1d width 4 + silu over {Cn} channels, RMS norm over {hp} features, forward + backward per GPU",
+                       "l2": f"{tokens * 2 * Cn * 2 / 1e6:.0f} MB moved by the smallest kernel, larger than the 126 MB L2",
+                       "parallelism": f"batch-sharded x{world}, no collective"},
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["achieved_GBps"], "peak": peak, "unit": "GB/s",
+                         "frac": kern[dom]["frac"], "peak_kind": peak_kind, "traffic": None, "avg_launch_ms": per[dom]},
+            "kernels": kern, "cpu_baseline": cpu, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=sorted(CFGS))
+    ap.add_argument("--workload", default="cfg1", choices=sorted(CFGS) + ["mixer_ops"],
+                    help="cfg1..cfg4 as in BASELINE.json; mixer_ops: the conv1d / RMS-norm kernels either side of the scan at cfg1 shapes")
     ap.add_argument("--algo", default="auto", choices=["auto", "fp32_cores", "tensor"])
     ap.add_argument("--ring", type=int, default=64, help="cfg2: distinct pre-drawn steps kept in HBM")
     ap.add_argument("--strong", action="store_true", help="cfg4: label the run strong scaling (fixed global L)")
@@ -514,7 +581,7 @@ def main():
     ap.add_argument("--profile-mode", action="store_true",
                     help="for captures under a profiler: exactly --warmup warm-ups, no per-kernel event pass, no CPU/e2e legs")
     args = ap.parse_args()
-    c = dict(CFGS[args.workload])
+    c = dict(CFGS["cfg1" if args.workload == "mixer_ops" else args.workload])
     if args.batch:
         c["B"] = args.batch
     if args.profile_mode:
@@ -526,6 +593,8 @@ def main():
     try:
         if args.workload == "cfg2":
             run_decode(args, c, rank, world, local)
+        elif args.workload == "mixer_ops":
+            run_mixer_ops(args, c, rank, world, local)
         else:
             run_train(args, c, rank, world, local)
     finally:
