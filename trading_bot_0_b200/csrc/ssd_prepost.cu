@@ -2,7 +2,7 @@
 //   before:  out = act(causal depthwise conv1d(in) + bias) over the (x | B | C) channels, act = silu or identity
 //   after :  out = in * rsqrt(mean(in^2) + eps) * weight   (RMS norm of the gated scan output, weight optional)
 // each with its backward.  Every tensor is read once and written once (the conv backward re-reads a
-// (width-1)-row halo per 64-token tile); arithmetic is fp32, storage bf16 or fp32, 16-byte accesses.
+// (width-1)-row halo per 32-token tile); arithmetic is fp32, storage bf16 or fp32, 16-byte accesses.
 // Reductions over tokens (dweight, dbias) are two-stage with a fixed summation order.
 //
 // The step-size activation softplus(dt + dt_bias) and the gate y*silu(z) need no kernel here: they are
@@ -42,20 +42,55 @@ template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-constexpr int CONV_THREADS = 128;   // 128 channel vectors (8 channels each) per block
-constexpr int CONV_TL = 64;         // tokens per tile
+// 8 storage elements as loaded (kept raw so that several rows can be in flight in few registers)
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> { uint4 v; };
+template <> struct Raw8<float> { float4 a, b; };
+__device__ __forceinline__ void load_raw(const __nv_bfloat16* p, Raw8<__nv_bfloat16>& r) { r.v = __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void load_raw(const float* p, Raw8<float>& r) {
+  r.a = __ldg(reinterpret_cast<const float4*>(p)); r.b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+}
+__device__ __forceinline__ void unpack_raw(const Raw8<__nv_bfloat16>& r, float (&v)[8]) {
+  const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void unpack_raw(const Raw8<float>& r, float (&v)[8]) {
+  v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+}
+
+// sigmoid for the silu: one tanh.approx (relative error 2^-11, below bf16 resolution) for bf16 storage, exp + fast
+// division for fp32 storage
+template <typename T> __device__ __forceinline__ float sig_(float a);
+template <> __device__ __forceinline__ float sig_<__nv_bfloat16>(float a) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * a));
+  return fmaf(0.5f, t, 0.5f);
+}
+template <> __device__ __forceinline__ float sig_<float>(float a) { return __fdividef(1.f, 1.f + __expf(-a)); }
+
+constexpr int CONV_THREADS = 128;
+constexpr int CONV_TL = 32;         // tokens per tile
+constexpr int CONV_ROWS = 2048;     // backward: thread rows (each walks several tiles and leaves one partial sum)
 
 // ---------------------------------------------------------------------------------------------
-// conv forward: thread = 8 channels, walks a tile of tokens keeping the last K-1 input rows in registers.
-// grid = (tiles, channel blocks, batch).
+// conv forward.  Work item = (batch, tile of 32 tokens, vector of 8 channels), channel vectors fastest so that a
+// warp reads contiguous pieces of a token row; the item's thread walks the tile keeping the last K-1 input rows
+// in registers, eight rows requested at a time.
 template <typename T, int K>
 __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const T* __restrict__ in,
                                                            const float* __restrict__ weight, const float* __restrict__ bias,
                                                            T* __restrict__ out) {
-  const int cv = blockIdx.y * CONV_THREADS + threadIdx.x;
+  const int CV = d.channels / 8, ntile = (d.seqlen + CONV_TL - 1) / CONV_TL;
+  const long long item = (long long)blockIdx.x * CONV_THREADS + threadIdx.x;
+  if (item >= (long long)d.batch * ntile * CV) return;
+  const int cv = (int)(item % CV);
+  const long long bt = item / CV;
+  const int b = (int)(bt / ntile), t0 = (int)(bt % ntile) * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
   const int c0 = cv * 8;
-  if (c0 >= d.channels) return;
-  const int b = blockIdx.z, t0 = blockIdx.x * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
   float w[8][K], bs[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -75,21 +110,31 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const 
       for (int j = 0; j < 8; ++j) win[k][j] = 0.f;
     }
   }
-  for (int t = t0; t < t1; ++t) {
-    load8<T>(ip + (long long)t * d.in_stride_l, win[K - 1]);
-    float o[8];
+  constexpr int CH = 8;   // rows requested together: enough bytes in flight per thread to cover the memory latency
+  for (int tc = t0; tc < t1; tc += CH) {
+    Raw8<T> raw[CH];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float a = bs[j];
+    for (int i = 0; i < CH; ++i)
+      if (tc + i < t1) load_raw(ip + (long long)(tc + i) * d.in_stride_l, raw[i]);
 #pragma unroll
-      for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
-      o[j] = d.activation ? a * sigmoidf_(a) : a;
+    for (int i = 0; i < CH; ++i) {
+      if (tc + i < t1) {
+        unpack_raw(raw[i], win[K - 1]);
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float a = bs[j];
+#pragma unroll
+          for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+          o[j] = d.activation ? a * sig_<T>(a) : a;
+        }
+        store8<T>(op + (long long)(tc + i) * d.out_stride_l, o);
+#pragma unroll
+        for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+      }
     }
-    store8<T>(op + (long long)t * d.out_stride_l, o);
-#pragma unroll
-    for (int k = 0; k < K - 1; ++k)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
   }
 }
 
@@ -98,8 +143,8 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const 
 // the input window, dpre[s] = dout[s] * act'(pre[s]) enters a second window, and
 //   din[s-K+1] = sum_j w[K-1-j] * dpre[s-K+1+j]          (complete once dpre[s] is known)
 //   dweight[k] += dpre[s] * in[s-K+1+k],  dbias += dpre[s]   (rows s of this tile only).
-// dout arrives as up to three channel segments (the scan's dx, dB, dC tensors).  Each block walks the (batch, tile)
-// pairs y, y+gridDim.x, ... and leaves one partial sum per block; k_conv_reduce adds them in block order.
+// dout arrives as up to three channel segments (the scan's dx, dB, dC tensors).  Thread = (row r, channel vector);
+// row r walks the (batch, tile) pairs r, r+rows, ... and leaves one partial sum; k_conv_reduce adds the rows in order.
 struct ConvSegs {
   const void* ptr[3];
   int c_begin[3];           // first channel of the segment; segment i covers [c_begin[i], c_begin[i+1])
@@ -108,13 +153,15 @@ struct ConvSegs {
 };
 
 template <typename T, int K>
-__global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, const T* __restrict__ in,
+__global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, int rows, const T* __restrict__ in,
                                                            const float* __restrict__ weight, const float* __restrict__ bias,
                                                            ConvSegs segs, T* __restrict__ din, long long din_stride_b,
                                                            long long din_stride_l, float* __restrict__ partial) {
-  const int cv = blockIdx.y * CONV_THREADS + threadIdx.x;
+  const int CV = d.channels / 8;
+  const long long item = (long long)blockIdx.x * CONV_THREADS + threadIdx.x;
+  if (item >= (long long)rows * CV) return;
+  const int cv = (int)(item % CV), row = (int)(item / CV);
   const int c0 = cv * 8;
-  if (c0 >= d.channels) return;
   float w[8][K], bs[8], dw[8][K], db[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -129,65 +176,79 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, const 
   const long long dosb = segs.stride_b[si], dosl = segs.stride_l[si];
 
   const int ntile = (d.seqlen + CONV_TL - 1) / CONV_TL;
-  for (int pair = blockIdx.x; pair < d.batch * ntile; pair += gridDim.x) {
+  for (int pair = row; pair < d.batch * ntile; pair += rows) {
     const int b = pair / ntile, t0 = (pair - b * ntile) * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
     const T* ip = in + (long long)b * d.in_stride_b + c0;
+    const T* gp = dop + (long long)b * dosb;
     float win[K][8], dpw[K][8];   // win[k] = in[s-K+1+k], dpw[k] = dpre[s-K+1+k]
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
       for (int j = 0; j < 8; ++j) { win[k][j] = 0.f; dpw[k][j] = 0.f; }
-    const int s_end = min(t1 + K - 1, d.seqlen + K - 1);
-    for (int s = t0 - (K - 1); s < s_end; ++s) {
-      // shift both windows, then bring in row s
+    const int s_begin = t0 - (K - 1), s_end = min(t1 + K - 1, d.seqlen + K - 1);
+    constexpr int CH = 4;     // rows of the input and of the gradient requested together
+    for (int sc = s_begin; sc < s_end; sc += CH) {
+      Raw8<T> rin[CH], rgo[CH];
 #pragma unroll
-      for (int k = 0; k < K - 1; ++k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { win[k][j] = win[k + 1][j]; dpw[k][j] = dpw[k + 1][j]; }
-      if (s >= 0 && s < d.seqlen) load8<T>(ip + (long long)s * d.in_stride_l, win[K - 1]);
-      else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) win[K - 1][j] = 0.f;
+      for (int i = 0; i < CH; ++i) {
+        const int s = sc + i;
+        if (s >= 0 && s < d.seqlen && s < s_end) load_raw(ip + (long long)s * d.in_stride_l, rin[i]);
+        if (s >= t0 && s < d.seqlen && s < s_end) load_raw(gp + (long long)s * dosl, rgo[i]);
       }
-      if (s >= t0 && s < d.seqlen) {
-        float go[8];
-        load8<T>(dop + (long long)b * dosb + (long long)s * dosl, go);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float a = bs[j];
+      for (int i = 0; i < CH; ++i) {
+        const int s = sc + i;
+        if (s >= s_end) break;
+        // shift both windows, then bring in row s
 #pragma unroll
-          for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
-          float g = go[j];
-          if (d.activation) {
-            const float sg = sigmoidf_(a);
-            g *= sg * (1.f + a * (1.f - sg));
-          }
-          dpw[K - 1][j] = g;
-          if (s < t1) {   // each row's weight / bias gradient is counted by exactly one tile
-            db[j] += g;
+        for (int k = 0; k < K - 1; ++k)
 #pragma unroll
-            for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
-          }
+          for (int j = 0; j < 8; ++j) { win[k][j] = win[k + 1][j]; dpw[k][j] = dpw[k + 1][j]; }
+        if (s >= 0 && s < d.seqlen) unpack_raw(rin[i], win[K - 1]);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) win[K - 1][j] = 0.f;
         }
-      } else {
+        if (s >= t0 && s < d.seqlen) {
+          float go[8];
+          unpack_raw(rgo[i], go);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dpw[K - 1][j] = 0.f;
-      }
-      const int t = s - (K - 1);
-      if (t >= t0 && t < t1) {
-        float o[8];
+          for (int j = 0; j < 8; ++j) {
+            float a = bs[j];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float a = 0.f;
+            for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+            float g = go[j];
+            if (d.activation) {
+              const float sg = sig_<T>(a);
+              g *= sg * (1.f + a * (1.f - sg));
+            }
+            dpw[K - 1][j] = g;
+            if (s < t1) {   // each row's weight / bias gradient is counted by exactly one tile
+              db[j] += g;
 #pragma unroll
-          for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dpw[q][j], a);
-          o[j] = a;
+              for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dpw[K - 1][j] = 0.f;
         }
-        store8<T>(din + (long long)b * din_stride_b + (long long)t * din_stride_l + c0, o);
+        const int t = s - (K - 1);
+        if (t >= t0 && t < t1) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float a = 0.f;
+#pragma unroll
+            for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dpw[q][j], a);
+            o[j] = a;
+          }
+          store8<T>(din + (long long)b * din_stride_b + (long long)t * din_stride_l + c0, o);
+        }
       }
     }
   }
-  float* pp = partial + ((size_t)blockIdx.x * d.channels + c0) * (K + 1);
+  float* pp = partial + ((size_t)row * d.channels + c0) * (K + 1);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
 #pragma unroll
@@ -333,10 +394,10 @@ __global__ void k_norm_reduce(int nblk, int width, const float* __restrict__ par
   dweight[i] = a;
 }
 
-int conv_blocks(const SsdConvDims* d) {
+int conv_rows(const SsdConvDims* d) {   // thread rows of the backward kernel = partial sums to add
   const int ntile = (d->seqlen + CONV_TL - 1) / CONV_TL;
   const long long pairs = (long long)d->batch * ntile;
-  return (int)(pairs < 296 ? pairs : 296);
+  return (int)(pairs < CONV_ROWS ? pairs : CONV_ROWS);
 }
 int norm_blocks(const SsdNormDims* d) {
   const long long need = (d->rows + NORM_THREADS / 32 - 1) / (NORM_THREADS / 32);
@@ -349,7 +410,6 @@ int check_conv(const SsdConvDims* d) {
   if (d->width < 2 || d->width > 4) { set_error("conv1d: width %d not supported (2..4)", d->width); return SSD_ERR_UNSUPPORTED; }
   if (d->channels % 8) { set_error("conv1d: channels (%d) must be a multiple of 8", d->channels); return SSD_ERR_UNSUPPORTED; }
   if (d->dtype != SSD_F32 && d->dtype != SSD_BF16) { set_error("conv1d: unknown dtype %d", d->dtype); return SSD_ERR_UNSUPPORTED; }
-  if (d->batch > 65535) { set_error("conv1d: batch must be <= 65535"); return SSD_ERR_BAD_SHAPE; }
   const int es = d->dtype == SSD_BF16 ? 2 : 4;
   const long long strides[4] = {d->in_stride_b, d->in_stride_l, d->out_stride_b, d->out_stride_l};
   for (long long st : strides)
@@ -369,7 +429,7 @@ extern "C" {
 size_t ssd_conv1d_workspace_bytes(const SsdConvDims* dims) {
   clear_error();
   if (check_conv(dims)) return 0;
-  return (size_t)conv_blocks(dims) * dims->channels * (dims->width + 1) * sizeof(float);
+  return (size_t)conv_rows(dims) * dims->channels * (dims->width + 1) * sizeof(float);
 }
 
 int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float* weight, const float* bias, void* out,
@@ -380,7 +440,8 @@ int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float*
   if (!in || !weight || !out) { set_error("conv1d: in / weight / out is NULL"); return SSD_ERR_NULL_POINTER; }
   if (!aligned16(in) || !aligned16(out)) { set_error("conv1d: in and out must be 16-byte aligned"); return SSD_ERR_BAD_ALIGNMENT; }
   cudaStream_t s = (cudaStream_t)cuda_stream;
-  const dim3 grid((dims->seqlen + CONV_TL - 1) / CONV_TL, (dims->channels / 8 + CONV_THREADS - 1) / CONV_THREADS, dims->batch);
+  const long long items = (long long)dims->batch * ((dims->seqlen + CONV_TL - 1) / CONV_TL) * (dims->channels / 8);
+  const unsigned grid = (unsigned)((items + CONV_THREADS - 1) / CONV_THREADS);
 #define CONV_FWD(T, K) k_conv_fwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, (const T*)in, weight, bias, (T*)out)
   if (dims->dtype == SSD_BF16) {
     if (dims->width == 4) CONV_FWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_FWD(__nv_bfloat16, 3); else CONV_FWD(__nv_bfloat16, 2);
@@ -423,13 +484,13 @@ int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float
     set_error("conv1d backward: in / din must be 16-byte aligned with strides that are multiples of 16 bytes");
     return SSD_ERR_BAD_ALIGNMENT;
   }
-  const int nblk = conv_blocks(dims);
+  const int nblk = conv_rows(dims);
   const size_t need = (size_t)nblk * dims->channels * (dims->width + 1) * sizeof(float);
   if (workspace_bytes < need) { set_error("conv1d backward: workspace too small: %zu < %zu", workspace_bytes, need); return SSD_ERR_WORKSPACE_TOO_SMALL; }
   cudaStream_t s = (cudaStream_t)cuda_stream;
-  const dim3 grid(nblk, (dims->channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
+  const unsigned grid = (unsigned)(((long long)nblk * (dims->channels / 8) + CONV_THREADS - 1) / CONV_THREADS);
   float* partial = (float*)workspace;
-#define CONV_BWD(T, K) k_conv_bwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial)
+#define CONV_BWD(T, K) k_conv_bwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, nblk, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial)
   if (dims->dtype == SSD_BF16) {
     if (dims->width == 4) CONV_BWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_BWD(__nv_bfloat16, 3); else CONV_BWD(__nv_bfloat16, 2);
   } else {
