@@ -42,25 +42,46 @@ template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// 8 storage elements as loaded (kept raw so that several rows can be in flight in few registers)
-template <typename T> struct Raw8;
-template <> struct Raw8<__nv_bfloat16> { uint4 v; };
-template <> struct Raw8<float> { float4 a, b; };
-__device__ __forceinline__ void load_raw(const __nv_bfloat16* p, Raw8<__nv_bfloat16>& r) { r.v = __ldg(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ void load_raw(const float* p, Raw8<float>& r) {
+// NC storage elements as loaded (kept raw so that several rows can be in flight in few registers)
+template <typename T, int NC> struct RawN;
+template <> struct RawN<__nv_bfloat16, 8> { uint4 v; };
+template <> struct RawN<__nv_bfloat16, 4> { uint2 v; };
+template <> struct RawN<float, 8> { float4 a, b; };
+template <> struct RawN<float, 4> { float4 a; };
+__device__ __forceinline__ void load_raw(const __nv_bfloat16* p, RawN<__nv_bfloat16, 8>& r) { r.v = __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void load_raw(const __nv_bfloat16* p, RawN<__nv_bfloat16, 4>& r) { r.v = __ldg(reinterpret_cast<const uint2*>(p)); }
+__device__ __forceinline__ void load_raw(const float* p, RawN<float, 8>& r) {
   r.a = __ldg(reinterpret_cast<const float4*>(p)); r.b = __ldg(reinterpret_cast<const float4*>(p) + 1);
 }
-__device__ __forceinline__ void unpack_raw(const Raw8<__nv_bfloat16>& r, float (&v)[8]) {
-  const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
-    v[2 * i] = f.x; v[2 * i + 1] = f.y;
-  }
+__device__ __forceinline__ void load_raw(const float* p, RawN<float, 4>& r) { r.a = __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float2 bf2_(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w)); }
+__device__ __forceinline__ void unpack_raw(const RawN<__nv_bfloat16, 8>& r, float (&v)[8]) {
+  const float2 a = bf2_(r.v.x), b = bf2_(r.v.y), c = bf2_(r.v.z), d = bf2_(r.v.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
 }
-__device__ __forceinline__ void unpack_raw(const Raw8<float>& r, float (&v)[8]) {
+__device__ __forceinline__ void unpack_raw(const RawN<__nv_bfloat16, 4>& r, float (&v)[4]) {
+  const float2 a = bf2_(r.v.x), b = bf2_(r.v.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void unpack_raw(const RawN<float, 8>& r, float (&v)[8]) {
   v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
 }
+__device__ __forceinline__ void unpack_raw(const RawN<float, 4>& r, float (&v)[4]) { v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; }
+__device__ __forceinline__ uint32_t bfpack_(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void store_n(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(bfpack_(v[0], v[1]), bfpack_(v[2], v[3]), bfpack_(v[4], v[5]), bfpack_(v[6], v[7]));
+}
+__device__ __forceinline__ void store_n(__nv_bfloat16* p, const float (&v)[4]) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(bfpack_(v[0], v[1]), bfpack_(v[2], v[3]));
+}
+__device__ __forceinline__ void store_n(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store_n(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
 
 // sigmoid for the silu: one tanh.approx (relative error 2^-11, below bf16 resolution) for bf16 storage, exp + fast
 // division for fp32 storage
@@ -77,42 +98,42 @@ constexpr int CONV_TL = 32;         // tokens per tile
 constexpr int CONV_ROWS = 2048;     // backward: thread rows (each walks several tiles and leaves one partial sum)
 
 // ---------------------------------------------------------------------------------------------
-// conv forward.  Work item = (batch, tile of 32 tokens, vector of 8 channels), channel vectors fastest so that a
+// conv forward.  Work item = (batch, tile of 32 tokens, vector of NC channels), channel vectors fastest so that a
 // warp reads contiguous pieces of a token row; the item's thread walks the tile keeping the last K-1 input rows
 // in registers, eight rows requested at a time.
-template <typename T, int K>
+template <typename T, int K, int NC>
 __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const T* __restrict__ in,
                                                            const float* __restrict__ weight, const float* __restrict__ bias,
                                                            T* __restrict__ out) {
-  const int CV = d.channels / 8, ntile = (d.seqlen + CONV_TL - 1) / CONV_TL;
+  const int CV = d.channels / NC, ntile = (d.seqlen + CONV_TL - 1) / CONV_TL;
   const long long item = (long long)blockIdx.x * CONV_THREADS + threadIdx.x;
   if (item >= (long long)d.batch * ntile * CV) return;
   const int cv = (int)(item % CV);
   const long long bt = item / CV;
   const int b = (int)(bt / ntile), t0 = (int)(bt % ntile) * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
-  const int c0 = cv * 8;
-  float w[8][K], bs[8];
+  const int c0 = cv * NC;
+  float w[NC][K], bs[NC];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NC; ++j) {
 #pragma unroll
     for (int k = 0; k < K; ++k) w[j][k] = __ldg(weight + (size_t)(c0 + j) * K + k);
     bs[j] = bias ? __ldg(bias + c0 + j) : 0.f;
   }
   const T* ip = in + (long long)b * d.in_stride_b + c0;
   T* op = out + (long long)b * d.out_stride_b + c0;
-  float win[K][8];   // win[k] = input row t - (K-1) + k
+  float win[K][NC];   // win[k] = input row t - (K-1) + k
 #pragma unroll
   for (int k = 0; k < K - 1; ++k) {
     const int t = t0 - (K - 1) + k;
-    if (t >= 0) load8<T>(ip + (long long)t * d.in_stride_l, win[k]);
+    if (t >= 0) { RawN<T, NC> r0; load_raw(ip + (long long)t * d.in_stride_l, r0); unpack_raw(r0, win[k]); }
     else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) win[k][j] = 0.f;
+      for (int j = 0; j < NC; ++j) win[k][j] = 0.f;
     }
   }
   constexpr int CH = 8;   // rows requested together: enough bytes in flight per thread to cover the memory latency
   for (int tc = t0; tc < t1; tc += CH) {
-    Raw8<T> raw[CH];
+    RawN<T, NC> raw[CH];
 #pragma unroll
     for (int i = 0; i < CH; ++i)
       if (tc + i < t1) load_raw(ip + (long long)(tc + i) * d.in_stride_l, raw[i]);
@@ -120,19 +141,19 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const 
     for (int i = 0; i < CH; ++i) {
       if (tc + i < t1) {
         unpack_raw(raw[i], win[K - 1]);
-        float o[8];
+        float o[NC];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < NC; ++j) {
           float a = bs[j];
 #pragma unroll
           for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
           o[j] = d.activation ? a * sig_<T>(a) : a;
         }
-        store8<T>(op + (long long)(tc + i) * d.out_stride_l, o);
+        store_n(op + (long long)(tc + i) * d.out_stride_l, o);
 #pragma unroll
         for (int k = 0; k < K - 1; ++k)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) win[k][j] = win[k + 1][j];
+          for (int j = 0; j < NC; ++j) win[k][j] = win[k + 1][j];
       }
     }
   }
@@ -152,19 +173,25 @@ struct ConvSegs {
   int n;
 };
 
-template <typename T, int K>
-__global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, int rows, const T* __restrict__ in,
+#ifndef CONV_BWD_CH
+#define CONV_BWD_CH 8
+#endif
+#ifndef CONV_BWD_MINB
+#define CONV_BWD_MINB 3
+#endif
+template <typename T, int K, int NC>
+__global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdConvDims d, int rows, const T* __restrict__ in,
                                                            const float* __restrict__ weight, const float* __restrict__ bias,
                                                            ConvSegs segs, T* __restrict__ din, long long din_stride_b,
                                                            long long din_stride_l, float* __restrict__ partial) {
-  const int CV = d.channels / 8;
+  const int CV = d.channels / NC;
   const long long item = (long long)blockIdx.x * CONV_THREADS + threadIdx.x;
   if (item >= (long long)rows * CV) return;
   const int cv = (int)(item % CV), row = (int)(item / CV);
-  const int c0 = cv * 8;
-  float w[8][K], bs[8], dw[8][K], db[8];
+  const int c0 = cv * NC;
+  float w[NC][K], bs[NC], dw[NC][K], db[NC];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NC; ++j) {
 #pragma unroll
     for (int k = 0; k < K; ++k) { w[j][k] = __ldg(weight + (size_t)(c0 + j) * K + k); dw[j][k] = 0.f; }
     bs[j] = bias ? __ldg(bias + c0 + j) : 0.f;
@@ -180,15 +207,15 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, int ro
     const int b = pair / ntile, t0 = (pair - b * ntile) * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
     const T* ip = in + (long long)b * d.in_stride_b + c0;
     const T* gp = dop + (long long)b * dosb;
-    float win[K][8], dpw[K][8];   // win[k] = in[s-K+1+k], dpw[k] = dpre[s-K+1+k]
+    float win[K][NC], dpw[K][NC];   // win[k] = in[s-K+1+k], dpw[k] = dpre[s-K+1+k]
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { win[k][j] = 0.f; dpw[k][j] = 0.f; }
+      for (int j = 0; j < NC; ++j) { win[k][j] = 0.f; dpw[k][j] = 0.f; }
     const int s_begin = t0 - (K - 1), s_end = min(t1 + K - 1, d.seqlen + K - 1);
-    constexpr int CH = 4;     // rows of the input and of the gradient requested together
+    constexpr int CH = CONV_BWD_CH;     // rows of the input and of the gradient requested together
     for (int sc = s_begin; sc < s_end; sc += CH) {
-      Raw8<T> rin[CH], rgo[CH];
+      RawN<T, NC> rin[CH], rgo[CH];
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int s = sc + i;
@@ -203,17 +230,17 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, int ro
 #pragma unroll
         for (int k = 0; k < K - 1; ++k)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) { win[k][j] = win[k + 1][j]; dpw[k][j] = dpw[k + 1][j]; }
+          for (int j = 0; j < NC; ++j) { win[k][j] = win[k + 1][j]; dpw[k][j] = dpw[k + 1][j]; }
         if (s >= 0 && s < d.seqlen) unpack_raw(rin[i], win[K - 1]);
         else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) win[K - 1][j] = 0.f;
+          for (int j = 0; j < NC; ++j) win[K - 1][j] = 0.f;
         }
         if (s >= t0 && s < d.seqlen) {
-          float go[8];
+          float go[NC];
           unpack_raw(rgo[i], go);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < NC; ++j) {
             float a = bs[j];
 #pragma unroll
             for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
@@ -231,26 +258,26 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_bwd(SsdConvDims d, int ro
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dpw[K - 1][j] = 0.f;
+          for (int j = 0; j < NC; ++j) dpw[K - 1][j] = 0.f;
         }
         const int t = s - (K - 1);
         if (t >= t0 && t < t1) {
-          float o[8];
+          float o[NC];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < NC; ++j) {
             float a = 0.f;
 #pragma unroll
             for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dpw[q][j], a);
             o[j] = a;
           }
-          store8<T>(din + (long long)b * din_stride_b + (long long)t * din_stride_l + c0, o);
+          store_n(din + (long long)b * din_stride_b + (long long)t * din_stride_l + c0, o);
         }
       }
     }
   }
   float* pp = partial + ((size_t)row * d.channels + c0) * (K + 1);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < NC; ++j) {
 #pragma unroll
     for (int k = 0; k < K; ++k) pp[j * (K + 1) + k] = dw[j][k];
     pp[j * (K + 1) + K] = db[j];
@@ -440,9 +467,10 @@ int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float*
   if (!in || !weight || !out) { set_error("conv1d: in / weight / out is NULL"); return SSD_ERR_NULL_POINTER; }
   if (!aligned16(in) || !aligned16(out)) { set_error("conv1d: in and out must be 16-byte aligned"); return SSD_ERR_BAD_ALIGNMENT; }
   cudaStream_t s = (cudaStream_t)cuda_stream;
-  const long long items = (long long)dims->batch * ((dims->seqlen + CONV_TL - 1) / CONV_TL) * (dims->channels / 8);
+  constexpr int NCF = 8;   // channels per thread, forward
+  const long long items = (long long)dims->batch * ((dims->seqlen + CONV_TL - 1) / CONV_TL) * (dims->channels / NCF);
   const unsigned grid = (unsigned)((items + CONV_THREADS - 1) / CONV_THREADS);
-#define CONV_FWD(T, K) k_conv_fwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, (const T*)in, weight, bias, (T*)out)
+#define CONV_FWD(T, K) k_conv_fwd<T, K, NCF><<<grid, CONV_THREADS, 0, s>>>(*dims, (const T*)in, weight, bias, (T*)out)
   if (dims->dtype == SSD_BF16) {
     if (dims->width == 4) CONV_FWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_FWD(__nv_bfloat16, 3); else CONV_FWD(__nv_bfloat16, 2);
   } else {
@@ -488,9 +516,10 @@ int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float
   const size_t need = (size_t)nblk * dims->channels * (dims->width + 1) * sizeof(float);
   if (workspace_bytes < need) { set_error("conv1d backward: workspace too small: %zu < %zu", workspace_bytes, need); return SSD_ERR_WORKSPACE_TOO_SMALL; }
   cudaStream_t s = (cudaStream_t)cuda_stream;
-  const unsigned grid = (unsigned)(((long long)nblk * (dims->channels / 8) + CONV_THREADS - 1) / CONV_THREADS);
+  constexpr int NCB = 4;   // channels per thread, backward (half the registers of 8: twice the resident warps)
+  const unsigned grid = (unsigned)(((long long)nblk * (dims->channels / NCB) + CONV_THREADS - 1) / CONV_THREADS);
   float* partial = (float*)workspace;
-#define CONV_BWD(T, K) k_conv_bwd<T, K><<<grid, CONV_THREADS, 0, s>>>(*dims, nblk, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial)
+#define CONV_BWD(T, K) k_conv_bwd<T, K, NCB><<<grid, CONV_THREADS, 0, s>>>(*dims, nblk, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial)
   if (dims->dtype == SSD_BF16) {
     if (dims->width == 4) CONV_BWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_BWD(__nv_bfloat16, 3); else CONV_BWD(__nv_bfloat16, 2);
   } else {
