@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
   constexpr int NB = N / 64;       // 64-column boxes of the B/C tile
   constexpr int HT = 128 / P;      // heads per 128-row accumulator
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sB = smem;                          // NB boxes
   uint8_t* sX = smem + NB * BOX_BYTES;         // 2 boxes: the x tile, scaled in place (high bf16 part)
   uint8_t* sL = sX + 2 * BOX_BYTES;            // 2 boxes: low bf16 part of the scaled tile
@@ -434,7 +434,7 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   constexpr int IN_BYTES = NBOX * BOX_BYTES + NB * SBOX_BYTES + HB * TAB_BYTES;
   constexpr uint32_t TM_COLS = 256;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sKeep = smem;                       // NB boxes kept for the whole CTA: C (modes 0,1) or B (mode 2)
   uint8_t* sBM = sKeep + NB * BOX_BYTES;       // the other tile (NB boxes), later the 32 KB M_h tile
   uint8_t* sIn = sBM + 2 * BOX_BYTES;          // IBUF x {x [, dy], state boxes, tables}
@@ -663,7 +663,7 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   constexpr int HB = 64 / P;
   constexpr uint32_t TM_COLS = (128 + 2 * N <= 256) ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sB = smem;                          // NB boxes
   uint8_t* sC = sB + NB * BOX_BYTES;           // NB boxes
   uint8_t* sM = sC + NB * BOX_BYTES;           // 32 KB W'_h tile, plain layout
@@ -903,7 +903,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   using Cfg = WsCfg<P, MODE>;
   constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM, NTH = Cfg::NTH;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sCB = smem;                                   // 2 x {keep tile, other tile}
   uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
   uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x [, dy], state box}
@@ -1262,7 +1262,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   using Cfg = BwCfg<P>;
   constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sCB = smem;                                   // 2 x {C tile, B tile}
   uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
   uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x box, dy box}
@@ -1573,7 +1573,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   using Cfg = DbCfg<P>;
   constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sCB = smem;                                   // 2 x {B tile, C tile}
   uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB W'_h tiles
   uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x box, dy box}
