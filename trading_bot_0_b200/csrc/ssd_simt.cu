@@ -598,18 +598,18 @@ __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, 
   __shared__ float wsum[NT / 32][HG], red1[NT / 32][HG], red2[NT / 32][HG], ssd[HG];
   const int qr = g.Q - 1 - q;   // reversed position: an inclusive prefix scan over q is a suffix sum over qr
   const bool ok = (q < g.Q);
-  const int lane = q & 31, w = q >> 5;
+  const int lane = q & 31, w = q >> 5, nwarp = blockDim.x >> 5;   // launched with 128 threads when the chunk is <= 128 long
   const int t = c * g.Q + qr;
   for (int h0 = 0; h0 < g.H; h0 += HG) {
-    if (w < HG) {   // warp w adds the partial sums of head h0 + w (fixed order: lane-strided, then a butterfly)
+    for (int hh = w; hh < HG; hh += nwarp) {   // a warp adds the partial sums of head h0 + hh (fixed order: lane-strided, then a butterfly)
       float s = 0.f;
-      if (h0 + w < g.H) {
-        const float* sp = sdot + ((size_t)(b * g.nc + c) * g.H + h0 + w) * nw;
+      if (h0 + hh < g.H) {
+        const float* sp = sdot + ((size_t)(b * g.nc + c) * g.H + h0 + hh) * nw;
         for (int i = lane; i < nw; i += 32) s += sp[i];
       }
 #pragma unroll
       for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (lane == 0) ssd[w] = s;
+      if (lane == 0) ssd[hh] = s;
     }
     float d[HG], dd[HG], v[HG], s2[HG];
 #pragma unroll
@@ -672,7 +672,7 @@ __global__ void __launch_bounds__(NT) k_ddt(Geo g, const float* __restrict__ A, 
     __syncthreads();
     if (q < HG && h0 + q < g.H) {
       float a1 = 0.f, a2 = 0.f;
-      for (int i = 0; i < NT / 32; ++i) { a1 += red1[i][q]; a2 += red2[i][q]; }
+      for (int i = 0; i < nwarp; ++i) { a1 += red1[i][q]; a2 += red2[i][q]; }
       dapart[(size_t)(b * g.nc + c) * g.H + h0 + q] = a1;
       ddpart[(size_t)(b * g.nc + c) * g.H + h0 + q] = a2;
     }
@@ -743,7 +743,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   if (stages & SSD_STAGE_LOCAL) {
     cudaMemsetAsync(status, 0, 256, s);
-    k_cumsum<T><<<dim3(g.nc, g.B), NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr);
+    k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
     if (tc) {
       int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, states, status, s);
@@ -894,7 +894,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
                                                                  cb, dst, (T*)p.dB);
       SSD_CUDA_CHECK_LAUNCH("dB");
     }
-    k_ddt<<<dim3(g.nc, g.B), NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, sdot_nw, p.ddt, dapart, ddpart);
+    k_ddt<<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, sdot_nw, p.ddt, dapart, ddpart);
     SSD_CUDA_CHECK_LAUNCH("ddt");
     k_reduce_heads<<<g.H, NT, 0, s>>>(g.B * g.nc, g.H, dapart, ddpart, p.dA, p.dD);
     SSD_CUDA_CHECK_LAUNCH("reduce_heads");

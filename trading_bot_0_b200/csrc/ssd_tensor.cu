@@ -867,17 +867,16 @@ constexpr int WS_SCALE_WARPS = 16, WS_EPI_WARPS = 8;
 
 template <int P, int MODE>
 struct WsCfg {
-  static constexpr int N = 64, NB = 1, HB = 64 / P;
+  static constexpr int N = 64, HB = 64 / P;
   static constexpr int NBOX = (MODE == 0) ? 1 : 2;
   static constexpr int NM = (MODE == 0) ? 3 : 2;                    // M_h ring depth = decay groups
   static constexpr int CB_BYTES = 2 * BOX_BYTES;                     // keep + other tile
   static constexpr int IN_BYTES = NBOX * BOX_BYTES + SBOX_BYTES;      // x [, dy] box + state box
-  static constexpr int TB_BYTES = HB * TAB_BYTES;                     // decay tables of one head block
   static constexpr int NTH = 4 * HB;                                  // table ring depth (one 2 KB table per head)
   static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
   static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + NTH * TAB_BYTES + RED_BYTES;
-  // warp roles: NM groups of four decay warps, then {producer, MMA issuer, 2 idle}, then 8 epilogue warps
-  // two MMA issuer warps (one per head of a head block) on the two least loaded schedulers, then the producer
+  // warp roles: NM groups of 4 * NCH decay warps, then two MMA issuer warps (one per head of a head block) on the two
+  // least loaded schedulers, the producer warp and an idle warp, then 8 epilogue warps
   static constexpr int NCH = 1;                                       // threads per row of the decay pass
   static constexpr int DW = 4 * NCH * NM, W_MMA = DW, W_PROD = DW + 2, W_EPI = DW + 4;
   static constexpr int NI = HB;                                       // active issuers: warps W_MMA .. W_MMA + NI - 1
