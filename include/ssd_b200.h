@@ -287,6 +287,16 @@ SSD_API int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, co
                                      void* cuda_stream);
 
 /*
+ * Failure detection.  Every wait inside the pipelined kernels (on a TMA transfer, an MMA completion, another warp role)
+ * is bounded: when it runs out the kernel writes a code into the first 4 bytes of the workspace (0 = healthy), skips its
+ * remaining waits and returns, and later kernels on the same workspace return at once; the context stays usable.
+ * ssd_selftest_bounded_wait exercises that path without touching a pipeline: one warp waits, for at most `max_cycles`
+ * clock cycles, on a barrier nothing arrives on, then writes 99 to *device_status (a device int32 the caller zeroed).
+ * No counterpart in the reference.
+ */
+SSD_API int32_t ssd_selftest_bounded_wait(int32_t* device_status, int64_t max_cycles, void* cuda_stream);
+
+/*
  * Tracing.  ssd_launch_count: kernels this library has launched in this process (all threads).
  * ssd_profile_begin/end: between the two calls every kernel launched from THIS thread gets a
  * CUDA event recorded behind it on its launch stream; _end synchronises on the last event and

@@ -222,3 +222,21 @@ def test_errors_are_reported_not_faulted(lib):
     # the context is still usable afterwards
     y, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=cfg.chunk)
     assert torch.isfinite(y).all()
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable(lib):
+    """A wait that nothing satisfies gives up after its bound and reports through a status word; the kernel returns
+    normally (no trap, no hang) and the next operator call on the same context is correct."""
+    import ctypes as C
+    import trading_bot_0_b200 as T
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rc = lib.ssd_selftest_bounded_wait(C.c_void_p(status.data_ptr()), 2_000_000, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 99
+    cfg = O.CONFIGS[0]
+    inp = O.make_inputs(cfg)
+    y_ref, _ = O.ssd_sequential(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"])
+    d = to_dev(inp, DEV)
+    y, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=cfg.chunk)
+    assert_close("y", y, y_ref, "fp32")

@@ -26,7 +26,7 @@ EXPORTS = [
     "ssd_last_error", "ssd_version", "ssd_compiled_arch", "ssd_launch_count", "ssd_profile_begin",
     "ssd_profile_end", "ssd_forward_noalloc", "ssd_noalloc_max_bytes",
     "ssd_conv1d_workspace_bytes", "ssd_conv1d_forward", "ssd_conv1d_backward",
-    "ssd_rmsnorm_workspace_bytes", "ssd_rmsnorm_forward", "ssd_rmsnorm_backward",
+    "ssd_rmsnorm_workspace_bytes", "ssd_rmsnorm_forward", "ssd_rmsnorm_backward", "ssd_selftest_bounded_wait",
 ]
 
 
@@ -128,6 +128,8 @@ def load() -> C.CDLL:
     lib.ssd_forward_noalloc.argtypes = [C.POINTER(SsdDims), C.POINTER(SsdFwdPtrs), vp]
     lib.ssd_noalloc_max_bytes.restype = sz
     lib.ssd_noalloc_max_bytes.argtypes = []
+    lib.ssd_selftest_bounded_wait.restype = i32
+    lib.ssd_selftest_bounded_wait.argtypes = [vp, i64, vp]
     lib.ssd_conv1d_workspace_bytes.restype = sz
     lib.ssd_conv1d_workspace_bytes.argtypes = [C.POINTER(SsdConvDims)]
     lib.ssd_conv1d_forward.restype = i32

@@ -305,6 +305,13 @@ int32_t ssd_state_update(const SsdStepDims* d, const SsdStepPtrs* p, void* cuda_
   return decode_step(e, *p, (cudaStream_t)cuda_stream);
 }
 
+int32_t ssd_selftest_bounded_wait(int32_t* device_status, int64_t max_cycles, void* cuda_stream) {
+  clear_error();
+  if (!device_status) { set_error("device_status is NULL"); return SSD_ERR_NULL_POINTER; }
+  if (max_cycles <= 0 || max_cycles > 2000000000LL) { set_error("max_cycles must be in (0, 2e9]"); return SSD_ERR_BAD_SHAPE; }
+  return tensor_selftest_wait((int*)device_status, (long long)max_cycles, (cudaStream_t)cuda_stream);
+}
+
 int32_t ssd_state_reset_rows(float* state, int64_t row_elems, const int64_t* stream_idx, int64_t count,
                              int64_t streams, void* cuda_stream) {
   clear_error();

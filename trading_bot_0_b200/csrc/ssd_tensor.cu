@@ -66,6 +66,15 @@ struct Waiter {
   }
 };
 
+// Self-test of the bounded wait: one warp waits on an mbarrier that nothing ever arrives on.  The wait gives up after
+// `max_cycles`, the kernel records the code like every pipeline kernel does and returns normally.
+__global__ void k_selftest_wait(int* status, long long max_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  __syncthreads();
+  if (!mbar_wait(&bar, 0, max_cycles) && threadIdx.x == 0) atomicExch(status, 99);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Decayed lower-triangular tile.  Source: a 128x128 fp32 accumulator in TMEM (C B^T or dY X^T).
 // Result: out[i,j] = src[i,j] * exp(cs_i - cs_j) * dt_j for j <= i, written as bf16 into a plain
@@ -2178,6 +2187,12 @@ int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense
 #define CALL(PP, NN) return launch_dbc<PP, NN>(g, m, tab, p.dB, p.dC, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
+}
+
+int tensor_selftest_wait(int* status, long long max_cycles, cudaStream_t s) {
+  k_selftest_wait<<<1, 32, 0, s>>>(status, max_cycles);
+  SSD_CUDA_CHECK_LAUNCH("selftest_wait");
+  return SSD_OK;
 }
 
 }  // namespace ssd
