@@ -419,6 +419,200 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Persistent version of k_state_tc for dstate 64: one CTA per SM walks over (batch, chunk, group) items and their
+// 128-row accumulator tiles.  Roles:
+//   warp 17 (one lane)  producer: a four-deep ring of x tiles + the two table sections this kernel reads (TMA), so that
+//                       about 100 KB of loads are in flight per SM all the time, and a two-deep ring of B (or C) tiles;
+//   warps 0-15          scale the tile in place (high bf16 part) and write the low part to a second buffer, one 64-token
+//                       half at a time, then store the PREVIOUS tile's accumulator;
+//   warp 16 (one lane)  issues the MMAs of a half as soon as that half is scaled, into one of two TMEM accumulators.
+// Every hand-over is a bounded mbarrier wait; a barrier is only ever waited on by a role that cannot fall two phases
+// behind it (each completion needs that role's own next step).
+template <int P>
+struct PsCfg {
+  static constexpr int N = 64, HT = 128 / P, NX = 4;
+  static constexpr int X_BYTES = 2 * BOX_BYTES;
+  static constexpr int TBH = 256;                 // floats of a head's table that this kernel reads: the T_CS and T_DT sections
+  static constexpr int TB_BYTES = HT * TBH * 4;
+  static constexpr int W_MMA = 16, W_PROD = 17, THREADS = 18 * 32;
+  static constexpr size_t SMEM = 1024 + NX * X_BYTES + X_BYTES + 2 * BOX_BYTES + NX * TB_BYTES;
+  static_assert(T_CS == 0 && T_DT == 128, "the two sections must be the first 1 KB of a table");
+};
+
+template <int P, int MODE>
+__global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const __grid_constant__ CUtensorMap tmX,
+                                                                   const __grid_constant__ CUtensorMap tmB,
+                                                                   const float* __restrict__ tab, float* __restrict__ out,
+                                                                   int* __restrict__ status) {
+  using Cfg = PsCfg<P>;
+  constexpr int N = Cfg::N, HT = Cfg::HT, NX = Cfg::NX;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
+  uint8_t* sX = smem;                                  // NX x {two 64-column boxes}: the tile, scaled in place (high part)
+  uint8_t* sL = sX + NX * Cfg::X_BYTES;                // low bf16 part of the tile being multiplied
+  uint8_t* sB = sL + Cfg::X_BYTES;                     // 2 x B (or C) tile of an item
+  uint8_t* sTabs = sB + 2 * BOX_BYTES;                 // NX x the table sections of a tile's heads
+  __shared__ __align__(8) uint64_t x_full[NX], x_free[NX], b_full[2], b_free[2], half_ready[2], h0_done, mma_done[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) s_abort = *(volatile int*)status;
+  __syncthreads();
+  if (s_abort) return;
+  if (tid == 0) {
+    for (int i = 0; i < NX; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_free[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&b_full[i], 1); mbar_init(&b_free[i], 1); mbar_init(&half_ready[i], 16);
+      mbar_init(&mma_done[i], 1); mbar_init(&acc_empty[i], 16);
+    }
+    mbar_init(&h0_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, 128);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  Waiter w{status, false};
+
+  const int MT = g.hpg * P / 128;
+  const int nitems = g.B * g.G * g.nc;
+  const int my_items = (nitems - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int total = my_items * MT;
+  auto coords = [&](int n, int& b, int& grp, int& c) {   // this CTA's n-th item
+    const int u = blockIdx.x + n * gridDim.x;
+    c = u % g.nc;
+    const int r = u / g.nc;
+    grp = r % g.G;
+    b = r / g.G;
+  };
+
+  if (warp == Cfg::W_PROD) {
+    if (lane == 0) {
+      int n = 0, mt = 0, b = 0, grp = 0, c = 0;
+      for (int k = 0; k < total; ++k) {
+        if (mt == 0) coords(n, b, grp, c);
+        const int slot = k % NX;
+        if (k >= NX) w.wait(&x_free[slot], ((k / NX) - 1) & 1, 14);
+        const int col = grp * g.hpg * P + mt * 128;
+        mbar_expect_tx(&x_full[slot], Cfg::X_BYTES + Cfg::TB_BYTES);
+        tma_load_3d(sX + slot * Cfg::X_BYTES, &tmX, col, c * QT, b, &x_full[slot]);
+        tma_load_3d(sX + slot * Cfg::X_BYTES + BOX_BYTES, &tmX, col + 64, c * QT, b, &x_full[slot]);
+        const float* t0 = tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + mt * HT) * TAB;
+        for (int hl = 0; hl < HT; ++hl)
+          bulk_load(sTabs + slot * Cfg::TB_BYTES + hl * Cfg::TBH * 4, t0 + (size_t)hl * TAB, Cfg::TBH * 4, &x_full[slot]);
+        if (mt == 0) {   // the item's B (or C) tile, after its first x tile so that this wait does not hold the x loads back
+          if (n >= 2) w.wait(&b_free[n & 1], ((n >> 1) - 1) & 1, 15);
+          mbar_expect_tx(&b_full[n & 1], BOX_BYTES);
+          tma_load_3d(sB + (n & 1) * BOX_BYTES, &tmB, grp * N, c * QT, b, &b_full[n & 1]);
+        }
+        if (++mt == MT) { mt = 0; ++n; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == Cfg::W_MMA) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(128, N, 1, 1);
+      const uint64_t dL0 = desc_sw128_mn(smem_u32(sL), 0, 0, BOX_BYTES);
+      int n = 0, mt = 0;
+      for (int k = 0; k < total; ++k) {
+        const int slot = k % NX;
+        const uint64_t dX0 = desc_sw128_mn(smem_u32(sX + slot * Cfg::X_BYTES), 0, 0, BOX_BYTES),
+                       dB0 = desc_sw128_mn(smem_u32(sB + (n & 1) * BOX_BYTES), 0, 0, BOX_BYTES);
+        const uint32_t acc = tm + (k & 1) * 64;
+        if (mt == 0) w.wait(&b_full[n & 1], (n >> 1) & 1, 12);
+        if (k >= 2) w.wait(&acc_empty[k & 1], ((k >> 1) - 1) & 1, 16);
+        w.wait(&half_ready[0], k & 1, 17);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_bf16(acc, desc_adv(dX0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_bf16(acc, desc_adv(dL0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
+        mma_commit(&h0_done);
+        w.wait(&half_ready[1], k & 1, 18);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 4; ks < 8; ++ks) mma_bf16(acc, desc_adv(dX0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
+#pragma unroll
+        for (int ks = 4; ks < 8; ++ks) mma_bf16(acc, desc_adv(dL0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
+        mma_commit(&mma_done[k & 1]);
+        mma_commit(&x_free[slot]);
+        if (mt == MT - 1) mma_commit(&b_free[n & 1]);
+        if (++mt == MT) { mt = 0; ++n; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const uint32_t ls = smem_u32(sL);
+    auto scale_half = [&](int h, uint32_t xs, const float* tb) {   // rows 64 h .. 64 h + 63 of both boxes
+      const int l = (tid >> 3) + 64 * h, pc = tid & 7;
+      const int lc = (pc ^ l) & 7;
+#pragma unroll
+      for (int box = 0; box < 2; ++box) {
+        const float* t = tb + ((box * 64 + lc * 8) / P) * Cfg::TBH;
+        const float wv = (MODE == 0) ? ex2(t[T_CS + 127] - t[T_CS + l]) * t[T_DT + l] : ex2(t[T_CS + l]);
+        const uint32_t off = box * BOX_BYTES + l * 128 + pc * 16;
+        float f[8];
+        unpack8(ld_shared_v4(xs + off), f);
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float f0 = f[2 * q] * wv, f1 = f[2 * q + 1] * wv;
+          hi[q] = pack_bf16(f0, f1);
+          const float2 hf = unpack_bf16(hi[q]);
+          lo[q] = pack_bf16(f0 - hf.x, f1 - hf.y);
+        }
+        st_shared_v4(xs + off, hi[0], hi[1], hi[2], hi[3]);
+        st_shared_v4(ls + off, lo[0], lo[1], lo[2], lo[3]);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&half_ready[h]);
+    };
+    auto epilogue = [&](int k, int b, int grp, int c, int mt) {   // accumulator of tile k -> global
+      const int h0 = grp * g.hpg + mt * HT;
+      const int row = tid & 127, part = tid >> 7;
+      float* o = out + (((size_t)(b * g.nc + c) * g.H + h0) * P + row) * N + part * (N / PARTS);
+      float v[16];
+      tmem_ld16(tmem_addr(tm + (k & 1) * 64, (warp & 3) * 32, part * (N / PARTS)), v);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[k & 1]);
+#pragma unroll
+      for (int j = 0; j < 16; j += 8)
+        st_global_32B(o + j, make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3])),
+                      make_uint4(__float_as_uint(v[j + 4]), __float_as_uint(v[j + 5]), __float_as_uint(v[j + 6]), __float_as_uint(v[j + 7])));
+    };
+    int n = 0, mt = 0, b = 0, grp = 0, c = 0;           // tile k
+    int pb = 0, pgrp = 0, pc_ = 0, pmt = 0;             // tile k - 1
+    for (int k = 0; k < total; ++k) {
+      if (mt == 0) coords(n, b, grp, c);
+      const int slot = k % NX;
+      const uint32_t xs = smem_u32(sX + slot * Cfg::X_BYTES);
+      const float* tb = (const float*)(sTabs + slot * Cfg::TB_BYTES);
+      w.wait(&x_full[slot], (k / NX) & 1, 11);
+      if (k > 0) w.wait(&h0_done, (k - 1) & 1, 19);          // first half of the low-part buffer is free
+      scale_half(0, xs, tb);
+      if (k > 0) {                                           // tile k-1 is complete: second half free, accumulator ready
+        w.wait(&mma_done[(k - 1) & 1], ((k - 1) >> 1) & 1, 13);
+        tc_fence_after();
+      }
+      scale_half(1, xs, tb);
+      if (k > 0) epilogue(k - 1, pb, pgrp, pc_, pmt);
+      pb = b; pgrp = grp; pc_ = c; pmt = mt;
+      if (++mt == MT) { mt = 0; ++n; }
+    }
+    w.wait(&mma_done[(total - 1) & 1], ((total - 1) >> 1) & 1, 13);
+    tc_fence_after();
+    epilogue(total - 1, pb, pgrp, pc_, pmt);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tm, 128);
+}
+
+// ---------------------------------------------------------------------------------------------
 // chunk_scan family.  grid = (nc, G, B).  G = C B^T (128x128, TMEM) once per CTA, then per head
 // the masked, decayed matrix M_h[i,j] = G[i,j] exp(cs_i-cs_j) dt_j (j <= i) goes to shared
 // memory as bf16 and feeds
@@ -1952,9 +2146,31 @@ constexpr size_t scan_smem() {
 template <int P, int N>
 constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * TAB_BYTES; }
 
+bool use_ws_scan();
+int sm_count();
+// SSD_B200_STATE=classic keeps the one-tile-per-CTA chunk-state kernel for dstate 64 too.
+static bool use_ps_state() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SSD_B200_STATE");
+    v = (e && strcmp(e, "classic") == 0) ? 0 : 1;
+  }
+  return v == 1 && use_ws_scan();
+}
+
 template <int P, int N, int MODE>
 int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* tab, float* out, int* status,
                  cudaStream_t s) {
+  if (N == 64 && use_ps_state()) {   // persistent, ring-fed version
+    auto kp = k_state_ps<P, MODE>;
+    constexpr size_t sm = PsCfg<P>::SMEM;
+    cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    const int nitems = g.B * g.G * g.nc;
+    const int grid = nitems < sm_count() ? nitems : sm_count();
+    kp<<<grid, PsCfg<P>::THREADS, sm, s>>>(g, tx, tb, tab, out, status);
+    SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_state_ps" : "dstates_local_ps");
+    return SSD_OK;
+  }
   auto k = k_state_tc<P, N, MODE>;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P, N>());
   k<<<dim3(g.nc, g.G, g.B), TC_THREADS, state_smem<P, N>(), s>>>(g, tx, tb, tab, out, status);
