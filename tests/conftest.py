@@ -18,3 +18,10 @@ def lib():
     from trading_bot_0_b200 import _lib, build
     build.build()
     return _lib.load()
+
+
+@pytest.fixture(scope="session")
+def torch_node_lib(lib):
+    """The libtorch autograd node library (host C++; built on demand with g++ against this image's libtorch)."""
+    from trading_bot_0_b200 import build
+    return build.build_torch()
