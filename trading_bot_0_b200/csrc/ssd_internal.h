@@ -20,6 +20,11 @@ int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, lo
 int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, void* st_bf,
                          int reverse, bool write, const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw,
                          cudaStream_t s);
+// both in one launch where it applies (dstate 64, full pass): fp32 `st` optional, bf16 `st_bf` always
+bool tensor_state_fused_applies(const Geo& g);
+int tensor_state_fused(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc, long long bsb,
+                       long long bsl, const float* tab, float* st, void* st_bf, const float* init, float* last,
+                       const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw, int* status, cudaStream_t s);
 int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const void* prev_bf, int* status,
                       cudaStream_t s);
 int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, void* dypb, float* dcsp,

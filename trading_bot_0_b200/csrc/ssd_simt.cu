@@ -741,11 +741,15 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   void* prev_bf = ws + w.prev_bf;
   const T* x = (const T*)p.x;
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
+  // a full pass (no sequence-parallel staging) computes the chunk states inside the scan over chunks where that kernel applies
+  const bool fused = tc && stages == (SSD_STAGE_LOCAL | SSD_STAGE_FINISH) && tensor_state_fused_applies(g);
   if (stages & SSD_STAGE_LOCAL) {
     cudaMemsetAsync(status, 0, 256, s);
     k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
-    if (tc) {
+    if (tc && fused) {
+      // chunk states and the scan over chunks run as one kernel in the FINISH stage
+    } else if (tc) {
       int rc = tensor_chunk_state(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, states, status, s);
       if (rc) return rc;
     } else {
@@ -765,7 +769,11 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
     }
   }
   if (stages & SSD_STAGE_FINISH) {
-    if (tc) {
+    if (tc && fused) {
+      int rc = tensor_state_fused(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, states, prev_bf, p.init_state, fin, nullptr,
+                                  nullptr, nullptr, nullptr, status, s);
+      if (rc) return rc;
+    } else if (tc) {
       int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
@@ -822,6 +830,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   // tensor-core family: the pre-gate gradient is dy itself, or (gated) a dense bf16 copy in the workspace
   const void* tc_dy = p.z ? (const void*)dyp : p.dy;
   const bool tc_dense = p.z != nullptr;
+  const bool fused = tc && stages == (SSD_STAGE_LOCAL | SSD_STAGE_FINISH) && tensor_state_fused_applies(g);
   if (stages & SSD_STAGE_LOCAL) {
     if (!p.fwd_saved) {
       SsdFwdPtrs f{};
@@ -840,9 +849,11 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       // ungated, dstate 64: the recompute pass is folded into the dx kernel of the FINISH stage
       int rc = tensor_bwd_merged_applies(g, p) ? SSD_OK : tensor_scan_bwd(g, p, tab, prev_bf, dyp, dcsp, ddot, status, s);
       if (rc) return rc;
-      rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
-                              tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, dst, status, s);
-      if (rc) return rc;
+      if (!fused) {
+        rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
+                                tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, dst, status, s);
+        if (rc) return rc;
+      }
     } else {
       // forward recompute with the backward epilogue: dz, pre-gate dy, dcsp, ddot
       k_chunk_scan<T, 1><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
@@ -865,7 +876,13 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   }
   int sdot_nw = 1;
   if (stages & SSD_STAGE_FINISH) {
-    if (tc) {
+    if (tc && fused) {
+      // local state gradients, the reverse scan and the <dS_end, S_end> partial sums in one kernel (no fp32 copy is kept)
+      int rc = tensor_state_fused(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
+                                  tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, nullptr, ds_bf,
+                                  p.dfinal_state, dini, states, fin, sdot, &sdot_nw, status, s);
+      if (rc) return rc;
+    } else if (tc) {
       // the reverse scan also leaves the warp-partial sums of <dS_end, S_end> per chunk
       int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, ds_bf, 1, true, states, fin, sdot, &sdot_nw, s);
       if (rc) return rc;

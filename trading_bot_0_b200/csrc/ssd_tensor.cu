@@ -613,6 +613,268 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Chunk states AND the scan over chunks in one persistent kernel (dstate 64): k_state_ps with the work ordered so that
+// one CTA walks the chunks of a (batch, group, 128-row tile) unit in scan order and keeps the running state of its
+// 128 x 64 tile in registers (16 floats per thread).  The fp32 per-chunk states then never travel to memory and back
+// between two kernels: the epilogue of chunk c writes the state ENTERING the chunk (fp32 for the backward pass, bf16 for
+// the tensor-core scan kernels), then folds the chunk's own contribution in:  run = exp(sum of dt*A over c) * run + local_c.
+//   MODE 0  forward:  units scan c = 0 .. nc-1 from `init` (or zero); `last` receives the final state.
+//   MODE 1  backward: c = nc-1 .. 0 from `init` = the gradient w.r.t. the final state (or zero); the value written for
+//           chunk c is the gradient w.r.t. the state LEAVING it (bf16 only: nothing reads an fp32 copy), and the epilogue
+//           also emits per-warp partial sums of <dS_end_c, S_end_c> (the per-chunk term of the dt*A gradient, S_end_c read
+//           from the forward pass's fp32 states), `nw` = 4 * P / 32 partials per (batch, chunk, head) in `sdot`;
+//           `last` receives the gradient w.r.t. the initial state.
+// Pipeline and barriers as in k_state_ps; the B (or C) tile now changes with every tile, so it has a ring of its own.
+template <int P>
+struct PfCfg {
+  static constexpr int N = 64, HT = 128 / P, NX = 4, NB = 3;
+  static constexpr int X_BYTES = 2 * BOX_BYTES;
+  static constexpr int TBH = 256;
+  static constexpr int TB_BYTES = HT * TBH * 4;
+  static constexpr int W_MMA = 16, W_PROD = 17, THREADS = 18 * 32;
+  static constexpr int SDOT_NW = 4 * (P / 32);
+  static constexpr size_t SMEM = 1024 + NX * X_BYTES + X_BYTES + NB * BOX_BYTES + NX * TB_BYTES;
+};
+
+struct StateScanArgs {
+  const float* tab;
+  float* st;            // [B,nc,H,P,N] fp32 out, optional
+  void* st_bf;          // [B,nc,H,P,N] bf16 out
+  const float* init;    // [B,H,P,N] fp32, optional
+  float* last;          // [B,H,P,N] fp32 out, optional
+  const float* fwd_prev;  // MODE 1: fp32 chunk-entry states of the forward pass
+  const float* fwd_fin;   // MODE 1: forward final state
+  float* sdot;            // MODE 1: [B,nc,H,SDOT_NW]
+};
+
+template <int P, int MODE>
+__global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, const __grid_constant__ CUtensorMap tmX,
+                                                                        const __grid_constant__ CUtensorMap tmB,
+                                                                        StateScanArgs a, int* __restrict__ status) {
+  using Cfg = PfCfg<P>;
+  constexpr int N = Cfg::N, HT = Cfg::HT, NX = Cfg::NX, NB = Cfg::NB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
+  uint8_t* sX = smem;                                  // NX x {two 64-column boxes}: the tile, scaled in place (high part)
+  uint8_t* sL = sX + NX * Cfg::X_BYTES;                // low bf16 part of the tile being multiplied
+  uint8_t* sB = sL + Cfg::X_BYTES;                     // NB x B (or C) tile
+  uint8_t* sTabs = sB + NB * BOX_BYTES;                // NX x the table sections of a tile's heads
+  __shared__ __align__(8) uint64_t x_full[NX], x_free[NX], b_full[NB], b_free[NB], half_ready[2], h0_done, mma_done[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) s_abort = *(volatile int*)status;
+  __syncthreads();
+  if (s_abort) return;
+  if (tid == 0) {
+    for (int i = 0; i < NX; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_free[i], 1); }
+    for (int i = 0; i < NB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_free[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&half_ready[i], 16); mbar_init(&mma_done[i], 1); mbar_init(&acc_empty[i], 16); }
+    mbar_init(&h0_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, 128);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  Waiter w{status, false};
+
+  const int MT = g.hpg * P / 128;
+  const int nunits = g.B * g.G * MT;
+  const int my_units = (nunits - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int total = my_units * g.nc;
+  auto coords = [&](int n, int& b, int& grp, int& mt) {   // this CTA's n-th unit; neighbouring units share a B/C tile
+    const int u = blockIdx.x + n * gridDim.x;
+    mt = u % MT;
+    const int r = u / MT;
+    grp = r % g.G;
+    b = r / g.G;
+  };
+  auto chunk_of = [&](int s) { return MODE == 0 ? s : g.nc - 1 - s; };
+
+  if (warp == Cfg::W_PROD) {
+    if (lane == 0) {
+      int n = 0, sidx = 0, b = 0, grp = 0, mt = 0;
+      for (int k = 0; k < total; ++k) {
+        if (sidx == 0) coords(n, b, grp, mt);
+        const int c = chunk_of(sidx);
+        const int slot = k % NX, bs = k % NB;
+        if (k >= NX) w.wait(&x_free[slot], ((k / NX) - 1) & 1, 14);
+        const int col = grp * g.hpg * P + mt * 128;
+        mbar_expect_tx(&x_full[slot], Cfg::X_BYTES + Cfg::TB_BYTES);
+        tma_load_3d(sX + slot * Cfg::X_BYTES, &tmX, col, c * QT, b, &x_full[slot]);
+        tma_load_3d(sX + slot * Cfg::X_BYTES + BOX_BYTES, &tmX, col + 64, c * QT, b, &x_full[slot]);
+        const float* t0 = a.tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + mt * HT) * TAB;
+        for (int hl = 0; hl < HT; ++hl)
+          bulk_load(sTabs + slot * Cfg::TB_BYTES + hl * Cfg::TBH * 4, t0 + (size_t)hl * TAB, Cfg::TBH * 4, &x_full[slot]);
+        if (k >= NB) w.wait(&b_free[bs], ((k / NB) - 1) & 1, 15);
+        mbar_expect_tx(&b_full[bs], BOX_BYTES);
+        tma_load_3d(sB + bs * BOX_BYTES, &tmB, grp * N, c * QT, b, &b_full[bs]);
+        if (++sidx == g.nc) { sidx = 0; ++n; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == Cfg::W_MMA) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(128, N, 1, 1);
+      const uint64_t dL0 = desc_sw128_mn(smem_u32(sL), 0, 0, BOX_BYTES);
+      for (int k = 0; k < total; ++k) {
+        const int slot = k % NX, bs = k % NB;
+        const uint64_t dX0 = desc_sw128_mn(smem_u32(sX + slot * Cfg::X_BYTES), 0, 0, BOX_BYTES),
+                       dB0 = desc_sw128_mn(smem_u32(sB + bs * BOX_BYTES), 0, 0, BOX_BYTES);
+        const uint32_t acc = tm + (k & 1) * 64;
+        w.wait(&b_full[bs], (k / NB) & 1, 12);
+        if (k >= 2) w.wait(&acc_empty[k & 1], ((k >> 1) - 1) & 1, 16);
+        w.wait(&half_ready[0], k & 1, 17);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_bf16(acc, desc_adv(dX0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) mma_bf16(acc, desc_adv(dL0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
+        mma_commit(&h0_done);
+        w.wait(&half_ready[1], k & 1, 18);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 4; ks < 8; ++ks) mma_bf16(acc, desc_adv(dX0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
+#pragma unroll
+        for (int ks = 4; ks < 8; ++ks) mma_bf16(acc, desc_adv(dL0, ks * 2048), desc_adv(dB0, ks * 2048), idesc, true);
+        mma_commit(&mma_done[k & 1]);
+        mma_commit(&x_free[slot]);
+        mma_commit(&b_free[bs]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const uint32_t ls = smem_u32(sL);
+    const int row = tid & 127, part = tid >> 7;
+    auto scale_half = [&](int h, uint32_t xs, const float* tb) {   // rows 64 h .. 64 h + 63 of both boxes
+      const int l = (tid >> 3) + 64 * h, pc = tid & 7;
+      const int lc = (pc ^ l) & 7;
+#pragma unroll
+      for (int box = 0; box < 2; ++box) {
+        const float* t = tb + ((box * 64 + lc * 8) / P) * Cfg::TBH;
+        const float wv = (MODE == 0) ? ex2(t[T_CS + 127] - t[T_CS + l]) * t[T_DT + l] : ex2(t[T_CS + l]);
+        const uint32_t off = box * BOX_BYTES + l * 128 + pc * 16;
+        float f[8];
+        unpack8(ld_shared_v4(xs + off), f);
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float f0 = f[2 * q] * wv, f1 = f[2 * q + 1] * wv;
+          hi[q] = pack_bf16(f0, f1);
+          const float2 hf = unpack_bf16(hi[q]);
+          lo[q] = pack_bf16(f0 - hf.x, f1 - hf.y);
+        }
+        st_shared_v4(xs + off, hi[0], hi[1], hi[2], hi[3]);
+        st_shared_v4(ls + off, lo[0], lo[1], lo[2], lo[3]);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&half_ready[h]);
+    };
+    float run[16];          // running state of this thread's (row, 16 columns)
+    float4 se[4];           // MODE 1: S_end of the tile whose epilogue comes next, fetched one scale phase ahead
+    struct Tile { int b, grp, mt, s; };
+    auto elem = [&](const Tile& t) {   // offset of this thread's 16 columns inside a [.., H, P, N] state
+      return ((size_t)(t.grp * g.hpg + t.mt * HT) * P + row) * N + part * 16;
+    };
+    auto fetch_send = [&](const Tile& t) {
+      if (MODE != 1 || !a.sdot) return;
+      const int c = chunk_of(t.s);
+      const float* src = (c + 1 < g.nc) ? a.fwd_prev + (size_t)(t.b * g.nc + c + 1) * g.H * P * N + elem(t)
+                                        : a.fwd_fin + (size_t)t.b * g.H * P * N + elem(t);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) se[j] = *reinterpret_cast<const float4*>(src + 4 * j);
+    };
+    auto epilogue = [&](int k, const Tile& t, float dec) {
+      const int c = chunk_of(t.s);
+      const size_t e = elem(t), bstate = (size_t)t.b * g.H * P * N;
+      if (t.s == 0) {
+        if (a.init) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 v4 = *reinterpret_cast<const float4*>(a.init + bstate + e + 4 * j);
+            run[4 * j] = v4.x; run[4 * j + 1] = v4.y; run[4 * j + 2] = v4.z; run[4 * j + 3] = v4.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) run[j] = 0.f;
+        }
+      }
+      float v[16];
+      tmem_ld16(tmem_addr(tm + (k & 1) * 64, (warp & 3) * 32, part * 16), v);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[k & 1]);
+      const size_t o = (size_t)(t.b * g.nc + c) * g.H * P * N + e;
+      if (a.st) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 8)
+          st_global_32B(a.st + o + j, make_uint4(__float_as_uint(run[j]), __float_as_uint(run[j + 1]), __float_as_uint(run[j + 2]), __float_as_uint(run[j + 3])),
+                        make_uint4(__float_as_uint(run[j + 4]), __float_as_uint(run[j + 5]), __float_as_uint(run[j + 6]), __float_as_uint(run[j + 7])));
+      }
+      st_global_32B((bf16*)a.st_bf + o,
+                    make_uint4(pack_bf16(run[0], run[1]), pack_bf16(run[2], run[3]), pack_bf16(run[4], run[5]), pack_bf16(run[6], run[7])),
+                    make_uint4(pack_bf16(run[8], run[9]), pack_bf16(run[10], run[11]), pack_bf16(run[12], run[13]), pack_bf16(run[14], run[15])));
+      if (MODE == 1 && a.sdot) {
+        float d = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          d += run[4 * j] * se[j].x + run[4 * j + 1] * se[j].y + run[4 * j + 2] * se[j].z + run[4 * j + 3] * se[j].w;
+#pragma unroll
+        for (int off = 16; off; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        if (lane == 0) {
+          const int q = warp & 3;                                  // 32-row quarter of the tile
+          const int h = t.grp * g.hpg + t.mt * HT + (q * 32) / P;
+          const int slot = part * (P / 32) + q % (P / 32);
+          a.sdot[((size_t)(t.b * g.nc + c) * g.H + h) * Cfg::SDOT_NW + slot] = d;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) run[j] = fmaf(dec, run[j], v[j]);
+      if (t.s == g.nc - 1 && a.last) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 8)
+          st_global_32B(a.last + bstate + e + j, make_uint4(__float_as_uint(run[j]), __float_as_uint(run[j + 1]), __float_as_uint(run[j + 2]), __float_as_uint(run[j + 3])),
+                        make_uint4(__float_as_uint(run[j + 4]), __float_as_uint(run[j + 5]), __float_as_uint(run[j + 6]), __float_as_uint(run[j + 7])));
+      }
+    };
+    Tile cur{0, 0, 0, 0}, prev{0, 0, 0, 0};
+    int n = 0;
+    float dec_prev = 0.f;
+    for (int k = 0; k < total; ++k) {
+      if (cur.s == 0) coords(n, cur.b, cur.grp, cur.mt);
+      const int slot = k % NX;
+      const uint32_t xs = smem_u32(sX + slot * Cfg::X_BYTES);
+      const float* tb = (const float*)(sTabs + slot * Cfg::TB_BYTES);
+      if (k > 0) fetch_send(prev);                             // lands while this tile is scaled
+      w.wait(&x_full[slot], (k / NX) & 1, 11);
+      const float dec = ex2(tb[(row / P) * Cfg::TBH + T_CS + 127]);   // decay over the whole chunk, for this tile's epilogue
+      if (k > 0) w.wait(&h0_done, (k - 1) & 1, 19);            // first half of the low-part buffer is free
+      scale_half(0, xs, tb);
+      if (k > 0) {                                             // tile k-1 is complete: second half free, accumulator ready
+        w.wait(&mma_done[(k - 1) & 1], ((k - 1) >> 1) & 1, 13);
+        tc_fence_after();
+      }
+      scale_half(1, xs, tb);
+      if (k > 0) epilogue(k - 1, prev, dec_prev);
+      prev = cur;
+      dec_prev = dec;
+      if (++cur.s == g.nc) { cur.s = 0; ++n; }
+    }
+    fetch_send(prev);
+    w.wait(&mma_done[(total - 1) & 1], ((total - 1) >> 1) & 1, 13);
+    tc_fence_after();
+    epilogue(total - 1, prev, dec_prev);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tm, 128);
+}
+
+// ---------------------------------------------------------------------------------------------
 // chunk_scan family.  grid = (nc, G, B).  G = C B^T (128x128, TMEM) once per CTA, then per head
 // the masked, decayed matrix M_h[i,j] = G[i,j] exp(cs_i-cs_j) dt_j (j <= i) goes to shared
 // memory as bf16 and feeds
@@ -2347,6 +2609,46 @@ int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, lo
                                       : launch_state<PP, NN, 1>(g, tx, tb, tab, out, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
+}
+
+// Chunk states and the scan over chunks in one launch (see k_state_scan_ps).  SSD_B200_STATE=classic or =split keeps
+// the two-kernel path.
+bool tensor_state_fused_applies(const Geo& g) {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SSD_B200_STATE");
+    v = (e && (strcmp(e, "classic") == 0 || strcmp(e, "split") == 0)) ? 0 : 1;
+  }
+  return v == 1 && g.N == 64 && use_ws_scan();
+}
+
+template <int P, int MODE>
+static int launch_state_scan(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const StateScanArgs& a, int* status,
+                             cudaStream_t s) {
+  auto k = k_state_scan_ps<P, MODE>;
+  constexpr size_t sm = PfCfg<P>::SMEM;
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  const int nunits = g.B * g.G * (g.hpg * P / 128);
+  const int grid = nunits < sm_count() ? nunits : sm_count();
+  k<<<grid, PfCfg<P>::THREADS, sm, s>>>(g, tx, tb, a, status);
+  SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_state_scan" : "dstate_scan");
+  return SSD_OK;
+}
+
+int tensor_state_fused(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc, long long bsb,
+                       long long bsl, const float* tab, float* st, void* st_bf, const float* init, float* last,
+                       const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw, int* status, cudaStream_t s) {
+  CUtensorMap tx, tb;
+  int rc = make_seq_map(&tx, xdy, (long long)g.H * g.P, g.L, g.B, sl, sb, "x/dy");
+  if (rc) return rc;
+  rc = make_seq_map(&tb, bc, (long long)g.G * g.N, g.L, g.B, bsl, bsb, "B/C");
+  if (rc) return rc;
+  StateScanArgs a{tab, st, st_bf, init, last, fwd_prev, fwd_fin, sdot};
+  if (sdot_nw) *sdot_nw = 4 * (g.P / 32);
+  if (g.P == 32) return mode == 0 ? launch_state_scan<32, 0>(g, tx, tb, a, status, s) : launch_state_scan<32, 1>(g, tx, tb, a, status, s);
+  if (g.P == 64) return mode == 0 ? launch_state_scan<64, 0>(g, tx, tb, a, status, s) : launch_state_scan<64, 1>(g, tx, tb, a, status, s);
+  set_error("tensor_state_fused: unsupported headdim %d", g.P);
+  return SSD_ERR_UNSUPPORTED;
 }
 
 int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const void* prev_bf, int* status,
