@@ -81,6 +81,9 @@ def kernel_bytes_per_token(name, c, e=2):
         "dC": (2 * gn + hp) * e, "dB": (2 * gn + hp) * e, "ddt": 4 * H, "sdot": st / 2,
         # tensor-core kernels: each reads its operand tiles once and writes its outputs once
         "chunk_state_tc": (hp + gn) * e, "dstates_local_tc": (hp + gn) * e,
+        "chunk_state_ps": (hp + gn) * e, "dstates_local_ps": (hp + gn) * e,
+        # chunk states fused with the scan over chunks: the operator's inputs on the way in; the states stay on chip
+        "chunk_state_scan": (hp + gn) * e, "dstate_scan": (hp + gn) * e,
         "chunk_scan_tc": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_tc": (2 * hp + 2 * gn) * e + 2 * zb,
         "dx_tc": (3 * hp + 2 * gn) * e, "dBdC_tc": (2 * hp + 4 * gn) * e,
         "chunk_scan_ws": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_ws": (2 * hp + 2 * gn) * e + 2 * zb,
@@ -100,9 +103,12 @@ def kernel_traffic_bytes_per_token(name, c, e=2):
     hp, gn, H = c["H"] * c["P"], c["G"] * c["N"], c["H"]
     st32 = H * c["P"] * c["N"] * 4 / c["Q"]          # fp32 chunk states, bytes per token, one way
     measured_reads = {"chunk_state_tc": 768.0, "dstates_local_tc": 768.0, "chunk_scan_ws": 1152.6,
-                      "scan_bwd_dx_ws": 1920.2, "dBdC_ws": 1920.2}
+                      "scan_bwd_dx_ws": 1920.2, "dBdC_ws": 1920.2,
+                      # profiles/state_scan_cfg1_batch128_ncu.md
+                      "chunk_state_scan": 704.3, "dstate_scan": 1216.3}
     writes = {"chunk_state_tc": st32, "dstates_local_tc": st32, "chunk_scan_ws": hp * e,
-              "scan_bwd_dx_ws": hp * e + 3 * 4 * H, "dBdC_ws": 2 * gn * e}
+              "scan_bwd_dx_ws": hp * e + 3 * 4 * H, "dBdC_ws": 2 * gn * e,
+              "chunk_state_scan": st32 + st32 / 2, "dstate_scan": st32 / 2 + 4 * 4 * H / c["Q"]}
     if name not in measured_reads:
         return None
     return measured_reads[name] + writes[name]
