@@ -173,17 +173,21 @@ struct ConvSegs {
   int n;
 };
 
-#ifndef CONV_BWD_CH
-#define CONV_BWD_CH 8
-#endif
-#ifndef CONV_BWD_MINB
-#define CONV_BWD_MINB 3
-#endif
+constexpr int CONV_TLB = 128;       // backward: tokens per tile (2 (K-1) halo rows per tile are recomputed: 5 % at K = 4)
+constexpr int CONV_BWD_CH = 4;      // rows of the input and of the gradient requested together (two such register sets;
+                                    // 8 rows per set spill at 168 registers and measured 40 % slower)
+constexpr int CONV_BWD_MINB = 3;
+
+template <typename T, int NC> __device__ __forceinline__ void zero_raw(RawN<T, NC>& r) {
+  r = RawN<T, NC>{};
+}
+
 template <typename T, int K, int NC>
 __global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdConvDims d, int rows, const T* __restrict__ in,
                                                            const float* __restrict__ weight, const float* __restrict__ bias,
                                                            ConvSegs segs, T* __restrict__ din, long long din_stride_b,
                                                            long long din_stride_l, float* __restrict__ partial) {
+  constexpr int CH = CONV_BWD_CH;
   const int CV = d.channels / NC;
   const long long item = (long long)blockIdx.x * CONV_THREADS + threadIdx.x;
   if (item >= (long long)rows * CV) return;
@@ -202,63 +206,57 @@ __global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdCon
   const T* dop = (const T*)segs.ptr[si] + (c0 - segs.c_begin[si]);
   const long long dosb = segs.stride_b[si], dosl = segs.stride_l[si];
 
-  const int ntile = (d.seqlen + CONV_TL - 1) / CONV_TL;
+  const int ntile = (d.seqlen + CONV_TLB - 1) / CONV_TLB;
   for (int pair = row; pair < d.batch * ntile; pair += rows) {
-    const int b = pair / ntile, t0 = (pair - b * ntile) * CONV_TL, t1 = min(t0 + CONV_TL, d.seqlen);
+    const int b = pair / ntile, t0 = (pair - b * ntile) * CONV_TLB, t1 = min(t0 + CONV_TLB, d.seqlen);
     const T* ip = in + (long long)b * d.in_stride_b + c0;
     const T* gp = dop + (long long)b * dosb;
+    T* dp = din + (long long)b * din_stride_b + c0;
     float win[K][NC], dpw[K][NC];   // win[k] = in[s-K+1+k], dpw[k] = dpre[s-K+1+k]
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
       for (int j = 0; j < NC; ++j) { win[k][j] = 0.f; dpw[k][j] = 0.f; }
+    // rows s_begin .. s_end-1: K-1 rows of input before the tile, the tile, K-1 rows after it (their dpre completes the
+    // tile's last din rows).  Rows outside the sequence or past s_end are zeros; a zero gradient row contributes nothing,
+    // so the row loop needs no early exit and the compiler keeps both windows in renamed registers.
     const int s_begin = t0 - (K - 1), s_end = min(t1 + K - 1, d.seqlen + K - 1);
-    constexpr int CH = CONV_BWD_CH;     // rows of the input and of the gradient requested together
-    for (int sc = s_begin; sc < s_end; sc += CH) {
-      RawN<T, NC> rin[CH], rgo[CH];
+    auto load_chunk = [&](int sc, RawN<T, NC> (&rin)[CH], RawN<T, NC> (&rgo)[CH]) {
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int s = sc + i;
-        if (s >= 0 && s < d.seqlen && s < s_end) load_raw(ip + (long long)s * d.in_stride_l, rin[i]);
-        if (s >= t0 && s < d.seqlen && s < s_end) load_raw(gp + (long long)s * dosl, rgo[i]);
+        if (s >= 0 && s < d.seqlen && s < s_end) load_raw(ip + (long long)s * d.in_stride_l, rin[i]); else zero_raw(rin[i]);
+        if (s >= t0 && s < d.seqlen && s < s_end) load_raw(gp + (long long)s * dosl, rgo[i]); else zero_raw(rgo[i]);
       }
+    };
+    auto compute_chunk = [&](int sc, const RawN<T, NC> (&rin)[CH], const RawN<T, NC> (&rgo)[CH]) {
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int s = sc + i;
-        if (s >= s_end) break;
-        // shift both windows, then bring in row s
 #pragma unroll
         for (int k = 0; k < K - 1; ++k)
 #pragma unroll
           for (int j = 0; j < NC; ++j) { win[k][j] = win[k + 1][j]; dpw[k][j] = dpw[k + 1][j]; }
-        if (s >= 0 && s < d.seqlen) unpack_raw(rin[i], win[K - 1]);
-        else {
+        unpack_raw(rin[i], win[K - 1]);
+        float go[NC];
+        unpack_raw(rgo[i], go);
+        const bool own = s < t1;    // each row's weight / bias gradient is counted by exactly one tile (warp-uniform)
 #pragma unroll
-          for (int j = 0; j < NC; ++j) win[K - 1][j] = 0.f;
-        }
-        if (s >= t0 && s < d.seqlen) {
-          float go[NC];
-          unpack_raw(rgo[i], go);
+        for (int j = 0; j < NC; ++j) {
+          float a = bs[j];
 #pragma unroll
-          for (int j = 0; j < NC; ++j) {
-            float a = bs[j];
-#pragma unroll
-            for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
-            float g = go[j];
-            if (d.activation) {
-              const float sg = sig_<T>(a);
-              g *= sg * (1.f + a * (1.f - sg));
-            }
-            dpw[K - 1][j] = g;
-            if (s < t1) {   // each row's weight / bias gradient is counted by exactly one tile
-              db[j] += g;
-#pragma unroll
-              for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
-            }
+          for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+          float g = go[j];
+          if (d.activation) {
+            const float sg = sig_<T>(a);
+            g *= sg * (1.f + a * (1.f - sg));
           }
-        } else {
+          dpw[K - 1][j] = g;
+          if (own) {
+            db[j] += g;
 #pragma unroll
-          for (int j = 0; j < NC; ++j) dpw[K - 1][j] = 0.f;
+            for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
+          }
         }
         const int t = s - (K - 1);
         if (t >= t0 && t < t1) {
@@ -270,9 +268,18 @@ __global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdCon
             for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dpw[q][j], a);
             o[j] = a;
           }
-          store_n(din + (long long)b * din_stride_b + (long long)t * din_stride_l + c0, o);
+          store_n(dp + (long long)t * din_stride_l, o);
         }
       }
+    };
+    // two register sets: the next chunk's rows are requested before the current chunk is worked on
+    RawN<T, NC> rinA[CH], rgoA[CH], rinB[CH], rgoB[CH];
+    load_chunk(s_begin, rinA, rgoA);
+    for (int sc = s_begin; sc < s_end; sc += 2 * CH) {
+      load_chunk(sc + CH, rinB, rgoB);
+      compute_chunk(sc, rinA, rgoA);
+      load_chunk(sc + 2 * CH, rinA, rgoA);
+      if (sc + CH < s_end) compute_chunk(sc + CH, rinB, rgoB);
     }
   }
   float* pp = partial + ((size_t)row * d.channels + c0) * (K + 1);
@@ -422,7 +429,7 @@ __global__ void k_norm_reduce(int nblk, int width, const float* __restrict__ par
 }
 
 int conv_rows(const SsdConvDims* d) {   // thread rows of the backward kernel = partial sums to add
-  const int ntile = (d->seqlen + CONV_TL - 1) / CONV_TL;
+  const int ntile = (d->seqlen + CONV_TLB - 1) / CONV_TLB;
   const long long pairs = (long long)d->batch * ntile;
   return (int)(pairs < CONV_ROWS ? pairs : CONV_ROWS);
 }
