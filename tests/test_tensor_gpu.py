@@ -105,3 +105,41 @@ def test_chunk_256_runs_on_the_tensor_family_as_two_128_chunks(lib):
         assert_close(k, g[k], ref[k], "bf16")
     y128, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d["z"], d["init_state"], chunk=128, algo="tensor")
     assert torch.equal(y, y128)
+
+
+@pytest.mark.parametrize("Bn,L,H,P,G", [(1, 128, 8, 32, 1), (3, 1280, 4, 64, 2), (2, 384, 16, 32, 2)])
+def test_fused_state_scan_matches_the_staged_two_kernel_path(lib, Bn, L, H, P, G):
+    """A full pass at dstate 64 computes the chunk states inside the scan over chunks (one kernel per pass, running state
+    in registers); the staged entry points (sequence-parallel callers) keep chunk-state kernel + scan kernel.  Same inputs,
+    both ways, incl. one chunk only, fewer units than SMs, an initial state and a gradient entering the final state:
+    results agree to fp32 rounding of the chunk decay (exp2 of the table value against expf of the cumsum) and both match
+    the oracle."""
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib as LL
+    cfg = O.SsdConfig("fs", Bn, L, H, P, 64, G, 128, "bf16", False)
+    inp = O.make_inputs(cfg, with_init_state=True)
+    dfinal = 0.1 * torch.randn(Bn, H, P, 64, generator=torch.Generator().manual_seed(8))
+    ref = oracle_all(inp, dfinal)
+    d = to_dev(inp, DEV)
+    args = (d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], None, d["init_state"])
+    res = {}
+    for name, stage_list in (("fused", [None]), ("staged", [LL.STAGE_LOCAL, LL.STAGE_FINISH])):
+        ws = y = fin = None
+        for st in stage_list:
+            y, fin, ws = T.forward(*args, chunk=128, algo="tensor", for_backward=True, stages=st, workspace=ws, y=y, final_state=fin)
+        g = None
+        for st in stage_list:
+            g = T.backward(d["dy"], *args, dfinal.to(DEV), chunk=128, algo="tensor", workspace=ws, fwd_saved=True,
+                           want_dinit=True, stages=st, out=g)
+        torch.cuda.synchronize()
+        assert status_word(ws) == 0
+        res[name] = dict(y=y, final_state=fin, **{k: g[k] for k in GRADS + ("dD", "dinit")})
+    for k, v in res["fused"].items():
+        if k == "dA":   # a sum over all tokens of terms that mostly cancel: gated at 6e-2 of its largest entry on these small cases
+            for w in (v, res["staged"][k]):
+                assert (w.double().cpu() - ref[k]).abs().max() <= 6e-2 * ref[k].abs().max()
+        else:
+            assert_close(k + " (fused)", v, ref[k], "bf16")
+            assert_close(k + " (staged)", res["staged"][k], ref[k], "bf16")
+        tol = 2e-2 if k == "dA" else 2e-3
+        assert mean_rel(v, res["staged"][k]) < tol, f"{k}: fused and staged paths differ by {mean_rel(v, res['staged'][k]):.3e}"
