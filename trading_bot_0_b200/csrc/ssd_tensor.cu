@@ -625,15 +625,17 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
 //           from the forward pass's fp32 states), `nw` = 4 * P / 32 partials per (batch, chunk, head) in `sdot`;
 //           `last` receives the gradient w.r.t. the initial state.
 // Pipeline and barriers as in k_state_ps; the B (or C) tile now changes with every tile, so it has a ring of its own.
-template <int P>
+template <int P, int MODE>
 struct PfCfg {
-  static constexpr int N = 64, HT = 128 / P, NX = 4, NB = 3;
+  // the backward kernel gives one slot of the x ring to the S_end tile (128 rows x 64 fp32 as two swizzled 16 KB boxes)
+  static constexpr int N = 64, HT = 128 / P, NX = MODE == 1 ? 3 : 4, NB = 3;
   static constexpr int X_BYTES = 2 * BOX_BYTES;
   static constexpr int TBH = 256;
   static constexpr int TB_BYTES = HT * TBH * 4;
-  static constexpr int W_MMA = 16, W_PROD = 17, THREADS = 18 * 32;
+  static constexpr int SE_BYTES = MODE == 1 ? 2 * BOX_BYTES : 0;
+  static constexpr int W_MMA = 16, W_PROD = 17, W_PROD2 = 18, THREADS = (MODE == 1 ? 19 : 18) * 32;
   static constexpr int SDOT_NW = 4 * (P / 32);
-  static constexpr size_t SMEM = 1024 + NX * X_BYTES + X_BYTES + NB * BOX_BYTES + NX * TB_BYTES;
+  static constexpr size_t SMEM = 1024 + NX * X_BYTES + X_BYTES + NB * BOX_BYTES + SE_BYTES + NX * TB_BYTES;
 };
 
 struct StateScanArgs {
@@ -648,18 +650,22 @@ struct StateScanArgs {
 };
 
 template <int P, int MODE>
-__global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, const __grid_constant__ CUtensorMap tmX,
-                                                                        const __grid_constant__ CUtensorMap tmB,
-                                                                        StateScanArgs a, int* __restrict__ status) {
-  using Cfg = PfCfg<P>;
+__global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Geo g, const __grid_constant__ CUtensorMap tmX,
+                                                                              const __grid_constant__ CUtensorMap tmB,
+                                                                              const __grid_constant__ CUtensorMap tmS,
+                                                                              const __grid_constant__ CUtensorMap tmF,
+                                                                              StateScanArgs a, int* __restrict__ status) {
+  using Cfg = PfCfg<P, MODE>;
   constexpr int N = Cfg::N, HT = Cfg::HT, NX = Cfg::NX, NB = Cfg::NB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sX = smem;                                  // NX x {two 64-column boxes}: the tile, scaled in place (high part)
   uint8_t* sL = sX + NX * Cfg::X_BYTES;                // low bf16 part of the tile being multiplied
   uint8_t* sB = sL + Cfg::X_BYTES;                     // NB x B (or C) tile
-  uint8_t* sTabs = sB + NB * BOX_BYTES;                // NX x the table sections of a tile's heads
-  __shared__ __align__(8) uint64_t x_full[NX], x_free[NX], b_full[NB], b_free[NB], half_ready[2], h0_done, mma_done[2], acc_empty[2];
+  uint8_t* sSE = sB + NB * BOX_BYTES;                  // MODE 1: S_end of the tile whose epilogue comes next (fp32, 128B swizzle)
+  uint8_t* sTabs = sSE + Cfg::SE_BYTES;                // NX x the table sections of a tile's heads
+  __shared__ __align__(8) uint64_t x_full[NX], x_free[NX], b_full[NB], b_free[NB], half_ready[2], h0_done, mma_done[2], acc_empty[2],
+      se_full, se_free;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -672,6 +678,7 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
     for (int i = 0; i < NB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_free[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&half_ready[i], 16); mbar_init(&mma_done[i], 1); mbar_init(&acc_empty[i], 16); }
     mbar_init(&h0_done, 1);
+    mbar_init(&se_full, 1); mbar_init(&se_free, 16);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, 128);
@@ -680,6 +687,7 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
   tc_fence_after();
   const uint32_t tm = tmem_slot;
   Waiter w{status, false};
+  const bool want_sdot = MODE == 1 && a.sdot != nullptr;
 
   const int MT = g.hpg * P / 128;
   const int nunits = g.B * g.G * MT;
@@ -712,6 +720,26 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
         if (k >= NB) w.wait(&b_free[bs], ((k / NB) - 1) & 1, 15);
         mbar_expect_tx(&b_full[bs], BOX_BYTES);
         tma_load_3d(sB + bs * BOX_BYTES, &tmB, grp * N, c * QT, b, &b_full[bs]);
+        if (++sidx == g.nc) { sidx = 0; ++n; }
+      }
+    }
+    __syncwarp();
+  } else if (MODE == 1 && warp == Cfg::W_PROD2) {
+    // second producer lane: the forward state leaving chunk c (= entering chunk c+1, or the final state), one tile ahead of
+    // the epilogue that multiplies it with the running gradient
+    if (lane == 0 && want_sdot) {
+      int n = 0, sidx = 0, b = 0, grp = 0, mt = 0;
+      for (int k = 0; k < total; ++k) {
+        if (sidx == 0) coords(n, b, grp, mt);
+        const int c = chunk_of(sidx);
+        const int h0 = grp * g.hpg + mt * HT;
+        if (k >= 1) w.wait(&se_free, (k - 1) & 1, 20);
+        mbar_expect_tx(&se_full, Cfg::SE_BYTES);
+        const bool last_chunk = c + 1 >= g.nc;
+        const CUtensorMap* m = last_chunk ? &tmF : &tmS;
+        const int row0 = last_chunk ? (b * g.H + h0) * P : ((b * g.nc + c + 1) * g.H + h0) * P;
+        tma_load_3d(sSE, m, 0, row0, 0, &se_full);
+        tma_load_3d(sSE + BOX_BYTES, m, 32, row0, 0, &se_full);
         if (++sidx == g.nc) { sidx = 0; ++n; }
       }
     }
@@ -775,18 +803,9 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
       if (lane == 0) mbar_arrive(&half_ready[h]);
     };
     float run[16];          // running state of this thread's (row, 16 columns)
-    float4 se[4];           // MODE 1: S_end of the tile whose epilogue comes next, fetched one scale phase ahead
     struct Tile { int b, grp, mt, s; };
     auto elem = [&](const Tile& t) {   // offset of this thread's 16 columns inside a [.., H, P, N] state
       return ((size_t)(t.grp * g.hpg + t.mt * HT) * P + row) * N + part * 16;
-    };
-    auto fetch_send = [&](const Tile& t) {
-      if (MODE != 1 || !a.sdot) return;
-      const int c = chunk_of(t.s);
-      const float* src = (c + 1 < g.nc) ? a.fwd_prev + (size_t)(t.b * g.nc + c + 1) * g.H * P * N + elem(t)
-                                        : a.fwd_fin + (size_t)t.b * g.H * P * N + elem(t);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) se[j] = *reinterpret_cast<const float4*>(src + 4 * j);
     };
     auto epilogue = [&](int k, const Tile& t, float dec) {
       const int c = chunk_of(t.s);
@@ -818,11 +837,18 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
       st_global_32B((bf16*)a.st_bf + o,
                     make_uint4(pack_bf16(run[0], run[1]), pack_bf16(run[2], run[3]), pack_bf16(run[4], run[5]), pack_bf16(run[6], run[7])),
                     make_uint4(pack_bf16(run[8], run[9]), pack_bf16(run[10], run[11]), pack_bf16(run[12], run[13]), pack_bf16(run[14], run[15])));
-      if (MODE == 1 && a.sdot) {
+      if (want_sdot) {
+        w.wait(&se_full, k & 1, 21);
         float d = 0.f;
+        const uint32_t sb = smem_u32(sSE) + (part >> 1) * BOX_BYTES;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          d += run[4 * j] * se[j].x + run[4 * j + 1] * se[j].y + run[4 * j + 2] * se[j].z + run[4 * j + 3] * se[j].w;
+        for (int j = 0; j < 4; ++j) {
+          const uint4 u = ld_shared_v4(sb + sw128_off(row, (part & 1) * 4 + j));
+          d += run[4 * j] * __uint_as_float(u.x) + run[4 * j + 1] * __uint_as_float(u.y) + run[4 * j + 2] * __uint_as_float(u.z) +
+               run[4 * j + 3] * __uint_as_float(u.w);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&se_free);
 #pragma unroll
         for (int off = 16; off; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
         if (lane == 0) {
@@ -849,7 +875,6 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
       const int slot = k % NX;
       const uint32_t xs = smem_u32(sX + slot * Cfg::X_BYTES);
       const float* tb = (const float*)(sTabs + slot * Cfg::TB_BYTES);
-      if (k > 0) fetch_send(prev);                             // lands while this tile is scaled
       w.wait(&x_full[slot], (k / NX) & 1, 11);
       const float dec = ex2(tb[(row / P) * Cfg::TBH + T_CS + 127]);   // decay over the whole chunk, for this tile's epilogue
       if (k > 0) w.wait(&h0_done, (k - 1) & 1, 19);            // first half of the low-part buffer is free
@@ -864,7 +889,6 @@ __global__ void __launch_bounds__(PfCfg<P>::THREADS, 1) k_state_scan_ps(Geo g, c
       dec_prev = dec;
       if (++cur.s == g.nc) { cur.s = 0; ++n; }
     }
-    fetch_send(prev);
     w.wait(&mma_done[(total - 1) & 1], ((total - 1) >> 1) & 1, 13);
     tc_fence_after();
     epilogue(total - 1, prev, dec_prev);
@@ -2387,6 +2411,20 @@ int make_map3(CUtensorMap* m, const void* ptr, long long d0, long long d1, long 
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r); return SSD_ERR_CUDA; }
   return SSD_OK;
 }
+// fp32 [rows, 64] state rows (dstate 64), 128B swizzle: box = 32 columns (128 bytes) x 128 rows
+int make_f32_rows_map(CUtensorMap* m, const float* ptr, long long rows, const char* what) {
+  EncodeFn enc = get_encode();
+  if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return SSD_ERR_CUDA; }
+  cuuint64_t dims[3] = {64, (cuuint64_t)rows, 1};
+  cuuint64_t strides[2] = {64 * 4, (cuuint64_t)rows * 64 * 4};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r); return SSD_ERR_CUDA; }
+  return SSD_OK;
+}
 // [batch, seqlen, cols] sequence tensor: box = 64 cols x 128 rows
 int make_seq_map(CUtensorMap* m, const void* ptr, long long cols, long long L, long long B, long long stride_l,
                  long long stride_b, const char* what) {
@@ -2623,14 +2661,14 @@ bool tensor_state_fused_applies(const Geo& g) {
 }
 
 template <int P, int MODE>
-static int launch_state_scan(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const StateScanArgs& a, int* status,
-                             cudaStream_t s) {
+static int launch_state_scan(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tf,
+                             const StateScanArgs& a, int* status, cudaStream_t s) {
   auto k = k_state_scan_ps<P, MODE>;
-  constexpr size_t sm = PfCfg<P>::SMEM;
+  constexpr size_t sm = PfCfg<P, MODE>::SMEM;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int nunits = g.B * g.G * (g.hpg * P / 128);
   const int grid = nunits < sm_count() ? nunits : sm_count();
-  k<<<grid, PfCfg<P>::THREADS, sm, s>>>(g, tx, tb, a, status);
+  k<<<grid, PfCfg<P, MODE>::THREADS, sm, s>>>(g, tx, tb, ts, tf, a, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_state_scan" : "dstate_scan");
   return SSD_OK;
 }
@@ -2645,8 +2683,15 @@ int tensor_state_fused(const Geo& g, int mode, const void* xdy, long long sb, lo
   if (rc) return rc;
   StateScanArgs a{tab, st, st_bf, init, last, fwd_prev, fwd_fin, sdot};
   if (sdot_nw) *sdot_nw = 4 * (g.P / 32);
-  if (g.P == 32) return mode == 0 ? launch_state_scan<32, 0>(g, tx, tb, a, status, s) : launch_state_scan<32, 1>(g, tx, tb, a, status, s);
-  if (g.P == 64) return mode == 0 ? launch_state_scan<64, 0>(g, tx, tb, a, status, s) : launch_state_scan<64, 1>(g, tx, tb, a, status, s);
+  CUtensorMap ts = tx, tf = tx;   // placeholders unless the backward kernel reads the forward states
+  if (mode == 1 && sdot) {
+    rc = make_f32_rows_map(&ts, fwd_prev, (long long)g.B * g.nc * g.H * g.P, "forward chunk-entry states");
+    if (rc) return rc;
+    rc = make_f32_rows_map(&tf, fwd_fin, (long long)g.B * g.H * g.P, "forward final state");
+    if (rc) return rc;
+  }
+  if (g.P == 32) return mode == 0 ? launch_state_scan<32, 0>(g, tx, tb, ts, tf, a, status, s) : launch_state_scan<32, 1>(g, tx, tb, ts, tf, a, status, s);
+  if (g.P == 64) return mode == 0 ? launch_state_scan<64, 0>(g, tx, tb, ts, tf, a, status, s) : launch_state_scan<64, 1>(g, tx, tb, ts, tf, a, status, s);
   set_error("tensor_state_fused: unsupported headdim %d", g.P);
   return SSD_ERR_UNSUPPORTED;
 }
