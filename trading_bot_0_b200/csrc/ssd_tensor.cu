@@ -2077,16 +2077,18 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   if (s_abort) return;
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 1);
-      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 1);
+      // two MMA issuer lanes (dC side, dB side): tcgen05.commit tracks the MMAs of its own thread only, so every barrier that
+      // releases something both of them read expects one commit from each
+      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 2);
+      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 2);
       mbar_init(&bars.w_full[i], 1); mbar_init(&bars.w_empty[i], WS_SCALE_WARPS);
-      mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 1);
+      mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 2);
     }
     for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS); }
-    mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 1);
+    mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 2);
     for (int i = 0; i < 2; ++i) { mbar_init(&bars.wraw_done[i], 1); mbar_init(&bars.sc_full[i], WS_SCALE_WARPS); }
-    mbar_init(&bars.acc_full, 1); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
-    mbar_init(&bars.done, 1);
+    mbar_init(&bars.acc_full, 2); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
+    mbar_init(&bars.done, 2);
     mbar_fence_init();
   }
   if (warp == 17) tmem_alloc(&tmem_slot, 512);
@@ -2159,15 +2161,18 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         }
       }
     }
-  } else if (warp == 17) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 17 || warp == 18) {
+    // ------------------------------------------------------------------ MMA issuers.  One lane alone is busy ~64 % of the
+    // kernel (every tcgen05.mma costs its issuing thread ~50 cycles, 22 per head here), so the products are split by side:
+    // lane A (warp 17) issues W = dY X^T and everything that accumulates into dC, lane B (warp 18) everything into dB.
     if (lane == 0) {
+      const bool side_c = warp == 17;
       PROF_DECL(2)
       const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
       const uint64_t dSm0 = desc_sw128_mn(smem_u32(sSt), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sSt + SBOX_BYTES), 0, 0, SBOX_BYTES);
       const int total_blocks = my_tiles * nblk;
       int kw = 0;   // W products issued so far (global head counter of the W stage)
-      auto issue_w_block = [&](int kg) {   // all W products of global block kg
+      auto issue_w_block = [&](int kg) {   // all W products of global block kg (lane A only)
         if (kg >= total_blocks) return;
         const int ib = kg & 1;
         PW(0, w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45));
@@ -2185,7 +2190,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         }
         mma_commit(&bars.wraw_done[kg & 1]);   // the raw boxes of this block have been read by every W product
       };
-      issue_w_block(0);
+      if (side_c) issue_w_block(0);
       int kb = 0, kh = 0;
       for (int t = 0; t < my_tiles; ++t) {
         PW(0, w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43));
@@ -2202,28 +2207,32 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             PW(0, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
-            const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
+            if (side_c) {
+              const uint64_t dMk = desc_plain_k(mt, 128, 0);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              mma_bf16(tmDC, desc_adv(dMk, ks * 4096), desc_adv(dBm0, ks * 2048), idC, !first || ks > 0);
-              mma_bf16(tmDB, desc_adv(dMt, ks * 256), desc_adv(dCm0, ks * 2048), idB, !first || ks > 0);
+              for (int ks = 0; ks < 8; ++ks) mma_bf16(tmDC, desc_adv(dMk, ks * 4096), desc_adv(dBm0, ks * 2048), idC, !first || ks > 0);
+            } else {
+              const uint64_t dMt = desc_plain_mn(mt, 128, 0, 0);
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks) mma_bf16(tmDB, desc_adv(dMt, ks * 256), desc_adv(dCm0, ks * 2048), idB, !first || ks > 0);
             }
             first = false;
             mma_commit(&bars.m_empty[ms]);
           }
           // the next block's W products go out before this block's state terms, so the decay warps
           // find their next input ready when they come back from scaling this block's boxes
-          issue_w_block(kb + 1);
+          if (side_c) issue_w_block(kb + 1);
           PW(0, w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59));
           PW(0, w.wait(&bars.st_full, kb & 1, 57));
           tc_fence_after();
-          {
-            const uint64_t dXk = desc_sw128_k(inb, 0), dDYk = desc_sw128_k(inb + BOX_BYTES, 0);
+          if (side_c) {
+            const uint64_t dDYk = desc_sw128_k(inb + BOX_BYTES, 0);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              mma_bf16(tmDC, desc_adv(dDYk, ks * 32), desc_adv(dSm0, ks * 2048), idC, true);
-              mma_bf16(tmDB, desc_adv(dXk, ks * 32), desc_adv(dDSm0, ks * 2048), idC, true);
-            }
+            for (int ks = 0; ks < 4; ++ks) mma_bf16(tmDC, desc_adv(dDYk, ks * 32), desc_adv(dSm0, ks * 2048), idC, true);
+          } else {
+            const uint64_t dXk = desc_sw128_k(inb, 0);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) mma_bf16(tmDB, desc_adv(dXk, ks * 32), desc_adv(dDSm0, ks * 2048), idC, true);
           }
           mma_commit(&bars.st_empty);
           mma_commit(&bars.in_empty[ib]);
@@ -2233,7 +2242,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
-      PROF_FLUSH(2, 2, true)
+      PROF_FLUSH(side_c ? 2 : 4, 2, true)
     }
   } else if (warp < WS_SCALE_WARPS) {
     // ------------------------------------------------------------------ decay pass warps
