@@ -428,30 +428,31 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_state_tc(Geo g, const __grid_
 //   warp 16 (one lane)  issues the MMAs of a half as soon as that half is scaled, into one of two TMEM accumulators.
 // Every hand-over is a bounded mbarrier wait; a barrier is only ever waited on by a role that cannot fall two phases
 // behind it (each completion needs that role's own next step).
-template <int P>
+template <int P, int N_>
 struct PsCfg {
-  static constexpr int N = 64, HT = 128 / P, NX = 4;
+  static constexpr int N = N_, HT = 128 / P, NX = (N_ == 64) ? 4 : 3, NBX = N_ / 64;   // NBX: 64-column boxes of a B/C tile
   static constexpr int X_BYTES = 2 * BOX_BYTES;
   static constexpr int TBH = 256;                 // floats of a head's table that this kernel reads: the T_CS and T_DT sections
   static constexpr int TB_BYTES = HT * TBH * 4;
   static constexpr int W_MMA = 16, W_PROD = 17, THREADS = 18 * 32;
-  static constexpr size_t SMEM = 1024 + NX * X_BYTES + X_BYTES + 2 * BOX_BYTES + NX * TB_BYTES;
+  static constexpr int B_BYTES = NBX * BOX_BYTES;
+  static constexpr size_t SMEM = 1024 + NX * X_BYTES + X_BYTES + 2 * B_BYTES + NX * TB_BYTES;
   static_assert(T_CS == 0 && T_DT == 128, "the two sections must be the first 1 KB of a table");
 };
 
-template <int P, int MODE>
-__global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const __grid_constant__ CUtensorMap tmX,
+template <int P, int N_, int MODE>
+__global__ void __launch_bounds__(PsCfg<P, N_>::THREADS, 1) k_state_ps(Geo g, const __grid_constant__ CUtensorMap tmX,
                                                                    const __grid_constant__ CUtensorMap tmB,
                                                                    const float* __restrict__ tab, float* __restrict__ out,
                                                                    int* __restrict__ status) {
-  using Cfg = PsCfg<P>;
+  using Cfg = PsCfg<P, N_>;
   constexpr int N = Cfg::N, HT = Cfg::HT, NX = Cfg::NX;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sX = smem;                                  // NX x {two 64-column boxes}: the tile, scaled in place (high part)
   uint8_t* sL = sX + NX * Cfg::X_BYTES;                // low bf16 part of the tile being multiplied
   uint8_t* sB = sL + Cfg::X_BYTES;                     // 2 x B (or C) tile of an item
-  uint8_t* sTabs = sB + 2 * BOX_BYTES;                 // NX x the table sections of a tile's heads
+  uint8_t* sTabs = sB + 2 * Cfg::B_BYTES;              // NX x the table sections of a tile's heads
   __shared__ __align__(8) uint64_t x_full[NX], x_free[NX], b_full[2], b_free[2], half_ready[2], h0_done, mma_done[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -469,7 +470,7 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
     mbar_init(&h0_done, 1);
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(&tmem_slot, 128);
+  if (warp == 1) tmem_alloc(&tmem_slot, 2 * N);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -504,8 +505,9 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
           bulk_load(sTabs + slot * Cfg::TB_BYTES + hl * Cfg::TBH * 4, t0 + (size_t)hl * TAB, Cfg::TBH * 4, &x_full[slot]);
         if (mt == 0) {   // the item's B (or C) tile, after its first x tile so that this wait does not hold the x loads back
           if (n >= 2) w.wait(&b_free[n & 1], ((n >> 1) - 1) & 1, 15);
-          mbar_expect_tx(&b_full[n & 1], BOX_BYTES);
-          tma_load_3d(sB + (n & 1) * BOX_BYTES, &tmB, grp * N, c * QT, b, &b_full[n & 1]);
+          mbar_expect_tx(&b_full[n & 1], Cfg::B_BYTES);
+          for (int kb = 0; kb < Cfg::NBX; ++kb)
+            tma_load_3d(sB + (n & 1) * Cfg::B_BYTES + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &b_full[n & 1]);
         }
         if (++mt == MT) { mt = 0; ++n; }
       }
@@ -519,8 +521,8 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
       for (int k = 0; k < total; ++k) {
         const int slot = k % NX;
         const uint64_t dX0 = desc_sw128_mn(smem_u32(sX + slot * Cfg::X_BYTES), 0, 0, BOX_BYTES),
-                       dB0 = desc_sw128_mn(smem_u32(sB + (n & 1) * BOX_BYTES), 0, 0, BOX_BYTES);
-        const uint32_t acc = tm + (k & 1) * 64;
+                       dB0 = desc_sw128_mn(smem_u32(sB + (n & 1) * Cfg::B_BYTES), 0, 0, BOX_BYTES);
+        const uint32_t acc = tm + (k & 1) * N;
         if (mt == 0) w.wait(&b_full[n & 1], (n >> 1) & 1, 12);
         if (k >= 2) w.wait(&acc_empty[k & 1], ((k >> 1) - 1) & 1, 16);
         w.wait(&half_ready[0], k & 1, 17);
@@ -574,15 +576,20 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
       const int h0 = grp * g.hpg + mt * HT;
       const int row = tid & 127, part = tid >> 7;
       float* o = out + (((size_t)(b * g.nc + c) * g.H + h0) * P + row) * N + part * (N / PARTS);
-      float v[16];
-      tmem_ld16(tmem_addr(tm + (k & 1) * 64, (warp & 3) * 32, part * (N / PARTS)), v);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[k & 1]);
 #pragma unroll
-      for (int j = 0; j < 16; j += 8)
-        st_global_32B(o + j, make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3])),
-                      make_uint4(__float_as_uint(v[j + 4]), __float_as_uint(v[j + 5]), __float_as_uint(v[j + 6]), __float_as_uint(v[j + 7])));
+      for (int q = 0; q < N / PARTS / 16; ++q) {
+        float v[16];
+        tmem_ld16(tmem_addr(tm + (k & 1) * N, (warp & 3) * 32, part * (N / PARTS) + q * 16), v);
+        if (q == N / PARTS / 16 - 1) {   // the accumulator is in registers: hand it back before the stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[k & 1]);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j += 8)
+          st_global_32B(o + q * 16 + j, make_uint4(__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3])),
+                        make_uint4(__float_as_uint(v[j + 4]), __float_as_uint(v[j + 5]), __float_as_uint(v[j + 6]), __float_as_uint(v[j + 7])));
+      }
     };
     int n = 0, mt = 0, b = 0, grp = 0, c = 0;           // tile k
     int pb = 0, pgrp = 0, pc_ = 0, pmt = 0;             // tile k - 1
@@ -609,7 +616,7 @@ __global__ void __launch_bounds__(PsCfg<P>::THREADS, 1) k_state_ps(Geo g, const 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tm, 128);
+  if (warp == 1) tmem_dealloc(tm, 2 * N);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -2470,13 +2477,13 @@ static bool use_ps_state() {
 template <int P, int N, int MODE>
 int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* tab, float* out, int* status,
                  cudaStream_t s) {
-  if (N == 64 && use_ps_state()) {   // persistent, ring-fed version
-    auto kp = k_state_ps<P, MODE>;
-    constexpr size_t sm = PsCfg<P>::SMEM;
+  if (use_ps_state()) {   // persistent, ring-fed version
+    auto kp = k_state_ps<P, N, MODE>;
+    constexpr size_t sm = PsCfg<P, N>::SMEM;
     cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     const int nitems = g.B * g.G * g.nc;
     const int grid = nitems < sm_count() ? nitems : sm_count();
-    kp<<<grid, PsCfg<P>::THREADS, sm, s>>>(g, tx, tb, tab, out, status);
+    kp<<<grid, PsCfg<P, N>::THREADS, sm, s>>>(g, tx, tb, tab, out, status);
     SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_state_ps" : "dstates_local_ps");
     return SSD_OK;
   }
