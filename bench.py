@@ -226,6 +226,15 @@ def cpu_decode(c, sample_streams, threads, steps=16):
     return dt
 
 
+def workload_name(c, workload, world):
+    """The `config.workload` string: one per workload, the same in both arms."""
+    if workload == "cfg2":
+        return f"{c['name']}: {c['B']} streams per GPU, H{c['H']} P{c['P']} N{c['N']} G{c['G']}, fp32 state, bf16 step vectors"
+    sp = workload == "cfg4"
+    return (f"{c['name']}: B{c['B']} L{c['L']} H{c['H']} P{c['P']} N{c['N']} G{c['G']} Q{c['Q']}"
+            f"{' z-gated' if c['z'] else ''} fwd+bwd per GPU" + (" (sequence sharded)" if sp else ""))
+
+
 def run_reference(args, c):
     """The CPU path on all host cores, bounded sample per step; rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -253,7 +262,7 @@ def run_reference(args, c):
     line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(times),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": c["name"], "sample": desc},
+            "config": {"workload": workload_name(c, args.workload, args.gpus), "sample": desc},
             "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -407,8 +416,7 @@ def run_train(args, c, rank, world, local):
             "steps": args.steps, "warmup": nwarm, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if sp_mode and args.strong else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"{c['name']}: B{c['B']} L{c['L']} H{c['H']} P{c['P']} N{c['N']} G{c['G']} Q{c['Q']}"
-                                   f"{' z-gated' if c['z'] else ''} fwd+bwd per GPU" + (" (sequence sharded)" if sp_mode else ""),
+            "config": {"workload": workload_name(c, args.workload, world),
                        "algo": args.algo, "l2": f"inputs+outputs {op_bytes / 1e6:.0f} MB per step, larger than the 126 MB L2",
                        "parallelism": "sequence-parallel" if sp_mode else f"batch-sharded x{world}, no collective"},
             "roofline": roof,
@@ -491,7 +499,7 @@ def run_decode(args, c, rank, world, local):
     line = {"metric": "ssd_decode_steps_per_s", "value": world * 1e3 / ms_step, "unit": "steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": nwarm, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{c['name']}: {S} streams per GPU, H{H} P{P} N{N} G{G}, fp32 state, bf16 step vectors",
+            "config": {"workload": workload_name(c, args.workload, world),
                        "streams_total": S * world, "l2": f"state {S * H * P * N * 4 / 1e6:.0f} MB per GPU, larger than the 126 MB L2",
                        "inputs": f"{ring} distinct pre-drawn steps cycled", "parallelism": f"stream-sharded x{world}, no collective"},
             "roofline": {"bound": "hbm", "kernel": name, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
