@@ -53,8 +53,14 @@ typedef enum SsdDtype { SSD_F32 = 0, SSD_BF16 = 1 } SsdDtype;
 typedef enum SsdPass { SSD_PASS_FWD = 0, SSD_PASS_BWD = 1 } SsdPass;
 
 /* Kernel family selection.  AUTO picks the tcgen05 tensor-core kernels when dtype is bf16 and
- * the shape is one they cover, else the exact-fp32 CUDA-core kernels. */
-typedef enum SsdAlgo { SSD_ALGO_AUTO = 0, SSD_ALGO_FP32_CORES = 1, SSD_ALGO_TENSOR = 2 } SsdAlgo;
+ * the shape is one they cover, else the exact-fp32 CUDA-core kernels.  TENSOR insists on the
+ * tensor-core family (an error where it does not apply).  TENSOR_ONETILE is the same family
+ * restricted to its one-tile-per-CTA kernels (no persistent pipelines, chunk states and the
+ * scan over chunks as two kernels): the comparison arm the persistent kernels are measured
+ * against.  The library reads no environment variable; this field is the only switch. */
+typedef enum SsdAlgo {
+  SSD_ALGO_AUTO = 0, SSD_ALGO_FP32_CORES = 1, SSD_ALGO_TENSOR = 2, SSD_ALGO_TENSOR_ONETILE = 3
+} SsdAlgo;
 
 /*
  * Problem geometry.  `dtype` is the storage type of x, dt, B, C, z, y and of dx, dB, dC, dz, dy;
@@ -226,6 +232,7 @@ SSD_API const char* ssd_last_error(void);
  * whose kernels could overlap on the GPU (different streams, or different host threads) race
  * and must be serialised by the caller; the array keeps the previous call's contents and the
  * entry point re-initialises what it needs.  Results equal ssd_forward's for the same inputs.
+ * A bounded wait that ran out inside such a call is reported by ssd_noalloc_status (below).
  * This entry point has no counterpart in the reference.
  */
 #define SSD_NOALLOC_MAX_BYTES ((size_t)32 << 20)
@@ -295,6 +302,25 @@ SSD_API int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, co
  * No counterpart in the reference.
  */
 SSD_API int32_t ssd_selftest_bounded_wait(int32_t* device_status, int64_t max_cycles, void* cuda_stream);
+
+/*
+ * Reading the status word.  The reference follows every FFI call with an error read
+ * (`get_and_reset_last_err`, trading_bots/src/torch/cuda/graph.rs:107-118); the device-side counterpart is this word.
+ *   ssd_workspace_status        copies the word of `workspace` to the host on `cuda_stream` and WAITS for the stream
+ *                               (so it also covers every call issued on that stream before it); returns SSD_OK, or
+ *                               SSD_ERR_TIMEOUT with the wait-site code in ssd_last_error() and in *code_out (optional).
+ *                               Not while the stream is being captured.
+ *   ssd_workspace_status_async  enqueues the 4-byte copy to `code_dst` (device or pinned host memory) and returns at
+ *                               once; legal during stream capture.  Feed the value to ssd_status_check after the
+ *                               stream (or graph launch) has completed.
+ *   ssd_status_check            maps a status word to SSD_OK / SSD_ERR_TIMEOUT (message set).
+ *   ssd_noalloc_status          ssd_workspace_status for the array ssd_forward_noalloc computes in, which the caller
+ *                               cannot address.
+ */
+SSD_API int32_t ssd_workspace_status(const void* workspace, void* cuda_stream, int32_t* code_out);
+SSD_API int32_t ssd_workspace_status_async(const void* workspace, int32_t* code_dst, void* cuda_stream);
+SSD_API int32_t ssd_status_check(int32_t code);
+SSD_API int32_t ssd_noalloc_status(void* cuda_stream, int32_t* code_out);
 
 /*
  * Tracing.  ssd_launch_count: kernels this library has launched in this process (all threads).

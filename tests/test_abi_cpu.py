@@ -74,6 +74,26 @@ def test_null_pointers_are_rejected_before_any_launch(lib):
     assert lib.ssd_sp_prefix_state(None, None, 2, 0, 1, 1, 1, None, None, None) == -6
 
 
+def test_misaligned_pointer_returns_bad_alignment_without_a_launch(lib):
+    """Tensor-core family, an output pointer 8 bytes off a 16-byte boundary: refused on the host (nothing is launched, so
+    this runs without a GPU); the same pointers pass for the CUDA-core family up to the launch itself, which is not made."""
+    from trading_bot_0_b200 import _lib
+    d = _dims(seqlen=128, nheads=8, headdim=32, dstate=64, chunk=128, dtype=_lib.SSD_BF16, algo=_lib.ALGO_TENSOR)
+    need = lib.ssd_workspace_bytes(C.byref(d), 0)
+    assert need > 0
+    base = 0x7f0000000000
+    p = _lib.SsdFwdPtrs(*[C.c_void_p(base + i * 0x1000000) for i in range(5)], None, None, None, C.c_void_p(base + 0x9000008),
+                        None, None)
+    rc = lib.ssd_forward(C.byref(d), C.byref(p), C.c_void_p(base + 0xa000000), need, None)
+    assert rc == -2 and "y must be 16-byte aligned" in lib.ssd_last_error().decode()
+
+
+def test_status_word_mapping_needs_no_device(lib):
+    assert lib.ssd_status_check(0) == 0
+    assert lib.ssd_status_check(47) == -7
+    assert "47" in lib.ssd_last_error().decode()
+
+
 def test_host_side_validation_raises_without_a_gpu():
     import torch
     import trading_bot_0_b200 as T

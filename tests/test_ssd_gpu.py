@@ -240,3 +240,70 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable(lib):
     d = to_dev(inp, DEV)
     y, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=cfg.chunk)
     assert_close("y", y, y_ref, "fp32")
+
+
+def test_timed_out_wait_is_reported_through_the_status_calls(lib):
+    """The self-test's timed-out wait, pointed at the status word of a workspace-shaped buffer: ssd_workspace_status maps the
+    word to SSD_ERR_TIMEOUT with the wait-site code in the message, the asynchronous copy + ssd_status_check do the same,
+    a healthy workspace reads 0, and nothing faults."""
+    import ctypes as C
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib as L
+    ws = torch.zeros(256, dtype=torch.uint8, device=DEV)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert T.ssd.workspace_status(ws) == 0
+    assert lib.ssd_selftest_bounded_wait(C.c_void_p(ws.data_ptr()), 2_000_000, stream) == 0
+    with pytest.raises(L.SsdError) as ei:
+        T.ssd.workspace_status(ws)
+    assert ei.value.code == -7 and "99" in str(ei.value)
+    code = C.c_int32(-1)
+    assert lib.ssd_workspace_status(C.c_void_p(ws.data_ptr()), stream, C.byref(code)) == -7 and code.value == 99
+    dst = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert lib.ssd_workspace_status_async(C.c_void_p(ws.data_ptr()), C.c_void_p(dst.data_ptr()), stream) == 0
+    torch.cuda.synchronize()
+    assert lib.ssd_status_check(int(dst.item())) == -7
+    assert lib.ssd_status_check(0) == 0
+    # the next operator call clears the word of the workspace it runs in and is correct
+    cfg = O.CONFIGS[0]
+    inp = O.make_inputs(cfg)
+    d = to_dev(inp, DEV)
+    y, _, w2 = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=cfg.chunk, check=True)
+    y_ref, _ = O.ssd_sequential(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"])
+    assert_close("y", y, y_ref, "fp32")
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_backward_twice_on_one_saved_workspace(lib, dtype):
+    """retain_graph-style use: two backward calls on the workspace one forward left (fwd_saved = 1) give the same, correct
+    gradients; the CUDA-core backward keeps its per-group W sums apart from the forward's C B^T."""
+    import trading_bot_0_b200 as T
+    cfg = cfg_like(0, has_z=True, dtype=dtype)
+    inp = O.make_inputs(cfg, with_init_state=True)
+    ref = oracle_all(inp)
+    d = to_dev(inp, DEV)
+    args = (d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], d["z"], d["init_state"])
+    y, fin, ws = T.forward(*args, chunk=cfg.chunk, algo="fp32_cores", for_backward=True)
+    outs = [T.backward(d["dy"], *args, chunk=cfg.chunk, algo="fp32_cores", workspace=ws, fwd_saved=True, want_dinit=True)
+            for _ in range(2)]
+    torch.cuda.synchronize()
+    for k in GRADS + ("dz", "dinit"):
+        assert_close(k + " (first)", outs[0][k], ref[k], dtype)
+        assert torch.equal(outs[0][k], outs[1][k]), f"{k}: the second backward differs from the first"
+
+
+def test_misaligned_pointer_is_an_error_code_not_a_fault(lib):
+    """A y view that starts 8 bytes into an allocation: the tensor-core family refuses it with SSD_ERR_BAD_ALIGNMENT before
+    any launch; the CUDA-core family accepts it."""
+    import trading_bot_0_b200 as T
+    from trading_bot_0_b200 import _lib as L
+    cfg = O.SsdConfig("al", 1, 128, 8, 32, 64, 1, 128, "bf16")
+    d = to_dev(O.make_inputs(cfg), DEV)
+    n = d["x"].numel()
+    y_off = torch.empty(n + 8, dtype=torch.bfloat16, device=DEV)[4:4 + n].view_as(d["x"])
+    assert y_off.data_ptr() % 16 == 8
+    with pytest.raises(L.SsdError) as ei:
+        T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=128, algo="tensor", y=y_off)
+    assert ei.value.code == -2 and "16-byte" in str(ei.value)
+    y_ok, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=128, algo="tensor")
+    y2, _, _ = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], chunk=128, algo="fp32_cores", y=y_off)
+    assert (y2.float() - y_ok.float()).abs().max().item() <= 2e-2

@@ -43,7 +43,11 @@ def test_noalloc_forward_equals_workspace_forward_twice(lib, base, kw):
         fin = torch.full_like(fin_ref, float("nan"))
         rc = _call_noalloc(T, L, d, cfg, y, fin)
         assert rc == 0, L.load().ssd_last_error().decode()
-        torch.cuda.synchronize()
+        # the built-in scratch is private, so its status word is read through the library (waits for the stream)
+        code = C.c_int32(-1)
+        stream = C.c_void_p(torch.cuda.current_stream(DEV).cuda_stream)
+        with torch.cuda.device(DEV):
+            assert L.load().ssd_noalloc_status(stream, C.byref(code)) == 0 and code.value == 0
         assert (y.float() - y_ref.float()).abs().max().item() <= tol, f"call {rep}: y differs"
         assert (fin - fin_ref).abs().max().item() <= tol, f"call {rep}: final_state differs"
 

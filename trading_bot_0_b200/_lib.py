@@ -17,7 +17,7 @@ LIB_PATH = Path(os.environ.get("SSD_B200_LIB") or (Path(__file__).resolve().pare
 
 SSD_F32, SSD_BF16 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1
-ALGO_AUTO, ALGO_FP32_CORES, ALGO_TENSOR = 0, 1, 2
+ALGO_AUTO, ALGO_FP32_CORES, ALGO_TENSOR, ALGO_TENSOR_ONETILE = 0, 1, 2, 3
 STAGE_LOCAL, STAGE_TOTAL, STAGE_FINISH = 1, 2, 4
 
 EXPORTS = [
@@ -27,6 +27,7 @@ EXPORTS = [
     "ssd_profile_end", "ssd_forward_noalloc", "ssd_noalloc_max_bytes",
     "ssd_conv1d_workspace_bytes", "ssd_conv1d_forward", "ssd_conv1d_backward",
     "ssd_rmsnorm_workspace_bytes", "ssd_rmsnorm_forward", "ssd_rmsnorm_backward", "ssd_selftest_bounded_wait",
+    "ssd_workspace_status", "ssd_workspace_status_async", "ssd_status_check", "ssd_noalloc_status",
 ]
 
 
@@ -130,6 +131,14 @@ def load() -> C.CDLL:
     lib.ssd_noalloc_max_bytes.argtypes = []
     lib.ssd_selftest_bounded_wait.restype = i32
     lib.ssd_selftest_bounded_wait.argtypes = [vp, i64, vp]
+    lib.ssd_workspace_status.restype = i32
+    lib.ssd_workspace_status.argtypes = [vp, vp, C.POINTER(i32)]
+    lib.ssd_workspace_status_async.restype = i32
+    lib.ssd_workspace_status_async.argtypes = [vp, vp, vp]
+    lib.ssd_status_check.restype = i32
+    lib.ssd_status_check.argtypes = [i32]
+    lib.ssd_noalloc_status.restype = i32
+    lib.ssd_noalloc_status.argtypes = [vp, C.POINTER(i32)]
     lib.ssd_conv1d_workspace_bytes.restype = sz
     lib.ssd_conv1d_workspace_bytes.argtypes = [C.POINTER(SsdConvDims)]
     lib.ssd_conv1d_forward.restype = i32

@@ -17,6 +17,7 @@ LIB = PKG / "lib" / "libssd_b200.so"
 SOURCES = ["ssd_api.cu", "ssd_simt.cu", "ssd_decode.cu", "ssd_tensor.cu", "ssd_noalloc.cu", "ssd_prepost.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared"]
+LINK_LIBS = ["-ldl"]
 
 
 def nvcc_path() -> str:
@@ -35,17 +36,44 @@ def needs_build() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
+def _headers():
+    return list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [PKG.parent / "include" / "ssd_b200.h", Path(__file__)]
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """One object per source file (compiled in parallel, rebuilt only when the source or a header is newer), then one
+    link step.  No relocatable device code: every kernel is launched from the file that defines it."""
     if not force and not needs_build():
         return LIB
+    from concurrent.futures import ThreadPoolExecutor
     LIB.parent.mkdir(parents=True, exist_ok=True)
-    cmd = [nvcc_path(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
-           *[str(CSRC / s) for s in SOURCES], "-o", str(LIB)]
+    objdir = LIB.parent / "obj"
+    objdir.mkdir(exist_ok=True)
+    hdr_t = max(h.stat().st_mtime for h in _headers())
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + (["-Xptxas", "-v"] if verbose else [])
+
+    def compile_one(src: str):
+        obj = objdir / (src + ".o")
+        if not force and obj.exists() and obj.stat().st_mtime >= max(hdr_t, (CSRC / src).stat().st_mtime):
+            return obj, None
+        cmd = [nvcc_path(), *flags, "-c", str(CSRC / src), "-o", str(obj)]
+        return obj, (cmd, subprocess.run(cmd, capture_output=True, text=True))
+
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
+        results = list(ex.map(compile_one, SOURCES))
+    for obj, run in results:
+        if run is None:
+            continue
+        cmd, r = run
+        if verbose or r.returncode:
+            sys.stderr.write(r.stdout + r.stderr)
+        if r.returncode:
+            raise RuntimeError("nvcc failed: " + " ".join(cmd))
+    cmd = [nvcc_path(), "-shared", "-Xcompiler", "-fPIC", *[str(o) for o, _ in results], "-o", str(LIB), *LINK_LIBS]
     r = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or r.returncode:
-        sys.stderr.write(r.stdout + r.stderr)
     if r.returncode:
-        raise RuntimeError("nvcc failed: " + " ".join(cmd))
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("link failed: " + " ".join(cmd))
     return LIB
 
 

@@ -17,6 +17,7 @@ struct Geo {
   int B, L, H, P, N, G, Q, nc, hpg;  // hpg = heads per group
   long long xsb, xsl, dtsb, dtsl, bsb, bsl, csb, csl, zsb, zsl, ysb, ysl;
   int dt_softplus;                     // step size = softplus(dt + dt_bias) instead of dt + dt_bias
+  int onetile;                         // tensor family: the one-tile-per-CTA kernels for every shape (SSD_ALGO_TENSOR_ONETILE)
 };
 
 // The step-size pre-activation of a Mamba-2 layer, fused where dt is first read.  Above 20 softplus is the
@@ -32,7 +33,7 @@ struct WsLayout {
   size_t cs, dtf, states, fin, cb;                   // forward
   size_t tab, prev_bf;                               // forward, tensor-core family only (else empty)
   size_t ds_bf;                                      // backward, tensor-core family only
-  size_t dstates, dyp, dcsp, ddtd, ddot, sdot, dapart, ddpart, dini;  // backward extras
+  size_t dstates, wsum, dyp, dcsp, ddtd, ddot, sdot, dapart, ddpart, dini;  // backward extras (wsum: CUDA-core family only)
   size_t total_fwd, total_bwd;
 };
 

@@ -59,14 +59,12 @@ static int make_geo(const SsdDims* d, Geo* g) {
   }
   if (d->chunk > 256) { set_error("chunk (%d) must be <= 256", d->chunk); return SSD_ERR_UNSUPPORTED; }
   if (d->dtype != SSD_F32 && d->dtype != SSD_BF16) { set_error("unknown dtype %d", d->dtype); return SSD_ERR_UNSUPPORTED; }
-  if (d->algo < SSD_ALGO_AUTO || d->algo > SSD_ALGO_TENSOR) { set_error("unknown algo %d", d->algo); return SSD_ERR_UNSUPPORTED; }
+  if (d->algo < SSD_ALGO_AUTO || d->algo > SSD_ALGO_TENSOR_ONETILE) { set_error("unknown algo %d", d->algo); return SSD_ERR_UNSUPPORTED; }
   g->B = d->batch; g->L = d->seqlen; g->H = d->nheads; g->P = d->headdim; g->N = d->dstate; g->G = d->ngroups;
   g->Q = d->chunk; g->nc = (d->seqlen + d->chunk - 1) / d->chunk; g->hpg = d->nheads / d->ngroups;
   g->dt_softplus = d->dt_softplus != 0;
-  if ((long long)g->nc * g->H > 65535 || g->B > 65535) {
-    set_error("grid limits: nchunks*nheads (%lld) and batch (%d) must each be <= 65535", (long long)g->nc * g->H, g->B);
-    return SSD_ERR_UNSUPPORTED;
-  }
+  g->onetile = d->algo == SSD_ALGO_TENSOR_ONETILE;
+  if (g->B > 65535) { set_error("batch (%d) must be <= 65535 (grid limit)", g->B); return SSD_ERR_UNSUPPORTED; }
   const long long HP = (long long)g->H * g->P, GN = (long long)g->G * g->N;
   auto pick = [](long long v, long long dflt) { return v ? v : dflt; };
   g->xsl = pick(d->x_stride_l, HP);     g->xsb = pick(d->x_stride_b, HP * g->L);
@@ -115,6 +113,7 @@ static void make_layout(const Geo& g, bool has_z, bool tcfam, WsLayout* w) {
   w->total_fwd = o;
   w->dstates = take(nst);
   w->ds_bf = take(tcfam ? nst / 2 : 0);
+  w->wsum = take(tcfam ? 0 : ncb);
   w->dyp = take(has_z ? (size_t)g.B * g.L * g.H * g.P * f : 0);
   w->dcsp = take(nq); w->ddtd = take(nq); w->ddot = take(nq);
   w->sdot = take(nbh * (tcfam ? 64 : 1));   // tensor family: up to 64 warp-partial sums per entry
@@ -127,13 +126,31 @@ static bool family_is_tensor(const Geo& g, const SsdDims* d) {
   return d->algo != SSD_ALGO_FP32_CORES && tensor_supported(g, d->dtype, nullptr);
 }
 
+// The CUDA-core kernels put (chunk, head) on one grid axis.
+static int check_core_grid(const Geo& g) {
+  if ((long long)g.nc * g.H > 65535) {
+    set_error("CUDA-core family: nchunks*nheads (%lld) must be <= 65535 (grid limit)", (long long)g.nc * g.H);
+    return SSD_ERR_UNSUPPORTED;
+  }
+  return 0;
+}
+
 // Kernel-family choice: 1 = tensor cores, 0 = CUDA cores, <0 = error.
 static int pick_family(const Geo& g, const SsdDims* d) {
-  if (d->algo == SSD_ALGO_FP32_CORES) return 0;
+  if (d->algo == SSD_ALGO_FP32_CORES) return check_core_grid(g);
   const char* why = "";
   if (tensor_supported(g, d->dtype, &why)) return 1;
-  if (d->algo == SSD_ALGO_TENSOR) { set_error("algo=TENSOR not possible for these dims: %s", why); return SSD_ERR_UNSUPPORTED; }
-  return 0;
+  if (d->algo != SSD_ALGO_AUTO) { set_error("algo=TENSOR not possible for these dims: %s", why); return SSD_ERR_UNSUPPORTED; }
+  return check_core_grid(g);
+}
+
+// The tensor-core kernels move whole 16-byte vectors through pointers that no tensor map checks (z, y, dx, dz, dB, dC).
+static int check_align16(const char* name, const void* p) {
+  if (p && ((uintptr_t)p & 15)) {
+    set_error("%s must be 16-byte aligned for the tensor-core kernels (got %p)", name, p);
+    return SSD_ERR_BAD_ALIGNMENT;
+  }
+  return SSD_OK;
 }
 
 static int check_ws(const void* ws, size_t have, size_t need) {
@@ -141,6 +158,25 @@ static int check_ws(const void* ws, size_t have, size_t need) {
   if (((uintptr_t)ws) & 255) { set_error("workspace must be 256-byte aligned"); return SSD_ERR_BAD_ALIGNMENT; }
   if (have < need) { set_error("workspace too small: have %zu bytes, need %zu", have, need); return SSD_ERR_WORKSPACE_TOO_SMALL; }
   return SSD_OK;
+}
+
+int status_code_to_rc(int32_t code, const char* where) {
+  if (code == 0) return SSD_OK;
+  set_error("%s: a bounded wait inside a pipelined kernel ran out (wait-site code %d); the results of that call are invalid, "
+            "the context is still usable", where, (int)code);
+  return SSD_ERR_TIMEOUT;
+}
+int read_status_sync(const void* word, void* cuda_stream, int32_t* code_out, const char* where) {
+  int32_t code = 0;
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  cudaError_t e = cudaMemcpyAsync(&code, word, sizeof(code), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    set_error("%s: reading the status word failed: %s (not usable while the stream is being captured)", where, cudaGetErrorString(e));
+    return SSD_ERR_CUDA;
+  }
+  if (code_out) *code_out = code;
+  return status_code_to_rc(code, where);
 }
 
 }  // namespace ssd
@@ -224,6 +260,12 @@ int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* works
   q.final_state = nullptr;  // kernels always leave the final state in the workspace; copied out below
   const int fam = pick_family(g, dims);
   if (fam < 0) return fam;
+  if (fam == 1) {
+    const void* ptrs[] = {p->x, p->Bm, p->Cm, p->z, p->y};
+    const char* names[] = {"x", "B", "C", "z", "y"};
+    for (int i = 0; i < 5; ++i)
+      if ((rc = check_align16(names[i], ptrs[i]))) return rc;
+  }
   rc = run_forward(g, dims->dtype, fam == 1, q, (char*)workspace, w, s, stages);
   if (rc) return rc;
   if (p->final_state && (stages & (SSD_STAGE_TOTAL | SSD_STAGE_FINISH))) {
@@ -261,6 +303,12 @@ int32_t ssd_backward_staged(const SsdDims* dims, const SsdBwdPtrs* p, void* work
   if (rc) return rc;
   const int fam = pick_family(g, dims);
   if (fam < 0) return fam;
+  if (fam == 1) {
+    const void* ptrs[] = {p->x, p->Bm, p->Cm, p->z, p->dy, p->dx, p->dz, p->dB, p->dC};
+    const char* names[] = {"x", "B", "C", "z", "dy", "dx", "dz", "dB", "dC"};
+    for (int i = 0; i < 9; ++i)
+      if ((rc = check_align16(names[i], ptrs[i]))) return rc;
+  }
   return run_backward(g, dims->dtype, fam == 1, *p, (char*)workspace, w, (cudaStream_t)cuda_stream, stages);
 }
 
@@ -303,6 +351,27 @@ int32_t ssd_state_update(const SsdStepDims* d, const SsdStepPtrs* p, void* cuda_
     }
   }
   return decode_step(e, *p, (cudaStream_t)cuda_stream);
+}
+
+// ---- status word ----------------------------------------------------------------------------------
+
+int32_t ssd_workspace_status(const void* workspace, void* cuda_stream, int32_t* code_out) {
+  clear_error();
+  if (!workspace) { set_error("workspace is NULL"); return SSD_ERR_NULL_POINTER; }
+  return read_status_sync(workspace, cuda_stream, code_out, "ssd_workspace_status");
+}
+
+int32_t ssd_workspace_status_async(const void* workspace, int32_t* code_dst, void* cuda_stream) {
+  clear_error();
+  if (!workspace || !code_dst) { set_error("workspace/code_dst is NULL"); return SSD_ERR_NULL_POINTER; }
+  cudaError_t e = cudaMemcpyAsync(code_dst, workspace, sizeof(int32_t), cudaMemcpyDefault, (cudaStream_t)cuda_stream);
+  if (e != cudaSuccess) { set_error("ssd_workspace_status_async: %s", cudaGetErrorString(e)); return SSD_ERR_CUDA; }
+  return SSD_OK;
+}
+
+int32_t ssd_status_check(int32_t code) {
+  clear_error();
+  return status_code_to_rc(code, "ssd_status_check");
 }
 
 int32_t ssd_selftest_bounded_wait(int32_t* device_status, int64_t max_cycles, void* cuda_stream) {

@@ -37,6 +37,10 @@ int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const
 int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
                const void* ds_bf, int* status, cudaStream_t s);
 
+// status word of a workspace -> SSD_OK / SSD_ERR_TIMEOUT (message set); the sync reader copies it to the host first
+int status_code_to_rc(int32_t code, const char* where);
+int read_status_sync(const void* word, void* cuda_stream, int32_t* code_out, const char* where);
+
 int tensor_selftest_wait(int* status, long long max_cycles, cudaStream_t s);
 int decode_step(const SsdStepDims& d, const SsdStepPtrs& p, cudaStream_t s);
 int reset_rows(float* state, long long row_elems, const long long* idx, long long count, long long streams,

@@ -816,6 +816,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   void* prev_bf = ws + w.prev_bf;
   void* ds_bf = ws + w.ds_bf;
   float* dst = (float*)(ws + w.dstates);
+  float* wsum = (float*)(ws + w.wsum);   // CUDA-core family: a segment of its own, so the forward's C B^T survives a backward
   float* dyp = (float*)(ws + w.dyp);
   float* dcsp = (float*)(ws + w.dcsp);
   float* ddtd = (float*)(ws + w.ddtd);
@@ -902,13 +903,13 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       k_dx<T><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, p.D, dys, cs, dtf, cb, dst,
                                                              (T*)p.dx, ddtd);
       SSD_CUDA_CHECK_LAUNCH("dx");
-      k_dw<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, x, dys, cs, dtf, cb /* reused as wsum */);
+      k_dw<T><<<dim3(tq * tq, g.nc * g.G, g.B), NT, 0, s>>>(g, x, dys, cs, dtf, wsum);
       SSD_CUDA_CHECK_LAUNCH("dw");
       k_dbc<T, 0><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, g.bsb, g.bsl, dys, cs, dtf,
-                                                                 cb, states, (T*)p.dC);
+                                                                 wsum, states, (T*)p.dC);
       SSD_CUDA_CHECK_LAUNCH("dC");
       k_dbc<T, 1><<<dim3(tq * tn, g.nc * g.G, g.B), NT, 0, s>>>(g, x, (const T*)p.Cm, g.csb, g.csl, dys, cs, dtf,
-                                                                 cb, dst, (T*)p.dB);
+                                                                 wsum, dst, (T*)p.dB);
       SSD_CUDA_CHECK_LAUNCH("dB");
     }
     k_ddt<<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, p.A, dtf, dcsp, ddtd, ddot, sdot, sdot_nw, p.ddt, dapart, ddpart);

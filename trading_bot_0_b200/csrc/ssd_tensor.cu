@@ -45,24 +45,12 @@ constexpr int T_CS = 0, T_DT = 128, T_CF = 256, T_DS = 384;   // table sections,
 struct Waiter {
   int* status;
   bool dead;
-#ifdef SSD_WS_DEBUG
-  unsigned long long* dbg;   // counters in shared memory: [code - 41] waiting cycles per wait site, 16.. free use
-  __device__ __forceinline__ void add(int idx, long long cycles) {
-    if (dbg && (threadIdx.x & 31) == 0) atomicAdd(dbg + idx, (unsigned long long)cycles);
-  }
-#endif
   __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
     if (dead) return;
-#ifdef SSD_WS_DEBUG
-    const long long t0 = clock64();
-#endif
     if (!mbar_wait(bar, parity)) {
       dead = true;
       atomicExch(status, code);
     }
-#ifdef SSD_WS_DEBUG
-    if (code >= 41 && code < 57) add(code - 41, clock64() - t0);
-#endif
   }
 };
 
@@ -1343,21 +1331,6 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // parity n&1 and `empty` with parity (n&1)^1 (a fresh barrier passes a wait on parity 1).
 // TMEM: G x2 (256 columns) + {Y, Y_off} x2 (256 columns) = 512.  Same math and operand layouts as
 // k_scan_tc; MODE as there.
-// Light per-role profiling of the persistent kernels (-DWS_PROF): register accumulators in one lane per role,
-// added to the 64-bit counters behind the status word when the role ends.
-#ifdef WS_PROF
-#define PROF_DECL(n) long long pw[n] = {0}; const long long p_start = clock64();
-#define PW(i, stmt) { const long long p0_ = clock64(); stmt; pw[i] += clock64() - p0_; }
-#define PROF_T(name) const long long name = clock64();
-#define PROF_ADD(i, name) pw[i] += clock64() - name;
-#define PROF_FLUSH(base, n, cond) if (cond) { pw[(n) - 1] = clock64() - p_start; for (int i_ = 0; i_ < (n); ++i_) atomicAdd((unsigned long long*)(status + 8) + (base) + i_, (unsigned long long)pw[i_]); }
-#else
-#define PROF_DECL(n)
-#define PW(i, stmt) { stmt; }
-#define PROF_T(name)
-#define PROF_ADD(i, name)
-#define PROF_FLUSH(base, n, cond)
-#endif
 constexpr int WS_THREADS = 28 * 32;
 constexpr int WS_SCALE_WARPS = 16, WS_EPI_WARPS = 8;
 
@@ -1452,12 +1425,11 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   if (warp == Cfg::W_PROD) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      PROF_DECL(4)
       auto load_cb = [&](int t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
         const int cs_ = t & 1;
-        PW(0, w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41));
+        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
         uint8_t* keep = sCB + cs_ * Cfg::CB_BYTES;
         mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
         tma_load_3d(keep, (MODE == 2) ? &tmB : &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
@@ -1471,7 +1443,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const int h0 = grp * g.hpg + (kg % nblk) * HB;
         for (int hl = 0; hl < HB; ++hl) {
           const int kh = kg * HB + hl, ts = kh % NTH;
-          PW(1, w.wait(&bars.tab_empty[ts], ((kh / NTH) & 1) ^ 1, 49));
+          w.wait(&bars.tab_empty[ts], ((kh / NTH) & 1) ^ 1, 49);
           mbar_expect_tx(&bars.tab_full[ts], TAB_BYTES);
           bulk_load(sTab + ts * TAB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0 + hl) * TAB, TAB_BYTES, &bars.tab_full[ts]);
         }
@@ -1486,7 +1458,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           load_tab(kb + 2);
           const int ib = kb & 1;
-          PW(2, w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42));
+          w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
           uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
           const int h0 = grp * g.hpg + blk * HB;
           const int col = grp * g.hpg * P + blk * 64;
@@ -1497,20 +1469,8 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
           // the next G while this tile is still being worked on
           if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
-#ifdef WS_PF_STREAM   // one block of the next tile per block of this one
-          if (t + 1 < my_tiles) {
-            int b2, grp2, c2;
-            tile_coords(t + 1, b2, grp2, c2);
-            tma_prefetch_3d(&tmX, grp2 * g.hpg * P + blk * 64, c2 * QT, b2);
-            if (NBOX == 2) tma_prefetch_3d(&tmDY, grp2 * g.hpg * P + blk * 64, c2 * QT, b2);
-#if WS_PF_STREAM > 1
-            tma_prefetch_3d(&tmS, 0, (grp2 * g.hpg + blk * HB) * P, b2 * g.nc + c2);
-#endif
-          }
-#endif
         }
       }
-      PROF_FLUSH(0, 4, true)
     }
   } else if (warp >= Cfg::W_MMA && warp < Cfg::W_MMA + Cfg::NI) {
     // ------------------------------------------------------------------ MMA issuers: issuer mi takes head mi of every
@@ -1518,13 +1478,12 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     // block-level barriers expect one arrival per issuer.
     const int mi = warp - Cfg::W_MMA;
     if (lane == 0) {
-      PROF_DECL(6)
       const uint32_t idG = make_idesc(128, 128, 0, 0);
       const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
       constexpr uint32_t M_STEP = (MODE == 2) ? 256 : 4096;
       auto issue_g = [&](int t) {
         const int s_ = t & 1;
-        PW(0, w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43); w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44));
+        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43); w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
         tc_fence_after();
         const uint32_t keep = smem_u32(sCB + s_ * Cfg::CB_BYTES), other = keep + BOX_BYTES;
         const uint64_t dc = desc_sw128_k((MODE == 2) ? other : keep, 0), db = desc_sw128_k((MODE == 2) ? keep : other, 0);
@@ -1540,13 +1499,12 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const int ib = kb & 1, ab = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
           const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
-          PW(1, w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45));
-          PW(2, w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46));
+          w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
+          w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46);
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             if (hl != mi) continue;
             const int ms = kh % NM;
-            PW(3, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
-            PROF_T(ph0)
+            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             const uint64_t dM0 = (MODE == 2) ? desc_plain_mn(mt, 128, 0, 0) : desc_plain_k(mt, 128, 0);
@@ -1560,7 +1518,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
               for (int ks = 0; ks < 4; ++ks) mma_bf16(tmYo, desc_adv(dK0, ks * 32), desc_adv(dS0, ks * 32), idO, ks > 0);
             }
             mma_commit(&bars.m_empty[ms]);
-            PROF_ADD(4, ph0)
           }
           mma_commit(&bars.in_empty[ib]);
           if (blk == nblk - 1) mma_commit(&bars.cb_empty[t & 1]);
@@ -1570,7 +1527,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
-      PROF_FLUSH(4 + 6 * mi, 6, true)
     }
   } else if (warp < Cfg::DW) {
     // ------------------------------------------------------------------ decay pass: group wg owns heads kh = wg (mod NM)
@@ -1578,25 +1534,23 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int wg = warp / (4 * Cfg::NCH), ch = (warp >> 2) % Cfg::NCH, rb = warp & 3, row = rb * 32 + lane;
     const uint32_t mrow = smem_u32(sM + wg * 2 * BOX_BYTES) + row * 16;
     int kh = 0;
-    PROF_DECL(6)
     for (int t = 0; t < my_tiles; ++t) {
       const int gs = t & 1;
-      PW(0, w.wait(&bars.g_full[gs], (t >> 1) & 1, 51));
+      w.wait(&bars.g_full[gs], (t >> 1) & 1, 51);
       tc_fence_after();
       const uint32_t tm_row = tmem_addr(tm + gs * 128, rb * 32, 0);
       for (int hh = 0; hh < nblk * HB; ++hh, ++kh) {
         if (kh % NM != wg) continue;
         const int ts = kh % NTH;
-        PW(1, w.wait(&bars.tab_full[ts], (kh / NTH) & 1, 52));
-        PW(2, w.wait(&bars.m_empty[wg], ((kh / NM) & 1) ^ 1, 53));
-        PW(3, decay_row<Cfg::NCH>(rb, ch, tm_row, (const float*)(sTab + ts * TAB_BYTES), row, mrow));
-        PW(4, fence_async_smem(); __syncwarp(); if (lane == 0) { mbar_arrive(&bars.m_full[wg]); mbar_arrive(&bars.tab_empty[ts]); });
+        w.wait(&bars.tab_full[ts], (kh / NTH) & 1, 52);
+        w.wait(&bars.m_empty[wg], ((kh / NM) & 1) ^ 1, 53);
+        decay_row<Cfg::NCH>(rb, ch, tm_row, (const float*)(sTab + ts * TAB_BYTES), row, mrow);
+        fence_async_smem(); __syncwarp(); if (lane == 0) { mbar_arrive(&bars.m_full[wg]); mbar_arrive(&bars.tab_empty[ts]); }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.g_empty[gs]);
     }
-    PROF_FLUSH(16, 6, lane == 0 && rb == 3 && wg == 0)
   } else if (warp >= Cfg::W_EPI) {
     // ------------------------------------------------------------------ epilogue warps
     reg_dec<Cfg::R_EPI>();
@@ -1604,7 +1558,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
     const int hl_e = (half * 32) / P;
     int kb = 0;
-    PROF_DECL(6)
     for (int t = 0; t < my_tiles; ++t) {
       int b, grp, c;
       tile_coords(t, b, grp, c);
@@ -1618,14 +1571,13 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
         const int h0 = grp * g.hpg + blk * HB, h_e = h0 + hl_e;
         const float Dh = D ? __ldg(D + h_e) : 0.f;
-        PW(0, w.wait(&bars.tab_full[ts], (khe / NTH) & 1, 56));
+        w.wait(&bars.tab_full[ts], (khe / NTH) & 1, 56);
         const float cs_r = tb[T_CS + row], dt_r = tb[T_DT + row];
         const float osc = (MODE == 2) ? dt_r * ex2(tb[T_CS + 127] - cs_r) : ex2(cs_r);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
-        PW(1, w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54));
-        PW(2, w.wait(&bars.acc_full[ab], (kb >> 1) & 1, 55));
-        PROF_T(pe0)
+        w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
+        w.wait(&bars.acc_full[ab], (kb >> 1) & 1, 55);
         tc_fence_after();
         const long long colo = (long long)h0 * P + half * 32;
         const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
@@ -1696,7 +1648,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           if (MODE == 0) st_global_32B(y + b * g.ysb + (long long)t_row * g.ysl + colo + h16 * 16, ov[0], ov[1]);
           if (MODE == 2) st_global_32B(dx + dense + h16 * 16, ov[0], ov[1]);
         }
-        PROF_ADD(3, pe0)
         if (MODE != 0) {
           if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
             asm volatile("bar.sync 1, 256;" ::: "memory");   // previous block's exchange fully read
@@ -1716,7 +1667,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
       }
     }
-    PROF_FLUSH(22, 6, lane == 0 && ew == 3)
   }
   tc_fence_before();
   __syncthreads();
@@ -1859,13 +1809,12 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   } else if (warp == 17) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      PROF_DECL(2)
       const uint32_t idG = make_idesc(128, 128, 0, 0);
       const uint32_t idY = make_idesc(128, P, 0, 1), idU = make_idesc(128, P, 1, 1), idO = make_idesc(128, 64, 0, 0);
       auto issue_g = [&](int t) {
         const int s_ = t & 1;
-        PW(0, w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43));
-        PW(0, w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44));
+        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43);
+        w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
         tc_fence_after();
         const uint32_t ct = smem_u32(sCB + s_ * Cfg::CB_BYTES);
         const uint64_t dc = desc_sw128_k(ct, 0), db = desc_sw128_k(ct + BOX_BYTES, 0);
@@ -1882,12 +1831,12 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           const int ib = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
-          PW(0, w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45));
-          PW(0, w.wait(&bars.st_full, kb & 1, 57));
-          PW(0, w.wait(&bars.acc_empty, (kb & 1) ^ 1, 46));
+          w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
+          w.wait(&bars.st_full, kb & 1, 57);
+          w.wait(&bars.acc_empty, (kb & 1) ^ 1, 46);
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             const int ms = kh % NM;
-            PW(0, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
+            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
@@ -1915,7 +1864,6 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
-      PROF_FLUSH(0, 2, true)
     }
   } else if (warp < WS_SCALE_WARPS) {
     // ------------------------------------------------------------------ decay pass warps (they hand registers to the epilogue)
@@ -2174,7 +2122,6 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     // lane A (warp 17) issues W = dY X^T and everything that accumulates into dC, lane B (warp 18) everything into dB.
     if (lane == 0) {
       const bool side_c = warp == 17;
-      PROF_DECL(2)
       const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
       const uint64_t dSm0 = desc_sw128_mn(smem_u32(sSt), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sSt + SBOX_BYTES), 0, 0, SBOX_BYTES);
       const int total_blocks = my_tiles * nblk;
@@ -2182,13 +2129,13 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       auto issue_w_block = [&](int kg) {   // all W products of global block kg (lane A only)
         if (kg >= total_blocks) return;
         const int ib = kg & 1;
-        PW(0, w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45));
+        w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45);
         tc_fence_after();
         const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
         const uint64_t dX0 = desc_sw128_k(inb, 0), dDY0 = desc_sw128_k(inb + BOX_BYTES, 0);
         for (int hl = 0; hl < HB; ++hl, ++kw) {
           const int ws = kw & 1;
-          PW(0, w.wait(&bars.w_empty[ws], ((kw >> 1) & 1) ^ 1, 58));
+          w.wait(&bars.w_empty[ws], ((kw >> 1) & 1) ^ 1, 58);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < P / 16; ++ks)
@@ -2200,8 +2147,8 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       if (side_c) issue_w_block(0);
       int kb = 0, kh = 0;
       for (int t = 0; t < my_tiles; ++t) {
-        PW(0, w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43));
-        PW(0, w.wait(&bars.acc_empty, (t & 1) ^ 1, 46));
+        w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43);
+        w.wait(&bars.acc_empty, (t & 1) ^ 1, 46);
         tc_fence_after();
         const uint32_t ct = smem_u32(sCB + (t & 1) * Cfg::CB_BYTES);
         const uint64_t dBm0 = desc_sw128_mn(ct, 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(ct + BOX_BYTES, 0, 0, BOX_BYTES);
@@ -2211,7 +2158,7 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             const int ms = kh % NM;
-            PW(0, w.wait(&bars.m_full[ms], (kh / NM) & 1, 47));
+            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             if (side_c) {
@@ -2229,8 +2176,8 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           // the next block's W products go out before this block's state terms, so the decay warps
           // find their next input ready when they come back from scaling this block's boxes
           if (side_c) issue_w_block(kb + 1);
-          PW(0, w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59));
-          PW(0, w.wait(&bars.st_full, kb & 1, 57));
+          w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59);
+          w.wait(&bars.st_full, kb & 1, 57);
           tc_fence_after();
           if (side_c) {
             const uint64_t dDYk = desc_sw128_k(inb + BOX_BYTES, 0);
@@ -2249,7 +2196,6 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
-      PROF_FLUSH(side_c ? 2 : 4, 2, true)
     }
   } else if (warp < WS_SCALE_WARPS) {
     // ------------------------------------------------------------------ decay pass warps
@@ -2462,22 +2408,12 @@ constexpr size_t scan_smem() {
 template <int P, int N>
 constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * TAB_BYTES; }
 
-bool use_ws_scan();
 int sm_count();
-// SSD_B200_STATE=classic keeps the one-tile-per-CTA chunk-state kernel for dstate 64 too.
-static bool use_ps_state() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("SSD_B200_STATE");
-    v = (e && strcmp(e, "classic") == 0) ? 0 : 1;
-  }
-  return v == 1 && use_ws_scan();
-}
 
 template <int P, int N, int MODE>
 int launch_state(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const float* tab, float* out, int* status,
                  cudaStream_t s) {
-  if (use_ps_state()) {   // persistent, ring-fed version
+  if (!g.onetile) {   // persistent, ring-fed version
     auto kp = k_state_ps<P, N, MODE>;
     constexpr size_t sm = PsCfg<P, N>::SMEM;
     cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
@@ -2504,16 +2440,6 @@ struct SeqMaps {
   CUtensorMap x, dy, b, c, s, ds;
 };
 
-// SSD_B200_SCAN=classic selects the one-tile-per-CTA kernels for every shape (default: the
-// persistent warp-specialised kernel where it applies, i.e. dstate 64).
-bool use_ws_scan() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("SSD_B200_SCAN");
-    v = (e && strcmp(e, "classic") == 0) ? 0 : 1;
-  }
-  return v == 1;
-}
 int sm_count() {
   static int n[64] = {0};
   int dev = 0;
@@ -2538,7 +2464,7 @@ int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const 
 
 template <int P, int N, int MODE>
 int launch_scan(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const ScanArgs& a, int* status, cudaStream_t s) {
-  if (N == 64 && use_ws_scan()) return launch_scan_ws<P, MODE>(g, m, ts, a, status, s);
+  if (N == 64 && !g.onetile) return launch_scan_ws<P, MODE>(g, m, ts, a, status, s);
   constexpr int IBUF = (MODE == 0 && N < 128) ? 2 : 1;
   auto k = k_scan_tc<P, N, IBUF, MODE>;
   constexpr size_t sm = scan_smem<P, N, IBUF, MODE>();
@@ -2576,7 +2502,7 @@ int launch_dbc_ws(const Geo& g, const SeqMaps& m, const float* tab, void* dB, vo
 
 template <int P, int N>
 int launch_dbc(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
-  if (N == 64 && use_ws_scan()) return launch_dbc_ws<P>(g, m, tab, dB, dC, status, s);
+  if (N == 64 && !g.onetile) return launch_dbc_ws<P>(g, m, tab, dB, dC, status, s);
   auto k = k_dbc_tc<P, N>;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dbc_smem<P, N>());
   k<<<dim3(g.nc, g.G, g.B), TC_THREADS, dbc_smem<P, N>(), s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, (bf16*)dB, (bf16*)dC,
@@ -2665,16 +2591,8 @@ int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, lo
 #undef CALL
 }
 
-// Chunk states and the scan over chunks in one launch (see k_state_scan_ps).  SSD_B200_STATE=classic or =split keeps
-// the two-kernel path.
-bool tensor_state_fused_applies(const Geo& g) {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("SSD_B200_STATE");
-    v = (e && (strcmp(e, "classic") == 0 || strcmp(e, "split") == 0)) ? 0 : 1;
-  }
-  return v == 1 && g.N == 64 && use_ws_scan();
-}
+// Chunk states and the scan over chunks in one launch (see k_state_scan_ps): dstate 64, persistent family.
+bool tensor_state_fused_applies(const Geo& g) { return g.N == 64 && !g.onetile; }
 
 template <int P, int MODE>
 static int launch_state_scan(const Geo& g, const CUtensorMap& tx, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tf,
@@ -2748,7 +2666,7 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
 }
 
 // ungated backward with dstate 64: recompute pass and dx pass in one kernel (false if not applicable)
-bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p) { return g.N == 64 && !p.z && use_ws_scan(); }
+bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p) { return g.N == 64 && !p.z && !g.onetile; }
 int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, const void* ds_bf,
                       float* dcsp, float* ddot, float* ddtd, int* status, cudaStream_t s) {
   SeqMaps m;

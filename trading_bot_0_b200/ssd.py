@@ -17,7 +17,8 @@ import torch
 from . import _lib as L
 
 _DT = {torch.float32: L.SSD_F32, torch.bfloat16: L.SSD_BF16}
-ALGOS = {"auto": L.ALGO_AUTO, "fp32_cores": L.ALGO_FP32_CORES, "tensor": L.ALGO_TENSOR}
+ALGOS = {"auto": L.ALGO_AUTO, "fp32_cores": L.ALGO_FP32_CORES, "tensor": L.ALGO_TENSOR,
+         "tensor_onetile": L.ALGO_TENSOR_ONETILE}
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -93,11 +94,33 @@ def alloc_workspace(dims: L.SsdDims, device, backward: bool = False) -> torch.Te
     return torch.empty(workspace_bytes(dims, backward), dtype=torch.uint8, device=device)
 
 
+def workspace_status(workspace: torch.Tensor) -> int:
+    """Wait for the current stream and read the status word of `workspace`: 0 when healthy; raises SsdError (code
+    SSD_ERR_TIMEOUT, wait-site in the message) when a bounded wait inside a pipelined kernel ran out.  The device-side
+    counterpart of the error read the reference makes after every FFI call (trading_bots/src/torch/cuda/graph.rs:107-118)."""
+    code = C.c_int32(0)
+    with torch.cuda.device(workspace.device):
+        L.check(L.load().ssd_workspace_status(_ptr(workspace), _stream(workspace.device), C.byref(code)))
+    return int(code.value)
+
+
+def _out_slot(o, key, shape, dtype, dev):
+    """A caller-provided output must be dense, 16-byte aligned and of the right shape; a missing one is allocated."""
+    t = o.get(key)
+    if t is None:
+        o[key] = torch.empty(*shape, dtype=dtype, device=dev)
+        return
+    _need(tuple(t.shape) == tuple(shape) and t.dtype == dtype and t.device == dev,
+          f"out[{key!r}]: expected {tuple(shape)} {dtype} on {dev}, got {tuple(t.shape)} {t.dtype} on {t.device}")
+    _need(t.is_contiguous() and t.data_ptr() % 16 == 0, f"out[{key!r}]: must be contiguous and 16-byte aligned")
+
+
 def forward(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk, algo="auto", workspace=None,
             y=None, final_state=None, return_final_state=True, for_backward=False, stages=None,
-            dt_bias=None, dt_softplus=False):
+            dt_bias=None, dt_softplus=False, check=False):
     """y, final_state, workspace = SSD(x, dt, A, B, C, D, z, init_state).  With `dt_bias` / `dt_softplus` the step
-    size is act(dt + dt_bias), evaluated inside the cumsum kernel (the pre-activation of a Mamba-2 layer)."""
+    size is act(dt + dt_bias), evaluated inside the cumsum kernel (the pre-activation of a Mamba-2 layer).
+    `check=True` waits for the stream afterwards and raises if a kernel reported a timed-out wait."""
     lib = L.load()
     dev = x.device
     if y is None:
@@ -125,12 +148,14 @@ def forward(x, dt, A, Bm, Cm, D=None, z=None, init_state=None, *, chunk, algo="a
         else:
             rc = lib.ssd_forward_staged(C.byref(d), C.byref(p), _ptr(workspace), workspace.numel(), _stream(dev), stages)
     L.check(rc)
+    if check:
+        workspace_status(workspace)
     return y, final_state, workspace
 
 
 def backward(dy, x, dt, A, Bm, Cm, D=None, z=None, init_state=None, dfinal_state=None, *, chunk, algo="auto",
              workspace=None, fwd_saved=False, want_dinit=False, stages=None, out=None, dt_bias=None,
-             dt_softplus=False):
+             dt_softplus=False, check=False):
     """Gradients of `forward`.  Returns a dict with dx, ddt, dA, dB, dC, dD, dz, dinit (and ddt_bias when dt_bias is
     given; ddt is then the gradient w.r.t. the dt passed in, before bias and activation)."""
     lib = L.load()
@@ -145,20 +170,20 @@ def backward(dy, x, dt, A, Bm, Cm, D=None, z=None, init_state=None, dfinal_state
     if dfinal_state is not None:
         _check_dense_f32("dfinal_state", dfinal_state, (Bn, H, P, N), dev)
     o = out if out is not None else {}
-    o.setdefault("dx", torch.empty(Bn, Ln, H, P, dtype=x.dtype, device=dev))
-    o.setdefault("ddt", torch.empty(Bn, Ln, H, dtype=torch.float32, device=dev))
-    o.setdefault("dA", torch.empty(H, dtype=torch.float32, device=dev))
-    o.setdefault("dB", torch.empty(Bn, Ln, G, N, dtype=x.dtype, device=dev))
-    o.setdefault("dC", torch.empty(Bn, Ln, G, N, dtype=x.dtype, device=dev))
+    _out_slot(o, "dx", (Bn, Ln, H, P), x.dtype, dev)
+    _out_slot(o, "ddt", (Bn, Ln, H), torch.float32, dev)
+    _out_slot(o, "dA", (H,), torch.float32, dev)
+    _out_slot(o, "dB", (Bn, Ln, G, N), x.dtype, dev)
+    _out_slot(o, "dC", (Bn, Ln, G, N), x.dtype, dev)
     if D is not None:
-        o.setdefault("dD", torch.empty(H, dtype=torch.float32, device=dev))
+        _out_slot(o, "dD", (H,), torch.float32, dev)
     if z is not None:
-        o.setdefault("dz", torch.empty(Bn, Ln, H, P, dtype=x.dtype, device=dev))
+        _out_slot(o, "dz", (Bn, Ln, H, P), x.dtype, dev)
     if want_dinit or init_state is not None:
-        o.setdefault("dinit", torch.empty(Bn, H, P, N, dtype=torch.float32, device=dev))
+        _out_slot(o, "dinit", (Bn, H, P, N), torch.float32, dev)
     if dt_bias is not None:
         _check_dense_f32("dt_bias", dt_bias, (H,), dev)
-        o.setdefault("ddt_bias", torch.empty(H, dtype=torch.float32, device=dev))
+        _out_slot(o, "ddt_bias", (H,), torch.float32, dev)
     if workspace is None:
         _need(not fwd_saved, "fwd_saved=True needs the workspace the forward ran in")
         workspace = alloc_workspace(d, dev, backward=True)
@@ -172,6 +197,8 @@ def backward(dy, x, dt, A, Bm, Cm, D=None, z=None, init_state=None, dfinal_state
         else:
             rc = lib.ssd_backward_staged(C.byref(d), C.byref(p), _ptr(workspace), workspace.numel(), _stream(dev), stages)
     L.check(rc)
+    if check:
+        workspace_status(workspace)
     o["workspace"] = workspace
     return o
 
