@@ -195,7 +195,14 @@ SSD_API int32_t ssd_state_reset_rows(float* state, int64_t row_elems, const int6
  *   -1: acc = boundary; for q = world-1 .. rank+1:    acc = exp(logdecay_q) * acc + state_q
  * No counterpart in the reference (it is a single-GPU program with no collective anywhere).
  */
-enum { SSD_STAGE_LOCAL = 1, SSD_STAGE_TOTAL = 2, SSD_STAGE_FINISH = 4 };
+/* SSD_STAGE_LOCAL can be given in two halves so that the exchange overlaps local work that does not need it:
+ *   SSD_STAGE_LOCAL_STATES - the part of LOCAL the TOTAL stage needs (backward: the local state gradients; forward: all
+ *                            of LOCAL)
+ *   SSD_STAGE_LOCAL_REST   - the remainder (backward, ungated: the forward recompute pass that yields the per-position
+ *                            row sums and is only read by FINISH; with a z gate the state gradients read what that pass
+ *                            writes, so LOCAL_STATES then runs both and LOCAL_REST is empty).  Call it after LOCAL_STATES,
+ *                            on any stream ordered after that call and before FINISH. */
+enum { SSD_STAGE_LOCAL = 1, SSD_STAGE_TOTAL = 2, SSD_STAGE_FINISH = 4, SSD_STAGE_LOCAL_STATES = 8, SSD_STAGE_LOCAL_REST = 16 };
 
 SSD_API int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* workspace, size_t workspace_bytes,
                            void* cuda_stream, int32_t stages);
@@ -212,6 +219,46 @@ SSD_API int32_t ssd_sp_total_logdecay(const SsdDims* dims, const void* workspace
 SSD_API int32_t ssd_sp_prefix_state(const float* gathered_states, const float* gathered_logdecay, int32_t world,
                             int32_t rank, int32_t direction, int64_t batch_heads, int64_t state_elems,
                             const float* boundary, float* state_in, void* cuda_stream);
+
+/*
+ * The exchange itself, for hosts that have no collective library of their own in reach (a Rust / tch program has no
+ * torch.distributed): NCCL over NVLink, bound at run time (dlopen of libnccl.so.2; nothing is loaded until the first
+ * ssd_sp_* call).  SsdSpComm is an owning handle with a new / free pair, the convention the reference uses for the
+ * objects it added to its shim (at_cuda_graph_new / at_cuda_graph_free, vendor/torch-sys-0.25.0/libtch/torch_api.cpp:378-401).
+ *   ssd_sp_unique_id   - rank 0 makes the 128-byte NCCL id; the host program hands it to the other ranks by its own means
+ *   ssd_sp_comm_new    - collective over all ranks, on the current device; NULL on failure (ssd_last_error)
+ *   ssd_sp_comm_wrap   - borrow an ncclComm_t the host already has (not destroyed by ssd_sp_comm_free)
+ *   ssd_sp_exchange_fwd / _bwd - after the LOCAL|TOTAL stages: reads the slice's total log-decay from the chunk cumsums in
+ *       `workspace`, all-gathers every rank's (slice-total state, log-decay) record into `exchange_buf` (LOCAL memory;
+ *       ssd_sp_exchange_bytes gives its size; one NCCL group), and folds the records of the ranks before (fwd) / after
+ *       (bwd) this one into `state_in` / `dstate_out`, which then goes to the FINISH stage as init_state / dfinal_state.
+ *       `init_state` / `dfinal_state` here are the boundary of the GLOBAL sequence (same on every rank, or NULL).
+ *       Everything is enqueued on `cuda_stream`.  timeout_ms == 0: return at once (legal during stream capture).
+ *       timeout_ms > 0 (checked mode): a fixed-size signature of the problem goes round first and is compared on the host
+ *       (SSD_ERR_BAD_SHAPE names the rank that disagrees), and the call waits for the exchange on the host for at most
+ *       that long: SSD_ERR_TIMEOUT when a rank never joined.  After a timeout the communicator is in an unknown state:
+ *       ssd_sp_comm_abort, then make a new one.  No kernel of this library and no TMA ever reads a peer's memory.
+ *   ssd_sp_allreduce_params - dA (and dD) summed over ranks in place: the parameters are replicated.
+ * No counterpart in the reference (single GPU, no collective anywhere).
+ */
+#define SSD_SP_UNIQUE_ID_BYTES 128
+typedef struct SsdSpComm SsdSpComm;
+SSD_API int32_t ssd_sp_unique_id(void* id128);
+SSD_API SsdSpComm* ssd_sp_comm_new(const void* id128, int32_t world, int32_t rank);
+SSD_API SsdSpComm* ssd_sp_comm_wrap(void* nccl_comm);
+SSD_API int32_t ssd_sp_comm_world(const SsdSpComm* comm);
+SSD_API int32_t ssd_sp_comm_rank(const SsdSpComm* comm);
+SSD_API void ssd_sp_comm_free(SsdSpComm* comm);
+SSD_API int32_t ssd_sp_comm_abort(SsdSpComm* comm);
+SSD_API size_t ssd_sp_exchange_bytes(const SsdDims* dims, int32_t world);
+SSD_API int32_t ssd_sp_exchange_fwd(const SsdDims* dims, const void* workspace, size_t workspace_bytes, SsdSpComm* comm,
+                                    const float* local_final_state, const float* init_state, float* state_in,
+                                    void* exchange_buf, size_t exchange_bytes, void* cuda_stream, int32_t timeout_ms);
+SSD_API int32_t ssd_sp_exchange_bwd(const SsdDims* dims, const void* workspace, size_t workspace_bytes, SsdSpComm* comm,
+                                    const float* local_dinit_state, const float* dfinal_state, float* dstate_out,
+                                    void* exchange_buf, size_t exchange_bytes, void* cuda_stream, int32_t timeout_ms);
+SSD_API int32_t ssd_sp_allreduce_params(SsdSpComm* comm, float* dA, float* dD /* optional */, int32_t nheads,
+                                        void* cuda_stream, int32_t timeout_ms);
 
 /* Message for the last failing call on this thread ("" if none); valid until the next call on
  * this thread.  Mirrors `get_and_reset_last_err` (trading_bots/src/torch/cuda/graph.rs:107-118). */

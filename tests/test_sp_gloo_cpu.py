@@ -2,7 +2,9 @@
 
 The device operations are replaced by the CPU oracle (injected through `ops`), so what is under
 test is the slice bookkeeping, the packed all-gather, the direction of both prefix scans, the
-boundary-state handling and the dA/dD reduction."""
+boundary-state handling, the dA/dD reduction, and the failure detection of the checked mode: a
+rank that never posts, ranks that disagree about the world size or the shapes.  Failures are made
+on the host (a rank that skips the call, a wrong argument); nothing here touches a GPU."""
 import os
 import socket
 
@@ -17,7 +19,7 @@ from trading_bot_0_b200 import _lib as L
 from trading_bot_0_b200 import sp
 
 
-class OracleOps:
+class OracleOps(sp.SpOps):
     """fp64 CPU stand-in for the CUDA operations behind `sp_forward` / `sp_backward`."""
 
     def _leaves(self, x, dt, A, Bm, Cm, D, z, init):
@@ -120,3 +122,84 @@ def test_slice_bounds():
         sp.slice_bounds(128, 4, 3, 128)
     with pytest.raises(ValueError):
         sp.slice_bounds(128, 2, 2, 64)
+
+
+# ---- failure detection (checked mode) ----------------------------------------------------------------------------
+def _spawn(target, world, extra=()):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q) + tuple(extra)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = sorted([q.get(timeout=120) for _ in range(world)], key=lambda t: t[0])
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert all(p.exitcode == 0 for p in procs)
+    return res
+
+
+def _slice_inputs(cfg, world, rank):
+    inp = O.make_inputs(cfg, with_init_state=True)
+    a, b = sp.slice_bounds(cfg.seqlen, world, rank, cfg.chunk)
+    return inp, {k: inp[k][:, a:b] for k in ("x", "dt", "B", "C", "dy")}
+
+
+def _fail_worker(rank, world, port, q, scenario):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        cfg = O.SsdConfig("spf", 1, 64, 2, 4, 8, 1, 16, "fp32", False)
+        inp, loc = _slice_inputs(cfg, world, rank)
+        ops = OracleOps()
+        err = None
+        try:
+            if scenario == "never_posts":
+                if rank != world - 1:      # the last rank skips the exchange altogether
+                    sp.sp_forward(loc["x"], loc["dt"], inp["A"], loc["B"], loc["C"], inp["D"], None, None, chunk=cfg.chunk,
+                                  ops=ops, timeout_s=1.0, tag="step1")
+            elif scenario == "world":
+                # one rank believes the job has one rank more than it has
+                sig = ("ssd_sp", +1, world + (1 if rank == 0 else 0), 1, 2, 4, 1, 8, cfg.chunk, "torch.float32")
+                sp.rendezvous(sig, None, 1.0, "step1")
+            elif scenario == "shapes":
+                x = loc["x"] if rank != 0 else loc["x"][..., :2]      # rank 0 comes with headdim 2 instead of 4
+                sp.sp_forward(x, loc["dt"], inp["A"], loc["B"], loc["C"], inp["D"], None, None, chunk=cfg.chunk, ops=ops,
+                              timeout_s=2.0, tag="step1")
+        except L.SsdError as e:
+            err = (e.code, str(e))
+        # the process group is still usable: a collective right after the failure, then a clean checked exchange
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t)
+        y, fin, ctx = sp.sp_forward(loc["x"], loc["dt"], inp["A"], loc["B"], loc["C"], inp["D"], None, None, chunk=cfg.chunk,
+                                    ops=ops, timeout_s=20.0, tag="retry")
+        q.put((rank, err, float(t.item()), y.detach(), fin.detach()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("scenario", ["never_posts", "world", "shapes"])
+def test_checked_exchange_reports_and_the_group_stays_usable(scenario):
+    world = 2
+    res = _spawn(_fail_worker, world, (scenario,))
+    cfg = O.SsdConfig("spf", 1, 64, 2, 4, 8, 1, 16, "fp32", False)
+    inp = O.make_inputs(cfg, with_init_state=True)
+    y_ref, fin_ref = O.ssd_sequential(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"])
+    errs = {r[0]: r[1] for r in res}
+    if scenario == "never_posts":
+        assert errs[0] is not None and errs[0][0] == sp.SSD_ERR_TIMEOUT and "[1]" in errs[0][1] and "did not post" in errs[0][1]
+        assert errs[1] is None
+    else:
+        for r in range(world):
+            assert errs[r] is not None and errs[r][0] == sp.SSD_ERR_BAD_SHAPE, errs
+            assert f"rank {1 - r} posted" in errs[r][1]
+    for r in res:
+        assert r[2] == 3.0                                   # the all-reduce after the failure
+    assert rel_err(torch.cat([r[3] for r in res], 1), y_ref) < 1e-5      # the clean retry
+    assert rel_err(res[-1][4], fin_ref) < 1e-5

@@ -163,23 +163,33 @@ def test_cuda_graph_capture_on_side_stream(lib):
         assert torch.equal(out[k], v), k
 
 
-def test_sequence_parallel_split_emulated(lib):
+@pytest.mark.parametrize("shape", ["cfg0_fp32_gated", "cfg4_heads_bf16", "cfg1_heads_bf16"])
+def test_sequence_parallel_split_emulated(lib, shape):
     """The staged entry points + prefix kernel, driven for W slices on one GPU, reproduce the
-    unsplit forward and backward (the cross-rank gather is emulated by stacking)."""
+    unsplit forward and backward (the cross-rank gather is emulated by stacking).  Run for the exact-fp32 family, for the
+    head shapes of the long-sequence workload (H24 P64 N128, chunk 256: the staged tensor-core path the sequence-parallel
+    ranks take) and for dstate 64; the backward is driven in the split order the overlapped exchange uses
+    (LOCAL_STATES|TOTAL, then LOCAL_REST, then FINISH)."""
     import trading_bot_0_b200 as T
     from trading_bot_0_b200 import _lib as L
     from trading_bot_0_b200.sp import CudaOps, slice_bounds
-    cfg = cfg_like(0, has_z=True, seqlen=512)
+    if shape == "cfg0_fp32_gated":
+        cfg, W, mode, dscale = cfg_like(0, has_z=True, seqlen=512), 4, "fp32", 1.0
+    elif shape == "cfg4_heads_bf16":
+        cfg, W, mode, dscale = O.SsdConfig("sp4", 1, 768, 24, 64, 128, 1, 256, "bf16", False), 3, "bf16", 0.1
+    else:
+        cfg, W, mode, dscale = O.SsdConfig("sp1", 2, 512, 8, 32, 64, 1, 128, "bf16", False), 2, "bf16", 0.1
     inp = O.make_inputs(cfg, with_init_state=True)
-    dfinal = torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.dstate, generator=torch.Generator().manual_seed(5))
+    dfinal = dscale * torch.randn(cfg.batch, cfg.nheads, cfg.headdim, cfg.dstate, generator=torch.Generator().manual_seed(5))
     ref = oracle_all(inp, dfinal)
     d = to_dev(inp, DEV)
-    ops, W = CudaOps(), 4
+    ops = CudaOps()
     sl = [slice_bounds(cfg.seqlen, W, r, cfg.chunk) for r in range(W)]
-    loc = [{k: d[k][:, a:b] for k in ("x", "dt", "B", "C", "z", "dy")} for a, b in sl]
-    args = lambda r: (loc[r]["x"], loc[r]["dt"], d["A"], loc[r]["B"], loc[r]["C"], d["D"], loc[r]["z"])
+    keys = ("x", "dt", "B", "C", "dy") + (("z",) if cfg.has_z else ())
+    loc = [{k: d[k][:, a:b] for k in keys} for a, b in sl]
+    args = lambda r: (loc[r]["x"], loc[r]["dt"], d["A"], loc[r]["B"], loc[r]["C"], d["D"], loc[r].get("z"))
     st = [ops.forward(L.STAGE_LOCAL | L.STAGE_TOTAL, *args(r), None, cfg.chunk, "auto", None, None, None) for r in range(W)]
-    gl = torch.stack([ops.total_logdecay(loc[r]["x"], loc[r]["dt"], d["A"], loc[r]["B"], loc[r]["C"], loc[r]["z"],
+    gl = torch.stack([ops.total_logdecay(loc[r]["x"], loc[r]["dt"], d["A"], loc[r]["B"], loc[r]["C"], loc[r].get("z"),
                                          cfg.chunk, "auto", st[r][2]) for r in range(W)])
     gs = torch.stack([s[1] for s in st])
     ys, sin = [], []
@@ -187,21 +197,23 @@ def test_sequence_parallel_split_emulated(lib):
         sin.append(ops.prefix_state(gs, gl, W, r, +1, d["init_state"]))
         y, fin, _ = ops.forward(L.STAGE_FINISH, *args(r), sin[r], cfg.chunk, "auto", st[r][2], st[r][0], st[r][1].clone())
         ys.append(y)
-    assert_close("y", torch.cat(ys, 1), ref["y"], "fp32")
-    assert_close("final_state", fin, ref["final_state"], "fp32")
+    assert_close("y", torch.cat(ys, 1), ref["y"], mode)
+    assert_close("final_state", fin, ref["final_state"], mode)
     outs = [dict() for _ in range(W)]
     for r in range(W):
-        ops.backward(L.STAGE_LOCAL | L.STAGE_TOTAL, loc[r]["dy"], *args(r), sin[r], None, cfg.chunk, "auto", st[r][2], outs[r])
+        ops.backward(L.STAGE_LOCAL_STATES | L.STAGE_TOTAL, loc[r]["dy"], *args(r), sin[r], None, cfg.chunk, "auto", st[r][2], outs[r])
     gd = torch.stack([o["dinit"].clone() for o in outs])
     dev_dfinal = dfinal.to(DEV)
     for r in range(W):
         dout = ops.prefix_state(gd, gl, W, r, -1, dev_dfinal)
+        ops.backward(L.STAGE_LOCAL_REST, loc[r]["dy"], *args(r), sin[r], None, cfg.chunk, "auto", st[r][2], outs[r])
         ops.backward(L.STAGE_FINISH, loc[r]["dy"], *args(r), sin[r], dout, cfg.chunk, "auto", st[r][2], outs[r])
-    for k in ("dx", "ddt", "dB", "dC", "dz"):
-        assert_close(k, torch.cat([o[k] for o in outs], 1), ref[k], "fp32")
-    assert_close("dA", sum(o["dA"] for o in outs), ref["dA"], "fp32")
-    assert_close("dD", sum(o["dD"] for o in outs), ref["dD"], "fp32")
-    assert_close("dinit", outs[0]["dinit"], ref["dinit"], "fp32")
+        assert T.ssd.workspace_status(st[r][2]) == 0
+    for k in ("dx", "ddt", "dB", "dC") + (("dz",) if cfg.has_z else ()):
+        assert_close(k, torch.cat([o[k] for o in outs], 1), ref[k], mode)
+    assert_close("dA", sum(o["dA"] for o in outs), ref["dA"], mode)
+    assert_close("dD", sum(o["dD"] for o in outs), ref["dD"], mode)
+    assert_close("dinit", outs[0]["dinit"], ref["dinit"], mode)
 
 
 def test_errors_are_reported_not_faulted(lib):

@@ -18,7 +18,8 @@ LIB_PATH = Path(os.environ.get("SSD_B200_LIB") or (Path(__file__).resolve().pare
 SSD_F32, SSD_BF16 = 0, 1
 PASS_FWD, PASS_BWD = 0, 1
 ALGO_AUTO, ALGO_FP32_CORES, ALGO_TENSOR, ALGO_TENSOR_ONETILE = 0, 1, 2, 3
-STAGE_LOCAL, STAGE_TOTAL, STAGE_FINISH = 1, 2, 4
+STAGE_LOCAL, STAGE_TOTAL, STAGE_FINISH, STAGE_LOCAL_STATES, STAGE_LOCAL_REST = 1, 2, 4, 8, 16
+SP_UNIQUE_ID_BYTES = 128
 
 EXPORTS = [
     "ssd_workspace_bytes", "ssd_forward", "ssd_backward", "ssd_forward_staged", "ssd_backward_staged",
@@ -28,6 +29,8 @@ EXPORTS = [
     "ssd_conv1d_workspace_bytes", "ssd_conv1d_forward", "ssd_conv1d_backward",
     "ssd_rmsnorm_workspace_bytes", "ssd_rmsnorm_forward", "ssd_rmsnorm_backward", "ssd_selftest_bounded_wait",
     "ssd_workspace_status", "ssd_workspace_status_async", "ssd_status_check", "ssd_noalloc_status",
+    "ssd_sp_unique_id", "ssd_sp_comm_new", "ssd_sp_comm_wrap", "ssd_sp_comm_world", "ssd_sp_comm_rank", "ssd_sp_comm_free",
+    "ssd_sp_comm_abort", "ssd_sp_exchange_bytes", "ssd_sp_exchange_fwd", "ssd_sp_exchange_bwd", "ssd_sp_allreduce_params",
 ]
 
 
@@ -131,6 +134,24 @@ def load() -> C.CDLL:
     lib.ssd_noalloc_max_bytes.argtypes = []
     lib.ssd_selftest_bounded_wait.restype = i32
     lib.ssd_selftest_bounded_wait.argtypes = [vp, i64, vp]
+    lib.ssd_sp_unique_id.restype = i32
+    lib.ssd_sp_unique_id.argtypes = [vp]
+    lib.ssd_sp_comm_new.restype = vp
+    lib.ssd_sp_comm_new.argtypes = [vp, i32, i32]
+    lib.ssd_sp_comm_wrap.restype = vp
+    lib.ssd_sp_comm_wrap.argtypes = [vp]
+    for name in ("ssd_sp_comm_world", "ssd_sp_comm_rank", "ssd_sp_comm_abort"):
+        getattr(lib, name).restype = i32
+        getattr(lib, name).argtypes = [vp]
+    lib.ssd_sp_comm_free.restype = None
+    lib.ssd_sp_comm_free.argtypes = [vp]
+    lib.ssd_sp_exchange_bytes.restype = sz
+    lib.ssd_sp_exchange_bytes.argtypes = [C.POINTER(SsdDims), i32]
+    for name in ("ssd_sp_exchange_fwd", "ssd_sp_exchange_bwd"):
+        getattr(lib, name).restype = i32
+        getattr(lib, name).argtypes = [C.POINTER(SsdDims), vp, sz, vp, vp, vp, vp, vp, sz, vp, i32]
+    lib.ssd_sp_allreduce_params.restype = i32
+    lib.ssd_sp_allreduce_params.argtypes = [vp, vp, vp, i32, vp, i32]
     lib.ssd_workspace_status.restype = i32
     lib.ssd_workspace_status.argtypes = [vp, vp, C.POINTER(i32)]
     lib.ssd_workspace_status_async.restype = i32

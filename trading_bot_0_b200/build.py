@@ -14,7 +14,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libssd_b200.so"
-SOURCES = ["ssd_api.cu", "ssd_simt.cu", "ssd_decode.cu", "ssd_tensor.cu", "ssd_noalloc.cu", "ssd_prepost.cu"]
+SOURCES = ["ssd_api.cu", "ssd_simt.cu", "ssd_decode.cu", "ssd_tensor.cu", "ssd_noalloc.cu", "ssd_prepost.cu", "ssd_sp.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared"]
 LINK_LIBS = ["-ldl"]

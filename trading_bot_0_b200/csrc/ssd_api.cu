@@ -250,7 +250,7 @@ int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* works
   if (!p->x || !p->dt || !p->A || !p->Bm || !p->Cm) { set_error("x, dt, A, B, C must be non-NULL"); return SSD_ERR_NULL_POINTER; }
   if ((stages & SSD_STAGE_FINISH) && !p->y) { set_error("y must be non-NULL"); return SSD_ERR_NULL_POINTER; }
   if ((p->z != nullptr) != (dims->has_z != 0)) { set_error("dims.has_z (%d) does not match the z pointer", dims->has_z); return SSD_ERR_BAD_SHAPE; }
-  if (stages == 0 || (stages & ~(SSD_STAGE_LOCAL | SSD_STAGE_TOTAL | SSD_STAGE_FINISH))) { set_error("bad stage mask %d", stages); return SSD_ERR_BAD_SHAPE; }
+  if (stages == 0 || (stages & ~(SSD_STAGE_LOCAL | SSD_STAGE_TOTAL | SSD_STAGE_FINISH | SSD_STAGE_LOCAL_STATES | SSD_STAGE_LOCAL_REST))) { set_error("bad stage mask %d", stages); return SSD_ERR_BAD_SHAPE; }
   WsLayout w;
   make_layout(g, dims->has_z != 0, family_is_tensor(g, dims), &w);
   rc = check_ws(workspace, workspace_bytes, w.total_fwd);
@@ -296,7 +296,7 @@ int32_t ssd_backward_staged(const SsdDims* dims, const SsdBwdPtrs* p, void* work
   }
   if ((p->z != nullptr) != (dims->has_z != 0)) { set_error("dims.has_z (%d) does not match the z pointer", dims->has_z); return SSD_ERR_BAD_SHAPE; }
   if (p->z && !p->dz) { set_error("dz must be non-NULL when z is given"); return SSD_ERR_NULL_POINTER; }
-  if (stages == 0 || (stages & ~(SSD_STAGE_LOCAL | SSD_STAGE_TOTAL | SSD_STAGE_FINISH))) { set_error("bad stage mask %d", stages); return SSD_ERR_BAD_SHAPE; }
+  if (stages == 0 || (stages & ~(SSD_STAGE_LOCAL | SSD_STAGE_TOTAL | SSD_STAGE_FINISH | SSD_STAGE_LOCAL_STATES | SSD_STAGE_LOCAL_REST))) { set_error("bad stage mask %d", stages); return SSD_ERR_BAD_SHAPE; }
   WsLayout w;
   make_layout(g, dims->has_z != 0, family_is_tensor(g, dims), &w);
   rc = check_ws(workspace, workspace_bytes, w.total_bwd);

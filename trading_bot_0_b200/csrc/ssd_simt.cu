@@ -743,7 +743,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   const int tp = cdiv(g.P, TM), tn = cdiv(g.N, TN), tq = cdiv(g.Q, TM);
   // a full pass (no sequence-parallel staging) computes the chunk states inside the scan over chunks where that kernel applies
   const bool fused = tc && stages == (SSD_STAGE_LOCAL | SSD_STAGE_FINISH) && tensor_state_fused_applies(g);
-  if (stages & SSD_STAGE_LOCAL) {
+  if (stages & (SSD_STAGE_LOCAL | SSD_STAGE_LOCAL_STATES)) {
     cudaMemsetAsync(status, 0, 256, s);
     k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
@@ -832,7 +832,12 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   const void* tc_dy = p.z ? (const void*)dyp : p.dy;
   const bool tc_dense = p.z != nullptr;
   const bool fused = tc && stages == (SSD_STAGE_LOCAL | SSD_STAGE_FINISH) && tensor_state_fused_applies(g);
-  if (stages & SSD_STAGE_LOCAL) {
+  // LOCAL in two halves (see SSD_STAGE_LOCAL_STATES / _REST): the recompute pass is only read by FINISH unless a z gate
+  // makes the local state gradients depend on the pre-gate dy it writes.
+  const bool want_states = (stages & (SSD_STAGE_LOCAL | SSD_STAGE_LOCAL_STATES)) != 0;
+  const bool want_rest = (stages & (SSD_STAGE_LOCAL | SSD_STAGE_LOCAL_REST)) != 0;
+  const bool do_recompute = p.z ? want_states : want_rest;
+  if (want_states) {
     if (!p.fwd_saved) {
       SsdFwdPtrs f{};
       f.x = p.x; f.dt = p.dt; f.A = p.A; f.Bm = p.Bm; f.Cm = p.Cm; f.D = p.D; f.z = p.z; f.dt_bias = p.dt_bias;
@@ -846,21 +851,28 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       cudaMemsetAsync(ddtd, 0, nq, s);
       cudaMemsetAsync(ddot, 0, nq, s);
     }
+  }
+  if (do_recompute) {
     if (tc) {
       // ungated, dstate 64: the recompute pass is folded into the dx kernel of the FINISH stage
       int rc = tensor_bwd_merged_applies(g, p) ? SSD_OK : tensor_scan_bwd(g, p, tab, prev_bf, dyp, dcsp, ddot, status, s);
       if (rc) return rc;
-      if (!fused) {
-        rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
-                                tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, dst, status, s);
-        if (rc) return rc;
-      }
     } else {
       // forward recompute with the backward epilogue: dz, pre-gate dy, dcsp, ddot
       k_chunk_scan<T, 1><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(
           g, x, (const T*)p.Cm, p.D, (const T*)p.z, cs, dtf, cb, states, nullptr, (const T*)p.dy, dyp, (T*)p.dz,
           dcsp, ddot);
       SSD_CUDA_CHECK_LAUNCH("chunk_scan_bwd_epilogue");
+    }
+  }
+  if (want_states) {
+    if (tc) {
+      if (!fused) {
+        int rc = tensor_chunk_state(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
+                                    tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, dst, status, s);
+        if (rc) return rc;
+      }
+    } else {
       k_chunk_state<T, 1><<<dim3(tp * tn, g.nc * g.H, g.B), NT, 0, s>>>(g, x, g.xsb, g.xsl, dys, (const T*)p.Cm,
                                                                          g.csb, g.csl, cs, dtf, dst);
       SSD_CUDA_CHECK_LAUNCH("dstates_local");
