@@ -848,7 +848,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=sorted(CFGS) + ["mixer_ops"],
                     help="cfg1..cfg4 as in BASELINE.json; mixer_ops: the conv1d / RMS-norm kernels either side of the scan at cfg1 shapes")
-    ap.add_argument("--algo", default="auto", choices=["auto", "fp32_cores", "tensor"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "fp32_cores", "tensor", "tensor_onetile"])
     ap.add_argument("--ring", type=int, default=64, help="cfg2: distinct pre-drawn steps kept in HBM")
     ap.add_argument("--strong", action="store_true", help="cfg4: label the run strong scaling (fixed global L)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")

@@ -262,6 +262,41 @@ __device__ __forceinline__ void decay_mask_block(uint32_t tm_src, const float* _
     st_shared_v4(mtile + plain_off(128, row, c0 + j8), pack_bf16(v[j8], v[j8 + 1]), pack_bf16(v[j8 + 2], v[j8 + 3]),
                  pack_bf16(v[j8 + 4], v[j8 + 5]), pack_bf16(v[j8 + 6], v[j8 + 7]));
 }
+// Accumulating variant for the one-tile dB / dC kernel: dC = sum_h W'_h B and dB = sum_h W'_h^T C are linear in W'_h, so
+// the decayed, masked tiles of all heads of a group are added up in registers (fp32; thread = row x one 32-column block)
+// and only their SUM goes to shared memory, once per tile.
+__device__ __forceinline__ void decay_acc_block(uint32_t tm_src, const float* __restrict__ tab, int row, int part, int warp,
+                                                float (&acc)[32]) {
+  const int rb = warp & 3, cb = part;   // both warp-uniform
+  if (cb > rb) return;
+  const int c0 = cb * 32;
+  float v[32];
+  tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
+  if (cb == rb) {
+    float run = 0.f;
+#pragma unroll
+    for (int k = 31; k >= 0; --k) {
+      const int j = c0 + k;
+      run = (j == row) ? 1.f : run * tab[T_DS + j];   // T_DS[j] = decay of step j+1
+      acc[k] = fmaf(v[k], run * tab[T_DT + j], acc[k]);
+    }
+  } else {
+    const float rf = ex2(tab[T_CS + row] - tab[T_CS + c0 + 31]);
+#pragma unroll
+    for (int k4 = 0; k4 < 32; k4 += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(tab + T_CF + c0 + k4);
+      acc[k4] = fmaf(v[k4], rf * f.x, acc[k4]); acc[k4 + 1] = fmaf(v[k4 + 1], rf * f.y, acc[k4 + 1]);
+      acc[k4 + 2] = fmaf(v[k4 + 2], rf * f.z, acc[k4 + 2]); acc[k4 + 3] = fmaf(v[k4 + 3], rf * f.w, acc[k4 + 3]);
+    }
+  }
+}
+__device__ __forceinline__ void store_acc_block(const float (&acc)[32], int row, int part, int warp, uint32_t mtile) {
+  if (part > (warp & 3)) return;
+#pragma unroll
+  for (int j8 = 0; j8 < 32; j8 += 8)
+    st_shared_v4(mtile + plain_off(128, row, part * 32 + j8), pack_bf16(acc[j8], acc[j8 + 1]), pack_bf16(acc[j8 + 2], acc[j8 + 3]),
+                 pack_bf16(acc[j8 + 4], acc[j8 + 5]), pack_bf16(acc[j8 + 6], acc[j8 + 7]));
+}
 __device__ __forceinline__ void zero_upper_block(int row, int part, int warp, uint32_t mtile) {
   if (part <= (warp & 3)) return;
 #pragma unroll
@@ -1219,9 +1254,14 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   };
   w.wait(&bar_cb, 0, 31);
   bool first = true;
+  // SUMW (one CTA per SM, registers to spare): W'_h is summed over the heads in registers and multiplied once per tile
+  constexpr bool SUMW = N > 64;
+  float acc[32];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) acc[k] = 0.f;
   for (int blk = 0; blk < nblk; ++blk) {
     const int h0 = grp * g.hpg + blk * HB;
-    zero_upper_block(row, part, warp, smem_u32(sM));   // the state boxes of the previous head block lived here
+    if (!SUMW) zero_upper_block(row, part, warp, smem_u32(sM));   // the state boxes of the previous head block lived here
     w.wait(&bar_x, xphase, 32);
     xphase ^= 1;
     tc_fence_before();
@@ -1230,11 +1270,34 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tc_fence_after();
       issue_w(0);
       mma_commit(&bar_mma);
+      if (SUMW) {   // nothing else lives in the W' tile until the end of the CTA: fetch this block's state boxes into it now
+        mbar_expect_tx(&bar_s, 2 * NB * SBOX_BYTES);
+        for (int kb = 0; kb < NB; ++kb) {
+          tma_load_3d(sS + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_s);
+          tma_load_3d(sDS + kb * SBOX_BYTES, &tmDS, kb * 64, h0 * P, b * g.nc + c, &bar_s);
+        }
+      }
     }
     w.wait(&bar_mma, mphase, 33);
     mphase ^= 1;
     tc_fence_after();
     for (int hl = 0; hl < HB; ++hl) {
+      if constexpr (SUMW) {
+        decay_acc_block(tmW, sTab + hl * TAB, row, part, warp, acc);
+        if (hl + 1 < HB) {
+          tc_fence_before();
+          __syncthreads();
+          if (tid == 0) {
+            tc_fence_after();
+            issue_w(hl + 1);
+            mma_commit(&bar_mma);
+          }
+          w.wait(&bar_mma, mphase, 34);
+          mphase ^= 1;
+          tc_fence_after();
+        }
+        continue;
+      }
       decay_mask_block(tmW, sTab + hl * TAB, row, part, warp, smem_u32(sM));
       fence_async_smem();
       tc_fence_before();
@@ -1257,7 +1320,7 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     // state terms of this head block: fetch the bf16 S_prev and dS_end boxes over the W' tile (its
     // last readers have completed), scale the dy box by exp(cs_i) and the x box by
     // exp(cs_end - cs_j) dt_j in place meanwhile, then one K = 64 product each
-    if (tid == 0) {
+    if (!SUMW && tid == 0) {
       mbar_expect_tx(&bar_s, 2 * NB * SBOX_BYTES);
       for (int kb = 0; kb < NB; ++kb) {
         tma_load_3d(sS + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_s);
@@ -1287,16 +1350,37 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        mma_bf16(tmDC, desc_adv(dDY0, ks * 32), desc_adv(dSm0, ks * 2048), idC, true);
-        mma_bf16(tmDB, desc_adv(dX0, ks * 32), desc_adv(dDSm0, ks * 2048), idC, true);
+        mma_bf16(tmDC, desc_adv(dDY0, ks * 32), desc_adv(dSm0, ks * 2048), idC, !first || ks > 0);
+        mma_bf16(tmDB, desc_adv(dX0, ks * 32), desc_adv(dDSm0, ks * 2048), idC, !first || ks > 0);
       }
       mma_commit(&bar_mma);
     }
+    first = false;
     w.wait(&bar_mma, mphase, 35);
     mphase ^= 1;
     tc_fence_after();
     __syncthreads();
     if (tid == 0 && blk + 1 < nblk) load_boxes(blk + 1);
+  }
+  if constexpr (SUMW) {
+    // the head sum -> bf16 -> the W' tile (the state boxes that lived there have been consumed), then one product per side
+    zero_upper_block(row, part, warp, smem_u32(sM));
+    store_acc_block(acc, row, part, warp, smem_u32(sM));
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_bf16(tmDC, desc_adv(dMk0, ks * 4096), desc_adv(dBm0, ks * 2048), idC, true);
+        mma_bf16(tmDB, desc_adv(dMt0, ks * 256), desc_adv(dCm0, ks * 2048), idB, true);
+      }
+      mma_commit(&bar_mma);
+    }
+    w.wait(&bar_mma, mphase, 37);
+    mphase ^= 1;
+    tc_fence_after();
   }
   // epilogue: this thread writes N/PARTS columns of row `row` of dC and of dB
   {
