@@ -854,7 +854,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   }
   if (do_recompute) {
     if (tc) {
-      // ungated, dstate 64: the recompute pass is folded into the dx kernel of the FINISH stage
+      // ungated (dstate 64, or dstate 128): the recompute pass is folded into the dx kernel of the FINISH stage
       int rc = tensor_bwd_merged_applies(g, p) ? SSD_OK : tensor_scan_bwd(g, p, tab, prev_bf, dyp, dcsp, ddot, status, s);
       if (rc) return rc;
     } else {

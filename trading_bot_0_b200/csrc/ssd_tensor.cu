@@ -1168,6 +1168,219 @@ k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Backward chunk_scan, ungated case, one tile per CTA (dstate 128): the recompute pass (MODE 1) and the dx pass (MODE 2) of
+// k_scan_tc share G and every M_h, so this kernel forms G once and does both from one decay pass per head:
+//   Y  = M_h X_h    (+) exp(cs_i) C S_prev^T                   -> dcsp[i] = sum_p dy*Y, ddot[i] = sum_p dy*x
+//   U' = M_h^T dY_h (+) dt_j exp(cs_end-cs_j) B dS_end^T       -> dx = D dy + U', ddtd[j] = sum_p x*U' / dt_j
+// grid = (nc, G, B), 512 threads, one CTA per SM.  TMEM: G (128) + {Y, Y_off, U, U_off} (4 x 64) of 512 columns.
+template <int P, int N>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+         const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmDS, const float* __restrict__ tab,
+         const float* __restrict__ D, bf16* __restrict__ dx, float* __restrict__ dcsp, float* __restrict__ ddot,
+         float* __restrict__ ddtd, int* __restrict__ status) {
+  constexpr int NB = N / 64;
+  constexpr int HB = 64 / P;                   // heads per 64-column box
+  constexpr int IN_BYTES = 2 * BOX_BYTES + 2 * NB * SBOX_BYTES + HB * TAB_BYTES;   // x, dy, S_prev boxes, dS_end boxes, tables
+  constexpr uint32_t TM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
+  uint8_t* sC = smem;                          // NB boxes, kept for the whole CTA (state term of Y)
+  uint8_t* sB = sC + NB * BOX_BYTES;           // NB boxes, kept for the whole CTA (state term of U')
+  uint8_t* sM = sB + NB * BOX_BYTES;           // the 32 KB M_h tile
+  uint8_t* sIn = sM + 2 * BOX_BYTES;           // x, dy, state boxes, tables of one head block
+  float* sRed = (float*)(sIn + IN_BYTES);      // [3][PARTS][128] partial row sums
+  __shared__ __align__(8) uint64_t bar_cb, bar_in, bar_mma;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) s_abort = *(volatile int*)status;   // an earlier CTA gave up: drain the grid quickly
+  __syncthreads();
+  if (s_abort) return;
+  const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
+  const int row = tid & 127, part = tid >> 7;
+  if (tid == 0) {
+    mbar_init(&bar_cb, 1); mbar_init(&bar_in, 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = tmem_slot;
+  const uint32_t tmG = tm, tmYd = tm + 128, tmYo = tm + 192, tmUd = tm + 256, tmUo = tm + 320;
+  Waiter w{status, false};
+
+  const int nblk = g.hpg / HB;
+  const int col_base = grp * g.hpg * P;
+  uint8_t* xt = sIn;
+  uint8_t* dyt = sIn + BOX_BYTES;
+  uint8_t* stS = sIn + 2 * BOX_BYTES;
+  uint8_t* stDS = stS + NB * SBOX_BYTES;
+  const float* tb = (const float*)(stDS + NB * SBOX_BYTES);   // [HB][TAB]
+  auto load_block = [&](int blk) {    // thread 0 only
+    const int h0 = grp * g.hpg + blk * HB;
+    mbar_expect_tx(&bar_in, IN_BYTES);
+    tma_load_3d(xt, &tmX, col_base + blk * 64, c * QT, b, &bar_in);
+    tma_load_3d(dyt, &tmDY, col_base + blk * 64, c * QT, b, &bar_in);
+    for (int kb = 0; kb < NB; ++kb) {
+      tma_load_3d(stS + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_in);
+      tma_load_3d(stDS + kb * SBOX_BYTES, &tmDS, kb * 64, h0 * P, b * g.nc + c, &bar_in);
+    }
+    bulk_load((void*)tb, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES, &bar_in);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
+    for (int kb = 0; kb < NB; ++kb) {
+      tma_load_3d(sC + kb * BOX_BYTES, &tmC, grp * N + kb * 64, c * QT, b, &bar_cb);
+      tma_load_3d(sB + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &bar_cb);
+    }
+    load_block(0);
+    for (int blk = 1; blk < nblk; ++blk) {   // later blocks: start them towards L2 now
+      const int h0 = grp * g.hpg + blk * HB;
+      tma_prefetch_3d(&tmX, col_base + blk * 64, c * QT, b);
+      tma_prefetch_3d(&tmDY, col_base + blk * 64, c * QT, b);
+      for (int kb = 0; kb < NB; ++kb) {
+        tma_prefetch_3d(&tmS, kb * 64, h0 * P, b * g.nc + c);
+        tma_prefetch_3d(&tmDS, kb * 64, h0 * P, b * g.nc + c);
+      }
+      bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
+    }
+  }
+  uint32_t inphase = 0, mphase = 0;
+  zero_upper_block(row, part, warp, smem_u32(sM));   // M_h never writes these blocks
+  w.wait(&bar_cb, 0, 21);
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t idG = make_idesc(128, 128, 0, 0);
+    const uint64_t dc = desc_sw128_k(smem_u32(sC), 0), db = desc_sw128_k(smem_u32(sB), 0);
+#pragma unroll
+    for (int kb = 0; kb < NB; ++kb)
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        mma_bf16(tmG, desc_adv(dc, kb * BOX_BYTES + ks * 32), desc_adv(db, kb * BOX_BYTES + ks * 32), idG, (kb | ks) > 0);
+    mma_commit(&bar_mma);
+  }
+  w.wait(&bar_mma, mphase, 22);
+  mphase ^= 1;
+  tc_fence_after();
+
+  const uint32_t idY = make_idesc(128, P, 0, 1), idU = make_idesc(128, P, 1, 1), idO = make_idesc(128, 64, 0, 0);
+  const uint64_t dMk0 = desc_plain_k(smem_u32(sM), 128, 0), dMt0 = desc_plain_mn(smem_u32(sM), 128, 0, 0);
+  const uint64_t dC0 = desc_sw128_k(smem_u32(sC), 0), dB0 = desc_sw128_k(smem_u32(sB), 0);
+  const int t_row = c * QT + row;
+  const int hl_e = (part * 16) / P;            // head (inside the block) of this thread's epilogue columns
+  for (int blk = 0; blk < nblk; ++blk) {
+    const int h0 = grp * g.hpg + blk * HB;
+    const int h_e = h0 + hl_e;
+    const float Dh = D ? __ldg(D + h_e) : 0.f;
+    w.wait(&bar_in, inphase, 23);
+    inphase ^= 1;
+    for (int hl = 0; hl < HB; ++hl) {
+      decay_mask_block(tmG, tb + hl * TAB, row, part, warp, smem_u32(sM));
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint64_t dX0 = desc_sw128_mn(smem_u32(xt), 0, hl * P * 2, 16), dY0 = desc_sw128_mn(smem_u32(dyt), 0, hl * P * 2, 16);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          mma_bf16(tmYd + hl * P, desc_adv(dMk0, ks * 4096), desc_adv(dX0, ks * 2048), idY, ks > 0);
+          mma_bf16(tmUd + hl * P, desc_adv(dMt0, ks * 256), desc_adv(dY0, ks * 2048), idU, ks > 0);
+        }
+        if (hl == 0) {
+          const uint64_t dS0 = desc_sw128_k(smem_u32(stS), 0), dDS0 = desc_sw128_k(smem_u32(stDS), 0);
+#pragma unroll
+          for (int kb = 0; kb < NB; ++kb)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              mma_bf16(tmYo, desc_adv(dC0, kb * BOX_BYTES + ks * 32), desc_adv(dS0, kb * SBOX_BYTES + ks * 32), idO, (kb | ks) > 0);
+              mma_bf16(tmUo, desc_adv(dB0, kb * BOX_BYTES + ks * 32), desc_adv(dDS0, kb * SBOX_BYTES + ks * 32), idO, (kb | ks) > 0);
+            }
+        }
+        mma_commit(&bar_mma);
+      }
+      w.wait(&bar_mma, mphase, 24);
+      mphase ^= 1;
+      tc_fence_after();
+    }
+    // ---- epilogue for the HB heads of this block: this thread has 64/PARTS = 16 of the 64 columns.
+    // Copy what is needed from the input buffers into registers first, so the buffers can be refilled.
+    uint4 xv[2], dv[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      xv[q] = ld_shared_v4(smem_u32(xt) + sw128_off(row, part * 2 + q));
+      dv[q] = ld_shared_v4(smem_u32(dyt) + sw128_off(row, part * 2 + q));
+    }
+    const float cs_r = tb[hl_e * TAB + T_CS + row], dt_r = tb[hl_e * TAB + T_DT + row];
+    const float osc_y = ex2(cs_r), osc_u = dt_r * ex2(tb[hl_e * TAB + T_CS + 127] - cs_r);
+    __syncthreads();
+    if (tid == 0 && blk + 1 < nblk) load_block(blk + 1);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+    {
+      float yd[16], yo[16];
+      tmem_ld16(tmem_addr(tmYd, (warp & 3) * 32, part * 16), yd);
+      tmem_ld16(tmem_addr(tmYo, (warp & 3) * 32, part * 16), yo);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        float xs[8], dys[8];
+        unpack8(xv[q], xs);
+        unpack8(dv[q], dys);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float acc = yd[q * 8 + k] + osc_y * yo[q * 8 + k];
+          s0 = fmaf(dys[k], acc, s0);
+          s1 = fmaf(dys[k], xs[k], s1);
+        }
+      }
+    }
+    {
+      float ud[16], uo[16];
+      tmem_ld16(tmem_addr(tmUd, (warp & 3) * 32, part * 16), ud);
+      tmem_ld16(tmem_addr(tmUo, (warp & 3) * 32, part * 16), uo);
+      const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + (size_t)h0 * P + part * 16;
+      uint4 ov[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        float xs[8], dys[8], o[8];
+        unpack8(xv[q], xs);
+        unpack8(dv[q], dys);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float acc = ud[q * 8 + k] + osc_u * uo[q * 8 + k];
+          o[k] = acc + Dh * dys[k];
+          s2 = fmaf(xs[k], acc, s2);
+        }
+        ov[q] = pack8(o);
+      }
+      st_global_32B(dx + dense, ov[0], ov[1]);
+    }
+    sRed[part * 128 + row] = s0;
+    sRed[(PARTS + part) * 128 + row] = s1;
+    sRed[(2 * PARTS + part) * 128 + row] = s2;
+    tc_fence_before();
+    __syncthreads();
+    if ((part % (P / 16)) == 0) {
+      float t0 = 0.f, t1 = 0.f, t2 = 0.f;
+#pragma unroll
+      for (int k = 0; k < P / 16; ++k) {
+        t0 += sRed[(part + k) * 128 + row];
+        t1 += sRed[(PARTS + part + k) * 128 + row];
+        t2 += sRed[(2 * PARTS + part + k) * 128 + row];
+      }
+      const size_t co = ((size_t)(b * g.H + h_e) * g.nc + c) * QT + row;
+      dcsp[co] = t0;
+      ddot[co] = t1;
+      ddtd[co] = dt_r > 0.f ? t2 / dt_r : 0.f;
+    }
+  }
+  if (warp == 1) tmem_dealloc(tm, TM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Backward, dB and dC.  grid = (nc, G, B).  Per head W_h = dY_h X_h^T (128x128, TMEM), masked and
 // decayed like M_h into W'_h (bf16, shared memory), then accumulated over the heads of the group
 //   dC[i,n] += W'_h B      (+ per head block)  (exp(cs_i) dY) S_prev
@@ -2572,6 +2785,21 @@ int launch_bwd_ws(const Geo& g, const SeqMaps& m, const float* tab, const float*
   return SSD_OK;
 }
 
+template <int P, int N>
+constexpr size_t bwd_tc_smem() {
+  return 1024 + 2 * (N / 64) * BOX_BYTES + 2 * BOX_BYTES + 2 * BOX_BYTES + 2 * (N / 64) * SBOX_BYTES + (64 / P) * TAB_BYTES + 3 * PARTS * 128 * 4;
+}
+template <int P, int N>
+int launch_bwd_tc(const Geo& g, const SeqMaps& m, const float* tab, const float* D, void* dx, float* dcsp, float* ddot,
+                  float* ddtd, int* status, cudaStream_t s) {
+  auto k = k_bwd_tc<P, N>;
+  constexpr size_t sm = bwd_tc_smem<P, N>();
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  k<<<dim3(g.nc, g.G, g.B), TC_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, D, (bf16*)dx, dcsp, ddot, ddtd, status);
+  SSD_CUDA_CHECK_LAUNCH("scan_bwd_dx_tc");
+  return SSD_OK;
+}
+
 template <int P>
 int launch_dbc_ws(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
   auto k = k_dbc_ws<P>;
@@ -2749,13 +2977,17 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
 #undef CALL
 }
 
-// ungated backward with dstate 64: recompute pass and dx pass in one kernel (false if not applicable)
-bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p) { return g.N == 64 && !p.z && !g.onetile; }
+// ungated backward: recompute pass and dx pass in one kernel (persistent for dstate 64, one tile per CTA for dstate 128)
+bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p) { return !p.z && (g.N == 128 || !g.onetile); }
 int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, const void* ds_bf,
                       float* dcsp, float* ddot, float* ddtd, int* status, cudaStream_t s) {
   SeqMaps m;
   int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, prev_bf, ds_bf, &m);
   if (rc) return rc;
+  if (g.N == 128) {   // one tile per CTA
+    if (g.P == 32) return launch_bwd_tc<32, 128>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
+    return launch_bwd_tc<64, 128>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
+  }
   if (g.P == 32) return launch_bwd_ws<32>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
   return launch_bwd_ws<64>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
 }
