@@ -31,7 +31,7 @@ __device__ __forceinline__ float dt_activation(float raw, float bias, int softpl
 struct WsLayout {
   size_t status;                                     // 256-byte status block (int32 code first)
   size_t cs, dtf, states, fin, cb;                   // forward
-  size_t tab, prev_bf;                               // forward, tensor-core family only (else empty)
+  size_t tab, prev_bf, hmax;                         // forward, tensor-core family only (else empty)
   size_t ds_bf;                                      // backward, tensor-core family only
   size_t dstates, wsum, dyp, dcsp, ddtd, ddot, sdot, dapart, ddpart, dini;  // backward extras (wsum: CUDA-core family only)
   size_t total_fwd, total_bwd;

@@ -110,6 +110,7 @@ static void make_layout(const Geo& g, bool has_z, bool tcfam, WsLayout* w) {
   w->cb = take(tcfam ? 0 : ncb);   // C B^T stays on chip in the tensor-core family
   w->tab = take(tcfam ? (size_t)g.B * g.nc * g.H * SSD_TAB_FLOATS * f : 0);
   w->prev_bf = take(tcfam ? nst / 2 : 0);
+  w->hmax = take(tcfam ? (size_t)g.H * f : 0);   // per head: largest |chunk total of dt*A| of the call
   w->total_fwd = o;
   w->dstates = take(nst);
   w->ds_bf = take(tcfam ? nst / 2 : 0);

@@ -34,8 +34,9 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
 bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p);
 int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, const void* ds_bf,
                       float* dcsp, float* ddot, float* ddtd, int* status, cudaStream_t s);
-int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
-               const void* ds_bf, int* status, cudaStream_t s);
+// `hmax` [H]: per head, the largest |sum of dt*A over a chunk| of the call (written by the cumsum kernel)
+int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const float* hmax,
+               const void* prev_bf, const void* ds_bf, int* status, cudaStream_t s);
 
 // status word of a workspace -> SSD_OK / SSD_ERR_TIMEOUT (message set); the sync reader copies it to the host first
 int status_code_to_rc(int32_t code, const char* where);

@@ -90,7 +90,7 @@ struct DySrc {
 template <typename T>
 __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ dt_bias,
                                                const float* __restrict__ A, float* __restrict__ cs,
-                                               float* __restrict__ dtf, float* __restrict__ tab) {
+                                               float* __restrict__ dtf, float* __restrict__ tab, float* __restrict__ hmax) {
   constexpr int HG = 8;
   const int c = blockIdx.x, b = blockIdx.y, q = threadIdx.x;
   __shared__ float wsum[NT / 32][HG];
@@ -137,6 +137,8 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
         // tensor-core family (chunk 128 only): the per-head decay table [cs*log2e | dt | exp(cs_r - cs) dt |
         // exp(dt_{l+1} A)], r = last position of the 32-block (lane 31 of this warp)
         const float vend = __shfl_sync(0xffffffffu, v[k], 31);
+        // per head, the largest decay exponent any chunk of the call accumulates (non-negative floats order like ints)
+        if (hmax && h < g.H && q == g.Q - 1) atomicMax(reinterpret_cast<int*>(hmax) + h, __float_as_int(fabsf(v[k])));
         if (tab && h < g.H && q < g.Q) {
           const float L2E = 1.4426950408889634f;
           float* t = tab + ((size_t)(b * g.nc + c) * g.H + h) * SSD_TAB_FLOATS + q;
@@ -745,7 +747,9 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   const bool fused = tc && stages == (SSD_STAGE_LOCAL | SSD_STAGE_FINISH) && tensor_state_fused_applies(g);
   if (stages & (SSD_STAGE_LOCAL | SSD_STAGE_LOCAL_STATES)) {
     cudaMemsetAsync(status, 0, 256, s);
-    k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr);
+    float* hmax = tc ? (float*)(ws + w.hmax) : nullptr;
+    if (tc) cudaMemsetAsync(hmax, 0, (size_t)g.H * sizeof(float), s);
+    k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr, hmax);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
     if (tc && fused) {
       // chunk states and the scan over chunks run as one kernel in the FINISH stage
@@ -909,7 +913,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       int rc = tensor_bwd_merged_applies(g, p) ? tensor_bwd_merged(g, p, tab, prev_bf, ds_bf, dcsp, ddot, ddtd, status, s)
                                                 : tensor_dx(g, p, tc_dy, tc_dense, tab, ds_bf, ddtd, status, s);
       if (rc) return rc;
-      rc = tensor_dbc(g, p, tc_dy, tc_dense, tab, prev_bf, ds_bf, status, s);
+      rc = tensor_dbc(g, p, tc_dy, tc_dense, tab, (const float*)(ws + w.hmax), prev_bf, ds_bf, status, s);
       if (rc) return rc;
     } else {
       k_dx<T><<<dim3(tq * tp, g.nc * g.H, g.B), NT, 0, s>>>(g, x, (const T*)p.Bm, p.D, dys, cs, dtf, cb, dst,

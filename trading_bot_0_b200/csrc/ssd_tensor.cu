@@ -80,7 +80,8 @@ __global__ void k_selftest_wait(int* status, long long max_cycles) {
 __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __restrict__ tab, int row, int part,
                                                 int warp, uint32_t mtile) {
   const int rb = warp & 3;                 // block row of this warp (warp-uniform)
-  const float csi = tab[T_CS + row];
+  const uint32_t ts = smem_u32(tab);       // the table sits in shared memory: read it through the shared-memory pipe
+  const float csi = lds_f32(ts + 4 * (T_CS + row));
   uint32_t raw[4][8];
 #pragma unroll
   for (int cb = 0; cb < 4; ++cb)
@@ -94,17 +95,17 @@ __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __
 #pragma unroll
     for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(raw[cb][k]);
     if (cb < rb) {
-      const float rf = ex2(csi - tab[T_CS + cb * 32 + 31]);
-      const float4 f0 = *reinterpret_cast<const float4*>(tab + T_CF + c0), f1 = *reinterpret_cast<const float4*>(tab + T_CF + c0 + 4);
+      const float rf = ex2(csi - lds_f32(ts + 4 * (T_CS + cb * 32 + 31)));
+      const float4 f0 = lds_v4f32(ts + 4 * (T_CF + c0)), f1 = lds_v4f32(ts + 4 * (T_CF + c0 + 4));
       v[0] *= rf * f0.x; v[1] *= rf * f0.y; v[2] *= rf * f0.z; v[3] *= rf * f0.w;
       v[4] *= rf * f1.x; v[5] *= rf * f1.y; v[6] *= rf * f1.z; v[7] *= rf * f1.w;
     } else {
       const int je = c0 + 7;
-      const float4 d0 = *reinterpret_cast<const float4*>(tab + T_DS + c0), d1 = *reinterpret_cast<const float4*>(tab + T_DS + c0 + 4);
-      const float4 t0 = *reinterpret_cast<const float4*>(tab + T_DT + c0), t1 = *reinterpret_cast<const float4*>(tab + T_DT + c0 + 4);
+      const float4 d0 = lds_v4f32(ts + 4 * (T_DS + c0)), d1 = lds_v4f32(ts + 4 * (T_DS + c0 + 4));
+      const float4 t0 = lds_v4f32(ts + 4 * (T_DT + c0)), t1 = lds_v4f32(ts + 4 * (T_DT + c0 + 4));
       const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};   // ds[k] = decay of step c0+k+1
       const float dt[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-      float run = (row >= je) ? ex2(csi - tab[T_CS + je]) : 0.f;
+      float run = (row >= je) ? ex2(csi - lds_f32(ts + 4 * (T_CS + je))) : 0.f;
       v[7] *= run * dt[7];
 #pragma unroll
       for (int k = 6; k >= 0; --k) {
@@ -112,6 +113,27 @@ __device__ __forceinline__ void decay_mask_tile(uint32_t tm_src, const float* __
         v[k] *= run * dt[k];
       }
     }
+    st_shared_v4(mtile + plain_off(128, row, c0), pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
+                 pack_bf16(v[6], v[7]));
+  }
+}
+// Lower-triangular mask only: source = a 128x128 fp32 accumulator in TMEM that already carries the decay (separable heads,
+// see k_dbc_ws), result = src[i,j] for j <= i as bf16 in a plain 128x128 tile.  Thread mapping of decay_mask_tile; blocks
+// above the diagonal are never written (they are zero in every ring tile for the whole kernel).
+__device__ __forceinline__ void mask_tril_tile(uint32_t tm_src, int row, int part, int warp, uint32_t mtile) {
+  const int rb = warp & 3;
+  uint32_t raw[4][8];
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb)
+    if (cb <= rb) tmem_ld8_issue(tmem_addr(tm_src, rb * 32, cb * 32 + part * 8), raw[cb]);
+  tmem_ld_wait();
+#pragma unroll
+  for (int cb = 0; cb < 4; ++cb) {
+    if (cb > rb) continue;
+    const int c0 = cb * 32 + part * 8;
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = (cb < rb || c0 + k <= row) ? __uint_as_float(raw[cb][k]) : 0.f;
     st_shared_v4(mtile + plain_off(128, row, c0), pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
                  pack_bf16(v[6], v[7]));
   }
@@ -309,6 +331,22 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 }
 __device__ __forceinline__ uint4 pack8(const float (&o)[8]) {
   return make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+}
+
+// Eight bf16 values (one 16-byte piece) times one fp32 factor, in packed bf16 arithmetic: the factor is split into a high
+// and a low bf16 part, out = v * f_hi + v * f_lo with one fused multiply-add, so the factor itself is carried to ~16 bits and
+// the result differs from an fp32 multiply followed by one rounding only by the rounding of the first product.  Two
+// instructions per pair of values instead of unpack, two multiplies and a (quarter-rate) convert.
+__device__ __forceinline__ uint4 scale8_bf16(const uint4& v, float f) {
+  const __nv_bfloat16 fh = __float2bfloat16_rn(f);
+  const __nv_bfloat16 fl = __float2bfloat16_rn(f - __bfloat162float(fh));
+  const __nv_bfloat162 h2 = __halves2bfloat162(fh, fh), l2 = __halves2bfloat162(fl, fl);
+  uint4 o;
+  const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&v);
+  __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) out[k] = __hfma2(in[k], l2, __hmul2(in[k], h2));
+  return o;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -940,8 +978,11 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
 // The state block (tmS) is the bf16 copy of S_prev (modes 0,1) or dS_end (mode 2).
 // IBUF = 2: the inputs of head block k+1 load while block k computes; IBUF = 1: they are
 // requested as soon as block k's epilogue has copied what it needs into registers.
+// Two CTAs per SM wherever shared memory allows it (dstate 64; dstate 128 forward): a CTA is a chain of phases that meet
+// at CTA-wide barriers, and a second resident CTA fills the gaps (dstate 128 forward: 0.95 -> 0.75 ms on the long-sequence
+// shapes).
 template <int P, int N, int IBUF, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1)
+__global__ void __launch_bounds__(TC_THREADS, (N <= 64 || MODE == 0) ? 2 : 1)
 k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
           const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
@@ -2283,25 +2324,42 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------------------------
-// Backward dB / dC, dstate 64, persistent and warp-specialised like k_scan_ws.  Per head
-//   W_h = dY_h X_h^T (K = P) into one of two TMEM slots -> decay pass -> W'_h (ring of 2 tiles) ->
-//   dC += W'_h B, dB += W'_h^T C;
-// per head block, once its raw x / dy boxes are no longer needed by a W product, the decay warps scale
-// them in place (dy by exp(cs_i), x by exp(cs_end-cs_j) dt_j) and one K = 64 product each adds the state
-// terms dC += dY' S_prev, dB += X' dS_end.  dC / dB stay in TMEM for the whole tile (one slot).
+// Backward dB / dC, dstate 64, persistent and warp-specialised like k_scan_ws.
+//
+// Block path (any head).  Per head W_h = dY_h X_h^T (K = P) into one of two TMEM slots -> decay pass (32x32 blocks, the
+// factorisation of decay_mask_tile) -> W'_h as bf16 in shared memory -> dC += W'_h B, dB += W'_h^T C.
+// Per head block, once its raw x / dy boxes are no longer needed by a W product, the decay warps scale them in place and
+// one K = 64 product each adds the state terms dC += dY' S_prev, dB += X' dS_end.  dC / dB stay in TMEM for the whole tile.
+//
+// Separable heads.  exp(cs_i - cs_j) dt_j = a_i b_j with a_i = exp(cs_i), b_j = exp(-cs_j) dt_j, and dC, dB are linear in
+// W'_h, so for a head whose decay over a chunk stays inside the range of the storage type (|cs_end| <= SEP_LOG_RANGE for
+// every chunk of the call; the cumsum kernel records the per-head maximum) the decay can ride on the OPERANDS:
+//   sum_h W'_h = tril( sum_h (a_h o dY_h) (b_h o X_h)^T ),
+// one accumulator for all such heads of the tile, filled by the tensor core from the boxes the decay warps scale in place
+// anyway for the state terms (dy by a, x by b; the factor exp(cs_end) that the x-side state term then lacks goes onto the
+// rows of the dS_end box).  Those heads need no per-head pass over a 128x128 tile at all; once per tile the accumulator is
+// masked to its lower triangle and multiplied like one more W'_h.  Heads outside the range (strong decay: a_i or b_j alone
+// would leave the range although every a_i b_j with j <= i is at most dt_j) keep the block path.
+//
+// With the per-head pass gone for most heads a tile is a short chain of scale -> multiply steps, and what bounds the kernel
+// is how far the loads run ahead of it: the x/dy boxes have a ring of three, the state boxes of two, the tables of four;
+// the B/C tiles (read at the END of a tile by the separable path) and the W' tile are single.
+constexpr float SEP_LOG_RANGE = 64.f;
+
 template <int P>
 struct DbCfg {
-  static constexpr int N = 64, HB = 64 / P, NM = 2, NT = 4;
+  static constexpr int N = 64, HB = 64 / P, NT = 4, NIN = 3, NST = 2;
   static constexpr int CB_BYTES = 2 * BOX_BYTES;             // B tile, C tile
   static constexpr int IN_BYTES = 2 * BOX_BYTES;             // x box, dy box
   static constexpr int ST_BYTES = 2 * SBOX_BYTES;            // S_prev box, dS_end box
   static constexpr int TB_BYTES = HB * TAB_BYTES;
-  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + ST_BYTES + NT * TB_BYTES;
+  static constexpr size_t SMEM = 1024 + CB_BYTES + 2 * BOX_BYTES + NIN * IN_BYTES + NST * ST_BYTES + NT * TB_BYTES;
 };
 
 struct DbBars {
-  uint64_t cb_full[2], cb_empty[2], in_full[2], in_empty[2], w_full[2], w_empty[2], m_full[2], m_empty[2];
-  uint64_t tab_full[4], tab_empty[4], st_full, st_empty, wraw_done[2], sc_full[2], acc_full, acc_empty, done;
+  uint64_t cb_full, cb_empty, in_full[3], in_empty[3], w_full[2], w_empty[2], m_full, m_empty;
+  uint64_t tab_full[4], tab_empty[4], st_full[2], st_empty[2], wraw_done[3], sc_full[3], acc_full, acc_empty, done;
+  uint64_t wsep_full, wsep_empty;
 };
 
 template <int P>
@@ -2309,16 +2367,17 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
 k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
          const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmDS,
-         const float* __restrict__ tab, bf16* __restrict__ dB, bf16* __restrict__ dC, int* __restrict__ status) {
+         const float* __restrict__ tab, const float* __restrict__ hmax, bf16* __restrict__ dB, bf16* __restrict__ dC,
+         int* __restrict__ status) {
   using Cfg = DbCfg<P>;
-  constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM;
+  constexpr int N = Cfg::N, HB = Cfg::HB, NIN = Cfg::NIN, NST = Cfg::NST, NT = Cfg::NT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
-  uint8_t* sCB = smem;                                   // 2 x {B tile, C tile}
-  uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB W'_h tiles
-  uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x box, dy box}
-  uint8_t* sSt = sIn + 2 * Cfg::IN_BYTES;                // S_prev box, dS_end box
-  uint8_t* sTab = sSt + Cfg::ST_BYTES;                   // NT x decay tables of a head block
+  uint8_t* sCB = smem;                                   // {B tile, C tile} of the current tile
+  uint8_t* sM = sCB + Cfg::CB_BYTES;                     // one 32 KB W' tile
+  uint8_t* sIn = sM + 2 * BOX_BYTES;                     // NIN x {x box, dy box}
+  uint8_t* sSt = sIn + NIN * Cfg::IN_BYTES;              // NST x {S_prev box, dS_end box}
+  uint8_t* sTab = sSt + NST * Cfg::ST_BYTES;             // NT x decay tables of a head block
   __shared__ __align__(8) DbBars bars;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
@@ -2328,32 +2387,43 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   __syncthreads();
   if (s_abort) return;
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
-      // two MMA issuer lanes (dC side, dB side): tcgen05.commit tracks the MMAs of its own thread only, so every barrier that
-      // releases something both of them read expects one commit from each
-      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 2);
+    // two MMA issuer lanes (dC side, dB side): tcgen05.commit tracks the MMAs of its own thread only, so every barrier that
+    // releases something both of them read expects one commit from each
+    mbar_init(&bars.cb_full, 1); mbar_init(&bars.cb_empty, 2);
+    for (int i = 0; i < NIN; ++i) {
       mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 2);
-      mbar_init(&bars.w_full[i], 1); mbar_init(&bars.w_empty[i], WS_SCALE_WARPS);
-      mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 2);
+      mbar_init(&bars.wraw_done[i], 1); mbar_init(&bars.sc_full[i], WS_SCALE_WARPS);
     }
-    for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS); }
-    mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 2);
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars.wraw_done[i], 1); mbar_init(&bars.sc_full[i], WS_SCALE_WARPS); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars.w_full[i], 1); mbar_init(&bars.w_empty[i], WS_SCALE_WARPS); }
+    mbar_init(&bars.m_full, WS_SCALE_WARPS); mbar_init(&bars.m_empty, 2);
+    for (int i = 0; i < NT; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS); }
+    for (int i = 0; i < NST; ++i) { mbar_init(&bars.st_full[i], 1); mbar_init(&bars.st_empty[i], 2); }
     mbar_init(&bars.acc_full, 2); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
     mbar_init(&bars.done, 2);
+    mbar_init(&bars.wsep_full, 1); mbar_init(&bars.wsep_empty, WS_SCALE_WARPS);
     mbar_fence_init();
   }
   if (warp == 17) tmem_alloc(&tmem_slot, 512);
   if (tid < 512) {
-    for (int i = 0; i < NM; ++i) zero_upper_blocks(tid & 127, tid >> 7, warp, smem_u32(sM + i * 2 * BOX_BYTES));
+    zero_upper_blocks(tid & 127, tid >> 7, warp, smem_u32(sM));
     fence_async_smem();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
-  const uint32_t tmDC = tm + 256, tmDB = tm + 320;
+  const uint32_t tmDC = tm + 256, tmDB = tm + 320, tmWsep = tm + 384;
   Waiter w{status, false};
+  // which heads take the separable path: one bit per head, the same in every role (up to 64 heads; beyond that none)
+  unsigned long long sepmask = 0ull;
+  if (hmax && g.H <= 64)
+    for (int h = 0; h < g.H; ++h)
+      if (__ldg(hmax + h) <= SEP_LOG_RANGE) sepmask |= 1ull << h;
+  auto is_sep = [&](int h) { return ((sepmask >> h) & 1ull) != 0; };
+  auto group_has_sep = [&](int grp) {
+    const unsigned long long gm = (g.hpg >= 64 ? ~0ull : ((1ull << g.hpg) - 1ull)) << (grp * g.hpg);
+    return (sepmask & gm) != 0ull;
+  };
 
   const int nblk = g.hpg / HB;
   const int ntiles = g.B * g.G * g.nc;
@@ -2365,32 +2435,27 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     grp = r % g.G;
     b = r / g.G;
   };
+  // use n (0, 1, 2, ...) of a ring of depth D sits in slot n % D; its `full` wait has parity (n / D) & 1, its `empty` wait the
+  // opposite (a fresh barrier passes a wait on parity 1)
+  auto par = [](int n, int depth) { return (uint32_t)((n / depth) & 1); };
 
+  // registers: the single-thread roles (warps 16-19, one aligned group of four) and the epilogue hand some back, the decay
+  // warps take them (80 * 512 + 64 * 128 + 48 * 256 <= the launch-time 72 * 896)
+  if (warp >= 16 && warp < 20) reg_dec<64>();
   if (warp == 16) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      auto load_cb = [&](int t) {
-        int b, grp, c;
-        tile_coords(t, b, grp, c);
-        const int cs_ = t & 1;
-        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
-        uint8_t* dst = sCB + cs_ * Cfg::CB_BYTES;
-        mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
-        tma_load_3d(dst, &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
-        tma_load_3d(dst + BOX_BYTES, &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
-      };
       const int total_blocks = my_tiles * nblk;
       auto load_tab = [&](int kg) {
         if (kg >= total_blocks) return;
         int b, grp, c;
         tile_coords(kg / nblk, b, grp, c);
-        const int h0 = grp * g.hpg + (kg % nblk) * HB, ts = kg % Cfg::NT;
-        w.wait(&bars.tab_empty[ts], ((kg / Cfg::NT) & 1) ^ 1, 49);
+        const int h0 = grp * g.hpg + (kg % nblk) * HB, ts = kg % NT;
+        w.wait(&bars.tab_empty[ts], par(kg, NT) ^ 1, 49);
         mbar_expect_tx(&bars.tab_full[ts], Cfg::TB_BYTES);
         bulk_load(sTab + ts * Cfg::TB_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, Cfg::TB_BYTES, &bars.tab_full[ts]);
       };
       int kb = 0;
-      load_cb(0);
       load_tab(0);
       load_tab(1);
       for (int t = 0; t < my_tiles; ++t) {
@@ -2398,97 +2463,136 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         tile_coords(t, b, grp, c);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           load_tab(kb + 2);
-          const int ib = kb & 1;
+          const int ib = kb % NIN, sb = kb % NST;
           const int h0 = grp * g.hpg + blk * HB, col = grp * g.hpg * P + blk * 64;
-          w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
+          w.wait(&bars.in_empty[ib], par(kb, NIN) ^ 1, 42);
           uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
           mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
           tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
           tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
-          w.wait(&bars.st_empty, (kb & 1) ^ 1, 50);
-          mbar_expect_tx(&bars.st_full, Cfg::ST_BYTES);
-          tma_load_3d(sSt, &tmS, 0, h0 * P, b * g.nc + c, &bars.st_full);
-          tma_load_3d(sSt + SBOX_BYTES, &tmDS, 0, h0 * P, b * g.nc + c, &bars.st_full);
-          if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+          w.wait(&bars.st_empty[sb], par(kb, NST) ^ 1, 50);
+          uint8_t* sd = sSt + sb * Cfg::ST_BYTES;
+          mbar_expect_tx(&bars.st_full[sb], Cfg::ST_BYTES);
+          tma_load_3d(sd, &tmS, 0, h0 * P, b * g.nc + c, &bars.st_full[sb]);
+          tma_load_3d(sd + SBOX_BYTES, &tmDS, 0, h0 * P, b * g.nc + c, &bars.st_full[sb]);
+          // this tile's B / C: single buffer, free once the previous tile's last products have completed; requested behind
+          // the tile's first boxes so that this wait does not hold the box stream back
+          if (blk == (nblk > 1 ? 1 : 0)) {
+            w.wait(&bars.cb_empty, (t & 1) ^ 1, 41);
+            mbar_expect_tx(&bars.cb_full, Cfg::CB_BYTES);
+            tma_load_3d(sCB, &tmB, grp * N, c * QT, b, &bars.cb_full);
+            tma_load_3d(sCB + BOX_BYTES, &tmC, grp * N, c * QT, b, &bars.cb_full);
+          }
         }
       }
     }
   } else if (warp == 17 || warp == 18) {
-    // ------------------------------------------------------------------ MMA issuers.  One lane alone is busy ~64 % of the
-    // kernel (every tcgen05.mma costs its issuing thread ~50 cycles, 22 per head here), so the products are split by side:
-    // lane A (warp 17) issues W = dY X^T and everything that accumulates into dC, lane B (warp 18) everything into dB.
+    // ------------------------------------------------------------------ MMA issuers.  The products are split by side:
+    // lane A (warp 17) issues every W product and everything that accumulates into dC, lane B (warp 18) everything into dB.
     if (lane == 0) {
       const bool side_c = warp == 17;
       const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
-      const uint64_t dSm0 = desc_sw128_mn(smem_u32(sSt), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sSt + SBOX_BYTES), 0, 0, SBOX_BYTES);
       const int total_blocks = my_tiles * nblk;
-      int kw = 0;   // W products issued so far (global head counter of the W stage)
-      auto issue_w_block = [&](int kg) {   // all W products of global block kg (lane A only)
+      int kw = 0;   // W products of block-path heads issued so far
+      auto issue_w_block = [&](int kg) {   // the W products of global block kg's heads on the block path (lane A only)
         if (kg >= total_blocks) return;
-        const int ib = kg & 1;
-        w.wait(&bars.in_full[ib], (kg >> 1) & 1, 45);
+        const int ib = kg % NIN;
+        int bb, gg, cc;
+        tile_coords(kg / nblk, bb, gg, cc);
+        const int h0 = gg * g.hpg + (kg % nblk) * HB;
+        bool any_block_path = false;
+        for (int hl = 0; hl < HB; ++hl) any_block_path |= !is_sep(h0 + hl);
+        if (!any_block_path) {   // nothing reads the raw boxes: release them at once, without waiting for them to land
+          mbar_arrive(&bars.wraw_done[ib]);
+          return;
+        }
+        w.wait(&bars.in_full[ib], par(kg, NIN), 45);
         tc_fence_after();
         const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
         const uint64_t dX0 = desc_sw128_k(inb, 0), dDY0 = desc_sw128_k(inb + BOX_BYTES, 0);
-        for (int hl = 0; hl < HB; ++hl, ++kw) {
+        for (int hl = 0; hl < HB; ++hl) {
+          if (is_sep(h0 + hl)) continue;
           const int ws = kw & 1;
-          w.wait(&bars.w_empty[ws], ((kw >> 1) & 1) ^ 1, 58);
+          w.wait(&bars.w_empty[ws], par(kw, 2) ^ 1, 58);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < P / 16; ++ks)
             mma_bf16(tm + ws * 128, desc_adv(dDY0, hl * P * 2 + ks * 32), desc_adv(dX0, hl * P * 2 + ks * 32), idW, ks > 0);
           mma_commit(&bars.w_full[ws]);
+          ++kw;
         }
-        mma_commit(&bars.wraw_done[kg & 1]);   // the raw boxes of this block have been read by every W product
+        mma_commit(&bars.wraw_done[ib]);   // the raw boxes of this block have been read by every W product
       };
       if (side_c) issue_w_block(0);
-      int kb = 0, kh = 0;
+      const uint64_t dBm0 = desc_sw128_mn(smem_u32(sCB), 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(smem_u32(sCB) + BOX_BYTES, 0, 0, BOX_BYTES);
+      const uint32_t mt = smem_u32(sM);
+      const uint64_t dMk = desc_plain_k(mt, 128, 0), dMt = desc_plain_mn(mt, 128, 0, 0);
+      int kb = 0, kh = 0, ksep = 0;   // kh: W' tiles consumed; ksep: tiles with separable heads so far
       for (int t = 0; t < my_tiles; ++t) {
-        w.wait(&bars.cb_full[t & 1], (t >> 1) & 1, 43);
         w.wait(&bars.acc_empty, (t & 1) ^ 1, 46);
         tc_fence_after();
-        const uint32_t ct = smem_u32(sCB + (t & 1) * Cfg::CB_BYTES);
-        const uint64_t dBm0 = desc_sw128_mn(ct, 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(ct + BOX_BYTES, 0, 0, BOX_BYTES);
-        bool first = true;
-        for (int blk = 0; blk < nblk; ++blk, ++kb) {
-          const int ib = kb & 1;
-          const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
-          for (int hl = 0; hl < HB; ++hl, ++kh) {
-            const int ms = kh % NM;
-            w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
-            tc_fence_after();
-            const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
-            if (side_c) {
-              const uint64_t dMk = desc_plain_k(mt, 128, 0);
+        int tb_, tg_, tc_;
+        tile_coords(t, tb_, tg_, tc_);
+        const bool anysep = group_has_sep(tg_);
+        bool first = true, firstsep = true, have_cb = false;
+        auto issue_m = [&]() {   // the W' tile -> dC (lane A) or dB (lane B)
+          if (!have_cb) { w.wait(&bars.cb_full, t & 1, 43); have_cb = true; }
+          w.wait(&bars.m_full, kh & 1, 47);
+          tc_fence_after();
+          if (side_c) {
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks) mma_bf16(tmDC, desc_adv(dMk, ks * 4096), desc_adv(dBm0, ks * 2048), idC, !first || ks > 0);
-            } else {
-              const uint64_t dMt = desc_plain_mn(mt, 128, 0, 0);
+            for (int ks = 0; ks < 8; ++ks) mma_bf16(tmDC, desc_adv(dMk, ks * 4096), desc_adv(dBm0, ks * 2048), idC, !first || ks > 0);
+          } else {
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks) mma_bf16(tmDB, desc_adv(dMt, ks * 256), desc_adv(dCm0, ks * 2048), idB, !first || ks > 0);
-            }
-            first = false;
-            mma_commit(&bars.m_empty[ms]);
+            for (int ks = 0; ks < 8; ++ks) mma_bf16(tmDB, desc_adv(dMt, ks * 256), desc_adv(dCm0, ks * 2048), idB, !first || ks > 0);
           }
+          first = false;
+          mma_commit(&bars.m_empty);
+          ++kh;
+        };
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          const int ib = kb % NIN, sb = kb % NST;
+          const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES), stb = smem_u32(sSt + sb * Cfg::ST_BYTES);
+          const int h0 = tg_ * g.hpg + blk * HB;
+          for (int hl = 0; hl < HB; ++hl)
+            if (!is_sep(h0 + hl)) issue_m();
           // the next block's W products go out before this block's state terms, so the decay warps
           // find their next input ready when they come back from scaling this block's boxes
           if (side_c) issue_w_block(kb + 1);
-          w.wait(&bars.sc_full[kb & 1], (kb >> 1) & 1, 59);
-          w.wait(&bars.st_full, kb & 1, 57);
+          w.wait(&bars.sc_full[ib], par(kb, NIN), 59);
+          w.wait(&bars.st_full[sb], par(kb, NST), 57);
           tc_fence_after();
           if (side_c) {
-            const uint64_t dDYk = desc_sw128_k(inb + BOX_BYTES, 0);
+            const uint64_t dDYk = desc_sw128_k(inb + BOX_BYTES, 0), dXk = desc_sw128_k(inb, 0);
+            const uint64_t dSm0 = desc_sw128_mn(stb, 0, 0, SBOX_BYTES);
+            // separable heads of this block: their W, decay included, adds up in one accumulator for the whole tile
+            for (int hl = 0; hl < HB; ++hl) {
+              if (!is_sep(h0 + hl)) continue;
+              if (firstsep) w.wait(&bars.wsep_empty, (ksep & 1) ^ 1, 60);   // the decay warps have read the previous tile's sum
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) mma_bf16(tmDC, desc_adv(dDYk, ks * 32), desc_adv(dSm0, ks * 2048), idC, true);
+              for (int ks = 0; ks < P / 16; ++ks)
+                mma_bf16(tmWsep, desc_adv(dDYk, hl * P * 2 + ks * 32), desc_adv(dXk, hl * P * 2 + ks * 32), idW, !firstsep || ks > 0);
+              firstsep = false;
+            }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) mma_bf16(tmDC, desc_adv(dDYk, ks * 32), desc_adv(dSm0, ks * 2048), idC, !first || ks > 0);
           } else {
             const uint64_t dXk = desc_sw128_k(inb, 0);
+            const uint64_t dDSm0 = desc_sw128_mn(stb + SBOX_BYTES, 0, 0, SBOX_BYTES);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) mma_bf16(tmDB, desc_adv(dXk, ks * 32), desc_adv(dDSm0, ks * 2048), idC, true);
+            for (int ks = 0; ks < 4; ++ks) mma_bf16(tmDB, desc_adv(dXk, ks * 32), desc_adv(dDSm0, ks * 2048), idC, !first || ks > 0);
           }
-          mma_commit(&bars.st_empty);
+          first = false;
+          mma_commit(&bars.st_empty[sb]);
           mma_commit(&bars.in_empty[ib]);
         }
-        mma_commit(&bars.cb_empty[t & 1]);
+        if (anysep) {
+          if (side_c) mma_commit(&bars.wsep_full);
+          ++ksep;
+          issue_m();   // the masked sum of the separable heads, handed over by the decay warps like one more W'_h
+        }
+        if (!have_cb) w.wait(&bars.cb_full, t & 1, 43);   // keep the barrier's phases in step even if nothing read the tiles
+        mma_commit(&bars.cb_empty);
         mma_commit(&bars.acc_full);
       }
       mma_commit(&bars.done);
@@ -2496,49 +2600,99 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     }
   } else if (warp < WS_SCALE_WARPS) {
     // ------------------------------------------------------------------ decay pass warps
+    reg_inc<80>();
     const int row = tid & 127, part = tid >> 7;
-    int kb = 0, kh = 0;
+    int kb = 0, kh = 0, kw = 0, ksep = 0;
     for (int t = 0; t < my_tiles; ++t) {
+      int tb_, tg_, tc_;
+      tile_coords(t, tb_, tg_, tc_);
+      const bool anysep = group_has_sep(tg_);
       for (int blk = 0; blk < nblk; ++blk, ++kb) {
-        const int ts = kb % Cfg::NT, ib = kb & 1;
+        const int ts = kb % NT, ib = kb % NIN, sb = kb % NST;
+        const int h0 = tg_ * g.hpg + blk * HB;
         const float* tb = (const float*)(sTab + ts * Cfg::TB_BYTES);
-        w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 52);
-        for (int hl = 0; hl < HB; ++hl, ++kh) {
-          const int ms = kh % NM, ws = kh & 1;
-          w.wait(&bars.w_full[ws], (kh >> 1) & 1, 51);
-          w.wait(&bars.m_empty[ms], ((kh / NM) & 1) ^ 1, 53);
+        const uint32_t tbs = smem_u32(sTab + ts * Cfg::TB_BYTES);
+        w.wait(&bars.tab_full[ts], par(kb, NT), 52);
+        for (int hl = 0; hl < HB; ++hl) {
+          if (is_sep(h0 + hl)) continue;
+          const int ws = kw & 1;
+          w.wait(&bars.w_full[ws], par(kw, 2), 51);
+          w.wait(&bars.m_empty, (kh & 1) ^ 1, 53);
           tc_fence_after();
-          decay_mask_tile(tm + ws * 128, tb + hl * TAB, row, part, warp, smem_u32(sM + ms * 2 * BOX_BYTES));
+          decay_mask_tile(tm + ws * 128, tb + hl * TAB, row, part, warp, smem_u32(sM));
           fence_async_smem();
+
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) { mbar_arrive(&bars.m_full[ms]); mbar_arrive(&bars.w_empty[ws]); }
+          if (lane == 0) { mbar_arrive(&bars.m_full); mbar_arrive(&bars.w_empty[ws]); }
+          ++kh;
+          ++kw;
         }
-        // scale this block's boxes in place for the state terms (x: box 0, dy: box 1)
-        w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
-        w.wait(&bars.wraw_done[kb & 1], (kb >> 1) & 1, 55);
+        // scale this block's boxes in place for the state terms (x: box 0, dy: box 1).  Block-path heads: x by
+        // exp(cs_end - cs_j) dt_j.  Separable heads: x by b_j = exp(-cs_j) dt_j (the operand of their W product as well),
+        // and the missing exp(cs_end) goes onto their rows of the dS_end box.
+        w.wait(&bars.in_full[ib], par(kb, NIN), 54);
+        w.wait(&bars.wraw_done[ib], par(kb, NIN), 55);
         uint8_t* xb = sIn + ib * Cfg::IN_BYTES;
+        // four 16-byte pieces per thread (x box: two, dy box: two): all loads first, then the factors, then the arithmetic,
+        // so that one warp has several independent chains in flight (four decay warps share a scheduler)
+        {
+          uint32_t adr[4];
+          uint4 raw[4];
+          float fac[4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int idx = tid + r * 512;
-          const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
-          const float* tt = tb + ((((pc ^ l) & 7) * 8) / P) * TAB;
-          const float f = box ? ex2(tt[T_CS + l]) : ex2(tt[T_CS + 127] - tt[T_CS + l]) * tt[T_DT + l];
-          const uint32_t a = smem_u32(xb + box * BOX_BYTES + l * 128 + pc * 16);
-          float v[8];
-          unpack8(ld_shared_v4(a), v);
+          for (int r = 0; r < 4; ++r) {
+            const int idx = tid + r * 512;
+            const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
+            adr[r] = smem_u32(xb + box * BOX_BYTES + l * 128 + pc * 16);
+            raw[r] = ld_shared_v4(adr[r]);
+          }
 #pragma unroll
-          for (int k = 0; k < 8; ++k) v[k] *= f;
-          const uint4 o = pack8(v);
-          st_shared_v4(a, o.x, o.y, o.z, o.w);
+          for (int r = 0; r < 4; ++r) {
+            const int idx = tid + r * 512;
+            const int box = idx >> 10, l = (idx >> 3) & 127, pc = idx & 7;
+            const int hl = (((pc ^ l) & 7) * 8) / P;
+            const uint32_t tt = tbs + hl * TAB_BYTES;
+            const float csl = lds_f32(tt + 4 * (T_CS + l));
+            fac[r] = box ? ex2(csl)
+                         : (is_sep(h0 + hl) ? ex2(-csl) : ex2(lds_f32(tt + 4 * (T_CS + 127)) - csl)) * lds_f32(tt + 4 * (T_DT + l));
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) raw[r] = scale8_bf16(raw[r], fac[r]);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) st_shared_v4(adr[r], raw[r].x, raw[r].y, raw[r].z, raw[r].w);
+        }
+        if (anysep) {
+          w.wait(&bars.st_full[sb], par(kb, NST), 61);
+          const int r = tid >> 3;                      // row (h,p) of the 64 x 64 dS_end box, one 16-byte piece per thread
+          const int hl = r / P;
+          if (is_sep(h0 + hl)) {
+            const float f = ex2(lds_f32(tbs + hl * TAB_BYTES + 4 * (T_CS + 127)));
+            const uint32_t a = smem_u32(sSt + sb * Cfg::ST_BYTES + SBOX_BYTES + r * 128 + (tid & 7) * 16);
+            const uint4 o = scale8_bf16(ld_shared_v4(a), f);
+            st_shared_v4(a, o.x, o.y, o.z, o.w);
+          }
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&bars.sc_full[kb & 1]); mbar_arrive(&bars.tab_empty[ts]); }
+        if (lane == 0) { mbar_arrive(&bars.sc_full[ib]); mbar_arrive(&bars.tab_empty[ts]); }
+      }
+      if (anysep) {   // the separable heads' sum: mask to the lower triangle, hand over like one more W'_h
+        w.wait(&bars.wsep_full, ksep & 1, 62);
+        ++ksep;
+        w.wait(&bars.m_empty, (kh & 1) ^ 1, 53);
+        tc_fence_after();
+        mask_tril_tile(tmWsep, row, part, warp, smem_u32(sM));
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&bars.m_full); mbar_arrive(&bars.wsep_empty); }
+        ++kh;
       }
     }
   } else if (warp >= 20) {
     // ------------------------------------------------------------------ epilogue warps: dC, dB of a finished tile
+    reg_dec<48>();
     const int ew = warp - 20;
     const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the 64 columns
     for (int t = 0; t < my_tiles; ++t) {
@@ -2546,21 +2700,23 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tile_coords(t, b, grp, c);
       w.wait(&bars.acc_full, t & 1, 56);
       tc_fence_after();
-      float vc[32], vb[32];
-      tmem_ld32(tmem_addr(tmDC, (ew & 3) * 32, half * 32), vc);
-      tmem_ld32(tmem_addr(tmDB, (ew & 3) * 32, half * 32), vb);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.acc_empty);
       const size_t o = (((size_t)b * g.L + c * QT + row) * g.G + grp) * N + half * 32;
 #pragma unroll
       for (int j = 0; j < 32; j += 16) {
+        float vc[16], vb[16];
+        tmem_ld16(tmem_addr(tmDC, (ew & 3) * 32, half * 32 + j), vc);
+        tmem_ld16(tmem_addr(tmDB, (ew & 3) * 32, half * 32 + j), vb);
+        if (j == 16) {   // both accumulators are in registers: hand them back before the stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.acc_empty);
+        }
         st_global_32B(dC + o + j,
-                      make_uint4(pack_bf16(vc[j], vc[j + 1]), pack_bf16(vc[j + 2], vc[j + 3]), pack_bf16(vc[j + 4], vc[j + 5]), pack_bf16(vc[j + 6], vc[j + 7])),
-                      make_uint4(pack_bf16(vc[j + 8], vc[j + 9]), pack_bf16(vc[j + 10], vc[j + 11]), pack_bf16(vc[j + 12], vc[j + 13]), pack_bf16(vc[j + 14], vc[j + 15])));
+                      make_uint4(pack_bf16(vc[0], vc[1]), pack_bf16(vc[2], vc[3]), pack_bf16(vc[4], vc[5]), pack_bf16(vc[6], vc[7])),
+                      make_uint4(pack_bf16(vc[8], vc[9]), pack_bf16(vc[10], vc[11]), pack_bf16(vc[12], vc[13]), pack_bf16(vc[14], vc[15])));
         st_global_32B(dB + o + j,
-                      make_uint4(pack_bf16(vb[j], vb[j + 1]), pack_bf16(vb[j + 2], vb[j + 3]), pack_bf16(vb[j + 4], vb[j + 5]), pack_bf16(vb[j + 6], vb[j + 7])),
-                      make_uint4(pack_bf16(vb[j + 8], vb[j + 9]), pack_bf16(vb[j + 10], vb[j + 11]), pack_bf16(vb[j + 12], vb[j + 13]), pack_bf16(vb[j + 14], vb[j + 15])));
+                      make_uint4(pack_bf16(vb[0], vb[1]), pack_bf16(vb[2], vb[3]), pack_bf16(vb[4], vb[5]), pack_bf16(vb[6], vb[7])),
+                      make_uint4(pack_bf16(vb[8], vb[9]), pack_bf16(vb[10], vb[11]), pack_bf16(vb[12], vb[13]), pack_bf16(vb[14], vb[15])));
       }
     }
   }
@@ -2801,20 +2957,20 @@ int launch_bwd_tc(const Geo& g, const SeqMaps& m, const float* tab, const float*
 }
 
 template <int P>
-int launch_dbc_ws(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
+int launch_dbc_ws(const Geo& g, const SeqMaps& m, const float* tab, const float* hmax, void* dB, void* dC, int* status, cudaStream_t s) {
   auto k = k_dbc_ws<P>;
   constexpr size_t sm = DbCfg<P>::SMEM;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int ntiles = g.B * g.G * g.nc;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  k<<<grid, WS_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, (bf16*)dB, (bf16*)dC, status);
+  k<<<grid, WS_THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, hmax, (bf16*)dB, (bf16*)dC, status);
   SSD_CUDA_CHECK_LAUNCH("dBdC_ws");
   return SSD_OK;
 }
 
 template <int P, int N>
-int launch_dbc(const Geo& g, const SeqMaps& m, const float* tab, void* dB, void* dC, int* status, cudaStream_t s) {
-  if (N == 64 && !g.onetile) return launch_dbc_ws<P>(g, m, tab, dB, dC, status, s);
+int launch_dbc(const Geo& g, const SeqMaps& m, const float* tab, const float* hmax, void* dB, void* dC, int* status, cudaStream_t s) {
+  if (N == 64 && !g.onetile) return launch_dbc_ws<P>(g, m, tab, hmax, dB, dC, status, s);
   auto k = k_dbc_tc<P, N>;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dbc_smem<P, N>());
   k<<<dim3(g.nc, g.G, g.B), TC_THREADS, dbc_smem<P, N>(), s>>>(g, m.x, m.dy, m.b, m.c, m.s, m.ds, tab, (bf16*)dB, (bf16*)dC,
@@ -2992,12 +3148,12 @@ int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const
   return launch_bwd_ws<64>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
 }
 
-int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const void* prev_bf,
-               const void* ds_bf, int* status, cudaStream_t s) {
+int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const float* hmax,
+               const void* prev_bf, const void* ds_bf, int* status, cudaStream_t s) {
   SeqMaps m;
   int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, prev_bf, ds_bf, &m);
   if (rc) return rc;
-#define CALL(PP, NN) return launch_dbc<PP, NN>(g, m, tab, p.dB, p.dC, status, s);
+#define CALL(PP, NN) return launch_dbc<PP, NN>(g, m, tab, hmax, p.dB, p.dC, status, s);
   DISPATCH_PN(CALL)
 #undef CALL
 }

@@ -252,6 +252,19 @@ __device__ __forceinline__ void st_global_32B(void* p, const uint4& a, const uin
     reinterpret_cast<uint4*>(p)[1] = b;
   }
 }
+// fp32 reads of shared memory through the shared-memory pipe.  A read through a plain `const float*` compiles to a generic
+// load when the compiler has lost track of the address space (pointers into the dynamic shared memory handed through
+// helper functions): generic loads take the long-latency path, and the decay passes are chains of dependent table reads.
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float4 lds_v4f32(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
