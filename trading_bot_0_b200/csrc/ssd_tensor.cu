@@ -167,11 +167,11 @@ __device__ __forceinline__ void tmem_ld_wait_2x16(uint32_t (&r)[16], uint32_t (&
                  "+r"(q[9]), "+r"(q[10]), "+r"(q[11]), "+r"(q[12]), "+r"(q[13]), "+r"(q[14]), "+r"(q[15])
                :: "memory");
 }
-// 16 columns of a block below the diagonal: out[k] = raw[k] * rf * cf[k]
-__device__ __forceinline__ void decay_off_half(const uint32_t (&raw)[16], float rf, const float* __restrict__ cf, uint32_t dst) {
+// 16 columns of a block below the diagonal: out[k] = raw[k] * rf * cf[k]; `cf` = shared-memory address of the column factors
+__device__ __forceinline__ void decay_off_half(const uint32_t (&raw)[16], float rf, uint32_t cf, uint32_t dst) {
 #pragma unroll
   for (int j8 = 0; j8 < 16; j8 += 8) {
-    const float4 f0 = *reinterpret_cast<const float4*>(cf + j8), f1 = *reinterpret_cast<const float4*>(cf + j8 + 4);
+    const float4 f0 = lds_v4f32(cf + 4 * j8), f1 = lds_v4f32(cf + 4 * (j8 + 4));
     const float v0 = __uint_as_float(raw[j8]) * f0.x * rf, v1 = __uint_as_float(raw[j8 + 1]) * f0.y * rf;
     const float v2 = __uint_as_float(raw[j8 + 2]) * f0.z * rf, v3 = __uint_as_float(raw[j8 + 3]) * f0.w * rf;
     const float v4 = __uint_as_float(raw[j8 + 4]) * f1.x * rf, v5 = __uint_as_float(raw[j8 + 5]) * f1.y * rf;
@@ -179,18 +179,18 @@ __device__ __forceinline__ void decay_off_half(const uint32_t (&raw)[16], float 
     st_shared_v4(dst + (j8 >> 3) * 2048, pack_bf16(v0, v1), pack_bf16(v2, v3), pack_bf16(v4, v5), pack_bf16(v6, v7));
   }
 }
-// 16 columns (starting at column c0) of the diagonal block: two independent 8-column walks
-__device__ __forceinline__ void decay_diag_half(const uint32_t (&raw)[16], const float* __restrict__ tab, int c0, int row,
-                                                float csi, uint32_t dst) {
+// 16 columns (starting at column c0) of the diagonal block: two independent 8-column walks; `ts` = shared-memory address
+// of the head's table
+__device__ __forceinline__ void decay_diag_half(const uint32_t (&raw)[16], uint32_t ts, int c0, int row, float csi, uint32_t dst) {
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
     const int cs0 = c0 + 8 * s, je = cs0 + 7;
-    const float4 d0 = *reinterpret_cast<const float4*>(tab + T_DS + cs0), d1 = *reinterpret_cast<const float4*>(tab + T_DS + cs0 + 4);
-    const float4 t0 = *reinterpret_cast<const float4*>(tab + T_DT + cs0), t1 = *reinterpret_cast<const float4*>(tab + T_DT + cs0 + 4);
+    const float4 d0 = lds_v4f32(ts + 4 * (T_DS + cs0)), d1 = lds_v4f32(ts + 4 * (T_DS + cs0 + 4));
+    const float4 t0 = lds_v4f32(ts + 4 * (T_DT + cs0)), t1 = lds_v4f32(ts + 4 * (T_DT + cs0 + 4));
     const float ds[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};   // ds[k] = decay of step cs0+k+1
     const float dt[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
     float v[8];
-    float run = (row >= je) ? ex2(csi - tab[T_CS + je]) : 0.f;
+    float run = (row >= je) ? ex2(csi - lds_f32(ts + 4 * (T_CS + je))) : 0.f;
     v[7] = __uint_as_float(raw[8 * s + 7]) * (run * dt[7]);
 #pragma unroll
     for (int k = 6; k >= 0; --k) {
@@ -204,28 +204,30 @@ __device__ __forceinline__ void decay_diag_half(const uint32_t (&raw)[16], const
 // source column); mrow: shared-memory address of this row's first 16 bytes in the plain 128x128 bf16 tile.
 // One compact loop body for every block row (the code has to stay resident in the instruction cache while
 // several groups run through it at different places); the two 16-column halves of the next block are
-// requested as soon as the registers of the current ones are free.
+// requested as soon as the registers of the current ones are free.  The table (in shared memory) is read through the
+// shared-memory pipe.
 template <int NCH>
 __device__ __forceinline__ void decay_row(int rb, int ch, uint32_t tm_row, const float* __restrict__ tab, int row, uint32_t mrow) {
-  const float csi = tab[T_CS + row];
+  const uint32_t ts = smem_u32(tab);
+  const float csi = lds_f32(ts + 4 * (T_CS + row));
   if (NCH == 1) {
     uint32_t a[16], b[16];
     tmem_ld16_issue(tm_row, a);
     tmem_ld16_issue(tm_row + 16, b);
 #pragma unroll 1
     for (int cb = 0; cb < rb; ++cb) {
-      const float rf = ex2(csi - tab[T_CS + cb * 32 + 31]);
-      const float* cf = tab + T_CF + cb * 32;
+      const float rf = ex2(csi - lds_f32(ts + 4 * (T_CS + cb * 32 + 31)));
+      const uint32_t cf = ts + 4 * (T_CF + cb * 32);
       const uint32_t dst = mrow + cb * 4 * 2048;
       tmem_ld_wait_2x16(a, b);
       decay_off_half(a, rf, cf, dst);
       tmem_ld16_issue(tm_row + (cb + 1) * 32, a);
-      decay_off_half(b, rf, cf + 16, dst + 2 * 2048);
+      decay_off_half(b, rf, cf + 64, dst + 2 * 2048);
       tmem_ld16_issue(tm_row + (cb + 1) * 32 + 16, b);
     }
     tmem_ld_wait_2x16(a, b);
-    decay_diag_half(a, tab, rb * 32, row, csi, mrow + rb * 4 * 2048);
-    decay_diag_half(b, tab, rb * 32 + 16, row, csi, mrow + rb * 4 * 2048 + 2 * 2048);
+    decay_diag_half(a, ts, rb * 32, row, csi, mrow + rb * 4 * 2048);
+    decay_diag_half(b, ts, rb * 32 + 16, row, csi, mrow + rb * 4 * 2048 + 2 * 2048);
   } else {
     // two threads per row: this one owns columns [16 ch, 16 ch + 16) of every block; two register sets so that
     // the load of the next block flies while the current one is worked on
@@ -238,18 +240,18 @@ __device__ __forceinline__ void decay_row(int rb, int ch, uint32_t tm_row, const
     for (; cb + 1 < rb; cb += 2) {
       tmem_ld16_issue(tmc + (cb + 1) * 32, b);
       tmem_ld_wait_2x16(a, b);
-      decay_off_half(a, ex2(csi - tab[T_CS + cb * 32 + 31]), tab + T_CF + cb * 32 + ch * 16, mr + cb * 4 * 2048);
+      decay_off_half(a, ex2(csi - lds_f32(ts + 4 * (T_CS + cb * 32 + 31))), ts + 4 * (T_CF + cb * 32 + ch * 16), mr + cb * 4 * 2048);
       tmem_ld16_issue(tmc + (cb + 2) * 32, a);
-      decay_off_half(b, ex2(csi - tab[T_CS + cb * 32 + 63]), tab + T_CF + cb * 32 + 32 + ch * 16, mr + (cb + 1) * 4 * 2048);
+      decay_off_half(b, ex2(csi - lds_f32(ts + 4 * (T_CS + cb * 32 + 63))), ts + 4 * (T_CF + cb * 32 + 32 + ch * 16), mr + (cb + 1) * 4 * 2048);
     }
     if (cb < rb) {   // one more block below the diagonal, then the diagonal block
       tmem_ld16_issue(tmc + (cb + 1) * 32, b);
       tmem_ld_wait_2x16(a, b);
-      decay_off_half(a, ex2(csi - tab[T_CS + cb * 32 + 31]), tab + T_CF + cb * 32 + ch * 16, mr + cb * 4 * 2048);
-      decay_diag_half(b, tab, rb * 32 + ch * 16, row, csi, mr + rb * 4 * 2048);
+      decay_off_half(a, ex2(csi - lds_f32(ts + 4 * (T_CS + cb * 32 + 31))), ts + 4 * (T_CF + cb * 32 + ch * 16), mr + cb * 4 * 2048);
+      decay_diag_half(b, ts, rb * 32 + ch * 16, row, csi, mr + rb * 4 * 2048);
     } else {
       tmem_ld_wait_2x16(a, b);
-      decay_diag_half(a, tab, rb * 32 + ch * 16, row, csi, mr + rb * 4 * 2048);
+      decay_diag_half(a, ts, rb * 32 + ch * 16, row, csi, mr + rb * 4 * 2048);
     }
   }
 }
@@ -261,21 +263,27 @@ __device__ __forceinline__ void decay_mask_block(uint32_t tm_src, const float* _
   const int rb = warp & 3, cb = part;   // both warp-uniform
   if (cb > rb) return;
   const int c0 = cb * 32;
+  const uint32_t ts = smem_u32(tab);    // the table sits in shared memory: read it through the shared-memory pipe
   float v[32];
   tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
   if (cb == rb) {
     float run = 0.f;
 #pragma unroll
-    for (int k = 31; k >= 0; --k) {
-      const int j = c0 + k;
-      run = (j == row) ? 1.f : run * tab[T_DS + j];   // T_DS[j] = decay of step j+1
-      v[k] = v[k] * run * tab[T_DT + j];
+    for (int k4 = 28; k4 >= 0; k4 -= 4) {
+      const float4 d = lds_v4f32(ts + 4 * (T_DS + c0 + k4)), t = lds_v4f32(ts + 4 * (T_DT + c0 + k4));   // T_DS[j] = decay of step j+1
+      const float ds[4] = {d.x, d.y, d.z, d.w}, dt[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int q = 3; q >= 0; --q) {
+        const int j = c0 + k4 + q;
+        run = (j == row) ? 1.f : run * ds[q];
+        v[k4 + q] = v[k4 + q] * run * dt[q];
+      }
     }
   } else {
-    const float rf = ex2(tab[T_CS + row] - tab[T_CS + c0 + 31]);
+    const float rf = ex2(lds_f32(ts + 4 * (T_CS + row)) - lds_f32(ts + 4 * (T_CS + c0 + 31)));
 #pragma unroll
     for (int k4 = 0; k4 < 32; k4 += 4) {
-      const float4 f = *reinterpret_cast<const float4*>(tab + T_CF + c0 + k4);
+      const float4 f = lds_v4f32(ts + 4 * (T_CF + c0 + k4));
       v[k4] *= rf * f.x; v[k4 + 1] *= rf * f.y; v[k4 + 2] *= rf * f.z; v[k4 + 3] *= rf * f.w;
     }
   }
@@ -292,21 +300,27 @@ __device__ __forceinline__ void decay_acc_block(uint32_t tm_src, const float* __
   const int rb = warp & 3, cb = part;   // both warp-uniform
   if (cb > rb) return;
   const int c0 = cb * 32;
+  const uint32_t ts = smem_u32(tab);
   float v[32];
   tmem_ld32(tmem_addr(tm_src, rb * 32, c0), v);
   if (cb == rb) {
     float run = 0.f;
 #pragma unroll
-    for (int k = 31; k >= 0; --k) {
-      const int j = c0 + k;
-      run = (j == row) ? 1.f : run * tab[T_DS + j];   // T_DS[j] = decay of step j+1
-      acc[k] = fmaf(v[k], run * tab[T_DT + j], acc[k]);
+    for (int k4 = 28; k4 >= 0; k4 -= 4) {
+      const float4 d = lds_v4f32(ts + 4 * (T_DS + c0 + k4)), t = lds_v4f32(ts + 4 * (T_DT + c0 + k4));
+      const float ds[4] = {d.x, d.y, d.z, d.w}, dt[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int q = 3; q >= 0; --q) {
+        const int j = c0 + k4 + q;
+        run = (j == row) ? 1.f : run * ds[q];
+        acc[k4 + q] = fmaf(v[k4 + q], run * dt[q], acc[k4 + q]);
+      }
     }
   } else {
-    const float rf = ex2(tab[T_CS + row] - tab[T_CS + c0 + 31]);
+    const float rf = ex2(lds_f32(ts + 4 * (T_CS + row)) - lds_f32(ts + 4 * (T_CS + c0 + 31)));
 #pragma unroll
     for (int k4 = 0; k4 < 32; k4 += 4) {
-      const float4 f = *reinterpret_cast<const float4*>(tab + T_CF + c0 + k4);
+      const float4 f = lds_v4f32(ts + 4 * (T_CF + c0 + k4));
       acc[k4] = fmaf(v[k4], rf * f.x, acc[k4]); acc[k4 + 1] = fmaf(v[k4 + 1], rf * f.y, acc[k4 + 1]);
       acc[k4 + 2] = fmaf(v[k4 + 2], rf * f.z, acc[k4 + 2]); acc[k4 + 3] = fmaf(v[k4 + 3], rf * f.w, acc[k4 + 3]);
     }
@@ -613,8 +627,9 @@ __global__ void __launch_bounds__(PsCfg<P, N_>::THREADS, 1) k_state_ps(Geo g, co
       const int lc = (pc ^ l) & 7;
 #pragma unroll
       for (int box = 0; box < 2; ++box) {
-        const float* t = tb + ((box * 64 + lc * 8) / P) * Cfg::TBH;
-        const float wv = (MODE == 0) ? ex2(t[T_CS + 127] - t[T_CS + l]) * t[T_DT + l] : ex2(t[T_CS + l]);
+        const uint32_t t = smem_u32(tb) + ((box * 64 + lc * 8) / P) * Cfg::TBH * 4;   // shared-pipe reads of the table
+        const float csl = lds_f32(t + 4 * (T_CS + l));
+        const float wv = (MODE == 0) ? ex2(lds_f32(t + 4 * (T_CS + 127)) - csl) * lds_f32(t + 4 * (T_DT + l)) : ex2(csl);
         const uint32_t off = box * BOX_BYTES + l * 128 + pc * 16;
         float f[8];
         unpack8(ld_shared_v4(xs + off), f);
@@ -850,8 +865,9 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
       const int lc = (pc ^ l) & 7;
 #pragma unroll
       for (int box = 0; box < 2; ++box) {
-        const float* t = tb + ((box * 64 + lc * 8) / P) * Cfg::TBH;
-        const float wv = (MODE == 0) ? ex2(t[T_CS + 127] - t[T_CS + l]) * t[T_DT + l] : ex2(t[T_CS + l]);
+        const uint32_t t = smem_u32(tb) + ((box * 64 + lc * 8) / P) * Cfg::TBH * 4;   // shared-pipe reads of the table
+        const float csl = lds_f32(t + 4 * (T_CS + l));
+        const float wv = (MODE == 0) ? ex2(lds_f32(t + 4 * (T_CS + 127)) - csl) * lds_f32(t + 4 * (T_DT + l)) : ex2(csl);
         const uint32_t off = box * BOX_BYTES + l * 128 + pc * 16;
         float f[8];
         unpack8(ld_shared_v4(xs + off), f);
@@ -944,7 +960,7 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
       const uint32_t xs = smem_u32(sX + slot * Cfg::X_BYTES);
       const float* tb = (const float*)(sTabs + slot * Cfg::TB_BYTES);
       w.wait(&x_full[slot], (k / NX) & 1, 11);
-      const float dec = ex2(tb[(row / P) * Cfg::TBH + T_CS + 127]);   // decay over the whole chunk, for this tile's epilogue
+      const float dec = ex2(lds_f32(smem_u32(tb) + 4 * ((row / P) * Cfg::TBH + T_CS + 127)));   // decay over the whole chunk, for this tile's epilogue
       if (k > 0) w.wait(&h0_done, (k - 1) & 1, 19);            // first half of the low-part buffer is free
       scale_half(0, xs, tb);
       if (k > 0) {                                             // tile k-1 is complete: second half free, accumulator ready
@@ -1910,8 +1926,9 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const int h0 = grp * g.hpg + blk * HB, h_e = h0 + hl_e;
         const float Dh = D ? __ldg(D + h_e) : 0.f;
         w.wait(&bars.tab_full[ts], (khe / NTH) & 1, 56);
-        const float cs_r = tb[T_CS + row], dt_r = tb[T_DT + row];
-        const float osc = (MODE == 2) ? dt_r * ex2(tb[T_CS + 127] - cs_r) : ex2(cs_r);
+        const uint32_t tbs = smem_u32(tb);
+        const float cs_r = lds_f32(tbs + 4 * (T_CS + row)), dt_r = lds_f32(tbs + 4 * (T_DT + row));
+        const float osc = (MODE == 2) ? dt_r * ex2(lds_f32(tbs + 4 * (T_CS + 127)) - cs_r) : ex2(cs_r);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
         w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
@@ -2249,8 +2266,9 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
         const int h0 = grp * g.hpg + blk * HB, h_e = h0 + hl_e;
         const float Dh = D ? __ldg(D + h_e) : 0.f;
         w.wait(&bars.tab_full[ts], (kb / Cfg::NT) & 1, 56);
-        const float cs_r = tb[T_CS + row], dt_r = tb[T_DT + row];
-        const float osc_y = ex2(cs_r), osc_u = dt_r * ex2(tb[T_CS + 127] - cs_r);
+        const uint32_t tbs = smem_u32(tb);
+        const float cs_r = lds_f32(tbs + 4 * (T_CS + row)), dt_r = lds_f32(tbs + 4 * (T_DT + row));
+        const float osc_y = ex2(cs_r), osc_u = dt_r * ex2(lds_f32(tbs + 4 * (T_CS + 127)) - cs_r);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tab_empty[ts]);
         w.wait(&bars.in_full[ib], (kb >> 1) & 1, 54);
