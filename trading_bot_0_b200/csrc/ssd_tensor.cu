@@ -998,7 +998,7 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
 // at CTA-wide barriers, and a second resident CTA fills the gaps (dstate 128 forward: 0.95 -> 0.75 ms on the long-sequence
 // shapes).
 template <int P, int N, int IBUF, int MODE>
-__global__ void __launch_bounds__(TC_THREADS, (N <= 64 || MODE == 0) ? 2 : 1)
+__global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1)
 k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
           const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
@@ -1949,8 +1949,14 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             xv[q] = ld_shared_v4(smem_u32(xt) + sw128_off(row, half * 4 + h16 * 2 + q));
             dv[q] = (MODE != 0) ? ld_shared_v4(smem_u32(dyt) + sw128_off(row, half * 4 + h16 * 2 + q)) : make_uint4(0u, 0u, 0u, 0u);
           }
-          tmem_ld16(tmem_addr(tmYd, (ew & 3) * 32, half * 32 + h16 * 16), yd);
-          tmem_ld16(tmem_addr(tmYo, (ew & 3) * 32, half * 32 + h16 * 16), yo);
+          {   // both accumulator slices in flight, one wait (the two loads used to wait for one another)
+            uint32_t rd[16], ro[16];
+            tmem_ld16_issue(tmem_addr(tmYd, (ew & 3) * 32, half * 32 + h16 * 16), rd);
+            tmem_ld16_issue(tmem_addr(tmYo, (ew & 3) * 32, half * 32 + h16 * 16), ro);
+            tmem_ld_wait_2x16(rd, ro);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) { yd[k] = __uint_as_float(rd[k]); yo[k] = __uint_as_float(ro[k]); }
+          }
           if (h16 == 1) {
             tc_fence_before();
             __syncwarp();
@@ -2287,8 +2293,14 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             xv[q] = ld_shared_v4(xt + sw128_off(row, half * 4 + h16 * 2 + q));
             dv[q] = ld_shared_v4(dyt + sw128_off(row, half * 4 + h16 * 2 + q));
           }
-          tmem_ld16(tmem_addr(upass ? tmUd : tmYd, (ew & 3) * 32, half * 32 + h16 * 16), a16);
-          tmem_ld16(tmem_addr(upass ? tmUo : tmYo, (ew & 3) * 32, half * 32 + h16 * 16), o16);
+          {   // both accumulator slices in flight, one wait
+            uint32_t ra[16], ro[16];
+            tmem_ld16_issue(tmem_addr(upass ? tmUd : tmYd, (ew & 3) * 32, half * 32 + h16 * 16), ra);
+            tmem_ld16_issue(tmem_addr(upass ? tmUo : tmYo, (ew & 3) * 32, half * 32 + h16 * 16), ro);
+            tmem_ld_wait_2x16(ra, ro);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) { a16[k] = __uint_as_float(ra[k]); o16[k] = __uint_as_float(ro[k]); }
+          }
           if (ph == 3) {   // everything read: hand the accumulators and the input slot back
             tc_fence_before();
             __syncwarp();
