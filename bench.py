@@ -326,6 +326,7 @@ def kernel_profile(fn, reps, device):
     from trading_bot_0_b200 import _lib
     agg = {}
     for _ in range(reps):
+        fn()   # keeps the device busy while the profiled pass is enqueued: the first bracket then holds no host time
         with _lib.profile(torch.cuda.current_stream(device).cuda_stream) as p:
             fn()
         for name, ms in p.entries:

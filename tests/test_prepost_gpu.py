@@ -19,7 +19,7 @@ def _autograd_ref(fn, leaves, dout):
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 @pytest.mark.parametrize("K,activation,use_bias", [(4, True, True), (3, False, False), (2, True, True)])
-@pytest.mark.parametrize("Bn,L,Cn", [(3, 200, 384), (2, 64, 24), (1, 7, 8)])
+@pytest.mark.parametrize("Bn,L,Cn", [(3, 200, 384), (2, 130, 200), (2, 64, 24), (1, 7, 8)])
 def test_conv1d_forward_backward(lib, dtype, K, activation, use_bias, Bn, L, Cn):
     from trading_bot_0_b200 import prepost as PP
     g = torch.Generator().manual_seed(7)

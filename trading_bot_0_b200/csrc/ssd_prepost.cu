@@ -54,6 +54,9 @@ __device__ __forceinline__ void load_raw(const float* p, RawN<float, 8>& r) {
   r.a = __ldg(reinterpret_cast<const float4*>(p)); r.b = __ldg(reinterpret_cast<const float4*>(p) + 1);
 }
 __device__ __forceinline__ void load_raw(const float* p, RawN<float, 4>& r) { r.a = __ldg(reinterpret_cast<const float4*>(p)); }
+template <> struct RawN<float, 2> { float2 a; };
+__device__ __forceinline__ void unpack_raw(const RawN<float, 2>& r, float (&v)[2]) { v[0] = r.a.x; v[1] = r.a.y; }
+__device__ __forceinline__ void store_n(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
 __device__ __forceinline__ float2 bf2_(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w)); }
 __device__ __forceinline__ void unpack_raw(const RawN<__nv_bfloat16, 8>& r, float (&v)[8]) {
   const float2 a = bf2_(r.v.x), b = bf2_(r.v.y), c = bf2_(r.v.z), d = bf2_(r.v.w);
@@ -157,6 +160,127 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const 
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// conv forward, shared-memory staged (the default where the channel count fills 16-byte vectors of a 256-byte
+// channel block).  A persistent CTA walks tiles of 64 tokens x 256 bytes of channels; every thread requests
+// 16-byte pieces of the tiles two and three ahead with cp.async (rows before the sequence start and channels past the
+// end are zero-filled by the copy itself), so the bytes in flight per SM are set by the ring, not by registers.
+// Thread = (16-byte channel vector, 4 consecutive tokens): K-1+4 row reads from shared memory, 4 row stores.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;   // src-size 0: the 16 bytes are written as zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int CONVS_THREADS = 256;
+constexpr int CONVS_TT = 64;        // tokens per tile
+constexpr int CONVS_ROWB = 256;     // bytes of channels per tile row
+constexpr int CONVS_STAGES = 4;
+constexpr int CONVS_CTAS_PER_SM = 3;
+
+template <typename T, int NC> __device__ __forceinline__ void lds_raw(const void* p, RawN<T, NC>& r) {
+  r = *reinterpret_cast<const RawN<T, NC>*>(p);
+}
+
+// Walk of a CTA over (batch, token tile) pairs with a fixed stride, in 32-bit arithmetic without divisions in the loop.
+struct PairWalk {
+  int b, tt, db, dtt, ntt;
+  __device__ __forceinline__ PairWalk(int first, int stride, int ntt_) : ntt(ntt_) {
+    b = first / ntt_; tt = first - b * ntt_;
+    db = stride / ntt_; dtt = stride - db * ntt_;
+  }
+  __device__ __forceinline__ void next() {
+    b += db; tt += dtt;
+    if (tt >= ntt) { tt -= ntt; ++b; }
+  }
+};
+
+template <typename T, int K>
+__global__ void __launch_bounds__(CONVS_THREADS, CONVS_CTAS_PER_SM)
+k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__ weight, const float* __restrict__ bias,
+              T* __restrict__ out, int ntt) {
+  constexpr int NC = 16 / (int)sizeof(T);            // channels per 16-byte vector
+  constexpr int CB = CONVS_ROWB / (int)sizeof(T);    // channels per tile
+  constexpr int ROWS = CONVS_TT + K - 1;
+  constexpr int STAGE_BYTES = ROWS * CONVS_ROWB;
+  extern __shared__ __align__(128) unsigned char conv_smem[];
+  const int tid = threadIdx.x, cv = tid & 15, seg = tid >> 4;
+  // grid = (pair walkers, channel blocks): the CTAs of one x walk the same token rows side by side, one channel block
+  // each, so whole rows (whole DRAM pages) are read and written at about the same time
+  const int c0 = blockIdx.y * CB + cv * NC;
+  const bool cok = c0 < d.channels;
+  const T* ibase = in + (cok ? c0 : 0);
+  const int npairs = d.batch * ntt;
+
+  auto request = [&](const PairWalk& pw, int stage) {
+    if (pw.b < d.batch) {
+      const int t0 = pw.tt * CONVS_TT;
+      const T* src = ibase + (long long)pw.b * d.in_stride_b + (long long)(t0 - (K - 1) + seg) * d.in_stride_l;
+      unsigned char* sp = conv_smem + stage * STAGE_BYTES + cv * 16 + seg * CONVS_ROWB;
+      int t = t0 - (K - 1) + seg;
+#pragma unroll
+      for (int j = 0; j < (ROWS + 15) / 16; ++j) {
+        if (seg + 16 * j < ROWS) {
+          const bool ok = cok && t >= 0 && t < d.seqlen;
+          cp_async16(sp, ok ? (const void*)src : (const void*)in, ok);
+        }
+        sp += 16 * CONVS_ROWB; src += 16 * d.in_stride_l; t += 16;
+      }
+    }
+    cp_async_commit();   // a group per tile slot even when it is empty: the wait below counts groups
+  };
+
+  PairWalk ahead((int)blockIdx.x, (int)gridDim.x, ntt), cur = ahead;
+#pragma unroll
+  for (int i = 0; i < CONVS_STAGES - 1; ++i) { request(ahead, i); ahead.next(); }
+  float w[NC][K], bs[NC];
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) w[j][k] = cok ? __ldg(weight + (size_t)(c0 + j) * K + k) : 0.f;
+    bs[j] = (cok && bias) ? __ldg(bias + c0 + j) : 0.f;
+  }
+  int stage = 0;
+  for (int pair = blockIdx.x; pair < npairs; pair += gridDim.x) {
+    cp_async_wait<CONVS_STAGES - 2>();
+    __syncthreads();           // this tile has landed for every thread; every thread is done with the previous one
+    request(ahead, stage == 0 ? CONVS_STAGES - 1 : stage - 1);
+    ahead.next();
+    const int t0 = cur.tt * CONVS_TT + seg * 4;
+    const unsigned char* sp = conv_smem + stage * STAGE_BYTES + cv * 16 + seg * 4 * CONVS_ROWB;
+    T* op = out + (long long)cur.b * d.out_stride_b + (long long)t0 * d.out_stride_l + c0;
+    cur.next();
+    stage = stage + 1 == CONVS_STAGES ? 0 : stage + 1;
+    if (!cok) continue;
+    float win[K][NC];
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) { RawN<T, NC> r0; lds_raw<T, NC>(sp + k * CONVS_ROWB, r0); unpack_raw(r0, win[k]); }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      RawN<T, NC> r0;
+      lds_raw<T, NC>(sp + (K - 1 + i) * CONVS_ROWB, r0);
+      unpack_raw(r0, win[K - 1]);
+      float o[NC];
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        float a = bs[j];
+#pragma unroll
+        for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+        o[j] = d.activation ? a * sig_<T>(a) : a;
+      }
+      if (t0 + i < d.seqlen) store_n(op, o);
+      op += d.out_stride_l;
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+        for (int j = 0; j < NC; ++j) win[k][j] = win[k + 1][j];
+    }
+  }
+  cp_async_wait<0>();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -291,6 +415,211 @@ __global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdCon
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// conv backward, shared-memory staged.  Grid = (tile walkers, channel blocks of 256 bytes); a CTA walks (batch, 64-token
+// tile) pairs of its channel block with the next tile's input rows and gradient rows arriving by cp.async while the
+// current tile is worked on in two phases:
+//   1. thread = (8 bytes of channels, 9 consecutive rows): recompute the pre-activation from a sliding input window,
+//      dpre = dout * act'(pre) into a shared fp32 tile, and the weight / bias gradient of the rows this tile owns;
+//   2. thread = (8 bytes of channels, 8 consecutive tokens): din from a sliding window over the dpre tile.
+// The tile carries K-1 halo rows on either side (zero-filled outside the sequence), so no row is recomputed in
+// registers and nothing is re-read from global memory but the halo.  A CTA leaves one partial weight-gradient row.
+__device__ __forceinline__ void ldf_vec(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void ldf_vec(const float* p, float (&v)[2]) {
+  const float2 a = *reinterpret_cast<const float2*>(p);
+  v[0] = a.x; v[1] = a.y;
+}
+constexpr int CONVB_STAGES = 2;
+constexpr int CONVB_CTAS_PER_SM = 2;
+
+template <typename T, int K>
+__global__ void __launch_bounds__(CONVS_THREADS, CONVB_CTAS_PER_SM)
+k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__ weight, const float* __restrict__ bias,
+              ConvSegs segs, T* __restrict__ din, long long din_stride_b, long long din_stride_l,
+              float* __restrict__ partial, int ntt) {
+  constexpr int NC = 16 / (int)sizeof(T);            // channels per 16-byte copy piece
+  constexpr int NP = 8 / (int)sizeof(T);             // channels per thread in the arithmetic phases
+  constexpr int CB = CONVS_ROWB / (int)sizeof(T);    // channels per tile
+  constexpr int IN_ROWS = CONVS_TT + 2 * (K - 1), GO_ROWS = CONVS_TT + K - 1;
+  constexpr int STAGE_BYTES = (IN_ROWS + GO_ROWS) * CONVS_ROWB;
+  constexpr int DPRE_ROWB = CB * 4;
+  constexpr int R1 = (GO_ROWS + 7) / 8;              // rows per thread in phase 1
+  extern __shared__ __align__(128) unsigned char conv_smem[];
+  unsigned char* dpre = conv_smem + CONVB_STAGES * STAGE_BYTES;
+  const int tid = threadIdx.x, cv = tid & 15, seg = tid >> 4, hv = tid & 31, rs = tid >> 5;
+  const int cb = blockIdx.y;
+
+  // copy role: the 16-byte piece `cv` of rows seg, seg+16, ...
+  const int cc = cb * CB + cv * NC;
+  const bool cok = cc < d.channels;
+  int si = 0;
+  for (int i = 1; i < segs.n; ++i) if (cc >= segs.c_begin[i]) si = i;
+  const T* gseg = (const T*)segs.ptr[si] + (cok ? cc - segs.c_begin[si] : 0);
+  const long long gsb = segs.stride_b[si], gsl = segs.stride_l[si];
+  const int npairs = d.batch * ntt;
+  const T* ibase = in + (cok ? cc : 0);
+  auto request = [&](const PairWalk& pw, int stage) {
+    if (pw.b < d.batch) {
+      const int t0 = pw.tt * CONVS_TT;
+      unsigned char* sp = conv_smem + stage * STAGE_BYTES + cv * 16 + seg * CONVS_ROWB;
+      {
+        const T* src = ibase + (long long)pw.b * d.in_stride_b + (long long)(t0 - (K - 1) + seg) * d.in_stride_l;
+        int t = t0 - (K - 1) + seg;
+#pragma unroll
+        for (int j = 0; j < (IN_ROWS + 15) / 16; ++j) {
+          if (seg + 16 * j < IN_ROWS) {
+            const bool ok = cok && t >= 0 && t < d.seqlen;
+            cp_async16(sp + j * 16 * CONVS_ROWB, ok ? (const void*)src : (const void*)in, ok);
+          }
+          src += 16 * d.in_stride_l; t += 16;
+        }
+      }
+      sp += IN_ROWS * CONVS_ROWB;
+      {
+        const T* src = gseg + (long long)pw.b * gsb + (long long)(t0 + seg) * gsl;
+        int t = t0 + seg;
+#pragma unroll
+        for (int j = 0; j < (GO_ROWS + 15) / 16; ++j) {
+          if (seg + 16 * j < GO_ROWS) {
+            const bool ok = cok && t < d.seqlen;
+            cp_async16(sp + j * 16 * CONVS_ROWB, ok ? (const void*)src : (const void*)in, ok);
+          }
+          src += 16 * gsl; t += 16;
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  // arithmetic role: NP channels starting at c0
+  const int c0 = cb * CB + hv * NP;
+  const bool live = c0 < d.channels;
+  float w[NP][K], bs[NP], dw[NP][K], db[NP];
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) { w[j][k] = live ? __ldg(weight + (size_t)(c0 + j) * K + k) : 0.f; dw[j][k] = 0.f; }
+    bs[j] = (live && bias) ? __ldg(bias + c0 + j) : 0.f;
+    db[j] = 0.f;
+  }
+
+  PairWalk ahead((int)blockIdx.x, (int)gridDim.x, ntt), cur = ahead;
+  request(ahead, 0);
+  ahead.next();
+  int stage = 0;
+  for (int pair = blockIdx.x; pair < npairs; pair += gridDim.x) {
+    cp_async_wait<0>();
+    __syncthreads();     // the tile has landed; phase 2 of the previous tile is over (dpre and the other stage are free)
+    request(ahead, stage ^ 1);
+    ahead.next();
+    const int b = cur.b, t0 = cur.tt * CONVS_TT;
+    cur.next();
+    const unsigned char* sin = conv_smem + stage * STAGE_BYTES + hv * 8;
+    const unsigned char* sgo = sin + IN_ROWS * CONVS_ROWB;
+    stage ^= 1;
+    // ---- phase 1: rows r0 .. r0+R1-1 of the gradient tile (row r <-> token t0 + r; input rows r .. r+K-1) ----
+    {
+      const int r0 = rs * R1;
+      float win[K][NP];
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k) {
+        RawN<T, NP> raw;
+        if (r0 + k < IN_ROWS) lds_raw<T, NP>(sin + (r0 + k) * CONVS_ROWB, raw); else zero_raw(raw);
+        unpack_raw(raw, win[k]);
+      }
+#pragma unroll
+      for (int i = 0; i < R1; ++i) {
+        const int r = r0 + i;
+        if (r < GO_ROWS) {
+          RawN<T, NP> raw, rg;
+          lds_raw<T, NP>(sin + (r + K - 1) * CONVS_ROWB, raw);
+          unpack_raw(raw, win[K - 1]);
+          lds_raw<T, NP>(sgo + r * CONVS_ROWB, rg);
+          float go[NP], dp[NP];
+          unpack_raw(rg, go);
+          const bool own = r < CONVS_TT;    // each row's weight / bias gradient is counted by exactly one tile
+#pragma unroll
+          for (int j = 0; j < NP; ++j) {
+            float a = bs[j];
+#pragma unroll
+            for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
+            float g = go[j];
+            if (d.activation) {
+              const float sg = sig_<T>(a);
+              g *= sg * (1.f + a * (1.f - sg));
+            }
+            dp[j] = g;
+            if (own) {
+              db[j] += g;
+#pragma unroll
+              for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
+            }
+          }
+          store_n(reinterpret_cast<float*>(dpre + r * DPRE_ROWB) + hv * NP, dp);
+#pragma unroll
+          for (int k = 0; k < K - 1; ++k)
+#pragma unroll
+            for (int j = 0; j < NP; ++j) win[k][j] = win[k + 1][j];
+        }
+      }
+    }
+    __syncthreads();
+    // ---- phase 2: din[t0 + i] = sum_q w[K-1-q] * dpre[i + q], tokens i0 .. i0+7 ----
+    if (live) {
+      const int i0 = rs * (CONVS_TT / 8);
+      const float* dpp = reinterpret_cast<const float*>(dpre) + hv * NP;
+      T* dp = din + (long long)b * din_stride_b + (long long)(t0 + i0) * din_stride_l + c0;
+      float dwin[K][NP];
+#pragma unroll
+      for (int q = 0; q < K - 1; ++q)
+        ldf_vec(dpp + (size_t)(i0 + q) * (DPRE_ROWB / 4), dwin[q]);
+#pragma unroll
+      for (int i = 0; i < CONVS_TT / 8; ++i) {
+        ldf_vec(dpp + (size_t)(i0 + i + K - 1) * (DPRE_ROWB / 4), dwin[K - 1]);
+        float o[NP];
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+          float a = 0.f;
+#pragma unroll
+          for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dwin[q][j], a);
+          o[j] = a;
+        }
+        if (t0 + i0 + i < d.seqlen) store_n(dp, o);
+        dp += din_stride_l;
+#pragma unroll
+        for (int q = 0; q < K - 1; ++q)
+#pragma unroll
+          for (int j = 0; j < NP; ++j) dwin[q][j] = dwin[q + 1][j];
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // the eight row groups add their weight / bias gradients in order, through the (now idle) stage memory
+  float* red = reinterpret_cast<float*>(conv_smem);
+  constexpr int PER = NP * (K + 1);
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) red[(rs * 32 + hv) * PER + j * (K + 1) + k] = dw[j][k];
+    red[(rs * 32 + hv) * PER + j * (K + 1) + K] = db[j];
+  }
+  __syncthreads();
+  for (int e = tid; e < 32 * PER; e += CONVS_THREADS) {
+    const int v = e / PER, rem = e - v * PER;
+    const int c = cb * CB + v * NP + rem / (K + 1);
+    if (c < d.channels) {
+      float a = 0.f;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) a += red[(g * 32 + v) * PER + rem];
+      partial[((size_t)blockIdx.x * d.channels + c) * (K + 1) + rem % (K + 1)] = a;
+    }
+  }
+}
+
 // dweight[c,k] / dbias[c] = sum over blocks of the partials, in block order
 __global__ void k_conv_reduce(int nblk, int channels, int K, const float* __restrict__ partial, float* __restrict__ dweight,
                               float* __restrict__ dbias) {
@@ -346,13 +675,15 @@ __global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_fwd(SsdNormDims d, con
 }
 
 // backward: n = in * rstd, dn = dout * weight, din = rstd * (dn - n * mean(dn * n)), dweight += dout * n.
-// Warps walk rows with a grid stride; a block leaves one dweight partial row.
+// Warps walk rows with a grid stride, RU rows requested together (narrow rows would otherwise leave one 1 KB request
+// per warp in flight); a block leaves one dweight partial row.
 template <typename T, int NV>
 __global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_bwd(SsdNormDims d, const T* __restrict__ in,
                                                               const float* __restrict__ weight, const float* __restrict__ rstd,
                                                               const T* __restrict__ dout, long long dout_stride_row,
                                                               T* __restrict__ din, long long din_stride_row,
                                                               float* __restrict__ partial) {
+  constexpr int RU = NV == 1 ? 4 : (NV == 2 ? 2 : 1);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nv = d.width / 8;
   float wv[NV][8], dwv[NV][8];
@@ -364,17 +695,38 @@ __global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_bwd(SsdNormDims d, con
     if (weight && vi < nv) load8<float>(weight + vi * 8, wv[i]);
   }
   const long long wstride = (long long)gridDim.x * (NORM_THREADS / 32);
-  for (long long row = (long long)blockIdx.x * (NORM_THREADS / 32) + warp; row < d.rows; row += wstride) {
-    const float r = rstd[row];
-    float n[NV][8], dn[NV][8];
-    float dot = 0.f;
+  for (long long row0 = (long long)blockIdx.x * (NORM_THREADS / 32) + warp; row0 < d.rows; row0 += wstride * RU) {
+    RawN<T, 8> rx[RU][NV], rg[RU][NV];
+    float rs_[RU];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = lane + 32 * i;
-      if (vi < nv) {
+    for (int u = 0; u < RU; ++u) {
+      const long long row = row0 + u * wstride;
+      const bool rok = row < d.rows;
+      rs_[u] = rok ? __ldg(rstd + row) : 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = lane + 32 * i;
+        if (rok && vi < nv) {
+          load_raw(in + row * d.in_stride_row + vi * 8, rx[u][i]);
+          load_raw(dout + row * dout_stride_row + vi * 8, rg[u][i]);
+        } else {
+          rx[u][i] = RawN<T, 8>{};
+          rg[u][i] = RawN<T, 8>{};
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const long long row = row0 + u * wstride;
+      if (row >= d.rows) break;      // warp-uniform
+      const float r = rs_[u];
+      float n[NV][8], dn[NV][8];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
         float x[8], g[8];
-        load8<T>(in + row * d.in_stride_row + vi * 8, x);
-        load8<T>(dout + row * dout_stride_row + vi * 8, g);
+        unpack_raw(rx[u][i], x);
+        unpack_raw(rg[u][i], g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           n[i][j] = x[j] * r;
@@ -383,18 +735,18 @@ __global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_bwd(SsdNormDims d, con
           dot = fmaf(dn[i][j], n[i][j], dot);
         }
       }
-    }
 #pragma unroll
-    for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float m = dot / (float)d.width;
+      for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float m = dot / (float)d.width;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = lane + 32 * i;
-      if (vi < nv) {
-        float o[8];
+      for (int i = 0; i < NV; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nv) {
+          float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = r * (dn[i][j] - n[i][j] * m);
-        store8<T>(din + row * din_stride_row + vi * 8, o);
+          for (int j = 0; j < 8; ++j) o[j] = r * (dn[i][j] - n[i][j] * m);
+          store8<T>(din + row * din_stride_row + vi * 8, o);
+        }
       }
     }
   }
@@ -420,12 +772,22 @@ __global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_bwd(SsdNormDims d, con
   }
 }
 
+// dweight[i] = sum over blocks of the partials: eight row groups per column add their rows in order, then the groups
+// are added in order (the same sum for the same grid, whatever the timing)
 __global__ void k_norm_reduce(int nblk, int width, const float* __restrict__ partial, float* __restrict__ dweight) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= width) return;
+  __shared__ float red[8][32];
+  const int i = blockIdx.x * 32 + threadIdx.x, g = threadIdx.y;
   float a = 0.f;
-  for (int r = 0; r < nblk; ++r) a += partial[(size_t)r * width + i];
-  dweight[i] = a;
+  if (i < width)
+    for (int r = g; r < nblk; r += 8) a += partial[(size_t)r * width + i];
+  red[g][threadIdx.x] = a;
+  __syncthreads();
+  if (g == 0 && i < width) {
+    float t = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += red[q][threadIdx.x];
+    dweight[i] = t;
+  }
 }
 
 int conv_rows(const SsdConvDims* d) {   // thread rows of the backward kernel = partial sums to add
@@ -474,6 +836,35 @@ int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float*
   if (!in || !weight || !out) { set_error("conv1d: in / weight / out is NULL"); return SSD_ERR_NULL_POINTER; }
   if (!aligned16(in) || !aligned16(out)) { set_error("conv1d: in and out must be 16-byte aligned"); return SSD_ERR_BAD_ALIGNMENT; }
   cudaStream_t s = (cudaStream_t)cuda_stream;
+  const int esz = dims->dtype == SSD_BF16 ? 2 : 4;
+  if ((long long)dims->channels * esz >= CONVS_ROWB / 2) {
+    // shared-memory staged kernel: tiles of 64 tokens x 256 bytes of channels, persistent CTAs
+    const int ntt = (dims->seqlen + CONVS_TT - 1) / CONVS_TT;
+    const int ncb = (dims->channels * esz + CONVS_ROWB - 1) / CONVS_ROWB;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long pairs = (long long)dims->batch * ntt;
+    if (pairs > 0x7fffffffLL) { set_error("conv1d: batch x token tiles exceeds 2^31"); return SSD_ERR_UNSUPPORTED; }
+    long long gx = ((long long)sms * CONVS_CTAS_PER_SM) / ncb;
+    if (gx < 1) gx = 1;
+    if (gx > pairs) gx = pairs;
+    if (ncb > 65535) { set_error("conv1d: too many channels"); return SSD_ERR_UNSUPPORTED; }
+    const dim3 grid((unsigned)gx, (unsigned)ncb);
+#define CONV_FWD_SM(T, K) do { \
+      constexpr int smem = (CONVS_TT + K - 1) * CONVS_ROWB * CONVS_STAGES; \
+      static bool attr_set = false; \
+      if (!attr_set) { cudaFuncSetAttribute(k_conv_fwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_set = true; } \
+      k_conv_fwd_sm<T, K><<<grid, CONVS_THREADS, smem, s>>>(*dims, (const T*)in, weight, bias, (T*)out, ntt); } while (0)
+    if (dims->dtype == SSD_BF16) {
+      if (dims->width == 4) CONV_FWD_SM(__nv_bfloat16, 4); else if (dims->width == 3) CONV_FWD_SM(__nv_bfloat16, 3); else CONV_FWD_SM(__nv_bfloat16, 2);
+    } else {
+      if (dims->width == 4) CONV_FWD_SM(float, 4); else if (dims->width == 3) CONV_FWD_SM(float, 3); else CONV_FWD_SM(float, 2);
+    }
+#undef CONV_FWD_SM
+    SSD_CUDA_CHECK_LAUNCH("conv1d_fwd");
+    return SSD_OK;
+  }
   constexpr int NCF = 8;   // channels per thread, forward
   const long long items = (long long)dims->batch * ((dims->seqlen + CONV_TL - 1) / CONV_TL) * (dims->channels / NCF);
   const unsigned grid = (unsigned)((items + CONV_THREADS - 1) / CONV_THREADS);
@@ -523,9 +914,38 @@ int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float
   const size_t need = (size_t)nblk * dims->channels * (dims->width + 1) * sizeof(float);
   if (workspace_bytes < need) { set_error("conv1d backward: workspace too small: %zu < %zu", workspace_bytes, need); return SSD_ERR_WORKSPACE_TOO_SMALL; }
   cudaStream_t s = (cudaStream_t)cuda_stream;
+  float* partial = (float*)workspace;
+  if ((long long)dims->channels * es >= CONVS_ROWB / 2) {
+    const int ntt = (dims->seqlen + CONVS_TT - 1) / CONVS_TT;
+    const int ncb = (dims->channels * es + CONVS_ROWB - 1) / CONVS_ROWB;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long long nx = ((long long)sms * CONVB_CTAS_PER_SM + ncb - 1) / ncb;
+    const long long pairs = (long long)dims->batch * ntt;
+    if (pairs > 0x7fffffffLL || ncb > 65535) { set_error("conv1d backward: batch x token tiles exceeds 2^31"); return SSD_ERR_UNSUPPORTED; }
+    if (nx > pairs) nx = pairs;
+    if (nx > nblk) nx = nblk;     // the workspace holds nblk partial rows
+    const dim3 grid((unsigned)nx, (unsigned)ncb);
+#define CONV_BWD_SM(T, K) do { \
+      constexpr int smem = CONVB_STAGES * (2 * CONVS_TT + 3 * (K - 1)) * CONVS_ROWB + (CONVS_TT + K - 1) * (CONVS_ROWB / (int)sizeof(T)) * 4; \
+      static bool attr_set = false; \
+      if (!attr_set) { cudaFuncSetAttribute(k_conv_bwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_set = true; } \
+      k_conv_bwd_sm<T, K><<<grid, CONVS_THREADS, smem, s>>>(*dims, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial, ntt); } while (0)
+    if (dims->dtype == SSD_BF16) {
+      if (dims->width == 4) CONV_BWD_SM(__nv_bfloat16, 4); else if (dims->width == 3) CONV_BWD_SM(__nv_bfloat16, 3); else CONV_BWD_SM(__nv_bfloat16, 2);
+    } else {
+      if (dims->width == 4) CONV_BWD_SM(float, 4); else if (dims->width == 3) CONV_BWD_SM(float, 3); else CONV_BWD_SM(float, 2);
+    }
+#undef CONV_BWD_SM
+    SSD_CUDA_CHECK_LAUNCH("conv1d_bwd");
+    const int n = dims->channels * (dims->width + 1);
+    k_conv_reduce<<<(n + 255) / 256, 256, 0, s>>>((int)nx, dims->channels, dims->width, partial, dweight, dbias);
+    SSD_CUDA_CHECK_LAUNCH("conv1d_reduce");
+    return SSD_OK;
+  }
   constexpr int NCB = 4;   // channels per thread, backward (half the registers of 8: twice the resident warps)
   const unsigned grid = (unsigned)(((long long)nblk * (dims->channels / NCB) + CONV_THREADS - 1) / CONV_THREADS);
-  float* partial = (float*)workspace;
 #define CONV_BWD(T, K) k_conv_bwd<T, K, NCB><<<grid, CONV_THREADS, 0, s>>>(*dims, nblk, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial)
   if (dims->dtype == SSD_BF16) {
     if (dims->width == 4) CONV_BWD(__nv_bfloat16, 4); else if (dims->width == 3) CONV_BWD(__nv_bfloat16, 3); else CONV_BWD(__nv_bfloat16, 2);
@@ -608,7 +1028,7 @@ int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, const floa
 #undef NORM_BWD
   SSD_CUDA_CHECK_LAUNCH("rmsnorm_bwd");
   if (dweight) {
-    k_norm_reduce<<<(dims->width + 255) / 256, 256, 0, s>>>(nblk, dims->width, partial, dweight);
+    k_norm_reduce<<<(dims->width + 31) / 32, dim3(32, 8), 0, s>>>(nblk, dims->width, partial, dweight);
     SSD_CUDA_CHECK_LAUNCH("rmsnorm_reduce");
   }
   return SSD_OK;
