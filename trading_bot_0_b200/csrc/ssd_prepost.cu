@@ -96,6 +96,38 @@ template <> __device__ __forceinline__ float sig_<__nv_bfloat16>(float a) {
 }
 template <> __device__ __forceinline__ float sig_<float>(float a) { return __fdividef(1.f, 1.f + __expf(-a)); }
 
+// Packed pairs of fp32 (one 64-bit register): sm_100 executes fma / add on both halves in one instruction, with the same
+// rounding as the scalar forms.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// NC storage elements -> NC/2 packed pairs
+__device__ __forceinline__ void unpack_pairs(const RawN<__nv_bfloat16, 8>& r, f32x2 (&v)[4]) {
+  const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+}
+__device__ __forceinline__ void unpack_pairs(const RawN<__nv_bfloat16, 4>& r, f32x2 (&v)[2]) {
+  v[0] = pack2(__uint_as_float(r.v.x << 16), __uint_as_float(r.v.x & 0xffff0000u));
+  v[1] = pack2(__uint_as_float(r.v.y << 16), __uint_as_float(r.v.y & 0xffff0000u));
+}
+__device__ __forceinline__ void unpack_pairs(const RawN<float, 4>& r, f32x2 (&v)[2]) { v[0] = pack2(r.a.x, r.a.y); v[1] = pack2(r.a.z, r.a.w); }
+__device__ __forceinline__ void unpack_pairs(const RawN<float, 2>& r, f32x2 (&v)[1]) { v[0] = pack2(r.a.x, r.a.y); }
+
 constexpr int CONV_THREADS = 128;
 constexpr int CONV_TL = 32;         // tokens per tile
 constexpr int CONV_ROWS = 2048;     // backward: thread rows (each walks several tiles and leaves one partial sum)
@@ -237,12 +269,13 @@ k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
   PairWalk ahead((int)blockIdx.x, (int)gridDim.x, ntt), cur = ahead;
 #pragma unroll
   for (int i = 0; i < CONVS_STAGES - 1; ++i) { request(ahead, i); ahead.next(); }
-  float w[NC][K], bs[NC];
+  f32x2 w[NC / 2][K], bs[NC / 2];     // channel pairs (2j, 2j+1)
 #pragma unroll
-  for (int j = 0; j < NC; ++j) {
+  for (int j = 0; j < NC / 2; ++j) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) w[j][k] = cok ? __ldg(weight + (size_t)(c0 + j) * K + k) : 0.f;
-    bs[j] = (cok && bias) ? __ldg(bias + c0 + j) : 0.f;
+    for (int k = 0; k < K; ++k)
+      w[j][k] = cok ? pack2(__ldg(weight + (size_t)(c0 + 2 * j) * K + k), __ldg(weight + (size_t)(c0 + 2 * j + 1) * K + k)) : 0ull;
+    bs[j] = (cok && bias) ? pack2(__ldg(bias + c0 + 2 * j), __ldg(bias + c0 + 2 * j + 1)) : 0ull;
   }
   int stage = 0;
   for (int pair = blockIdx.x; pair < npairs; pair += gridDim.x) {
@@ -256,28 +289,31 @@ k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     cur.next();
     stage = stage + 1 == CONVS_STAGES ? 0 : stage + 1;
     if (!cok) continue;
-    float win[K][NC];
+    f32x2 win[K][NC / 2];
 #pragma unroll
-    for (int k = 0; k < K - 1; ++k) { RawN<T, NC> r0; lds_raw<T, NC>(sp + k * CONVS_ROWB, r0); unpack_raw(r0, win[k]); }
+    for (int k = 0; k < K - 1; ++k) { RawN<T, NC> r0; lds_raw<T, NC>(sp + k * CONVS_ROWB, r0); unpack_pairs(r0, win[k]); }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       RawN<T, NC> r0;
       lds_raw<T, NC>(sp + (K - 1 + i) * CONVS_ROWB, r0);
-      unpack_raw(r0, win[K - 1]);
+      unpack_pairs(r0, win[K - 1]);
       float o[NC];
 #pragma unroll
-      for (int j = 0; j < NC; ++j) {
-        float a = bs[j];
+      for (int j = 0; j < NC / 2; ++j) {
+        f32x2 a2 = bs[j];
 #pragma unroll
-        for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
-        o[j] = d.activation ? a * sig_<T>(a) : a;
+        for (int k = 0; k < K; ++k) a2 = fma2(w[j][k], win[k][j], a2);
+        float a, b;
+        unpack2(a2, a, b);
+        o[2 * j] = d.activation ? a * sig_<T>(a) : a;
+        o[2 * j + 1] = d.activation ? b * sig_<T>(b) : b;
       }
       if (t0 + i < d.seqlen) store_n(op, o);
       op += d.out_stride_l;
 #pragma unroll
       for (int k = 0; k < K - 1; ++k)
 #pragma unroll
-        for (int j = 0; j < NC; ++j) win[k][j] = win[k + 1][j];
+        for (int j = 0; j < NC / 2; ++j) win[k][j] = win[k + 1][j];
     }
   }
   cp_async_wait<0>();
@@ -494,16 +530,20 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     cp_async_commit();
   };
 
-  // arithmetic role: NP channels starting at c0
+  // arithmetic role: NP channels starting at c0, held as NP/2 packed pairs
+  constexpr int NH = NP / 2;
   const int c0 = cb * CB + hv * NP;
   const bool live = c0 < d.channels;
-  float w[NP][K], bs[NP], dw[NP][K], db[NP];
+  f32x2 w[NH][K], bs[NH], dw[NH][K], db[NH];
 #pragma unroll
-  for (int j = 0; j < NP; ++j) {
+  for (int j = 0; j < NH; ++j) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) { w[j][k] = live ? __ldg(weight + (size_t)(c0 + j) * K + k) : 0.f; dw[j][k] = 0.f; }
-    bs[j] = (live && bias) ? __ldg(bias + c0 + j) : 0.f;
-    db[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+      w[j][k] = live ? pack2(__ldg(weight + (size_t)(c0 + 2 * j) * K + k), __ldg(weight + (size_t)(c0 + 2 * j + 1) * K + k)) : 0ull;
+      dw[j][k] = 0ull;
+    }
+    bs[j] = (live && bias) ? pack2(__ldg(bias + c0 + 2 * j), __ldg(bias + c0 + 2 * j + 1)) : 0ull;
+    db[j] = 0ull;
   }
 
   PairWalk ahead((int)blockIdx.x, (int)gridDim.x, ntt), cur = ahead;
@@ -523,12 +563,12 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     // ---- phase 1: rows r0 .. r0+R1-1 of the gradient tile (row r <-> token t0 + r; input rows r .. r+K-1) ----
     {
       const int r0 = rs * R1;
-      float win[K][NP];
+      f32x2 win[K][NH];
 #pragma unroll
       for (int k = 0; k < K - 1; ++k) {
         RawN<T, NP> raw;
         if (r0 + k < IN_ROWS) lds_raw<T, NP>(sin + (r0 + k) * CONVS_ROWB, raw); else zero_raw(raw);
-        unpack_raw(raw, win[k]);
+        unpack_pairs(raw, win[k]);
       }
 #pragma unroll
       for (int i = 0; i < R1; ++i) {
@@ -536,33 +576,38 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
         if (r < GO_ROWS) {
           RawN<T, NP> raw, rg;
           lds_raw<T, NP>(sin + (r + K - 1) * CONVS_ROWB, raw);
-          unpack_raw(raw, win[K - 1]);
+          unpack_pairs(raw, win[K - 1]);
           lds_raw<T, NP>(sgo + r * CONVS_ROWB, rg);
-          float go[NP], dp[NP];
-          unpack_raw(rg, go);
+          f32x2 go[NH], dp[NH];
+          unpack_pairs(rg, go);
           const bool own = r < CONVS_TT;    // each row's weight / bias gradient is counted by exactly one tile
 #pragma unroll
-          for (int j = 0; j < NP; ++j) {
-            float a = bs[j];
+          for (int j = 0; j < NH; ++j) {
+            f32x2 a2 = bs[j];
 #pragma unroll
-            for (int k = 0; k < K; ++k) a = fmaf(w[j][k], win[k][j], a);
-            float g = go[j];
+            for (int k = 0; k < K; ++k) a2 = fma2(w[j][k], win[k][j], a2);
+            f32x2 g = go[j];
             if (d.activation) {
-              const float sg = sig_<T>(a);
-              g *= sg * (1.f + a * (1.f - sg));
+              float a0, a1;
+              unpack2(a2, a0, a1);
+              const float s0 = sig_<T>(a0), s1 = sig_<T>(a1);
+              // silu'(a) = s (1 + a (1 - s))
+              g = fma2(g, pack2(fmaf(s0, fmaf(-a0, s0, a0), s0), fmaf(s1, fmaf(-a1, s1, a1), s1)), 0ull);
             }
             dp[j] = g;
             if (own) {
-              db[j] += g;
+              db[j] = add2(db[j], g);
 #pragma unroll
-              for (int k = 0; k < K; ++k) dw[j][k] = fmaf(g, win[k][j], dw[j][k]);
+              for (int k = 0; k < K; ++k) dw[j][k] = fma2(g, win[k][j], dw[j][k]);
             }
           }
-          store_n(reinterpret_cast<float*>(dpre + r * DPRE_ROWB) + hv * NP, dp);
+          f32x2* dst = reinterpret_cast<f32x2*>(dpre + r * DPRE_ROWB) + hv * NH;
+          if constexpr (NH == 2) *reinterpret_cast<ulonglong2*>(dst) = make_ulonglong2(dp[0], dp[1]);
+          else dst[0] = dp[0];
 #pragma unroll
           for (int k = 0; k < K - 1; ++k)
 #pragma unroll
-            for (int j = 0; j < NP; ++j) win[k][j] = win[k + 1][j];
+            for (int j = 0; j < NH; ++j) win[k][j] = win[k + 1][j];
         }
       }
     }
@@ -570,29 +615,33 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     // ---- phase 2: din[t0 + i] = sum_q w[K-1-q] * dpre[i + q], tokens i0 .. i0+7 ----
     if (live) {
       const int i0 = rs * (CONVS_TT / 8);
-      const float* dpp = reinterpret_cast<const float*>(dpre) + hv * NP;
+      const f32x2* dpp = reinterpret_cast<const f32x2*>(dpre) + hv * NH;
+      auto load_row = [&](int row, f32x2 (&v)[NH]) {
+        const f32x2* q = dpp + (size_t)row * (DPRE_ROWB / 8);
+        if constexpr (NH == 2) { const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(q); v[0] = t.x; v[1] = t.y; }
+        else v[0] = q[0];
+      };
       T* dp = din + (long long)b * din_stride_b + (long long)(t0 + i0) * din_stride_l + c0;
-      float dwin[K][NP];
+      f32x2 dwin[K][NH];
 #pragma unroll
-      for (int q = 0; q < K - 1; ++q)
-        ldf_vec(dpp + (size_t)(i0 + q) * (DPRE_ROWB / 4), dwin[q]);
+      for (int q = 0; q < K - 1; ++q) load_row(i0 + q, dwin[q]);
 #pragma unroll
       for (int i = 0; i < CONVS_TT / 8; ++i) {
-        ldf_vec(dpp + (size_t)(i0 + i + K - 1) * (DPRE_ROWB / 4), dwin[K - 1]);
+        load_row(i0 + i + K - 1, dwin[K - 1]);
         float o[NP];
 #pragma unroll
-        for (int j = 0; j < NP; ++j) {
-          float a = 0.f;
+        for (int j = 0; j < NH; ++j) {
+          f32x2 a2 = 0ull;
 #pragma unroll
-          for (int q = 0; q < K; ++q) a = fmaf(w[j][K - 1 - q], dwin[q][j], a);
-          o[j] = a;
+          for (int q = 0; q < K; ++q) a2 = fma2(w[j][K - 1 - q], dwin[q][j], a2);
+          unpack2(a2, o[2 * j], o[2 * j + 1]);
         }
         if (t0 + i0 + i < d.seqlen) store_n(dp, o);
         dp += din_stride_l;
 #pragma unroll
         for (int q = 0; q < K - 1; ++q)
 #pragma unroll
-          for (int j = 0; j < NP; ++j) dwin[q][j] = dwin[q + 1][j];
+          for (int j = 0; j < NH; ++j) dwin[q][j] = dwin[q + 1][j];
       }
     }
   }
@@ -602,10 +651,11 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
   float* red = reinterpret_cast<float*>(conv_smem);
   constexpr int PER = NP * (K + 1);
 #pragma unroll
-  for (int j = 0; j < NP; ++j) {
+  for (int j = 0; j < NH; ++j) {
+    float* rp = red + (rs * 32 + hv) * PER + 2 * j * (K + 1);
 #pragma unroll
-    for (int k = 0; k < K; ++k) red[(rs * 32 + hv) * PER + j * (K + 1) + k] = dw[j][k];
-    red[(rs * 32 + hv) * PER + j * (K + 1) + K] = db[j];
+    for (int k = 0; k < K; ++k) unpack2(dw[j][k], rp[k], rp[K + 1 + k]);
+    unpack2(db[j], rp[K], rp[2 * K + 1]);
   }
   __syncthreads();
   for (int e = tid; e < 32 * PER; e += CONVS_THREADS) {
