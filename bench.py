@@ -99,7 +99,7 @@ def kernel_bytes_per_token(name, c, e=2):
 
 
 TRAFFIC_SOURCE = ("derived, not measured in this run: dram__bytes_read.sum per token of an ncu capture at batch 128 "
-                  "(library as of commit 2988a11) scaled by the tokens of a launch, plus the kernel's output bytes")
+                  "(library as of commit 16fc4c5) scaled by the tokens of a launch, plus the kernel's output bytes")
 
 
 def kernel_traffic_bytes_per_token(name, c, e=2):
@@ -113,8 +113,8 @@ def kernel_traffic_bytes_per_token(name, c, e=2):
     hp, gn, H = c["H"] * c["P"], c["G"] * c["N"], c["H"]
     st32 = H * c["P"] * c["N"] * 4 / c["Q"]          # fp32 chunk states, bytes per token, one way
     measured_reads = {"chunk_state_tc": 768.0, "dstates_local_tc": 768.0, "chunk_scan_ws": 1152.6,
-                      "scan_bwd_dx_ws": 1920.2, "dBdC_ws": 1920.2,
-                      "chunk_state_scan": 704.3, "dstate_scan": 1216.3}
+                      "scan_bwd_dx_ws": 1920.6, "dBdC_ws": 1923.1,
+                      "chunk_state_scan": 704.6, "dstate_scan": 1216.3}
     writes = {"chunk_state_tc": st32, "dstates_local_tc": st32, "chunk_scan_ws": hp * e,
               "scan_bwd_dx_ws": hp * e + 3 * 4 * H, "dBdC_ws": 2 * gn * e,
               "chunk_state_scan": st32 + st32 / 2, "dstate_scan": st32 / 2 + 4 * 4 * H / c["Q"]}
@@ -857,12 +857,15 @@ def main():
     ap.add_argument("--inner", type=int, default=40, help="passes over the batch inside one timed step (cfg1/cfg3/cfg4)")
     ap.add_argument("--no-sub", action="store_true", help="cfg1: skip the cases / decode / sequence-parallel sub-records")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch / stream count (profiling a small case)")
+    ap.add_argument("--seqlen", type=int, default=0, help="override the sequence length (profiling a small case)")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for captures under a profiler: exactly --warmup warm-ups, no per-kernel event pass, no CPU/e2e legs")
     args = ap.parse_args()
     c = dict(CFGS["cfg1" if args.workload == "mixer_ops" else args.workload])
     if args.batch:
         c["B"] = args.batch
+    if args.seqlen:
+        c["L"] = args.seqlen
     if args.profile_mode:
         args.no_cpu = args.no_e2e = True
     if args.impl == "reference":

@@ -43,6 +43,23 @@ __global__ void __launch_bounds__(DEC_THREADS) k_state_update(SsdStepDims d, Ssd
   const int lir = lane % LPR, riw = lane / LPR;
   const int P = d.headdim;
 
+  // The state rows of the first pass are requested before anything else: the step's small vectors (dt, A, B, C, x) sit
+  // behind a dependent exp, and a warp that waited for them first would request its state a memory round trip later.
+  float* st = p.state + (size_t)sh * P * N;
+  float4 sv[UNROLL][V];
+  auto load_state = [&](int p0) {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int pr = p0 + riw + u * RPB;
+      if (pr < P) {
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+          sv[u][v] = *reinterpret_cast<const float4*>(st + (size_t)pr * N + 4 * (lir + v * LPR));
+      }
+    }
+  };
+  load_state(warp * RPW);
+
   const T* xs = (const T*)p.x + s * d.x_stride_s + (long long)h * P;
   const float dtv = dt_activation(ldf((const T*)p.dt + s * d.dt_stride_s + h), p.dt_bias ? __ldg(p.dt_bias + h) : 0.f, d.dt_softplus);
   const float a = expf(dtv * __ldg(p.A + h));
@@ -56,23 +73,17 @@ __global__ void __launch_bounds__(DEC_THREADS) k_state_update(SsdStepDims d, Ssd
     Bv[v] = Vec4Load<T>::ld(Bp + n);
     Cv[v] = Vec4Load<T>::ld(Cp + n);
   }
-  float* st = p.state + (size_t)sh * P * N;
   const T* zs = p.z ? (const T*)p.z + s * d.z_stride_s + (long long)h * P : nullptr;
   T* ys = (T*)p.y + s * d.y_stride_s + (long long)h * P;
 
   for (int p0 = warp * RPW; p0 < P; p0 += RPB * UNROLL) {  // warp-uniform trip count
     const int pbase = p0 + riw;
-    float4 sv[UNROLL][V];
+    if (p0 != warp * RPW) load_state(p0);
     float xv[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int pr = pbase + u * RPB;
-      if (pr < P) {
-#pragma unroll
-        for (int v = 0; v < V; ++v)
-          sv[u][v] = *reinterpret_cast<const float4*>(st + (size_t)pr * N + 4 * (lir + v * LPR));
-        xv[u] = ldf(xs + pr);
-      }
+      if (pr < P) xv[u] = ldf(xs + pr);
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {

@@ -138,7 +138,11 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
         // exp(dt_{l+1} A)], r = last position of the 32-block (lane 31 of this warp)
         const float vend = __shfl_sync(0xffffffffu, v[k], 31);
         // per head, the largest decay exponent any chunk of the call accumulates (non-negative floats order like ints)
-        if (hmax && h < g.H && q == g.Q - 1) atomicMax(reinterpret_cast<int*>(hmax) + h, __float_as_int(fabsf(v[k])));
+        // (the word only grows, so a plain read that already shows a larger value makes the atomic unnecessary)
+        if (hmax && h < g.H && q == g.Q - 1) {
+          const int bits = __float_as_int(fabsf(v[k]));
+          if (bits > *reinterpret_cast<volatile int*>(hmax + h)) atomicMax(reinterpret_cast<int*>(hmax) + h, bits);
+        }
         if (tab && h < g.H && q < g.Q) {
           const float L2E = 1.4426950408889634f;
           float* t = tab + ((size_t)(b * g.nc + c) * g.H + h) * SSD_TAB_FLOATS + q;
