@@ -91,7 +91,7 @@ def kernel_bytes_per_token(name, c, e=2):
         # chunk states fused with the scan over chunks: the operator's inputs on the way in; the states stay on chip
         "chunk_state_scan": (hp + gn) * e, "dstate_scan": (hp + gn) * e,
         "chunk_scan_tc": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_tc": (2 * hp + 2 * gn) * e + 2 * zb,
-        "dx_tc": (3 * hp + 2 * gn) * e, "dBdC_tc": (2 * hp + 4 * gn) * e,
+        "dx_tc": (3 * hp + 2 * gn) * e, "scan_bwd_dx_tc": (3 * hp + 2 * gn) * e, "dBdC_tc": (2 * hp + 4 * gn) * e,
         "chunk_scan_ws": (2 * hp + 2 * gn) * e + zb, "chunk_scan_bwd_ws": (2 * hp + 2 * gn) * e + 2 * zb,
         "dx_ws": (3 * hp + 2 * gn) * e, "scan_bwd_dx_ws": (3 * hp + 2 * gn) * e, "dBdC_ws": (2 * hp + 4 * gn) * e,
     }
@@ -680,8 +680,8 @@ def run_train(args, c, rank, world, local):
             "op_roofline": {"bound": "hbm", "achieved": op_ach, "peak": peak, "unit": "GB/s", "frac": op_ach / peak,
                             "peak_kind": peak_kind, "algorithmic_bytes_per_step": op_bytes},
             "kernels": {k: {"launches_per_pass": v[0], "avg_ms": round(v[1], 5)} for k, v in prof.items()},
-            "kernels_note": "CUDA events behind every launch of one pass; the first interval also holds the host's launch "
-                            "preparation of the call it belongs to",
+            "kernels_note": "CUDA events behind every launch of one pass, enqueued behind an unprofiled pass (no host time in "
+                            "any interval); a forward interval includes the memset in front of its kernel",
             "host_ms_per_pass": host_ms,
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
     line.update(subs)
