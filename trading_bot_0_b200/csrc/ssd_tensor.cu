@@ -1685,24 +1685,41 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // parity n&1 and `empty` with parity (n&1)^1 (a fresh barrier passes a wait on parity 1).
 // TMEM: G x2 (256 columns) + {Y, Y_off} x2 (256 columns) = 512.  Same math and operand layouts as
 // k_scan_tc; MODE as there.
+// sigmoid through one tanh.approx (relative error 2^-11, below the bf16 resolution of the gated output): the exact
+// form costs an exp, an IEEE division and its slow path per element, which made the gated epilogue 2.4x the ungated one
+__device__ __forceinline__ float sigmoid_fast(float a) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * a));
+  return fmaf(0.5f, t, 0.5f);
+}
 constexpr int WS_THREADS = 28 * 32;
 constexpr int WS_SCALE_WARPS = 16, WS_EPI_WARPS = 8;
 
-template <int P, int MODE>
+template <int P, int MODE, int N_ = 64>
 struct WsCfg {
-  static constexpr int N = 64, HB = 64 / P;
+  static constexpr int N = N_, HB = 64 / P, NB64 = N_ / 64;
+  // dstate 128: the C and B tiles are 32 KB each, so there is ONE C/B slot (and one G), and the state boxes of a head
+  // block live in a buffer of their own whose MMA is issued first in the block (it does not depend on M_h)
+  static constexpr bool SPLIT = N_ == 128;
+  static constexpr int NCBS = SPLIT ? 1 : 2;                          // C/B slots = G buffers
   static constexpr int NBOX = (MODE == 0) ? 1 : 2;
   static constexpr int NM = (MODE == 0) ? 3 : 2;                    // M_h ring depth = decay groups
-  static constexpr int CB_BYTES = 2 * BOX_BYTES;                     // keep + other tile
-  static constexpr int IN_BYTES = NBOX * BOX_BYTES + SBOX_BYTES;      // x [, dy] box + state box
+  static constexpr int CB_BYTES = 2 * NB64 * BOX_BYTES;              // keep + other tile
+  static constexpr int ST_BYTES = NB64 * SBOX_BYTES;                 // state boxes of one head block
+  static constexpr int IN_BYTES = NBOX * BOX_BYTES + (SPLIT ? 0 : ST_BYTES);   // x [, dy] box [+ state box]
   static constexpr int NTH = 4 * HB;                                  // table ring depth (one 2 KB table per head)
   static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
-  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + NTH * TAB_BYTES + RED_BYTES;
+  static constexpr size_t SMEM = 1024 + NCBS * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + (SPLIT ? ST_BYTES : 0) +
+                                 NTH * TAB_BYTES + RED_BYTES;
+  static_assert(SMEM <= 232448, "shared-memory plan exceeds the 227 KB a CTA can have");
   // warp roles: NM groups of 4 * NCH decay warps, then two MMA issuer warps (one per head of a head block) on the two
   // least loaded schedulers, the producer warp and an idle warp, then 8 epilogue warps
   static constexpr int NCH = 1;                                       // threads per row of the decay pass
   static constexpr int DW = 4 * NCH * NM, W_MMA = DW, W_PROD = DW + 2, W_EPI = DW + 4;
-  static constexpr int NI = HB;                                       // active issuers: warps W_MMA .. W_MMA + NI - 1
+  // active issuers: warps W_MMA .. W_MMA + NI - 1, one per head of a head block; with one (64-wide) head per block and
+  // dstate 128 the second lane issues the state term (8 instructions per head beside the head's own 8)
+  static constexpr int NI = (SPLIT && HB == 1) ? 2 : HB;
+  static constexpr int ST_ISSUER = (SPLIT && HB == 1) ? 1 : 0;
   static constexpr int THREADS = (DW + 4 + WS_EPI_WARPS) * 32;
   // registers per thread after re-balancing (launch share: 80 at 768 threads, 96 at 640)
   static constexpr int R_DECAY = (THREADS == 768) ? 88 : (THREADS == 640 ? 128 : (MODE == 0 ? 80 : 72)),
@@ -1712,24 +1729,28 @@ struct WsCfg {
 
 struct WsBars {
   uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], acc_full[2], acc_empty[2];
-  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], done;
+  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], st_full, st_empty, done;
 };
 
-template <int P, int MODE>
-__global__ void __launch_bounds__(WsCfg<P, MODE>::THREADS, 1)
+template <int P, int MODE, int N_ = 64, bool GATED = false>
+__global__ void __launch_bounds__(WsCfg<P, MODE, N_>::THREADS, 1)
 k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
           const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
-          const bf16* __restrict__ z, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
+          const bf16* __restrict__ z_, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
           bf16* __restrict__ dx, float* __restrict__ rs0, float* __restrict__ rs1, int* __restrict__ status) {
-  using Cfg = WsCfg<P, MODE>;
-  constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM, NTH = Cfg::NTH;
+  using Cfg = WsCfg<P, MODE, N_>;
+  const bf16* __restrict__ z = GATED ? z_ : nullptr;     // the ungated instantiation carries none of the gate's registers
+  constexpr bool ZAHEAD = GATED && MODE == 0;             // forward: the gate one block ahead; recompute: at the block's start
+  constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM, NTH = Cfg::NTH, NB64 = Cfg::NB64, NCBS = Cfg::NCBS;
+  constexpr bool SPLIT = Cfg::SPLIT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
-  uint8_t* sCB = smem;                                   // 2 x {keep tile, other tile}
-  uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
-  uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x [, dy], state box}
-  uint8_t* sTab = sIn + 2 * Cfg::IN_BYTES;               // NTH x decay table of one head (they run further ahead)
+  uint8_t* sCB = smem;                                   // NCBS x {keep tile, other tile}
+  uint8_t* sM = sCB + NCBS * Cfg::CB_BYTES;              // NM x 32 KB
+  uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x [, dy] [, state box]}
+  uint8_t* sSt = sIn + 2 * Cfg::IN_BYTES;                // dstate 128: the state boxes of one head block
+  uint8_t* sTab = sSt + (SPLIT ? Cfg::ST_BYTES : 0);     // NTH x decay table of one head (they run further ahead)
   float* sRed = (float*)(sTab + NTH * TAB_BYTES);          // [2][256] (P = 64 row-sum exchange)
   __shared__ __align__(8) WsBars bars;
   __shared__ uint32_t tmem_slot;
@@ -1749,6 +1770,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     for (int i = 0; i < 3; ++i) { mbar_init(&bars.m_full[i], 4 * Cfg::NCH); mbar_init(&bars.m_empty[i], 1); }
     // a head's table is read by the warps of its decay group and by the epilogue warps of its columns
     for (int i = 0; i < NTH; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], 4 * Cfg::NCH + WS_EPI_WARPS / HB); }
+    mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 1);
     mbar_init(&bars.done, Cfg::NI);
     mbar_fence_init();
   }
@@ -1782,12 +1804,15 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       auto load_cb = [&](int t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
-        const int cs_ = t & 1;
-        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
+        const int cs_ = t % NCBS;
+        w.wait(&bars.cb_empty[cs_], ((t / NCBS) & 1) ^ 1, 41);
         uint8_t* keep = sCB + cs_ * Cfg::CB_BYTES;
         mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
-        tma_load_3d(keep, (MODE == 2) ? &tmB : &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
-        tma_load_3d(keep + BOX_BYTES, (MODE == 2) ? &tmC : &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
+#pragma unroll
+        for (int j = 0; j < NB64; ++j) {
+          tma_load_3d(keep + j * BOX_BYTES, (MODE == 2) ? &tmB : &tmC, grp * N + 64 * j, c * QT, b, &bars.cb_full[cs_]);
+          tma_load_3d(keep + (NB64 + j) * BOX_BYTES, (MODE == 2) ? &tmC : &tmB, grp * N + 64 * j, c * QT, b, &bars.cb_full[cs_]);
+        }
       };
       const int total_blocks = my_tiles * nblk;
       auto load_tab = [&](int kg) {        // tables of the heads of global block kg: they run two blocks ahead of the boxes
@@ -1819,11 +1844,21 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
           tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
           if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
-          tma_load_3d(dst + NBOX * BOX_BYTES, &tmS, 0, h0 * P, b * g.nc + c, &bars.in_full[ib]);
-          // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
-          // the next G while this tile is still being worked on
-          if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+          if constexpr (!SPLIT) {
+            tma_load_3d(dst + NBOX * BOX_BYTES, &tmS, 0, h0 * P, b * g.nc + c, &bars.in_full[ib]);
+            // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
+            // the next G while this tile is still being worked on
+            if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+          } else {
+            w.wait(&bars.st_empty, (kb & 1) ^ 1, 57);
+            mbar_expect_tx(&bars.st_full, Cfg::ST_BYTES);
+#pragma unroll
+            for (int j = 0; j < NB64; ++j)
+              tma_load_3d(sSt + j * SBOX_BYTES, &tmS, 64 * j, h0 * P, b * g.nc + c, &bars.st_full);
+          }
         }
+        // one C/B slot: the next tile's C/B can only follow this tile's last block
+        if (SPLIT && t + 1 < my_tiles) load_cb(t + 1);
       }
     }
   } else if (warp >= Cfg::W_MMA && warp < Cfg::W_MMA + Cfg::NI) {
@@ -1836,25 +1871,43 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const uint32_t idY = make_idesc(128, P, (MODE == 2) ? 1 : 0, 1), idO = make_idesc(128, 64, 0, 0);
       constexpr uint32_t M_STEP = (MODE == 2) ? 256 : 4096;
       auto issue_g = [&](int t) {
-        const int s_ = t & 1;
-        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43); w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
+        const int s_ = t % NCBS;
+        w.wait(&bars.cb_full[s_], (t / NCBS) & 1, 43); w.wait(&bars.g_empty[s_], ((t / NCBS) & 1) ^ 1, 44);
         tc_fence_after();
-        const uint32_t keep = smem_u32(sCB + s_ * Cfg::CB_BYTES), other = keep + BOX_BYTES;
-        const uint64_t dc = desc_sw128_k((MODE == 2) ? other : keep, 0), db = desc_sw128_k((MODE == 2) ? keep : other, 0);
+        const uint32_t keep = smem_u32(sCB + s_ * Cfg::CB_BYTES), other = keep + NB64 * BOX_BYTES;
 #pragma unroll 1
-        for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, ks > 0);
+        for (int j = 0; j < NB64; ++j) {
+          const uint64_t dc = desc_sw128_k(((MODE == 2) ? other : keep) + j * BOX_BYTES, 0),
+                         db = desc_sw128_k(((MODE == 2) ? keep : other) + j * BOX_BYTES, 0);
+#pragma unroll 1
+          for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, (j | ks) > 0);
+        }
         mma_commit(&bars.g_full[s_]);
       };
       if (mi == 0) issue_g(0);
       int kb = 0, kh = 0;
       for (int t = 0; t < my_tiles; ++t) {
-        const uint64_t dK0 = desc_sw128_k(smem_u32(sCB + (t & 1) * Cfg::CB_BYTES), 0);
+        const uint32_t keep_t = smem_u32(sCB + (t % NCBS) * Cfg::CB_BYTES);
+        const uint64_t dK0 = desc_sw128_k(keep_t, 0);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           const int ib = kb & 1, ab = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
           const uint32_t tmYd = tm + 256 + ab * 128, tmYo = tmYd + 64;
           w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
           w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46);
+          if constexpr (SPLIT) {
+            if (mi == Cfg::ST_ISSUER) {    // the state term first: it needs the keep tile and the state boxes, not M_h
+              w.wait(&bars.st_full, kb & 1, 58);
+              tc_fence_after();
+#pragma unroll 1
+              for (int j = 0; j < NB64; ++j) {
+                const uint64_t dKj = desc_sw128_k(keep_t + j * BOX_BYTES, 0), dSj = desc_sw128_k(smem_u32(sSt + j * SBOX_BYTES), 0);
+#pragma unroll 1
+                for (int ks = 0; ks < 4; ++ks) mma_bf16(tmYo, desc_adv(dKj, ks * 32), desc_adv(dSj, ks * 32), idO, (j | ks) > 0);
+              }
+              mma_commit(&bars.st_empty);
+            }
+          }
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             if (hl != mi) continue;
             const int ms = kh % NM;
@@ -1866,7 +1919,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll 1
             for (int ks = 0; ks < 8; ++ks)
               mma_bf16(tmYd + hl * P, desc_adv(dM0, ks * M_STEP), desc_adv(dO0, ks * 2048), idY, ks > 0);
-            if (hl == 0) {
+            if (!SPLIT && hl == 0) {
               const uint64_t dS0 = desc_sw128_k(inb + NBOX * BOX_BYTES, 0);
 #pragma unroll 1
               for (int ks = 0; ks < 4; ++ks) mma_bf16(tmYo, desc_adv(dK0, ks * 32), desc_adv(dS0, ks * 32), idO, ks > 0);
@@ -1874,10 +1927,11 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             mma_commit(&bars.m_empty[ms]);
           }
           mma_commit(&bars.in_empty[ib]);
-          if (blk == nblk - 1) mma_commit(&bars.cb_empty[t & 1]);
+          if (blk == nblk - 1) mma_commit(&bars.cb_empty[t % NCBS]);
           mma_commit(&bars.acc_full[ab]);
-          if (mi == 0 && blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
+          if (!SPLIT && mi == 0 && blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
         }
+        if (SPLIT && mi == 0 && t + 1 < my_tiles) issue_g(t + 1);
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
@@ -1889,8 +1943,8 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const uint32_t mrow = smem_u32(sM + wg * 2 * BOX_BYTES) + row * 16;
     int kh = 0;
     for (int t = 0; t < my_tiles; ++t) {
-      const int gs = t & 1;
-      w.wait(&bars.g_full[gs], (t >> 1) & 1, 51);
+      const int gs = t % NCBS;
+      w.wait(&bars.g_full[gs], (t / NCBS) & 1, 51);
       tc_fence_after();
       const uint32_t tm_row = tmem_addr(tm + gs * 128, rb * 32, 0);
       for (int hh = 0; hh < nblk * HB; ++hh, ++kh) {
@@ -1912,11 +1966,25 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
     const int hl_e = (half * 32) / P;
     int kb = 0;
+    // the gate is the one operand the epilogue reads from global memory: this thread's 64 bytes of it are requested one
+    // head block ahead (registers), so no accumulator slice waits for a round trip to DRAM
+    uint4 zq[GATED ? 4 : 1] = {}, zn[ZAHEAD ? 4 : 1] = {};
+    auto load_z = [&](int t_, int blk_, auto& dst) {
+      if (!GATED || t_ >= my_tiles) return;
+      int b_, grp_, c_;
+      tile_coords(t_, b_, grp_, c_);
+      const bf16* zp_ = z + b_ * g.zsb + (long long)(c_ * QT + row) * g.zsl + (long long)(grp_ * g.hpg + blk_ * HB) * P + half * 32;
+#pragma unroll
+      for (int i = 0; i < (GATED ? 4 : 1); ++i) dst[i] = __ldg(reinterpret_cast<const uint4*>(zp_) + i);
+    };
+    if (ZAHEAD) load_z(0, 0, zq);
     for (int t = 0; t < my_tiles; ++t) {
       int b, grp, c;
       tile_coords(t, b, grp, c);
       const int t_row = c * QT + row;
       for (int blk = 0; blk < nblk; ++blk, ++kb) {
+        if constexpr (ZAHEAD) { if (blk + 1 < nblk) load_z(t, blk + 1, zn); else load_z(t + 1, 0, zn); }
+        else if constexpr (GATED) load_z(t, blk, zq);
         const int ib = kb & 1, ab = kb & 1;
         uint8_t* xt = sIn + ib * Cfg::IN_BYTES;
         uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;
@@ -1935,7 +2003,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         w.wait(&bars.acc_full[ab], (kb >> 1) & 1, 55);
         tc_fence_after();
         const long long colo = (long long)h0 * P + half * 32;
-        const bf16* zp = z ? z + b * g.zsb + (long long)t_row * g.zsl + colo : nullptr;
         const size_t dense = ((size_t)b * g.L + t_row) * g.H * P + colo;
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -1970,13 +2037,13 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             unpack8(xv[q], xs);
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] = yd[q * 8 + k] + osc * yo[q * 8 + k];
-            if (z) unpack8(*reinterpret_cast<const uint4*>(zp + k8), zs);
+            if (GATED) unpack8(zq[GATED ? h16 * 2 + q : 0], zs);
             if (MODE != 0) unpack8(dv[q], dys);
             if (MODE == 0) {
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
                 o[k] = acc[k] + Dh * xs[k];
-                if (z) o[k] *= zs[k] * sigmoidf_(zs[k]);
+                if (GATED) o[k] *= zs[k] * sigmoid_fast(zs[k]);
               }
               ov[q] = pack8(o);
             } else if (MODE == 1) {
@@ -1984,8 +2051,8 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
                 float dyv = dys[k];
-                if (z) {
-                  const float sg = 1.f / (1.f + __expf(-zs[k]));
+                if (GATED) {
+                  const float sg = sigmoid_fast(zs[k]);
                   o[k] = dyv * (acc[k] + Dh * xs[k]) * sg * (1.f + zs[k] * (1.f - sg));   // dz
                   dyv *= zs[k] * sg;
                 }
@@ -1993,7 +2060,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 s0 = fmaf(dyv, acc[k], s0);
                 s1 = fmaf(dyv, xs[k], s1);
               }
-              if (z) {
+              if (GATED) {
                 *reinterpret_cast<uint4*>(dz + dense + k8) = pack8(o);
                 *reinterpret_cast<uint4*>(dypb + dense + k8) = pack8(dp);
               }
@@ -2008,6 +2075,10 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           }
           if (MODE == 0) st_global_32B(y + b * g.ysb + (long long)t_row * g.ysl + colo + h16 * 16, ov[0], ov[1]);
           if (MODE == 2) st_global_32B(dx + dense + h16 * 16, ov[0], ov[1]);
+        }
+        if constexpr (ZAHEAD) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) zq[i] = zn[i];
         }
         if (MODE != 0) {
           if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
@@ -2932,14 +3003,17 @@ int sm_count() {
   return n[dev] > 0 ? n[dev] : 132;
 }
 
-template <int P, int MODE>
+template <int P, int MODE, int N, bool GATED = false>
 int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const ScanArgs& a, int* status, cudaStream_t s) {
-  auto k = k_scan_ws<P, MODE>;
-  constexpr size_t sm = WsCfg<P, MODE>::SMEM;
+  if constexpr (!GATED && MODE != 2) {
+    if (a.z) return launch_scan_ws<P, MODE, N, true>(g, m, ts, a, status, s);
+  }
+  auto k = k_scan_ws<P, MODE, N, GATED>;
+  constexpr size_t sm = WsCfg<P, MODE, N>::SMEM;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int ntiles = g.B * g.G * g.nc;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  k<<<grid, WsCfg<P, MODE>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
+  k<<<grid, WsCfg<P, MODE, N>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
                                  (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_ws" : (MODE == 1 ? "chunk_scan_bwd_ws" : "dx_ws"));
   return SSD_OK;
@@ -2947,7 +3021,7 @@ int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const 
 
 template <int P, int N, int MODE>
 int launch_scan(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const ScanArgs& a, int* status, cudaStream_t s) {
-  if (N == 64 && !g.onetile) return launch_scan_ws<P, MODE>(g, m, ts, a, status, s);
+  if (!g.onetile) return launch_scan_ws<P, MODE, N>(g, m, ts, a, status, s);
   constexpr int IBUF = (MODE == 0 && N < 128) ? 2 : 1;
   auto k = k_scan_tc<P, N, IBUF, MODE>;
   constexpr size_t sm = scan_smem<P, N, IBUF, MODE>();
