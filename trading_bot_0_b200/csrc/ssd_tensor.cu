@@ -1974,8 +1974,10 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       int b_, grp_, c_;
       tile_coords(t_, b_, grp_, c_);
       const bf16* zp_ = z + b_ * g.zsb + (long long)(c_ * QT + row) * g.zsl + (long long)(grp_ * g.hpg + blk_ * HB) * P + half * 32;
-#pragma unroll
-      for (int i = 0; i < (GATED ? 4 : 1); ++i) dst[i] = __ldg(reinterpret_cast<const uint4*>(zp_) + i);
+      if constexpr (GATED) {
+        ld_global_32B(zp_, dst[0], dst[1]);
+        ld_global_32B(zp_ + 16, dst[2], dst[3]);
+      }
     };
     if (ZAHEAD) load_z(0, 0, zq);
     for (int t = 0; t < my_tiles; ++t) {
@@ -2029,10 +2031,9 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             __syncwarp();
             if (lane == 0) { mbar_arrive(&bars.acc_empty[ab]); mbar_arrive(&bars.in_empty[ib]); }
           }
-          uint4 ov[2];
+          uint4 ov[2], dpk[2];
 #pragma unroll
           for (int q = 0; q < 2; ++q) {
-            const int k8 = h16 * 16 + q * 8;
             float xs[8], zs[8], dys[8], o[8], acc[8];
             unpack8(xv[q], xs);
 #pragma unroll
@@ -2060,10 +2061,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 s0 = fmaf(dyv, acc[k], s0);
                 s1 = fmaf(dyv, xs[k], s1);
               }
-              if (GATED) {
-                *reinterpret_cast<uint4*>(dz + dense + k8) = pack8(o);
-                *reinterpret_cast<uint4*>(dypb + dense + k8) = pack8(dp);
-              }
+              if (GATED) { ov[q] = pack8(o); dpk[q] = pack8(dp); }
             } else {
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
@@ -2072,6 +2070,10 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
               }
               ov[q] = pack8(o);
             }
+          }
+          if (MODE == 1 && GATED) {
+            st_global_32B(dz + dense + h16 * 16, ov[0], ov[1]);
+            st_global_32B(dypb + dense + h16 * 16, dpk[0], dpk[1]);
           }
           if (MODE == 0) st_global_32B(y + b * g.ysb + (long long)t_row * g.ysl + colo + h16 * 16, ov[0], ov[1]);
           if (MODE == 2) st_global_32B(dx + dense + h16 * 16, ov[0], ov[1]);

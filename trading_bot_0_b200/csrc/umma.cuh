@@ -243,6 +243,17 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 // 32 contiguous bytes to global memory: one full sector per thread when `p` is 32-byte aligned, else two halves
+// 32 read-only bytes per thread in one request where the address allows it (two 16-byte requests otherwise): rows read by
+// one thread each cost one L1 wavefront per lane and instruction, so half the instructions is half the wavefronts.
+__device__ __forceinline__ void ld_global_32B(const void* p, uint4& a, uint4& b) {
+  if ((reinterpret_cast<uintptr_t>(p) & 31) == 0) {
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
+  } else {
+    a = __ldg(reinterpret_cast<const uint4*>(p));
+    b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  }
+}
 __device__ __forceinline__ void st_global_32B(void* p, const uint4& a, const uint4& b) {
   if ((reinterpret_cast<uintptr_t>(p) & 31) == 0) {
     asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x),
