@@ -1729,19 +1729,24 @@ struct WsCfg {
 
 struct WsBars {
   uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], acc_full[2], acc_empty[2];
-  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], st_full, st_empty, done;
+  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], st_full, st_empty, out_ready[2], done;
 };
 
 template <int P, int MODE, int N_ = 64, bool GATED = false>
 __global__ void __launch_bounds__(WsCfg<P, MODE, N_>::THREADS, 1)
 k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
-          const __grid_constant__ CUtensorMap tmS, const float* __restrict__ tab, const float* __restrict__ D,
+          const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmOut,
+          const float* __restrict__ tab, const float* __restrict__ D,
           const bf16* __restrict__ z_, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
           bf16* __restrict__ dx, float* __restrict__ rs0, float* __restrict__ rs1, int* __restrict__ status) {
   using Cfg = WsCfg<P, MODE, N_>;
   const bf16* __restrict__ z = GATED ? z_ : nullptr;     // the ungated instantiation carries none of the gate's registers
   constexpr bool ZAHEAD = GATED && MODE == 0;             // forward: the gate one block ahead; recompute: at the block's start
+  // Forward and dx: the output block (128 rows x 64 columns bf16) has the shape and layout of the x (dy) box the epilogue
+  // reads, so the epilogue writes it over that box and a spare lane sends it out as ONE TMA tile store.  A row-per-thread
+  // global store costs one L1 wavefront per lane and instruction, and the L1 data stage is what these kernels share.
+  constexpr bool TSTORE = MODE != 1;
   constexpr int N = Cfg::N, HB = Cfg::HB, NBOX = Cfg::NBOX, NM = Cfg::NM, NTH = Cfg::NTH, NB64 = Cfg::NB64, NCBS = Cfg::NCBS;
   constexpr bool SPLIT = Cfg::SPLIT;
   extern __shared__ uint8_t smem_raw[];
@@ -1764,8 +1769,9 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], Cfg::NI);
       mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], Cfg::DW);
-      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], Cfg::NI + WS_EPI_WARPS);
+      mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], Cfg::NI + (TSTORE ? 1 : WS_EPI_WARPS));
       mbar_init(&bars.acc_full[i], Cfg::NI); mbar_init(&bars.acc_empty[i], WS_EPI_WARPS);
+      mbar_init(&bars.out_ready[i], WS_EPI_WARPS);
     }
     for (int i = 0; i < 3; ++i) { mbar_init(&bars.m_full[i], 4 * Cfg::NCH); mbar_init(&bars.m_empty[i], 1); }
     // a head's table is read by the warps of its decay group and by the epilogue warps of its columns
@@ -1936,6 +1942,24 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
     }
+  } else if (TSTORE && warp == Cfg::W_PROD + 1) {
+    // ------------------------------------------------------------------ store lane: output blocks leave as TMA tiles
+    if (lane == 0) {
+      int kb = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          const int ib = kb & 1;
+          w.wait(&bars.out_ready[ib], (kb >> 1) & 1, 59);
+          tma_store_3d(&tmOut, sIn + ib * Cfg::IN_BYTES + (NBOX - 1) * BOX_BYTES, grp * g.hpg * P + blk * 64, c * QT, b);
+          bulk_commit();
+          bulk_wait_read0();            // the box has been read: the slot may be refilled
+          mbar_arrive(&bars.in_empty[ib]);
+        }
+      }
+      bulk_wait0();
+    }
   } else if (warp < Cfg::DW) {
     // ------------------------------------------------------------------ decay pass: group wg owns heads kh = wg (mod NM)
     reg_inc<Cfg::R_DECAY>();
@@ -2029,7 +2053,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           if (h16 == 1) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&bars.acc_empty[ab]); mbar_arrive(&bars.in_empty[ib]); }
+            if (lane == 0) { mbar_arrive(&bars.acc_empty[ab]); if (!TSTORE) mbar_arrive(&bars.in_empty[ib]); }
           }
           uint4 ov[2], dpk[2];
 #pragma unroll
@@ -2075,8 +2099,16 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             st_global_32B(dz + dense + h16 * 16, ov[0], ov[1]);
             st_global_32B(dypb + dense + h16 * 16, dpk[0], dpk[1]);
           }
-          if (MODE == 0) st_global_32B(y + b * g.ysb + (long long)t_row * g.ysl + colo + h16 * 16, ov[0], ov[1]);
-          if (MODE == 2) st_global_32B(dx + dense + h16 * 16, ov[0], ov[1]);
+          if (TSTORE) {   // over the chunks of the x (dy) box this thread has just read
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+              st_shared_v4(smem_u32(dyt) + sw128_off(row, half * 4 + h16 * 2 + q), ov[q].x, ov[q].y, ov[q].z, ov[q].w);
+          }
+        }
+        if (TSTORE) {
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.out_ready[ib]);
         }
         if constexpr (ZAHEAD) {
 #pragma unroll
@@ -2994,6 +3026,7 @@ struct ScanArgs {
 };
 struct SeqMaps {
   CUtensorMap x, dy, b, c, s, ds;
+  CUtensorMap out;     // the output of the persistent scan kernels (y, or the dense dx), written by TMA tile stores
 };
 
 int sm_count() {
@@ -3015,7 +3048,7 @@ int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const 
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int ntiles = g.B * g.G * g.nc;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  k<<<grid, WsCfg<P, MODE, N>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
+  k<<<grid, WsCfg<P, MODE, N>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, m.out, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
                                  (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_ws" : (MODE == 1 ? "chunk_scan_bwd_ws" : "dx_ws"));
   return SSD_OK;
@@ -3209,6 +3242,8 @@ int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const
   SeqMaps m;
   int rc = make_maps(g, p.x, nullptr, false, p.Bm, p.Cm, prev_bf, nullptr, &m);
   if (rc) return rc;
+  rc = make_seq_map(&m.out, p.y, (long long)g.H * g.P, g.L, g.B, g.ysl, g.ysb, "y");
+  if (rc) return rc;
   ScanArgs a{tab, p.D, p.z, p.y, nullptr, nullptr, nullptr, nullptr, nullptr};
 #define CALL(PP, NN) return launch_scan<PP, NN, 0>(g, m, m.s, a, status, s);
   DISPATCH_PN(CALL)
@@ -3221,6 +3256,7 @@ int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const v
   SeqMaps m;
   int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, prev_bf, nullptr, &m);
   if (rc) return rc;
+  m.out = m.x;
   ScanArgs a{tab, p.D, p.z, nullptr, dypb, p.dz, nullptr, dcsp, ddot};
 #define CALL(PP, NN) return launch_scan<PP, NN, 1>(g, m, m.s, a, status, s);
   DISPATCH_PN(CALL)
@@ -3233,6 +3269,11 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
   SeqMaps m;
   int rc = make_maps(g, p.x, dyp, dy_dense, p.Bm, p.Cm, nullptr, ds_bf, &m);
   if (rc) return rc;
+  {
+    const long long HP = (long long)g.H * g.P;
+    rc = make_seq_map(&m.out, p.dx, HP, g.L, g.B, HP, HP * g.L, "dx");
+    if (rc) return rc;
+  }
   ScanArgs a{tab, p.D, nullptr, nullptr, nullptr, nullptr, p.dx, ddtd, nullptr};
 #define CALL(PP, NN) return launch_scan<PP, NN, 2>(g, m, m.ds, a, status, s);
   DISPATCH_PN(CALL)
