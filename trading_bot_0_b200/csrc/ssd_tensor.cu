@@ -1248,7 +1248,7 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   uint8_t* sM = sB + NB * BOX_BYTES;           // the 32 KB M_h tile
   uint8_t* sIn = sM + 2 * BOX_BYTES;           // x, dy, state boxes, tables of one head block
   float* sRed = (float*)(sIn + IN_BYTES);      // [3][PARTS][128] partial row sums
-  __shared__ __align__(8) uint64_t bar_cb, bar_in, bar_mma;
+  __shared__ __align__(8) uint64_t bar_cb, bar_in, bar_mma, bar_g;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -1259,7 +1259,7 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
   const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
-    mbar_init(&bar_cb, 1); mbar_init(&bar_in, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_cb, 1); mbar_init(&bar_in, 1); mbar_init(&bar_mma, 4); mbar_init(&bar_g, 1);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
@@ -1318,10 +1318,9 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
         mma_bf16(tmG, desc_adv(dc, kb * BOX_BYTES + ks * 32), desc_adv(db, kb * BOX_BYTES + ks * 32), idG, (kb | ks) > 0);
-    mma_commit(&bar_mma);
+    mma_commit(&bar_g);
   }
-  w.wait(&bar_mma, mphase, 22);
-  mphase ^= 1;
+  w.wait(&bar_g, 0, 22);
   tc_fence_after();
 
   const uint32_t idY = make_idesc(128, P, 0, 1), idU = make_idesc(128, P, 1, 1), idO = make_idesc(128, 64, 0, 0);
@@ -1340,23 +1339,26 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
-      if (tid == 0) {
+      // four issuing lanes (one per product: Y, U', and the two state terms), each committing its own instructions
+      if ((tid & 31) == 0 && warp < 4) {
         tc_fence_after();
-        const uint64_t dX0 = desc_sw128_mn(smem_u32(xt), 0, hl * P * 2, 16), dY0 = desc_sw128_mn(smem_u32(dyt), 0, hl * P * 2, 16);
+        if (warp == 0) {
+          const uint64_t dX0 = desc_sw128_mn(smem_u32(xt), 0, hl * P * 2, 16);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          mma_bf16(tmYd + hl * P, desc_adv(dMk0, ks * 4096), desc_adv(dX0, ks * 2048), idY, ks > 0);
-          mma_bf16(tmUd + hl * P, desc_adv(dMt0, ks * 256), desc_adv(dY0, ks * 2048), idU, ks > 0);
-        }
-        if (hl == 0) {
-          const uint64_t dS0 = desc_sw128_k(smem_u32(stS), 0), dDS0 = desc_sw128_k(smem_u32(stDS), 0);
+          for (int ks = 0; ks < 8; ++ks) mma_bf16(tmYd + hl * P, desc_adv(dMk0, ks * 4096), desc_adv(dX0, ks * 2048), idY, ks > 0);
+        } else if (warp == 1) {
+          const uint64_t dY0 = desc_sw128_mn(smem_u32(dyt), 0, hl * P * 2, 16);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) mma_bf16(tmUd + hl * P, desc_adv(dMt0, ks * 256), desc_adv(dY0, ks * 2048), idU, ks > 0);
+        } else if (hl == 0) {
+          const uint64_t dA0 = (warp == 2) ? dC0 : dB0;
+          const uint64_t dS0 = desc_sw128_k(smem_u32(warp == 2 ? stS : stDS), 0);
+          const uint32_t tmO = (warp == 2) ? tmYo : tmUo;
 #pragma unroll
           for (int kb = 0; kb < NB; ++kb)
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              mma_bf16(tmYo, desc_adv(dC0, kb * BOX_BYTES + ks * 32), desc_adv(dS0, kb * SBOX_BYTES + ks * 32), idO, (kb | ks) > 0);
-              mma_bf16(tmUo, desc_adv(dB0, kb * BOX_BYTES + ks * 32), desc_adv(dDS0, kb * SBOX_BYTES + ks * 32), idO, (kb | ks) > 0);
-            }
+            for (int ks = 0; ks < 4; ++ks)
+              mma_bf16(tmO, desc_adv(dA0, kb * BOX_BYTES + ks * 32), desc_adv(dS0, kb * SBOX_BYTES + ks * 32), idO, (kb | ks) > 0);
         }
         mma_commit(&bar_mma);
       }
@@ -2908,7 +2910,9 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
       if (s < g.nc) {   // block-uniform
         const int c = reverse ? g.nc - 1 - s : s;
         if (WRITE && valid) {
-          *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+          // the reverse scan's fp32 values have no reader in this family (the scans take the bf16 copy, the state
+          // gradient entering the slice leaves through `last`): a third of its bytes stay unwritten
+          if (!reverse || !st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
           if (st_bf)
             *reinterpret_cast<uint2*>(st_bf + boff + (size_t)c * cstride) =
                 make_uint2(pack_bf16(run.x, run.y), pack_bf16(run.z, run.w));
