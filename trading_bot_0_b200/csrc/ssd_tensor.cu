@@ -1239,16 +1239,21 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
          float* __restrict__ ddtd, int* __restrict__ status) {
   constexpr int NB = N / 64;
   constexpr int HB = 64 / P;                   // heads per 64-column box
-  constexpr int IN_BYTES = 2 * BOX_BYTES + 2 * NB * SBOX_BYTES + HB * TAB_BYTES;   // x, dy, S_prev boxes, dS_end boxes, tables
+  // x box, dy box and tables of a head block: two sets (the next block's is requested a whole block ahead); the S_prev and
+  // dS_end boxes: one set, refilled as soon as the block's products have completed
+  constexpr int XSET = 2 * BOX_BYTES + HB * TAB_BYTES;
+  constexpr int ST_BYTES = 2 * NB * SBOX_BYTES;
   constexpr uint32_t TM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
   uint8_t* sC = smem;                          // NB boxes, kept for the whole CTA (state term of Y)
   uint8_t* sB = sC + NB * BOX_BYTES;           // NB boxes, kept for the whole CTA (state term of U')
   uint8_t* sM = sB + NB * BOX_BYTES;           // the 32 KB M_h tile
-  uint8_t* sIn = sM + 2 * BOX_BYTES;           // x, dy, state boxes, tables of one head block
-  float* sRed = (float*)(sIn + IN_BYTES);      // [3][PARTS][128] partial row sums
-  __shared__ __align__(8) uint64_t bar_cb, bar_in, bar_mma, bar_g;
+  uint8_t* sXset = sM + 2 * BOX_BYTES;         // 2 x {x, dy, tables}
+  uint8_t* stS = sXset + 2 * XSET;             // S_prev boxes
+  uint8_t* stDS = stS + NB * SBOX_BYTES;       // dS_end boxes
+  float* sRed = (float*)(stDS + NB * SBOX_BYTES);      // [3][PARTS][128] partial row sums
+  __shared__ __align__(8) uint64_t bar_cb, bar_x[2], bar_st, bar_mma, bar_g;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -1259,7 +1264,8 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
   const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
-    mbar_init(&bar_cb, 1); mbar_init(&bar_in, 1); mbar_init(&bar_mma, 4); mbar_init(&bar_g, 1);
+    mbar_init(&bar_cb, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_st, 1);
+    mbar_init(&bar_mma, 4); mbar_init(&bar_g, 1);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
@@ -1272,21 +1278,25 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 
   const int nblk = g.hpg / HB;
   const int col_base = grp * g.hpg * P;
-  uint8_t* xt = sIn;
-  uint8_t* dyt = sIn + BOX_BYTES;
-  uint8_t* stS = sIn + 2 * BOX_BYTES;
-  uint8_t* stDS = stS + NB * SBOX_BYTES;
-  const float* tb = (const float*)(stDS + NB * SBOX_BYTES);   // [HB][TAB]
-  auto load_block = [&](int blk) {    // thread 0 only
+  uint8_t* xt = sXset;
+  uint8_t* dyt = xt + BOX_BYTES;
+  const float* tb = (const float*)(dyt + BOX_BYTES);   // [HB][TAB]
+  auto load_xset = [&](int blk) {     // thread 0 only
     const int h0 = grp * g.hpg + blk * HB;
-    mbar_expect_tx(&bar_in, IN_BYTES);
-    tma_load_3d(xt, &tmX, col_base + blk * 64, c * QT, b, &bar_in);
-    tma_load_3d(dyt, &tmDY, col_base + blk * 64, c * QT, b, &bar_in);
+    uint8_t* set = sXset + (blk & 1) * XSET;
+    uint64_t* bar = &bar_x[blk & 1];
+    mbar_expect_tx(bar, XSET);
+    tma_load_3d(set, &tmX, col_base + blk * 64, c * QT, b, bar);
+    tma_load_3d(set + BOX_BYTES, &tmDY, col_base + blk * 64, c * QT, b, bar);
+    bulk_load(set + 2 * BOX_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES, bar);
+  };
+  auto load_states = [&](int blk) {   // thread 0 only
+    const int h0 = grp * g.hpg + blk * HB;
+    mbar_expect_tx(&bar_st, ST_BYTES);
     for (int kb = 0; kb < NB; ++kb) {
-      tma_load_3d(stS + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_in);
-      tma_load_3d(stDS + kb * SBOX_BYTES, &tmDS, kb * 64, h0 * P, b * g.nc + c, &bar_in);
+      tma_load_3d(stS + kb * SBOX_BYTES, &tmS, kb * 64, h0 * P, b * g.nc + c, &bar_st);
+      tma_load_3d(stDS + kb * SBOX_BYTES, &tmDS, kb * 64, h0 * P, b * g.nc + c, &bar_st);
     }
-    bulk_load((void*)tb, tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES, &bar_in);
   };
   if (tid == 0) {
     mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
@@ -1294,7 +1304,8 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       tma_load_3d(sC + kb * BOX_BYTES, &tmC, grp * N + kb * 64, c * QT, b, &bar_cb);
       tma_load_3d(sB + kb * BOX_BYTES, &tmB, grp * N + kb * 64, c * QT, b, &bar_cb);
     }
-    load_block(0);
+    load_xset(0);
+    load_states(0);
     for (int blk = 1; blk < nblk; ++blk) {   // later blocks: start them towards L2 now
       const int h0 = grp * g.hpg + blk * HB;
       tma_prefetch_3d(&tmX, col_base + blk * 64, c * QT, b);
@@ -1306,7 +1317,7 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       bulk_prefetch(tab + ((size_t)(b * g.nc + c) * g.H + h0) * TAB, HB * TAB_BYTES);
     }
   }
-  uint32_t inphase = 0, mphase = 0;
+  uint32_t mphase = 0;
   zero_upper_block(row, part, warp, smem_u32(sM));   // M_h never writes these blocks
   w.wait(&bar_cb, 0, 21);
   if (tid == 0) {
@@ -1332,8 +1343,12 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     const int h0 = grp * g.hpg + blk * HB;
     const int h_e = h0 + hl_e;
     const float Dh = D ? __ldg(D + h_e) : 0.f;
-    w.wait(&bar_in, inphase, 23);
-    inphase ^= 1;
+    xt = sXset + (blk & 1) * XSET;
+    dyt = xt + BOX_BYTES;
+    tb = (const float*)(dyt + BOX_BYTES);
+    w.wait(&bar_x[blk & 1], (blk >> 1) & 1, 23);
+    w.wait(&bar_st, blk & 1, 25);
+    if (tid == 0 && blk + 1 < nblk) load_xset(blk + 1);   // the other set: its readers finished with the previous block
     for (int hl = 0; hl < HB; ++hl) {
       decay_mask_block(tmG, tb + hl * TAB, row, part, warp, smem_u32(sM));
       fence_async_smem();
@@ -1377,7 +1392,7 @@ k_bwd_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     const float cs_r = tb[hl_e * TAB + T_CS + row], dt_r = tb[hl_e * TAB + T_DT + row];
     const float osc_y = ex2(cs_r), osc_u = dt_r * ex2(tb[hl_e * TAB + T_CS + 127] - cs_r);
     __syncthreads();
-    if (tid == 0 && blk + 1 < nblk) load_block(blk + 1);
+    if (tid == 0 && blk + 1 < nblk) load_states(blk + 1);
     float s0 = 0.f, s1 = 0.f, s2 = 0.f;
     {
       float yd[16], yo[16];
@@ -1458,12 +1473,14 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   uint8_t* sB = smem;                          // NB boxes
   uint8_t* sC = sB + NB * BOX_BYTES;           // NB boxes
   uint8_t* sM = sC + NB * BOX_BYTES;           // 32 KB W'_h tile, plain layout
-  uint8_t* sX = sM + 2 * BOX_BYTES;            // x box
-  uint8_t* sDY = sX + BOX_BYTES;               // dy box
+  // x box, dy box and the tables of a head block: NBUF sets, so that at dstate 128 (one CTA per SM) the next block's set is
+  // requested a whole block ahead instead of behind the current block's last product
+  constexpr int NBUF = (N > 64) ? 2 : 1;
+  constexpr int XSET = 2 * BOX_BYTES + HB * TAB_BYTES;
+  uint8_t* sXset = sM + 2 * BOX_BYTES;
   uint8_t* sS = sM;                            // S_prev boxes (NB x 8 KB): reuse the W' tile after the head loop
   uint8_t* sDS = sM + NB * SBOX_BYTES;         // dS_end boxes
-  float* sTab = (float*)(sDY + BOX_BYTES);     // [HB][TAB]
-  __shared__ __align__(8) uint64_t bar_cb, bar_x, bar_s, bar_mma;
+  __shared__ __align__(8) uint64_t bar_cb, bar_x[2], bar_s, bar_mma;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
 
@@ -1474,7 +1491,7 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   const int c = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
   const int row = tid & 127, part = tid >> 7;
   if (tid == 0) {
-    mbar_init(&bar_cb, 1); mbar_init(&bar_x, 1); mbar_init(&bar_s, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_cb, 1); mbar_init(&bar_x[0], 1); mbar_init(&bar_x[1], 1); mbar_init(&bar_s, 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_slot, TM_COLS);
@@ -1488,10 +1505,12 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   const int nblk = g.hpg / HB;
   const int col_base = grp * g.hpg * P;
   auto load_boxes = [&](int blk) {             // thread 0 only
-    mbar_expect_tx(&bar_x, 2 * BOX_BYTES + HB * TAB_BYTES);
-    tma_load_3d(sX, &tmX, col_base + blk * 64, c * QT, b, &bar_x);
-    tma_load_3d(sDY, &tmDY, col_base + blk * 64, c * QT, b, &bar_x);
-    bulk_load(sTab, tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + blk * HB) * TAB, HB * TAB_BYTES, &bar_x);
+    uint8_t* set = sXset + (blk % NBUF) * XSET;
+    uint64_t* bar = &bar_x[blk % NBUF];
+    mbar_expect_tx(bar, XSET);
+    tma_load_3d(set, &tmX, col_base + blk * 64, c * QT, b, bar);
+    tma_load_3d(set + BOX_BYTES, &tmDY, col_base + blk * 64, c * QT, b, bar);
+    bulk_load(set + 2 * BOX_BYTES, tab + ((size_t)(b * g.nc + c) * g.H + grp * g.hpg + blk * HB) * TAB, HB * TAB_BYTES, bar);
   };
   if (tid == 0) {
     mbar_expect_tx(&bar_cb, 2 * NB * BOX_BYTES);
@@ -1513,9 +1532,12 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       }
     }
   }
-  uint32_t xphase = 0, sphase = 0, mphase = 0;
+  uint32_t sphase = 0, mphase = 0;
   const uint32_t idW = make_idesc(128, 128, 0, 0), idC = make_idesc(128, N, 0, 1), idB = make_idesc(128, N, 1, 1);
-  const uint64_t dDY0 = desc_sw128_k(smem_u32(sDY), 0), dX0 = desc_sw128_k(smem_u32(sX), 0);
+  uint8_t* sX = sXset;
+  uint8_t* sDY = sX + BOX_BYTES;
+  const float* sTab = (const float*)(sDY + BOX_BYTES);     // [HB][TAB]
+  uint64_t dDY0 = desc_sw128_k(smem_u32(sDY), 0), dX0 = desc_sw128_k(smem_u32(sX), 0);
   const uint64_t dMk0 = desc_plain_k(smem_u32(sM), 128, 0), dMt0 = desc_plain_mn(smem_u32(sM), 128, 0, 0);
   const uint64_t dBm0 = desc_sw128_mn(smem_u32(sB), 0, 0, BOX_BYTES), dCm0 = desc_sw128_mn(smem_u32(sC), 0, 0, BOX_BYTES);
   const uint64_t dSm0 = desc_sw128_mn(smem_u32(sS), 0, 0, SBOX_BYTES), dDSm0 = desc_sw128_mn(smem_u32(sDS), 0, 0, SBOX_BYTES);
@@ -1534,12 +1556,17 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   for (int blk = 0; blk < nblk; ++blk) {
     const int h0 = grp * g.hpg + blk * HB;
     if (!SUMW) zero_upper_block(row, part, warp, smem_u32(sM));   // the state boxes of the previous head block lived here
-    w.wait(&bar_x, xphase, 32);
-    xphase ^= 1;
+    sX = sXset + (blk % NBUF) * XSET;
+    sDY = sX + BOX_BYTES;
+    sTab = (const float*)(sDY + BOX_BYTES);
+    dDY0 = desc_sw128_k(smem_u32(sDY), 0);
+    dX0 = desc_sw128_k(smem_u32(sX), 0);
+    w.wait(&bar_x[blk % NBUF], (blk / NBUF) & 1, 32);
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
+      if (NBUF == 2 && blk + 1 < nblk) load_boxes(blk + 1);   // the other set: its last readers finished a block ago
       issue_w(0);
       mma_commit(&bar_mma);
       if (SUMW) {   // nothing else lives in the W' tile until the end of the CTA: fetch this block's state boxes into it now
@@ -1632,7 +1659,7 @@ k_dbc_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     mphase ^= 1;
     tc_fence_after();
     __syncthreads();
-    if (tid == 0 && blk + 1 < nblk) load_boxes(blk + 1);
+    if (NBUF == 1 && tid == 0 && blk + 1 < nblk) load_boxes(blk + 1);
   }
   if constexpr (SUMW) {
     // the head sum -> bf16 -> the W' tile (the state boxes that lived there have been consumed), then one product per side
@@ -2998,7 +3025,9 @@ constexpr size_t scan_smem() {
          (MODE == 0 ? 0 : 2 * PARTS * 128 * 4);
 }
 template <int P, int N>
-constexpr size_t dbc_smem() { return 1024 + 2 * (N / 64) * BOX_BYTES + 4 * BOX_BYTES + (64 / P) * TAB_BYTES; }
+constexpr size_t dbc_smem() {
+  return 1024 + 2 * (N / 64) * BOX_BYTES + 2 * BOX_BYTES + (N > 64 ? 2 : 1) * (2 * BOX_BYTES + (64 / P) * TAB_BYTES);
+}
 
 int sm_count();
 
@@ -3086,7 +3115,8 @@ int launch_bwd_ws(const Geo& g, const SeqMaps& m, const float* tab, const float*
 
 template <int P, int N>
 constexpr size_t bwd_tc_smem() {
-  return 1024 + 2 * (N / 64) * BOX_BYTES + 2 * BOX_BYTES + 2 * BOX_BYTES + 2 * (N / 64) * SBOX_BYTES + (64 / P) * TAB_BYTES + 3 * PARTS * 128 * 4;
+  return 1024 + 2 * (N / 64) * BOX_BYTES + 2 * BOX_BYTES + 2 * (2 * BOX_BYTES + (64 / P) * TAB_BYTES) + 2 * (N / 64) * SBOX_BYTES +
+         3 * PARTS * 128 * 4;
 }
 template <int P, int N>
 int launch_bwd_tc(const Geo& g, const SeqMaps& m, const float* tab, const float* D, void* dx, float* dcsp, float* ddot,
