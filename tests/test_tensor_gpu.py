@@ -48,6 +48,29 @@ def test_tensor_forward_backward_matches_oracle(lib, H, P, N, G, has_z, use_D, w
         assert_close(k + " (recompute)", g2[k], ref[k], "bf16")
 
 
+@pytest.mark.parametrize("H,P,N,G", [(8, 32, 64, 1), (24, 64, 128, 1), (8, 32, 128, 2), (4, 64, 64, 2)])
+@pytest.mark.parametrize("has_z", [False, True])
+def test_one_tile_arm_matches_oracle(lib, H, P, N, G, has_z):
+    """The one-tile-per-CTA kernels (algo = tensor_onetile), which the default path no longer reaches except for the merged
+    backward and dB/dC at dstate 128: same gates as the persistent kernels."""
+    import trading_bot_0_b200 as T
+    cfg = O.SsdConfig("tc", 3, 384, H, P, N, G, 128, "bf16", has_z)
+    inp = O.make_inputs(cfg, with_init_state=True)
+    dfinal = 0.1 * torch.randn(3, H, P, N, generator=torch.Generator().manual_seed(4))
+    ref = oracle_all(inp, dfinal)
+    d = to_dev(inp, DEV)
+    y, fin, ws = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d.get("D"), d.get("z"), d.get("init_state"),
+                           chunk=128, algo="tensor_onetile", for_backward=True)
+    g = T.backward(d["dy"], d["x"], d["dt"], d["A"], d["B"], d["C"], d.get("D"), d.get("z"), d.get("init_state"),
+                   dfinal.to(DEV), chunk=128, algo="tensor_onetile", workspace=ws, fwd_saved=True, want_dinit=True)
+    torch.cuda.synchronize()
+    assert status_word(ws) == 0
+    assert_close("y", y, ref["y"], "bf16")
+    assert_close("final_state", fin, ref["final_state"], "bf16")
+    for k in GRADS + ("dinit", "dD") + (("dz",) if has_z else ()):
+        assert_close(k, g[k], ref[k], "bf16")
+
+
 def test_tensor_matches_cuda_core_family(lib):
     """Same bf16 inputs through both kernel families: outputs agree to bf16 rounding."""
     import trading_bot_0_b200 as T

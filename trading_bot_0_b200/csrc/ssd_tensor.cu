@@ -994,9 +994,9 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
 // The state block (tmS) is the bf16 copy of S_prev (modes 0,1) or dS_end (mode 2).
 // IBUF = 2: the inputs of head block k+1 load while block k computes; IBUF = 1: they are
 // requested as soon as block k's epilogue has copied what it needs into registers.
-// Two CTAs per SM wherever shared memory allows it (dstate 64; dstate 128 forward): a CTA is a chain of phases that meet
-// at CTA-wide barriers, and a second resident CTA fills the gaps (dstate 128 forward: 0.95 -> 0.75 ms on the long-sequence
-// shapes).
+// Two CTAs per SM at dstate 64 (a CTA is a chain of phases that meet at CTA-wide barriers, and a second resident CTA
+// fills the gaps), one at dstate 128.  These are the kernels of the one-tile arm (SSD_ALGO_TENSOR_ONETILE); the default
+// path runs k_scan_ws at both state widths.
 template <int P, int N, int IBUF, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, (N <= 64) ? 2 : 1)
 k_scan_tc(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
