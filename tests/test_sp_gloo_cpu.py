@@ -57,6 +57,14 @@ class OracleOps(sp.SpOps):
         return out
 
 
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _t(a):
+    return torch.from_numpy(a)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -79,7 +87,8 @@ def _worker(rank, world, port, q):
         y, fin, ctx = sp.sp_forward(loc["x"], loc["dt"], inp["A"], loc["B"], loc["C"], inp["D"], loc["z"],
                                     inp["init_state"], chunk=cfg.chunk, ops=ops)
         g = sp.sp_backward(loc["dy"], ctx, dfin, ops=ops)
-        q.put((rank, a, b, y.detach(), fin.detach(), {k: v.detach() for k, v in g.items() if isinstance(v, torch.Tensor)}))
+        # by value (numpy), not as shared-memory handles: a rank may exit before the parent has unpickled its item
+        q.put((rank, a, b, _np(y), _np(fin), {k: _np(v) for k, v in g.items() if isinstance(v, torch.Tensor)}))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -106,13 +115,13 @@ def test_sp_forward_backward_over_gloo(world):
     dfin = torch.randn(2, 2, 4, 8, generator=torch.Generator().manual_seed(9))
     ref = O.ssd_grads_autograd(O.ssd_sequential, inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], inp["D"],
                                inp["dy"], inp["z"], inp["init_state"], dfin)
-    assert rel_err(torch.cat([r[3] for r in res], 1), ref["y"]) < 1e-5
-    assert rel_err(res[-1][4], ref["final_state"]) < 1e-5
+    assert rel_err(torch.cat([_t(r[3]) for r in res], 1), ref["y"]) < 1e-5
+    assert rel_err(_t(res[-1][4]), ref["final_state"]) < 1e-5
     for k in ("dx", "ddt", "dB", "dC", "dz"):
-        assert rel_err(torch.cat([r[5][k] for r in res], 1), ref[k]) < 1e-5, k
+        assert rel_err(torch.cat([_t(r[5][k]) for r in res], 1), ref[k]) < 1e-5, k
     for r in res:  # replicated-parameter gradients are already summed on every rank
-        assert rel_err(r[5]["dA"], ref["dA"]) < 1e-5 and rel_err(r[5]["dD"], ref["dD"]) < 1e-5
-    assert rel_err(res[0][5]["dinit"], ref["dinit"]) < 1e-5
+        assert rel_err(_t(r[5]["dA"]), ref["dA"]) < 1e-5 and rel_err(_t(r[5]["dD"]), ref["dD"]) < 1e-5
+    assert rel_err(_t(res[0][5]["dinit"]), ref["dinit"]) < 1e-5
 
 
 def test_slice_bounds():
@@ -178,7 +187,7 @@ def _fail_worker(rank, world, port, q, scenario):
         dist.all_reduce(t)
         y, fin, ctx = sp.sp_forward(loc["x"], loc["dt"], inp["A"], loc["B"], loc["C"], inp["D"], None, None, chunk=cfg.chunk,
                                     ops=ops, timeout_s=20.0, tag="retry")
-        q.put((rank, err, float(t.item()), y.detach(), fin.detach()))
+        q.put((rank, err, float(t.item()), _np(y), _np(fin)))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -201,5 +210,5 @@ def test_checked_exchange_reports_and_the_group_stays_usable(scenario):
             assert f"rank {1 - r} posted" in errs[r][1]
     for r in res:
         assert r[2] == 3.0                                   # the all-reduce after the failure
-    assert rel_err(torch.cat([r[3] for r in res], 1), y_ref) < 1e-5      # the clean retry
-    assert rel_err(res[-1][4], fin_ref) < 1e-5
+    assert rel_err(torch.cat([_t(r[3]) for r in res], 1), y_ref) < 1e-5      # the clean retry
+    assert rel_err(_t(res[-1][4]), fin_ref) < 1e-5

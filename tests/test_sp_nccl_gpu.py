@@ -45,7 +45,9 @@ def _worker(rank, world, port, q, which):
         from trading_bot_0_b200.ssd import workspace_status
         assert workspace_status(ctx.workspace) == 0
         torch.cuda.synchronize()
-        q.put((rank, y.cpu(), fin.cpu(), {k: v.cpu() for k, v in g.items() if isinstance(v, torch.Tensor) and k != "workspace"}))
+        # by value (numpy), not as shared-memory handles: a rank may exit before the parent has unpickled its item
+        npy = lambda t: t.detach().float().cpu().numpy()
+        q.put((rank, npy(y), npy(fin), {k: npy(v) for k, v in g.items() if isinstance(v, torch.Tensor) and k != "workspace"}))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -70,6 +72,7 @@ def test_sequence_parallel_over_nccl_matches_oracle(lib, which):
             if p.is_alive():
                 p.kill()
     assert all(p.exitcode == 0 for p in procs)
+    res = [(r[0], torch.from_numpy(r[1]), torch.from_numpy(r[2]), {k: torch.from_numpy(v) for k, v in r[3].items()}) for r in res]
     inp = O.make_inputs(CFG, with_init_state=True)
     dfin = 0.1 * torch.randn(CFG.batch, CFG.nheads, CFG.headdim, CFG.dstate, generator=torch.Generator().manual_seed(9))
     ref = oracle_all(inp, dfin)
