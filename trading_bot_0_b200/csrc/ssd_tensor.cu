@@ -1748,7 +1748,6 @@ struct WsCfg {
   // active issuers: warps W_MMA .. W_MMA + NI - 1, one per head of a head block; with one (64-wide) head per block and
   // dstate 128 the second lane issues the state term (8 instructions per head beside the head's own 8)
   static constexpr int NI = (SPLIT && HB == 1) ? 2 : HB;
-  static constexpr int ST_ISSUER = (SPLIT && HB == 1) ? 1 : 0;
   static constexpr int THREADS = (DW + 4 + WS_EPI_WARPS) * 32;
   // registers per thread after re-balancing (launch share: 80 at 768 threads, 96 at 640)
   static constexpr int R_DECAY = (THREADS == 768) ? 88 : (THREADS == 640 ? 128 : (MODE == 0 ? 80 : 72)),
@@ -1931,7 +1930,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
           w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46);
           if constexpr (SPLIT) {
-            if (mi == Cfg::ST_ISSUER) {    // the state term first: it needs the keep tile and the state boxes, not M_h
+            if (mi == ((SPLIT && HB == 1) ? 1 : 0)) {    // the state term first: it needs the keep tile and the state boxes, not M_h
               w.wait(&bars.st_full, kb & 1, 58);
               tc_fence_after();
 #pragma unroll 1
@@ -2023,11 +2022,11 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     // head block ahead (registers), so no accumulator slice waits for a round trip to DRAM
     uint4 zq[GATED ? 4 : 1] = {}, zn[ZAHEAD ? 4 : 1] = {};
     auto load_z = [&](int t_, int blk_, auto& dst) {
-      if (!GATED || t_ >= my_tiles) return;
-      int b_, grp_, c_;
-      tile_coords(t_, b_, grp_, c_);
-      const bf16* zp_ = z + b_ * g.zsb + (long long)(c_ * QT + row) * g.zsl + (long long)(grp_ * g.hpg + blk_ * HB) * P + half * 32;
       if constexpr (GATED) {
+        if (t_ >= my_tiles) return;
+        int b_, grp_, c_;
+        tile_coords(t_, b_, grp_, c_);
+        const bf16* zp_ = z + b_ * g.zsb + (long long)(c_ * QT + row) * g.zsl + (long long)(grp_ * g.hpg + blk_ * HB) * P + half * 32;
         ld_global_32B(zp_, dst[0], dst[1]);
         ld_global_32B(zp_ + 16, dst[2], dst[3]);
       }
@@ -2176,35 +2175,43 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 // Same roles, rings and parities as k_scan_ws.  TMEM: G x2 (256) + {Y, Y_off, U, U_off} (256, one
 // slot: the epilogue hands it back as soon as it has read it).  The two state boxes (S_prev, dS_end)
 // have a buffer of their own that is refilled while the second head of a block is worked on.
-template <int P>
+// dstate 128 (SPLIT): one C/B slot and one G; the S_prev and dS_end boxes (32 KB per head block at this width) pass as four
+// 8 KB pieces through a two-slot ring with a producer lane and an issuer lane of their own (warps 19 and 18), so the state
+// products run beside the head's own products and the whole plan stays inside 227 KB.
+template <int P, int N_ = 64>
 struct BwCfg {
-  static constexpr int N = 64, HB = 64 / P, NM = 2, NT = 4;
-  static constexpr int CB_BYTES = 2 * BOX_BYTES;             // C tile, B tile
+  static constexpr int N = N_, NB64 = N_ / 64, HB = 64 / P, NM = 2, NT = 4;
+  static constexpr bool SPLIT = N_ == 128;
+  static constexpr int NCBS = SPLIT ? 1 : 2;
+  static constexpr int CB_BYTES = 2 * NB64 * BOX_BYTES;      // C tile, B tile
   static constexpr int IN_BYTES = 2 * BOX_BYTES;             // x box, dy box
-  static constexpr int ST_BYTES = 2 * SBOX_BYTES;            // S_prev box, dS_end box
+  static constexpr int ST_BYTES = 2 * SBOX_BYTES;            // dstate 64: S_prev box, dS_end box; dstate 128: two ring slots
   static constexpr int TB_BYTES = HB * TAB_BYTES;
   static constexpr int RED_BYTES = (P == 64) ? 3 * 256 * 4 : 0;
-  static constexpr size_t SMEM = 1024 + 2 * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + ST_BYTES + NT * TB_BYTES + RED_BYTES;
+  static constexpr size_t SMEM = 1024 + NCBS * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + ST_BYTES + NT * TB_BYTES + RED_BYTES;
+  static_assert(SMEM <= 232448, "shared-memory plan exceeds the 227 KB a CTA can have");
 };
 
 struct BwBars {
   uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], m_full[2], m_empty[2];
   uint64_t tab_full[4], tab_empty[4], st_full, st_empty, acc_full, acc_empty, done;
+  uint64_t stp_full[2], stp_empty[2];
 };
 
-template <int P>
+template <int P, int N_ = 64>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
          const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmDS,
          const float* __restrict__ tab, const float* __restrict__ D, bf16* __restrict__ dx, float* __restrict__ dcsp,
          float* __restrict__ ddot, float* __restrict__ ddtd, int* __restrict__ status) {
-  using Cfg = BwCfg<P>;
-  constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM;
+  using Cfg = BwCfg<P, N_>;
+  constexpr int N = Cfg::N, HB = Cfg::HB, NM = Cfg::NM, NB64 = Cfg::NB64, NCBS = Cfg::NCBS;
+  constexpr bool SPLIT = Cfg::SPLIT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // 1 KB aligned, still known to be shared memory
-  uint8_t* sCB = smem;                                   // 2 x {C tile, B tile}
-  uint8_t* sM = sCB + 2 * Cfg::CB_BYTES;                 // NM x 32 KB
+  uint8_t* sCB = smem;                                   // NCBS x {C tile, B tile}
+  uint8_t* sM = sCB + NCBS * Cfg::CB_BYTES;              // NM x 32 KB
   uint8_t* sIn = sM + NM * 2 * BOX_BYTES;                // 2 x {x box, dy box}
   uint8_t* sSt = sIn + 2 * Cfg::IN_BYTES;                // S_prev box, dS_end box
   uint8_t* sTab = sSt + Cfg::ST_BYTES;                   // NT x decay tables of a head block
@@ -2219,14 +2226,15 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   if (s_abort) return;
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], 1);
+      mbar_init(&bars.cb_full[i], 1); mbar_init(&bars.cb_empty[i], SPLIT ? 2 : 1);
+      mbar_init(&bars.stp_full[i], 1); mbar_init(&bars.stp_empty[i], 1);
       mbar_init(&bars.g_full[i], 1); mbar_init(&bars.g_empty[i], WS_SCALE_WARPS);
       mbar_init(&bars.in_full[i], 1); mbar_init(&bars.in_empty[i], 1 + WS_EPI_WARPS);
       mbar_init(&bars.m_full[i], WS_SCALE_WARPS); mbar_init(&bars.m_empty[i], 1);
     }
     for (int i = 0; i < 4; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], WS_SCALE_WARPS + WS_EPI_WARPS); }
     mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 1);
-    mbar_init(&bars.acc_full, 1); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
+    mbar_init(&bars.acc_full, SPLIT ? 2 : 1); mbar_init(&bars.acc_empty, WS_EPI_WARPS);
     mbar_init(&bars.done, 1);
     mbar_fence_init();
   }
@@ -2260,12 +2268,15 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       auto load_cb = [&](int t) {
         int b, grp, c;
         tile_coords(t, b, grp, c);
-        const int cs_ = t & 1;
-        w.wait(&bars.cb_empty[cs_], ((t >> 1) & 1) ^ 1, 41);
+        const int cs_ = t % NCBS;
+        w.wait(&bars.cb_empty[cs_], ((t / NCBS) & 1) ^ 1, 41);
         uint8_t* dst = sCB + cs_ * Cfg::CB_BYTES;
         mbar_expect_tx(&bars.cb_full[cs_], Cfg::CB_BYTES);
-        tma_load_3d(dst, &tmC, grp * N, c * QT, b, &bars.cb_full[cs_]);
-        tma_load_3d(dst + BOX_BYTES, &tmB, grp * N, c * QT, b, &bars.cb_full[cs_]);
+#pragma unroll
+        for (int j = 0; j < NB64; ++j) {
+          tma_load_3d(dst + j * BOX_BYTES, &tmC, grp * N + 64 * j, c * QT, b, &bars.cb_full[cs_]);
+          tma_load_3d(dst + (NB64 + j) * BOX_BYTES, &tmB, grp * N + 64 * j, c * QT, b, &bars.cb_full[cs_]);
+        }
       };
       const int total_blocks = my_tiles * nblk;
       auto load_tab = [&](int kg) {
@@ -2293,11 +2304,61 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
           mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
           tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
           tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
-          w.wait(&bars.st_empty, (kb & 1) ^ 1, 50);
-          mbar_expect_tx(&bars.st_full, Cfg::ST_BYTES);
-          tma_load_3d(sSt, &tmS, 0, h0 * P, b * g.nc + c, &bars.st_full);
-          tma_load_3d(sSt + SBOX_BYTES, &tmDS, 0, h0 * P, b * g.nc + c, &bars.st_full);
-          if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+          if constexpr (!SPLIT) {
+            w.wait(&bars.st_empty, (kb & 1) ^ 1, 50);
+            mbar_expect_tx(&bars.st_full, Cfg::ST_BYTES);
+            tma_load_3d(sSt, &tmS, 0, h0 * P, b * g.nc + c, &bars.st_full);
+            tma_load_3d(sSt + SBOX_BYTES, &tmDS, 0, h0 * P, b * g.nc + c, &bars.st_full);
+            if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
+          }
+        }
+        if (SPLIT && t + 1 < my_tiles) load_cb(t + 1);   // one C/B slot: after the tile's last block
+      }
+    }
+  } else if (SPLIT && warp == 19) {
+    // ------------------------------------------------------------------ dstate 128: producer of the state pieces
+    // piece p of a head block: 0,1 = the two 64-column halves of S_prev, 2,3 = those of dS_end; piece q = 4 kb + p uses
+    // ring slot q & 1 for the (q >> 1)-th time
+    if (lane == 0) {
+      int q = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        int b, grp, c;
+        tile_coords(t, b, grp, c);
+        for (int blk = 0; blk < nblk; ++blk) {
+          const int h0 = grp * g.hpg + blk * HB;
+          for (int p = 0; p < 4; ++p, ++q) {
+            const int slot = q & 1;
+            w.wait(&bars.stp_empty[slot], ((q >> 1) & 1) ^ 1, 60);
+            mbar_expect_tx(&bars.stp_full[slot], SBOX_BYTES);
+            tma_load_3d(sSt + slot * SBOX_BYTES, p < 2 ? &tmS : &tmDS, 64 * (p & 1), h0 * P, b * g.nc + c, &bars.stp_full[slot]);
+          }
+        }
+      }
+    }
+  } else if (SPLIT && warp == 18) {
+    // ------------------------------------------------------------------ dstate 128: issuer of the state products
+    if (lane == 0) {
+      const uint32_t idO = make_idesc(128, 64, 0, 0);
+      const uint32_t tmYo_ = tm + 320, tmUo_ = tm + 448;
+      int kb = 0, q = 0;
+      for (int t = 0; t < my_tiles; ++t) {
+        w.wait(&bars.cb_full[0], t & 1, 61);
+        const uint32_t ct = smem_u32(sCB);
+        for (int blk = 0; blk < nblk; ++blk, ++kb) {
+          w.wait(&bars.acc_empty, (kb & 1) ^ 1, 62);
+          for (int p = 0; p < 4; ++p, ++q) {
+            const int slot = q & 1;
+            w.wait(&bars.stp_full[slot], (q >> 1) & 1, 63);
+            tc_fence_after();
+            // C boxes 0,1 then B boxes 0,1 lie one after the other in the C/B slot: piece p multiplies box p
+            const uint64_t dA = desc_sw128_k(ct + p * BOX_BYTES, 0), dS = desc_sw128_k(smem_u32(sSt + slot * SBOX_BYTES), 0);
+#pragma unroll 1
+            for (int ks = 0; ks < 4; ++ks)
+              mma_bf16(p < 2 ? tmYo_ : tmUo_, desc_adv(dA, ks * 32), desc_adv(dS, ks * 32), idO, ((p & 1) | ks) > 0);
+            mma_commit(&bars.stp_empty[slot]);
+          }
+          if (blk == nblk - 1) mma_commit(&bars.cb_empty[0]);
+          mma_commit(&bars.acc_full);
         }
       }
     }
@@ -2307,27 +2368,30 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
       const uint32_t idG = make_idesc(128, 128, 0, 0);
       const uint32_t idY = make_idesc(128, P, 0, 1), idU = make_idesc(128, P, 1, 1), idO = make_idesc(128, 64, 0, 0);
       auto issue_g = [&](int t) {
-        const int s_ = t & 1;
-        w.wait(&bars.cb_full[s_], (t >> 1) & 1, 43);
-        w.wait(&bars.g_empty[s_], ((t >> 1) & 1) ^ 1, 44);
+        const int s_ = t % NCBS;
+        w.wait(&bars.cb_full[s_], (t / NCBS) & 1, 43);
+        w.wait(&bars.g_empty[s_], ((t / NCBS) & 1) ^ 1, 44);
         tc_fence_after();
         const uint32_t ct = smem_u32(sCB + s_ * Cfg::CB_BYTES);
-        const uint64_t dc = desc_sw128_k(ct, 0), db = desc_sw128_k(ct + BOX_BYTES, 0);
+#pragma unroll 1
+        for (int j = 0; j < NB64; ++j) {
+          const uint64_t dc = desc_sw128_k(ct + j * BOX_BYTES, 0), db = desc_sw128_k(ct + (NB64 + j) * BOX_BYTES, 0);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, ks > 0);
+          for (int ks = 0; ks < 4; ++ks) mma_bf16(tm + s_ * 128, desc_adv(dc, ks * 32), desc_adv(db, ks * 32), idG, (j | ks) > 0);
+        }
         mma_commit(&bars.g_full[s_]);
       };
       issue_g(0);
       const uint64_t dS0 = desc_sw128_k(smem_u32(sSt), 0), dDS0 = desc_sw128_k(smem_u32(sSt + SBOX_BYTES), 0);
       int kb = 0, kh = 0;
       for (int t = 0; t < my_tiles; ++t) {
-        const uint32_t ct = smem_u32(sCB + (t & 1) * Cfg::CB_BYTES);
+        const uint32_t ct = smem_u32(sCB + (t % NCBS) * Cfg::CB_BYTES);
         const uint64_t dC0 = desc_sw128_k(ct, 0), dB0 = desc_sw128_k(ct + BOX_BYTES, 0);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           const int ib = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
           w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
-          w.wait(&bars.st_full, kb & 1, 57);
+          if (!SPLIT) w.wait(&bars.st_full, kb & 1, 57);
           w.wait(&bars.acc_empty, (kb & 1) ^ 1, 46);
           for (int hl = 0; hl < HB; ++hl, ++kh) {
             const int ms = kh % NM;
@@ -2341,7 +2405,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
               mma_bf16(tmYd + hl * P, desc_adv(dMk, ks * 4096), desc_adv(dX0, ks * 2048), idY, ks > 0);
               mma_bf16(tmUd + hl * P, desc_adv(dMt, ks * 256), desc_adv(dY0, ks * 2048), idU, ks > 0);
             }
-            if (hl == 0) {
+            if (!SPLIT && hl == 0) {
 #pragma unroll
               for (int ks = 0; ks < 4; ++ks) {
                 mma_bf16(tmYo, desc_adv(dC0, ks * 32), desc_adv(dS0, ks * 32), idO, ks > 0);
@@ -2352,10 +2416,11 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
             mma_commit(&bars.m_empty[ms]);
           }
           mma_commit(&bars.in_empty[ib]);
-          if (blk == nblk - 1) mma_commit(&bars.cb_empty[t & 1]);
+          if (blk == nblk - 1) mma_commit(&bars.cb_empty[t % NCBS]);
           mma_commit(&bars.acc_full);
-          if (blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
+          if (!SPLIT && blk == 0 && t + 1 < my_tiles) issue_g(t + 1);
         }
+        if (SPLIT && t + 1 < my_tiles) issue_g(t + 1);
       }
       mma_commit(&bars.done);
       w.wait(&bars.done, 0, 48);
@@ -2366,8 +2431,8 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
     const int row = tid & 127, part = tid >> 7;
     int kb = 0, kh = 0;
     for (int t = 0; t < my_tiles; ++t) {
-      const int gs = t & 1;
-      w.wait(&bars.g_full[gs], (t >> 1) & 1, 51);
+      const int gs = t % NCBS;
+      w.wait(&bars.g_full[gs], (t / NCBS) & 1, 51);
       tc_fence_after();
       for (int blk = 0; blk < nblk; ++blk, ++kb) {
         const int ts = kb % Cfg::NT;
@@ -3100,11 +3165,11 @@ int launch_scan(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const Sca
   return SSD_OK;
 }
 
-template <int P>
+template <int P, int N = 64>
 int launch_bwd_ws(const Geo& g, const SeqMaps& m, const float* tab, const float* D, void* dx, float* dcsp, float* ddot,
                   float* ddtd, int* status, cudaStream_t s) {
-  auto k = k_bwd_ws<P>;
-  constexpr size_t sm = BwCfg<P>::SMEM;
+  auto k = k_bwd_ws<P, N>;
+  constexpr size_t sm = BwCfg<P, N>::SMEM;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int ntiles = g.B * g.G * g.nc;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
@@ -3321,9 +3386,13 @@ int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const
   SeqMaps m;
   int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, prev_bf, ds_bf, &m);
   if (rc) return rc;
-  if (g.N == 128) {   // one tile per CTA
+  if (g.N == 128 && g.onetile) {   // one tile per CTA
     if (g.P == 32) return launch_bwd_tc<32, 128>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
     return launch_bwd_tc<64, 128>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
+  }
+  if (g.N == 128) {
+    if (g.P == 32) return launch_bwd_ws<32, 128>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
+    return launch_bwd_ws<64, 128>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
   }
   if (g.P == 32) return launch_bwd_ws<32>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
   return launch_bwd_ws<64>(g, m, tab, p.D, p.dx, dcsp, ddot, ddtd, status, s);
