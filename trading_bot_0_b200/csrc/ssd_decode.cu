@@ -30,7 +30,7 @@ template <> struct Vec4Load<__nv_bfloat16> {
 // One block per (stream, head).  N is a power of two in [16, 256].
 //   LPR = lanes that share a state row, V = float4 pieces per lane per row, RPW = rows per warp.
 template <typename T, int N>
-__global__ void __launch_bounds__(DEC_THREADS) k_state_update(SsdStepDims d, SsdStepPtrs p) {
+__global__ void __launch_bounds__(DEC_THREADS, 8) k_state_update(SsdStepDims d, SsdStepPtrs p) {
   constexpr int LPR = (N / 4 < 32) ? N / 4 : 32;
   constexpr int V = N / (4 * LPR);
   constexpr int RPW = 32 / LPR;
