@@ -27,6 +27,9 @@ template <> struct Vec4Load<__nv_bfloat16> {
   }
 };
 
+__device__ __forceinline__ float ldf_shared(const float* p) { return *p; }
+__device__ __forceinline__ float ldf_shared(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
 // One block per (stream, head).  N is a power of two in [16, 256].
 //   LPR = lanes that share a state row, V = float4 pieces per lane per row, RPW = rows per warp.
 template <typename T, int N>
@@ -119,6 +122,125 @@ __global__ void __launch_bounds__(DEC_THREADS, 8) k_state_update(SsdStepDims d, 
   }
 }
 
+// The same update with the state staged through shared memory: a persistent block walks (stream, head) items and keeps
+// the next DEC_STAGES - 1 items' state (and their x, B, C vectors) on the way with 16-byte cp.async copies, so the bytes in
+// flight per SM are set by the ring (7 blocks x 3 items x 8 KB at headdim 32, dstate 64), not by the registers a thread can
+// hold.  The step size of the next item is fetched one item ahead.  Layout of a ring slot: the item's state as it lies in
+// global memory, then x, B, C.  R = state rows per thread (headdim = R * rows per block pass).
+constexpr int DEC_STAGES = 4;
+
+template <typename T, int N, int R>
+__global__ void __launch_bounds__(DEC_THREADS) k_state_update_ring(SsdStepDims d, SsdStepPtrs p, long long items) {
+  constexpr int LPR = (N / 4 < 32) ? N / 4 : 32;
+  constexpr int V = N / (4 * LPR);
+  constexpr int RPW = 32 / LPR;
+  constexpr int RPB = RPW * (DEC_THREADS / 32);
+  constexpr int P = R * RPB;
+  constexpr int ES = (int)sizeof(T);
+  constexpr int ST_B = P * N * 4, X_B = P * ES, BC_B = N * ES;
+  constexpr int STAGE = ST_B + X_B + 2 * BC_B;
+  constexpr int NXP = X_B / 16, NBP = BC_B / 16;   // 16-byte pieces of x and of B (C); the host checked the divisibility
+  extern __shared__ __align__(16) unsigned char dec_ring[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lir = lane % LPR, riw = lane / LPR;
+  const int H = d.nheads, hpg = d.nheads / d.ngroups;
+  const int row0 = warp * RPW + riw;
+
+  auto issue = [&](long long it, int stage) {
+    if (it < items) {
+      const long long s = it / H;
+      const int h = (int)(it - s * H);
+      unsigned char* sm = dec_ring + stage * STAGE;
+      const float* gst = p.state + it * (long long)(P * N);
+#pragma unroll
+      for (int u = 0; u < R; ++u)
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          const int off = (row0 + u * RPB) * N + 4 * (lir + v * LPR);
+          cp_async16(sm + off * 4, gst + off, true);
+        }
+      const int t = threadIdx.x;
+      if (t < NXP) cp_async16(sm + ST_B + t * 16, (const char*)((const T*)p.x + s * d.x_stride_s + (long long)h * P) + t * 16, true);
+      else if (t < NXP + NBP)
+        cp_async16(sm + ST_B + X_B + (t - NXP) * 16, (const char*)((const T*)p.Bm + s * d.b_stride_s + (long long)(h / hpg) * N) + (t - NXP) * 16, true);
+      else if (t < NXP + 2 * NBP)
+        cp_async16(sm + ST_B + X_B + BC_B + (t - NXP - NBP) * 16,
+                   (const char*)((const T*)p.Cm + s * d.c_stride_s + (long long)(h / hpg) * N) + (t - NXP - NBP) * 16, true);
+    }
+    cp_async_commit();   // a group per slot even when it is empty: the wait counts groups
+  };
+  auto load_dt = [&](long long it) -> float {
+    if (it >= items) return 0.f;
+    const long long s = it / H;
+    return ldf((const T*)p.dt + s * d.dt_stride_s + (it - s * H));
+  };
+
+  const long long first = blockIdx.x, stride = gridDim.x;
+#pragma unroll
+  for (int k = 0; k < DEC_STAGES - 1; ++k) issue(first + k * stride, k);
+  float dt_next = load_dt(first);
+  int stage = 0;
+  for (long long it = first; it < items; it += stride) {
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncthreads();     // every thread's pieces of this item have landed; every thread is done with the previous slot
+    issue(it + (DEC_STAGES - 1) * stride, stage == 0 ? DEC_STAGES - 1 : stage - 1);
+    const float dt_raw = dt_next;
+    dt_next = load_dt(it + stride);
+    const long long s = it / H;
+    const int h = (int)(it - s * H);
+    const unsigned char* sm = dec_ring + stage * STAGE;
+    stage = stage + 1 == DEC_STAGES ? 0 : stage + 1;
+    const float dtv = dt_activation(dt_raw, p.dt_bias ? __ldg(p.dt_bias + h) : 0.f, d.dt_softplus);
+    const float a = expf(dtv * __ldg(p.A + h));
+    const float Dh = p.D ? __ldg(p.D + h) : 0.f;
+    const T* sx = reinterpret_cast<const T*>(sm + ST_B);
+    const T* sB = reinterpret_cast<const T*>(sm + ST_B + X_B);
+    const T* sC = reinterpret_cast<const T*>(sm + ST_B + X_B + BC_B);
+    float Bv[V][4], Cv[V][4];
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        Bv[v][j] = ldf_shared(sB + 4 * (lir + v * LPR) + j);
+        Cv[v][j] = ldf_shared(sC + 4 * (lir + v * LPR) + j);
+      }
+    float* gst = p.state + it * (long long)(P * N);
+    const T* zs = p.z ? (const T*)p.z + s * d.z_stride_s + (long long)h * P : nullptr;
+    T* ys = (T*)p.y + s * d.y_stride_s + (long long)h * P;
+#pragma unroll
+    for (int u = 0; u < R; ++u) {
+      const int pr = row0 + u * RPB;
+      const float xv = ldf_shared(sx + pr), dx = dtv * xv;
+      float acc = 0.f;
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        const int off = pr * N + 4 * (lir + v * LPR);
+        float4 t = *reinterpret_cast<const float4*>(sm + off * 4);
+        t.x = fmaf(a, t.x, dx * Bv[v][0]);
+        t.y = fmaf(a, t.y, dx * Bv[v][1]);
+        t.z = fmaf(a, t.z, dx * Bv[v][2]);
+        t.w = fmaf(a, t.w, dx * Bv[v][3]);
+        *reinterpret_cast<float4*>(gst + off) = t;
+        acc = fmaf(t.x, Cv[v][0], acc);
+        acc = fmaf(t.y, Cv[v][1], acc);
+        acc = fmaf(t.z, Cv[v][2], acc);
+        acc = fmaf(t.w, Cv[v][3], acc);
+      }
+#pragma unroll
+      for (int o = LPR / 2; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lir == 0) {
+        float yv = acc + Dh * xv;
+        if (zs) {
+          const float zv = ldf(zs + pr);
+          yv *= zv * sigmoidf_(zv);
+        }
+        stf(ys + pr, yv);
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // Any other dstate: one warp per state row, lanes stride over n.
 template <typename T>
 __global__ void __launch_bounds__(DEC_THREADS) k_state_update_generic(SsdStepDims d, SsdStepPtrs p) {
@@ -197,9 +319,37 @@ __global__ void k_sp_prefix(const float* __restrict__ gs, const float* __restric
 
 }  // namespace
 
+// The ring kernel covers the shapes whose item (headdim x dstate fp32) is 8 KB at 4 or 8 rows per thread, with x / B / C
+// rows that are whole, 16-byte aligned pieces; everything else takes the register kernels.
+template <typename T, int N, int R>
+static bool launch_ring(const SsdStepDims& d, const SsdStepPtrs& p, cudaStream_t s) {
+  constexpr int LPR = (N / 4 < 32) ? N / 4 : 32, RPB = (32 / LPR) * (DEC_THREADS / 32), P = R * RPB, ES = (int)sizeof(T);
+  constexpr int STAGE = P * N * 4 + P * ES + 2 * N * ES;
+  if (d.headdim != P || (P * ES) % 16 || (N * ES) % 16) return false;
+  auto al = [&](const void* q, long long stride) { return ((uintptr_t)q % 16) == 0 && (stride * ES) % 16 == 0; };
+  if (!al(p.x, d.x_stride_s) || !al(p.Bm, d.b_stride_s) || !al(p.Cm, d.c_stride_s) || ((uintptr_t)p.state % 16)) return false;
+  const long long items = (long long)d.streams * d.nheads;
+  constexpr int smem = DEC_STAGES * STAGE;
+  auto k = k_state_update_ring<T, N, R>;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int per_sm = (227 * 1024) / (smem + 1024) < 8 ? (227 * 1024) / (smem + 1024) : 8;
+  long long grid = (long long)sms * (per_sm > 0 ? per_sm : 1);
+  if (grid > items) grid = items;
+  k<<<(unsigned)grid, DEC_THREADS, smem, s>>>(d, p, items);
+  return true;
+}
+
 template <typename T>
 static int decode_t(const SsdStepDims& d, const SsdStepPtrs& p, cudaStream_t s) {
   const unsigned blocks = (unsigned)((long long)d.streams * d.nheads);
+  if (d.dstate == 64 && d.headdim == 32 && launch_ring<T, 64, 4>(d, p, s)) {
+    SSD_CUDA_CHECK_LAUNCH("state_update");
+    return SSD_OK;
+  }
   switch (d.dstate) {
     case 16: k_state_update<T, 16><<<blocks, DEC_THREADS, 0, s>>>(d, p); break;
     case 32: k_state_update<T, 32><<<blocks, DEC_THREADS, 0, s>>>(d, p); break;

@@ -55,7 +55,6 @@ __device__ __forceinline__ void load_raw(const float* p, RawN<float, 8>& r) {
 }
 __device__ __forceinline__ void load_raw(const float* p, RawN<float, 4>& r) { r.a = __ldg(reinterpret_cast<const float4*>(p)); }
 template <> struct RawN<float, 2> { float2 a; };
-__device__ __forceinline__ void unpack_raw(const RawN<float, 2>& r, float (&v)[2]) { v[0] = r.a.x; v[1] = r.a.y; }
 __device__ __forceinline__ void store_n(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
 __device__ __forceinline__ float2 bf2_(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w)); }
 __device__ __forceinline__ void unpack_raw(const RawN<__nv_bfloat16, 8>& r, float (&v)[8]) {
@@ -200,14 +199,6 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const 
 // 16-byte pieces of the tiles two and three ahead with cp.async (rows before the sequence start and channels past the
 // end are zero-filled by the copy itself), so the bytes in flight per SM are set by the ring, not by registers.
 // Thread = (16-byte channel vector, 4 consecutive tokens): K-1+4 row reads from shared memory, 4 row stores.
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  const int n = valid ? 16 : 0;   // src-size 0: the 16 bytes are written as zeros, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 constexpr int CONVS_THREADS = 256;
 constexpr int CONVS_TT = 64;        // tokens per tile
 constexpr int CONVS_ROWB = 256;     // bytes of channels per tile row
@@ -460,14 +451,6 @@ __global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdCon
 //   2. thread = (8 bytes of channels, 8 consecutive tokens): din from a sliding window over the dpre tile.
 // The tile carries K-1 halo rows on either side (zero-filled outside the sequence), so no row is recomputed in
 // registers and nothing is re-read from global memory but the halo.  A CTA leaves one partial weight-gradient row.
-__device__ __forceinline__ void ldf_vec(const float* p, float (&v)[4]) {
-  const float4 a = *reinterpret_cast<const float4*>(p);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-}
-__device__ __forceinline__ void ldf_vec(const float* p, float (&v)[2]) {
-  const float2 a = *reinterpret_cast<const float2*>(p);
-  v[0] = a.x; v[1] = a.y;
-}
 constexpr int CONVB_STAGES = 2;
 constexpr int CONVB_CTAS_PER_SM = 2;
 
