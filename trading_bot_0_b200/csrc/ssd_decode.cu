@@ -124,10 +124,11 @@ __global__ void __launch_bounds__(DEC_THREADS, 8) k_state_update(SsdStepDims d, 
 
 // The same update with the state staged through shared memory: a persistent block walks (stream, head) items and keeps
 // the next DEC_STAGES - 1 items' state (and their x, B, C vectors) on the way with 16-byte cp.async copies, so the bytes in
-// flight per SM are set by the ring (7 blocks x 3 items x 8 KB at headdim 32, dstate 64), not by the registers a thread can
-// hold.  The step size of the next item is fetched one item ahead.  Layout of a ring slot: the item's state as it lies in
+// flight per SM are set by the ring (8 blocks x 2 items x 8 KB at headdim 32, dstate 64), not by the registers a thread can
+// hold.  Measured at 8192 streams x 8 heads: 2 stages (12 blocks per SM) 0.213 ms, 3 stages (8 blocks) 0.175 ms, 4 stages
+// (6 blocks) 0.193 ms, 6 stages (4 blocks) 0.223 ms; the register kernel 0.205 ms.  The step size of the next item is fetched one item ahead.  Layout of a ring slot: the item's state as it lies in
 // global memory, then x, B, C.  R = state rows per thread (headdim = R * rows per block pass).
-constexpr int DEC_STAGES = 4;
+constexpr int DEC_STAGES = 3;
 
 template <typename T, int N, int R>
 __global__ void __launch_bounds__(DEC_THREADS) k_state_update_ring(SsdStepDims d, SsdStepPtrs p, long long items) {
@@ -336,7 +337,7 @@ static bool launch_ring(const SsdStepDims& d, const SsdStepPtrs& p, cudaStream_t
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int per_sm = (227 * 1024) / (smem + 1024) < 8 ? (227 * 1024) / (smem + 1024) : 8;
+  const int per_sm = (227 * 1024) / (smem + 1024) < 16 ? (227 * 1024) / (smem + 1024) : 16;
   long long grid = (long long)sms * (per_sm > 0 ? per_sm : 1);
   if (grid > items) grid = items;
   k<<<(unsigned)grid, DEC_THREADS, smem, s>>>(d, p, items);
