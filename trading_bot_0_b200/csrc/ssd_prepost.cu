@@ -805,6 +805,138 @@ __global__ void __launch_bounds__(NORM_THREADS) k_rmsnorm_bwd(SsdNormDims d, con
   }
 }
 
+// RMS norm backward, rows staged through shared memory: every WARP walks pairs of rows with a cp.async ring of its own
+// (three stages of {two rows of in, two rows of dout}), so nothing but the warp's own copies has to be waited for and the
+// bytes in flight are set by the ring and the number of resident warps (6 KB per warp at 256 bf16 features, eight blocks
+// per SM) instead of by registers.  Same arithmetic and the same per-block dweight partial as k_rmsnorm_bwd.
+constexpr int NORMR_ROWS = 2, NORMR_STAGES = 3;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(NORM_THREADS, 8) k_rmsnorm_bwd_ring(SsdNormDims d, const T* __restrict__ in,
+                                                                      const float* __restrict__ weight, const float* __restrict__ rstd,
+                                                                      const T* __restrict__ dout, long long dout_stride_row,
+                                                                      T* __restrict__ din, long long din_stride_row,
+                                                                      float* __restrict__ partial) {
+  constexpr int ES = (int)sizeof(T), RW = NORMR_ROWS, S = NORMR_STAGES;
+  extern __shared__ __align__(16) unsigned char norm_ring[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nv = d.width / 8;
+  const int row_bytes = d.width * ES, ppr = row_bytes / 16;      // 16-byte pieces per row
+  const int stage_bytes = 2 * RW * row_bytes;
+  unsigned char* wring = norm_ring + warp * (S * stage_bytes);
+  float wv[NV][8], dwv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int vi = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { wv[i][j] = 1.f; dwv[i][j] = 0.f; }
+    if (weight && vi < nv) load8<float>(weight + vi * 8, wv[i]);
+  }
+  const long long nitems = (d.rows + RW - 1) / RW;
+  const long long first = (long long)blockIdx.x * (NORM_THREADS / 32) + warp, stride = (long long)gridDim.x * (NORM_THREADS / 32);
+  auto issue = [&](long long it, int stage) {
+    if (it < nitems) {
+      unsigned char* sm = wring + stage * stage_bytes;
+#pragma unroll
+      for (int u = 0; u < RW; ++u) {
+        const long long row = it * RW + u;
+        const bool ok = row < d.rows;
+        const char* gi = (const char*)(in + (ok ? row : 0) * d.in_stride_row);
+        const char* go = (const char*)(dout + (ok ? row : 0) * dout_stride_row);
+        for (int c = lane; c < ppr; c += 32) {
+          cp_async16(sm + u * row_bytes + c * 16, gi + c * 16, ok);
+          cp_async16(sm + (RW + u) * row_bytes + c * 16, go + c * 16, ok);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  auto load_rstd = [&](long long it, float (&r)[RW]) {
+#pragma unroll
+    for (int u = 0; u < RW; ++u) {
+      const long long row = it * RW + u;
+      r[u] = (it < nitems && row < d.rows) ? __ldg(rstd + row) : 0.f;
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < S - 1; ++k) issue(first + k * stride, k);
+  float rs_next[RW];
+  load_rstd(first, rs_next);
+  int stage = 0;
+  for (long long it = first; it < nitems; it += stride) {
+    cp_async_wait<S - 2>();
+    __syncwarp();          // the warp's own copies of this item have landed; its lanes are done with the previous slot
+    issue(it + (S - 1) * stride, stage == 0 ? S - 1 : stage - 1);
+    float rs_[RW];
+#pragma unroll
+    for (int u = 0; u < RW; ++u) rs_[u] = rs_next[u];
+    load_rstd(it + stride, rs_next);
+    const unsigned char* sm = wring + stage * stage_bytes;
+    stage = stage + 1 == S ? 0 : stage + 1;
+#pragma unroll
+    for (int u = 0; u < RW; ++u) {
+      const long long row = it * RW + u;
+      if (row >= d.rows) break;      // warp-uniform
+      const float r = rs_[u];
+      float n[NV][8], dn[NV][8];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nv) {
+          float x[8], g[8];
+          RawN<T, 8> rx, rg;
+          lds_raw<T, 8>(sm + u * row_bytes + vi * 8 * ES, rx);
+          lds_raw<T, 8>(sm + (RW + u) * row_bytes + vi * 8 * ES, rg);
+          unpack_raw(rx, x);
+          unpack_raw(rg, g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            n[i][j] = x[j] * r;
+            dn[i][j] = g[j] * wv[i][j];
+            dwv[i][j] = fmaf(g[j], n[i][j], dwv[i][j]);
+            dot = fmaf(dn[i][j], n[i][j], dot);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float m = dot / (float)d.width;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int vi = lane + 32 * i;
+        if (vi < nv) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = r * (dn[i][j] - n[i][j] * m);
+          store8<T>(din + row * din_stride_row + vi * 8, o);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  if (!partial) return;
+  // the four warps of the block add their weight-gradient rows in warp order, through shared memory
+  __shared__ float sred[NORM_THREADS / 32][32 * 8 + 1];
+  for (int i = 0; i < NV; ++i) {   // block-uniform trip count
+    if (i * 32 >= nv) break;
+    const int vi = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sred[warp][lane * 8 + j] = dwv[i][j];
+    __syncthreads();
+    if (warp == 0 && vi < nv) {
+      float* pp = partial + (size_t)blockIdx.x * d.width + vi * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float a = 0.f;
+        for (int ww = 0; ww < NORM_THREADS / 32; ++ww) a += sred[ww][lane * 8 + j];
+        pp[j] = a;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // dweight[i] = sum over blocks of the partials: eight row groups per column add their rows in order, then the groups
 // are added in order (the same sum for the same grid, whatever the timing)
 __global__ void k_norm_reduce(int nblk, int width, const float* __restrict__ partial, float* __restrict__ dweight) {
@@ -830,7 +962,7 @@ int conv_rows(const SsdConvDims* d) {   // thread rows of the backward kernel = 
 }
 int norm_blocks(const SsdNormDims* d) {
   const long long need = (d->rows + NORM_THREADS / 32 - 1) / (NORM_THREADS / 32);
-  return (int)(need < 592 ? need : 592);
+  return (int)(need < 1184 ? need : 1184);
 }
 
 int check_conv(const SsdConvDims* d) {
@@ -1056,7 +1188,17 @@ int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, const floa
   const int nvl = (dims->width / 8 + 31) / 32;
 #define NORM_BWD(T, NV) k_rmsnorm_bwd<T, NV><<<nblk, NORM_THREADS, 0, s>>>(*dims, (const T*)in, weight, rstd, (const T*)dout, dout_stride_row, (T*)din, din_stride_row, partial)
 #define NORM_BWD_T(T) do { if (nvl <= 1) NORM_BWD(T, 1); else if (nvl <= 2) NORM_BWD(T, 2); else if (nvl <= 4) NORM_BWD(T, 4); else NORM_BWD(T, 8); } while (0)
-  if (dims->dtype == SSD_BF16) NORM_BWD_T(__nv_bfloat16); else NORM_BWD_T(float);
+  const int row_bytes = dims->width * es;
+  const int ring_smem = (NORM_THREADS / 32) * NORMR_STAGES * 2 * NORMR_ROWS * row_bytes;
+  const bool ring = nvl <= 1 && (row_bytes % 16) == 0 && ring_smem <= 96 * 1024 && (dims->in_stride_row * es) % 16 == 0;
+  if (ring) {
+#define NORM_BWD_RING(T, NV) do { \
+      static int attr = 0; \
+      if (attr < ring_smem) { cudaFuncSetAttribute(k_rmsnorm_bwd_ring<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_smem); attr = ring_smem; } \
+      k_rmsnorm_bwd_ring<T, NV><<<nblk, NORM_THREADS, ring_smem, s>>>(*dims, (const T*)in, weight, rstd, (const T*)dout, dout_stride_row, (T*)din, din_stride_row, partial); } while (0)
+    if (dims->dtype == SSD_BF16) NORM_BWD_RING(__nv_bfloat16, 1); else NORM_BWD_RING(float, 1);
+#undef NORM_BWD_RING
+  } else if (dims->dtype == SSD_BF16) NORM_BWD_T(__nv_bfloat16); else NORM_BWD_T(float);
 #undef NORM_BWD_T
 #undef NORM_BWD
   SSD_CUDA_CHECK_LAUNCH("rmsnorm_bwd");
