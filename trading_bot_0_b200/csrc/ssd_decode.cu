@@ -332,8 +332,7 @@ static bool launch_ring(const SsdStepDims& d, const SsdStepPtrs& p, cudaStream_t
   const long long items = (long long)d.streams * d.nheads;
   constexpr int smem = DEC_STAGES * STAGE;
   auto k = k_state_update_ring<T, N, R>;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr = true; }
+  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   // per device, so at every launch
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

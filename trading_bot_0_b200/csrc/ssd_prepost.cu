@@ -1018,8 +1018,7 @@ int32_t ssd_conv1d_forward(const SsdConvDims* dims, const void* in, const float*
     const dim3 grid((unsigned)gx, (unsigned)ncb);
 #define CONV_FWD_SM(T, K) do { \
       constexpr int smem = (CONVS_TT + K - 1) * CONVS_ROWB * CONVS_STAGES; \
-      static bool attr_set = false; \
-      if (!attr_set) { cudaFuncSetAttribute(k_conv_fwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_set = true; } \
+      cudaFuncSetAttribute(k_conv_fwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       k_conv_fwd_sm<T, K><<<grid, CONVS_THREADS, smem, s>>>(*dims, (const T*)in, weight, bias, (T*)out, ntt); } while (0)
     if (dims->dtype == SSD_BF16) {
       if (dims->width == 4) CONV_FWD_SM(__nv_bfloat16, 4); else if (dims->width == 3) CONV_FWD_SM(__nv_bfloat16, 3); else CONV_FWD_SM(__nv_bfloat16, 2);
@@ -1094,8 +1093,7 @@ int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float
     const dim3 grid((unsigned)nx, (unsigned)ncb);
 #define CONV_BWD_SM(T, K) do { \
       constexpr int smem = CONVB_STAGES * (2 * CONVS_TT + 3 * (K - 1)) * CONVS_ROWB + (CONVS_TT + K - 1) * (CONVS_ROWB / (int)sizeof(T)) * 4; \
-      static bool attr_set = false; \
-      if (!attr_set) { cudaFuncSetAttribute(k_conv_bwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); attr_set = true; } \
+      cudaFuncSetAttribute(k_conv_bwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       k_conv_bwd_sm<T, K><<<grid, CONVS_THREADS, smem, s>>>(*dims, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial, ntt); } while (0)
     if (dims->dtype == SSD_BF16) {
       if (dims->width == 4) CONV_BWD_SM(__nv_bfloat16, 4); else if (dims->width == 3) CONV_BWD_SM(__nv_bfloat16, 3); else CONV_BWD_SM(__nv_bfloat16, 2);
@@ -1193,8 +1191,7 @@ int32_t ssd_rmsnorm_backward(const SsdNormDims* dims, const void* in, const floa
   const bool ring = nvl <= 1 && (row_bytes % 16) == 0 && ring_smem <= 96 * 1024 && (dims->in_stride_row * es) % 16 == 0;
   if (ring) {
 #define NORM_BWD_RING(T, NV) do { \
-      static int attr = 0; \
-      if (attr < ring_smem) { cudaFuncSetAttribute(k_rmsnorm_bwd_ring<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_smem); attr = ring_smem; } \
+      cudaFuncSetAttribute(k_rmsnorm_bwd_ring<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_smem); \
       k_rmsnorm_bwd_ring<T, NV><<<nblk, NORM_THREADS, ring_smem, s>>>(*dims, (const T*)in, weight, rstd, (const T*)dout, dout_stride_row, (T*)din, din_stride_row, partial); } while (0)
     if (dims->dtype == SSD_BF16) NORM_BWD_RING(__nv_bfloat16, 1); else NORM_BWD_RING(float, 1);
 #undef NORM_BWD_RING
