@@ -27,6 +27,13 @@ __device__ __forceinline__ float dt_activation(float raw, float bias, int softpl
   return (softplus && v <= 20.f) ? log1pf(expf(v)) : v;
 }
 
+// |sum of dt*A over a chunk| up to which exp(+-sum) stays well inside the range of bf16 / fp32 with room for the data:
+// heads within it may carry their decay on the operands of the dB/dC product.  The cumsum kernel marks the heads beyond it
+// without any zeroing pass: every launch has a tag of its own, writes it to word [H] of the `hmax` segment and to word [h]
+// for every head h whose chunk total exceeds the range; a head is "within range" iff word [h] differs from word [H].  A
+// stale or accidental match can only mark a head that did not need it (it then takes the general path): never the reverse.
+constexpr float SSD_SEP_LOG_RANGE = 64.f;
+
 // Workspace segments (offsets in bytes from the workspace base; 0-size segments unused).
 struct WsLayout {
   size_t status;                                     // 256-byte status block (int32 code first)

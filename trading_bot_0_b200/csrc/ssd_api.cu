@@ -110,7 +110,7 @@ static void make_layout(const Geo& g, bool has_z, bool tcfam, WsLayout* w) {
   w->cb = take(tcfam ? 0 : ncb);   // C B^T stays on chip in the tensor-core family
   w->tab = take(tcfam ? (size_t)g.B * g.nc * g.H * SSD_TAB_FLOATS * f : 0);
   w->prev_bf = take(tcfam ? nst / 2 : 0);
-  w->hmax = take(tcfam ? (size_t)g.H * f : 0);   // per head: largest |chunk total of dt*A| of the call
+  w->hmax = take(tcfam ? (size_t)(g.H + 1) * f : 0);   // per head: tag of the last cumsum launch that saw a strong decay; [H]: current tag
   w->total_fwd = o;
   w->dstates = take(nst);
   w->ds_bf = take(tcfam ? nst / 2 : 0);

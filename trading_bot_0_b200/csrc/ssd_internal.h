@@ -34,7 +34,8 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
 bool tensor_bwd_merged_applies(const Geo& g, const SsdBwdPtrs& p);
 int tensor_bwd_merged(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, const void* ds_bf,
                       float* dcsp, float* ddot, float* ddtd, int* status, cudaStream_t s);
-// `hmax` [H]: per head, the largest |sum of dt*A over a chunk| of the call (written by the cumsum kernel)
+// `hmax` [H + 1] int32 tags written by the cumsum kernel: head h decays beyond SSD_SEP_LOG_RANGE inside some chunk iff
+// word [h] equals word [H]
 int tensor_dbc(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense, const float* tab, const float* hmax,
                const void* prev_bf, const void* ds_bf, int* status, cudaStream_t s);
 

@@ -6,6 +6,7 @@
 // All contractions share one tile routine: a 256-thread block accumulates a 64x64 output tile,
 // 4x4 per thread, staging 16-deep slabs of both operands in shared memory through element
 // functors, so a stage is defined by "what is A(m,k), what is B(n,k), what does the epilogue do".
+#include <atomic>
 #include "common.cuh"
 #include "ssd_internal.h"
 
@@ -90,11 +91,13 @@ struct DySrc {
 template <typename T>
 __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, const float* __restrict__ dt_bias,
                                                const float* __restrict__ A, float* __restrict__ cs,
-                                               float* __restrict__ dtf, float* __restrict__ tab, float* __restrict__ hmax) {
+                                               float* __restrict__ dtf, float* __restrict__ tab, int* __restrict__ hmax,
+                                               int tag) {
   constexpr int HG = 8;
   const int c = blockIdx.x, b = blockIdx.y, q = threadIdx.x;
   __shared__ float wsum[NT / 32][HG];
   const int t = c * g.Q + q;
+  if (hmax && c == 0 && b == 0 && q == 0) hmax[g.H] = tag;
   const bool live = (q < g.Q) && (t < g.L);
   const int lane = q & 31, w = q >> 5;
   const T* row = dt + b * g.dtsb + (long long)t * g.dtsl;
@@ -137,12 +140,10 @@ __global__ void __launch_bounds__(NT) k_cumsum(Geo g, const T* __restrict__ dt, 
         // tensor-core family (chunk 128 only): the per-head decay table [cs*log2e | dt | exp(cs_r - cs) dt |
         // exp(dt_{l+1} A)], r = last position of the 32-block (lane 31 of this warp)
         const float vend = __shfl_sync(0xffffffffu, v[k], 31);
-        // per head, the largest decay exponent any chunk of the call accumulates (non-negative floats order like ints)
-        // (the word only grows, so a plain read that already shows a larger value makes the atomic unnecessary)
-        if (hmax && h < g.H && q == g.Q - 1) {
-          const int bits = __float_as_int(fabsf(v[k]));
-          if (bits > *reinterpret_cast<volatile int*>(hmax + h)) atomicMax(reinterpret_cast<int*>(hmax) + h, bits);
-        }
+        // per head: does any chunk of the call accumulate a decay exponent beyond the range inside which dB/dC may carry the
+        // decay on the operands?  Only then this launch's tag is written to the head's word (plain store), so the usual case
+        // costs nothing and nothing has to be zeroed.
+        if (hmax && h < g.H && q == g.Q - 1 && fabsf(v[k]) > SSD_SEP_LOG_RANGE) hmax[h] = tag;
         if (tab && h < g.H && q < g.Q) {
           const float L2E = 1.4426950408889634f;
           float* t = tab + ((size_t)(b * g.nc + c) * g.H + h) * SSD_TAB_FLOATS + q;
@@ -751,9 +752,11 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   const bool fused = tc && stages == (SSD_STAGE_LOCAL | SSD_STAGE_FINISH) && tensor_state_fused_applies(g);
   if (stages & (SSD_STAGE_LOCAL | SSD_STAGE_LOCAL_STATES)) {
     cudaMemsetAsync(status, 0, 256, s);
-    float* hmax = tc ? (float*)(ws + w.hmax) : nullptr;
-    if (tc) cudaMemsetAsync(hmax, 0, (size_t)g.H * sizeof(float), s);
-    k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr, hmax);
+    int* hmax = tc ? (int*)(ws + w.hmax) : nullptr;
+    static std::atomic<int> launch_tag{1};
+    int tag = launch_tag.fetch_add(1, std::memory_order_relaxed);
+    if (tag == 0) tag = launch_tag.fetch_add(1, std::memory_order_relaxed);
+    k_cumsum<T><<<dim3(g.nc, g.B), g.Q <= 128 ? 128 : NT, 0, s>>>(g, (const T*)p.dt, p.dt_bias, p.A, cs, dtf, tc ? tab : nullptr, hmax, tag);
     SSD_CUDA_CHECK_LAUNCH("cumsum");
     if (tc && fused) {
       // chunk states and the scan over chunks run as one kernel in the FINISH stage

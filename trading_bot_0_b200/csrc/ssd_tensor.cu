@@ -2573,7 +2573,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // With the per-head pass gone for most heads a tile is a short chain of scale -> multiply steps, and what bounds the kernel
 // is how far the loads run ahead of it: the x/dy boxes have a ring of three, the state boxes of two, the tables of four;
 // the B/C tiles (read at the END of a tile by the separable path) and the W' tile are single.
-constexpr float SEP_LOG_RANGE = 64.f;
+constexpr float SEP_LOG_RANGE = SSD_SEP_LOG_RANGE;
 
 template <int P>
 struct DbCfg {
@@ -2645,9 +2645,12 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
   Waiter w{status, false};
   // which heads take the separable path: one bit per head, the same in every role (up to 64 heads; beyond that none)
   unsigned long long sepmask = 0ull;
-  if (hmax && g.H <= 64)
+  if (hmax && g.H <= 64) {
+    const int* tags = reinterpret_cast<const int*>(hmax);
+    const int cur = __ldg(tags + g.H);
     for (int h = 0; h < g.H; ++h)
-      if (__ldg(hmax + h) <= SEP_LOG_RANGE) sepmask |= 1ull << h;
+      if (__ldg(tags + h) != cur) sepmask |= 1ull << h;
+  }
   auto is_sep = [&](int h) { return ((sepmask >> h) & 1ull) != 0; };
   auto group_has_sep = [&](int grp) {
     const unsigned long long gm = (g.hpg >= 64 ? ~0ull : ((1ull << g.hpg) - 1ull)) << (grp * g.hpg);
