@@ -469,7 +469,7 @@ def sub_sp(c4, L_global, rank, world, local, reps, label):
     ms = time_fn(make_step(ops), reps, world, dev)
     ms_local = time_fn(make_step(_LocalOnlyOps(ops)), reps, world, dev)
     return {"workload": f"{label}: B{c4['B']} L{L_global} ({L_loc} per rank) H{c4['H']} P{c4['P']} N{c4['N']} Q{c4['Q']} fwd+bwd, "
-                        f"sequence sharded over {world} ranks, NCCL all-gather of the boundary records + prefix kernel",
+                        f"sequence sharded over {world} ranks, NCCL point-to-point exchange of the boundary records + prefix kernel",
             "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "ms_local_only": ms_local,
             "exchange_exposed_ms": ms - ms_local}
 

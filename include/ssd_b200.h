@@ -188,9 +188,9 @@ SSD_API int32_t ssd_state_reset_rows(float* state, int64_t row_elems, const int6
  *                      forward writes it to final_state, backward to dinit_state
  *   SSD_STAGE_FINISH - the scan with the true boundary state (init_state / dfinal_state) and
  *                      everything downstream of it
- * ssd_forward == stages LOCAL|FINISH.  Between TOTAL and FINISH the host gathers every rank's
- * (total state, total log-decay) record with one all-gather, and ssd_sp_prefix_state folds the
- * records of the ranks before (direction +1) or after (direction -1) this one:
+ * ssd_forward == stages LOCAL|FINISH.  Between TOTAL and FINISH every rank obtains the (total state,
+ * total log-decay) records of the ranks before (direction +1) or after (direction -1) it, and
+ * ssd_sp_prefix_state folds them:
  *   +1: acc = boundary; for q = 0 .. rank-1:          acc = exp(logdecay_q) * acc + state_q
  *   -1: acc = boundary; for q = world-1 .. rank+1:    acc = exp(logdecay_q) * acc + state_q
  * No counterpart in the reference (it is a single-GPU program with no collective anywhere).
@@ -229,9 +229,9 @@ SSD_API int32_t ssd_sp_prefix_state(const float* gathered_states, const float* g
  *   ssd_sp_comm_new    - collective over all ranks, on the current device; NULL on failure (ssd_last_error)
  *   ssd_sp_comm_wrap   - borrow an ncclComm_t the host already has (not destroyed by ssd_sp_comm_free)
  *   ssd_sp_exchange_fwd / _bwd - after the LOCAL|TOTAL stages: reads the slice's total log-decay from the chunk cumsums in
- *       `workspace`, all-gathers every rank's (slice-total state, log-decay) record into `exchange_buf` (LOCAL memory;
- *       ssd_sp_exchange_bytes gives its size; one NCCL group), and folds the records of the ranks before (fwd) / after
- *       (bwd) this one into `state_in` / `dstate_out`, which then goes to the FINISH stage as init_state / dfinal_state.
+ *       `workspace`, sends this rank's (slice-total state, log-decay) record to the ranks after (fwd) / before (bwd) it and
+ *       receives theirs from the ranks before / after it into `exchange_buf` (LOCAL memory; ssd_sp_exchange_bytes gives its
+ *       size; one NCCL group of point-to-point transfers), and folds the received records into `state_in` / `dstate_out`, which then goes to the FINISH stage as init_state / dfinal_state.
  *       `init_state` / `dfinal_state` here are the boundary of the GLOBAL sequence (same on every rank, or NULL).
  *       Everything is enqueued on `cuda_stream`.  timeout_ms == 0: return at once (legal during stream capture).
  *       timeout_ms > 0 (checked mode): a fixed-size signature of the problem goes round first and is compared on the host

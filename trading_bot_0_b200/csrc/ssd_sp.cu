@@ -3,9 +3,9 @@
 //
 // A rank that owns a contiguous slice of the sequence runs the local stages with a zero boundary
 // state, then calls ssd_sp_exchange_fwd: the slice's total log-decay is read from the chunk cumsums
-// in the workspace, every rank's (state, log-decay) record is all-gathered into a LOCAL buffer (one
-// NCCL group, two collectives), and k_sp_prefix folds the records of the ranks before this one into
-// the state entering the slice.  ssd_sp_exchange_bwd is the mirror image for the state gradient.
+// in the workspace, the (state, log-decay) records of the ranks before this one arrive in a LOCAL buffer
+// (one NCCL group of point-to-point transfers: a rank sends its record to the ranks after it), and
+// k_sp_prefix folds them into the state entering the slice.  ssd_sp_exchange_bwd is the mirror image for the state gradient.
 // Only NCCL reads a peer's memory; every kernel of this library reads the local copy.
 //
 // NCCL is bound at run time (dlopen of libnccl.so.2, the copy already loaded by the host program if

@@ -11,7 +11,7 @@ path at all (no collective call site anywhere in its tree); this module is new w
 counterpart.
 
 On the GPU the exchange is the library's own C entry point (`ssd_sp_exchange_fwd/_bwd`: NCCL
-all-gather into local memory + the prefix kernel), so this file is a thin caller: what a Rust/tch
+point-to-point transfers into local memory + the prefix kernel), so this file is a thin caller: what a Rust/tch
 host does with the same entry points.  `ops` is the set of device operations used; it is a
 parameter so that the host-side logic (slice bookkeeping, exchange order, boundary handling, the
 rendezvous that detects a missing or disagreeing rank) can be exercised by CPU ranks in tests.
