@@ -443,16 +443,20 @@ __global__ void __launch_bounds__(CONV_THREADS, CONV_BWD_MINB) k_conv_bwd(SsdCon
 }
 
 // ---------------------------------------------------------------------------------------------
-// conv backward, shared-memory staged.  Grid = (tile walkers, channel blocks of 256 bytes); a CTA walks (batch, 64-token
+// conv backward, shared-memory staged.  Grid = (tile walkers, channel blocks of 256 bytes); a CTA walks (batch, 32-token
 // tile) pairs of its channel block with the next tile's input rows and gradient rows arriving by cp.async while the
 // current tile is worked on in two phases:
-//   1. thread = (8 bytes of channels, 9 consecutive rows): recompute the pre-activation from a sliding input window,
+//   1. thread = (8 bytes of channels, 5 consecutive rows): recompute the pre-activation from a sliding input window,
 //      dpre = dout * act'(pre) into a shared fp32 tile, and the weight / bias gradient of the rows this tile owns;
-//   2. thread = (8 bytes of channels, 8 consecutive tokens): din from a sliding window over the dpre tile.
+//   2. thread = (8 bytes of channels, 4 consecutive tokens): din from a sliding window over the dpre tile.
 // The tile carries K-1 halo rows on either side (zero-filled outside the sequence), so no row is recomputed in
 // registers and nothing is re-read from global memory but the halo.  A CTA leaves one partial weight-gradient row.
 constexpr int CONVB_STAGES = 2;
-constexpr int CONVB_CTAS_PER_SM = 2;
+constexpr int CONVB_CTAS_PER_SM = 3;
+// 32-token tiles: 55 KB of shared memory and 80 registers per thread let three blocks (24 warps) share an SM, which an
+// issue-bound kernel needs more than it needs long tiles (64-token tiles, two blocks of 126 registers: 0.424 ms; this:
+// 0.357 ms; four blocks at 64 registers spill: 0.51 ms)
+constexpr int CONVB_TT = 32;
 
 template <typename T, int K>
 __global__ void __launch_bounds__(CONVS_THREADS, CONVB_CTAS_PER_SM)
@@ -462,7 +466,7 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
   constexpr int NC = 16 / (int)sizeof(T);            // channels per 16-byte copy piece
   constexpr int NP = 8 / (int)sizeof(T);             // channels per thread in the arithmetic phases
   constexpr int CB = CONVS_ROWB / (int)sizeof(T);    // channels per tile
-  constexpr int IN_ROWS = CONVS_TT + 2 * (K - 1), GO_ROWS = CONVS_TT + K - 1;
+  constexpr int IN_ROWS = CONVB_TT + 2 * (K - 1), GO_ROWS = CONVB_TT + K - 1;
   constexpr int STAGE_BYTES = (IN_ROWS + GO_ROWS) * CONVS_ROWB;
   constexpr int DPRE_ROWB = CB * 4;
   constexpr int R1 = (GO_ROWS + 7) / 8;              // rows per thread in phase 1
@@ -482,7 +486,7 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
   const T* ibase = in + (cok ? cc : 0);
   auto request = [&](const PairWalk& pw, int stage) {
     if (pw.b < d.batch) {
-      const int t0 = pw.tt * CONVS_TT;
+      const int t0 = pw.tt * CONVB_TT;
       unsigned char* sp = conv_smem + stage * STAGE_BYTES + cv * 16 + seg * CONVS_ROWB;
       {
         const T* src = ibase + (long long)pw.b * d.in_stride_b + (long long)(t0 - (K - 1) + seg) * d.in_stride_l;
@@ -538,7 +542,7 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     __syncthreads();     // the tile has landed; phase 2 of the previous tile is over (dpre and the other stage are free)
     request(ahead, stage ^ 1);
     ahead.next();
-    const int b = cur.b, t0 = cur.tt * CONVS_TT;
+    const int b = cur.b, t0 = cur.tt * CONVB_TT;
     cur.next();
     const unsigned char* sin = conv_smem + stage * STAGE_BYTES + hv * 8;
     const unsigned char* sgo = sin + IN_ROWS * CONVS_ROWB;
@@ -563,7 +567,7 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
           lds_raw<T, NP>(sgo + r * CONVS_ROWB, rg);
           f32x2 go[NH], dp[NH];
           unpack_pairs(rg, go);
-          const bool own = r < CONVS_TT;    // each row's weight / bias gradient is counted by exactly one tile
+          const bool own = r < CONVB_TT;    // each row's weight / bias gradient is counted by exactly one tile
 #pragma unroll
           for (int j = 0; j < NH; ++j) {
             f32x2 a2 = bs[j];
@@ -597,7 +601,7 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     __syncthreads();
     // ---- phase 2: din[t0 + i] = sum_q w[K-1-q] * dpre[i + q], tokens i0 .. i0+7 ----
     if (live) {
-      const int i0 = rs * (CONVS_TT / 8);
+      const int i0 = rs * (CONVB_TT / 8);
       const f32x2* dpp = reinterpret_cast<const f32x2*>(dpre) + hv * NH;
       auto load_row = [&](int row, f32x2 (&v)[NH]) {
         const f32x2* q = dpp + (size_t)row * (DPRE_ROWB / 8);
@@ -609,7 +613,7 @@ k_conv_bwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
 #pragma unroll
       for (int q = 0; q < K - 1; ++q) load_row(i0 + q, dwin[q]);
 #pragma unroll
-      for (int i = 0; i < CONVS_TT / 8; ++i) {
+      for (int i = 0; i < CONVB_TT / 8; ++i) {
         load_row(i0 + i + K - 1, dwin[K - 1]);
         float o[NP];
 #pragma unroll
@@ -1080,7 +1084,7 @@ int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float
   cudaStream_t s = (cudaStream_t)cuda_stream;
   float* partial = (float*)workspace;
   if ((long long)dims->channels * es >= CONVS_ROWB / 2) {
-    const int ntt = (dims->seqlen + CONVS_TT - 1) / CONVS_TT;
+    const int ntt = (dims->seqlen + CONVB_TT - 1) / CONVB_TT;
     const int ncb = (dims->channels * es + CONVS_ROWB - 1) / CONVS_ROWB;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
@@ -1092,7 +1096,7 @@ int32_t ssd_conv1d_backward(const SsdConvDims* dims, const void* in, const float
     if (nx > nblk) nx = nblk;     // the workspace holds nblk partial rows
     const dim3 grid((unsigned)nx, (unsigned)ncb);
 #define CONV_BWD_SM(T, K) do { \
-      constexpr int smem = CONVB_STAGES * (2 * CONVS_TT + 3 * (K - 1)) * CONVS_ROWB + (CONVS_TT + K - 1) * (CONVS_ROWB / (int)sizeof(T)) * 4; \
+      constexpr int smem = CONVB_STAGES * (2 * CONVB_TT + 3 * (K - 1)) * CONVS_ROWB + (CONVB_TT + K - 1) * (CONVS_ROWB / (int)sizeof(T)) * 4; \
       cudaFuncSetAttribute(k_conv_bwd_sm<T, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       k_conv_bwd_sm<T, K><<<grid, CONVS_THREADS, smem, s>>>(*dims, (const T*)in, weight, bias, segs, (T*)din, din_stride_b, din_stride_l, partial, ntt); } while (0)
     if (dims->dtype == SSD_BF16) {
