@@ -202,8 +202,8 @@ __global__ void __launch_bounds__(CONV_THREADS) k_conv_fwd(SsdConvDims d, const 
 constexpr int CONVS_THREADS = 256;
 constexpr int CONVS_TT = 64;        // tokens per tile
 constexpr int CONVS_ROWB = 256;     // bytes of channels per tile row
-constexpr int CONVS_STAGES = 4;
-constexpr int CONVS_CTAS_PER_SM = 3;
+constexpr int CONVS_STAGES = 3;
+constexpr int CONVS_CTAS_PER_SM = 4;
 
 template <typename T, int NC> __device__ __forceinline__ void lds_raw(const void* p, RawN<T, NC>& r) {
   r = *reinterpret_cast<const RawN<T, NC>*>(p);
@@ -226,12 +226,15 @@ template <typename T, int K>
 __global__ void __launch_bounds__(CONVS_THREADS, CONVS_CTAS_PER_SM)
 k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__ weight, const float* __restrict__ bias,
               T* __restrict__ out, int ntt) {
-  constexpr int NC = 16 / (int)sizeof(T);            // channels per 16-byte vector
+  constexpr int NC = 16 / (int)sizeof(T);            // channels per 16-byte copy piece
+  constexpr int NP = 8 / (int)sizeof(T);             // channels per thread in the arithmetic (8 bytes: half the weights in
+                                                     // registers of a 16-byte mapping, so a fourth block fits an SM)
   constexpr int CB = CONVS_ROWB / (int)sizeof(T);    // channels per tile
   constexpr int ROWS = CONVS_TT + K - 1;
   constexpr int STAGE_BYTES = ROWS * CONVS_ROWB;
   extern __shared__ __align__(128) unsigned char conv_smem[];
-  const int tid = threadIdx.x, cv = tid & 15, seg = tid >> 4;
+  const int tid = threadIdx.x, cv = tid & 15, seg = tid >> 4;      // copy role: 16-byte piece cv of rows seg, seg + 16, ...
+  const int hv = tid & 31, rs = tid >> 5;                           // arithmetic role: 8-byte piece hv, tokens 8 rs .. 8 rs + 7
   // grid = (pair walkers, channel blocks): the CTAs of one x walk the same token rows side by side, one channel block
   // each, so whole rows (whole DRAM pages) are read and written at about the same time
   const int c0 = blockIdx.y * CB + cv * NC;
@@ -260,13 +263,15 @@ k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
   PairWalk ahead((int)blockIdx.x, (int)gridDim.x, ntt), cur = ahead;
 #pragma unroll
   for (int i = 0; i < CONVS_STAGES - 1; ++i) { request(ahead, i); ahead.next(); }
-  f32x2 w[NC / 2][K], bs[NC / 2];     // channel pairs (2j, 2j+1)
+  const int c1 = blockIdx.y * CB + hv * NP;
+  const bool live = c1 < d.channels;
+  f32x2 w[NP / 2][K], bs[NP / 2];     // channel pairs (2j, 2j+1)
 #pragma unroll
-  for (int j = 0; j < NC / 2; ++j) {
+  for (int j = 0; j < NP / 2; ++j) {
 #pragma unroll
     for (int k = 0; k < K; ++k)
-      w[j][k] = cok ? pack2(__ldg(weight + (size_t)(c0 + 2 * j) * K + k), __ldg(weight + (size_t)(c0 + 2 * j + 1) * K + k)) : 0ull;
-    bs[j] = (cok && bias) ? pack2(__ldg(bias + c0 + 2 * j), __ldg(bias + c0 + 2 * j + 1)) : 0ull;
+      w[j][k] = live ? pack2(__ldg(weight + (size_t)(c1 + 2 * j) * K + k), __ldg(weight + (size_t)(c1 + 2 * j + 1) * K + k)) : 0ull;
+    bs[j] = (live && bias) ? pack2(__ldg(bias + c1 + 2 * j), __ldg(bias + c1 + 2 * j + 1)) : 0ull;
   }
   int stage = 0;
   for (int pair = blockIdx.x; pair < npairs; pair += gridDim.x) {
@@ -274,23 +279,24 @@ k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
     __syncthreads();           // this tile has landed for every thread; every thread is done with the previous one
     request(ahead, stage == 0 ? CONVS_STAGES - 1 : stage - 1);
     ahead.next();
-    const int t0 = cur.tt * CONVS_TT + seg * 4;
-    const unsigned char* sp = conv_smem + stage * STAGE_BYTES + cv * 16 + seg * 4 * CONVS_ROWB;
-    T* op = out + (long long)cur.b * d.out_stride_b + (long long)t0 * d.out_stride_l + c0;
+    constexpr int TPT = CONVS_TT / (CONVS_THREADS / 32);   // tokens per thread
+    const int t0 = cur.tt * CONVS_TT + rs * TPT;
+    const unsigned char* sp = conv_smem + stage * STAGE_BYTES + hv * 8 + rs * TPT * CONVS_ROWB;
+    T* op = out + (long long)cur.b * d.out_stride_b + (long long)t0 * d.out_stride_l + c1;
     cur.next();
     stage = stage + 1 == CONVS_STAGES ? 0 : stage + 1;
-    if (!cok) continue;
-    f32x2 win[K][NC / 2];
+    if (!live) continue;
+    f32x2 win[K][NP / 2];
 #pragma unroll
-    for (int k = 0; k < K - 1; ++k) { RawN<T, NC> r0; lds_raw<T, NC>(sp + k * CONVS_ROWB, r0); unpack_pairs(r0, win[k]); }
+    for (int k = 0; k < K - 1; ++k) { RawN<T, NP> r0; lds_raw<T, NP>(sp + k * CONVS_ROWB, r0); unpack_pairs(r0, win[k]); }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      RawN<T, NC> r0;
-      lds_raw<T, NC>(sp + (K - 1 + i) * CONVS_ROWB, r0);
+    for (int i = 0; i < TPT; ++i) {
+      RawN<T, NP> r0;
+      lds_raw<T, NP>(sp + (K - 1 + i) * CONVS_ROWB, r0);
       unpack_pairs(r0, win[K - 1]);
-      float o[NC];
+      float o[NP];
 #pragma unroll
-      for (int j = 0; j < NC / 2; ++j) {
+      for (int j = 0; j < NP / 2; ++j) {
         f32x2 a2 = bs[j];
 #pragma unroll
         for (int k = 0; k < K; ++k) a2 = fma2(w[j][k], win[k][j], a2);
@@ -304,7 +310,7 @@ k_conv_fwd_sm(SsdConvDims d, const T* __restrict__ in, const float* __restrict__
 #pragma unroll
       for (int k = 0; k < K - 1; ++k)
 #pragma unroll
-        for (int j = 0; j < NC / 2; ++j) win[k][j] = win[k + 1][j];
+        for (int j = 0; j < NP / 2; ++j) win[k][j] = win[k + 1][j];
     }
   }
   cp_async_wait<0>();
