@@ -1923,6 +1923,9 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       for (int t = 0; t < my_tiles; ++t) {
         const uint32_t keep_t = smem_u32(sCB + (t % NCBS) * Cfg::CB_BYTES);
         const uint64_t dK0 = desc_sw128_k(keep_t, 0);
+        // the lane that issues the state term reads the keep tile; when that is not the lane that formed G (and waited
+        // for the tile there), it has to see the tile's arrival itself: the first x box of a tile can land before its C/B
+        if (SPLIT && HB == 1 && mi == 1) w.wait(&bars.cb_full[t % NCBS], (t / NCBS) & 1, 64);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           const int ib = kb & 1, ab = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
