@@ -169,6 +169,28 @@ def test_cut_and_resume_from_carried_state(lib, name):
     assert rel(s2, fin) <= 1e-3
 
 
+@pytest.mark.parametrize("name,B,L", [("cfg1", 128, 1024), ("cfg3", 4, 4096), ("cfg4_one_gpu", 2, 16384)])
+def test_repeated_runs_are_bit_identical(lib, name, B, L):
+    """Every kernel adds in a fixed order, so a second and a third run over the same buffers must reproduce every output
+    bit for bit; a hand-off that lets a consumer read a buffer before it has fully arrived shows up here as a difference."""
+    import trading_bot_0_b200 as T
+    c = CFGS[name]
+    d = draw(c, L=L, B=B)
+    z = d.get("z")
+
+    def run():
+        y, fin, ws = T.forward(d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], z, chunk=c["Q"], for_backward=True)
+        g = T.backward(d["dy"], d["x"], d["dt"], d["A"], d["B"], d["C"], d["D"], z, chunk=c["Q"], workspace=ws, fwd_saved=True)
+        torch.cuda.synchronize()
+        return dict(y=y.clone(), fin=fin.clone(), **{k: v.clone() for k, v in g.items() if isinstance(v, torch.Tensor) and k != "workspace"})
+
+    first = run()
+    for _ in range(3):
+        again = run()
+        for k, v in first.items():
+            assert torch.equal(v, again[k]), k
+
+
 def test_batch_rows_are_independent(lib):
     import trading_bot_0_b200 as T
     c = CFGS["cfg1"]
