@@ -1724,7 +1724,7 @@ __device__ __forceinline__ float sigmoid_fast(float a) {
 constexpr int WS_THREADS = 28 * 32;
 constexpr int WS_SCALE_WARPS = 16, WS_EPI_WARPS = 8;
 
-template <int P, int MODE, int N_ = 64>
+template <int P, int MODE, int N_ = 64, bool GATED_ = false>
 struct WsCfg {
   static constexpr int N = N_, HB = 64 / P, NB64 = N_ / 64;
   // dstate 128: the C and B tiles are 32 KB each, so there is ONE C/B slot (and one G), and the state boxes of a head
@@ -1732,10 +1732,14 @@ struct WsCfg {
   static constexpr bool SPLIT = N_ == 128;
   static constexpr int NCBS = SPLIT ? 1 : 2;                          // C/B slots = G buffers
   static constexpr int NBOX = (MODE == 0) ? 1 : 2;
-  static constexpr int NM = (MODE == 0) ? 3 : 2;                    // M_h ring depth = decay groups
+  // gated forward: the gate's box arrives by TMA beside the x box (a thread-per-row read of it from global memory costs one
+  // L1 wavefront per lane and instruction); its 2 x 16 KB take the place of the third M_h slot
+  static constexpr int ZB = (GATED_ && MODE == 0) ? 1 : 0;
+  static constexpr int NM = (MODE == 0 && !ZB) ? 3 : 2;             // M_h ring depth = decay groups
   static constexpr int CB_BYTES = 2 * NB64 * BOX_BYTES;              // keep + other tile
   static constexpr int ST_BYTES = NB64 * SBOX_BYTES;                 // state boxes of one head block
-  static constexpr int IN_BYTES = NBOX * BOX_BYTES + (SPLIT ? 0 : ST_BYTES);   // x [, dy] box [+ state box]
+  static constexpr int ZOFF = NBOX * BOX_BYTES + (SPLIT ? 0 : ST_BYTES);       // the gate's box comes last in a slot
+  static constexpr int IN_BYTES = ZOFF + ZB * BOX_BYTES;                       // x [, dy] box [+ state box] [+ z box]
   static constexpr int NTH = 4 * HB;                                  // table ring depth (one 2 KB table per head)
   static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
   static constexpr size_t SMEM = 1024 + NCBS * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + (SPLIT ? ST_BYTES : 0) +
@@ -1761,16 +1765,16 @@ struct WsBars {
 };
 
 template <int P, int MODE, int N_ = 64, bool GATED = false>
-__global__ void __launch_bounds__(WsCfg<P, MODE, N_>::THREADS, 1)
+__global__ void __launch_bounds__(WsCfg<P, MODE, N_, GATED>::THREADS, 1)
 k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
           const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmOut,
-          const float* __restrict__ tab, const float* __restrict__ D,
+          const __grid_constant__ CUtensorMap tmZ, const float* __restrict__ tab, const float* __restrict__ D,
           const bf16* __restrict__ z_, bf16* __restrict__ y, bf16* __restrict__ dypb, bf16* __restrict__ dz,
           bf16* __restrict__ dx, float* __restrict__ rs0, float* __restrict__ rs1, int* __restrict__ status) {
-  using Cfg = WsCfg<P, MODE, N_>;
+  using Cfg = WsCfg<P, MODE, N_, GATED>;
   const bf16* __restrict__ z = GATED ? z_ : nullptr;     // the ungated instantiation carries none of the gate's registers
-  constexpr bool ZAHEAD = GATED && MODE == 0;             // forward: the gate one block ahead; recompute: at the block's start
+  constexpr bool ZSMEM = Cfg::ZB != 0;                    // forward: the gate's box is in the input slot
   // Forward and dx: the output block (128 rows x 64 columns bf16) has the shape and layout of the x (dy) box the epilogue
   // reads, so the epilogue writes it over that box and a spare lane sends it out as ONE TMA tile store.  A row-per-thread
   // global store costs one L1 wavefront per lane and instruction, and the L1 data stage is what these kernels share.
@@ -1878,6 +1882,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           mbar_expect_tx(&bars.in_full[ib], Cfg::IN_BYTES);
           tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
           if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
+          if (ZSMEM) tma_load_3d(dst + Cfg::ZOFF, &tmZ, col, c * QT, b, &bars.in_full[ib]);
           if constexpr (!SPLIT) {
             tma_load_3d(dst + NBOX * BOX_BYTES, &tmS, 0, h0 * P, b * g.nc + c, &bars.in_full[ib]);
             // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
@@ -2021,9 +2026,9 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int row = (ew & 3) * 32 + lane, half = ew >> 2;     // 32 of the block's 64 columns
     const int hl_e = (half * 32) / P;
     int kb = 0;
-    // the gate is the one operand the epilogue reads from global memory: this thread's 64 bytes of it are requested one
-    // head block ahead (registers), so no accumulator slice waits for a round trip to DRAM
-    uint4 zq[GATED ? 4 : 1] = {}, zn[ZAHEAD ? 4 : 1] = {};
+    // gated recompute (MODE 1): the gate is the one operand the epilogue reads from global memory; this thread's 64 bytes
+    // of it are requested at the start of the block, before the waits (the forward gets the gate's box by TMA)
+    uint4 zq[GATED ? 4 : 1] = {};
     auto load_z = [&](int t_, int blk_, auto& dst) {
       if constexpr (GATED) {
         if (t_ >= my_tiles) return;
@@ -2034,14 +2039,12 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         ld_global_32B(zp_ + 16, dst[2], dst[3]);
       }
     };
-    if (ZAHEAD) load_z(0, 0, zq);
     for (int t = 0; t < my_tiles; ++t) {
       int b, grp, c;
       tile_coords(t, b, grp, c);
       const int t_row = c * QT + row;
       for (int blk = 0; blk < nblk; ++blk, ++kb) {
-        if constexpr (ZAHEAD) { if (blk + 1 < nblk) load_z(t, blk + 1, zn); else load_z(t + 1, 0, zn); }
-        else if constexpr (GATED) load_z(t, blk, zq);
+        if constexpr (GATED && !ZSMEM) load_z(t, blk, zq);
         const int ib = kb & 1, ab = kb & 1;
         uint8_t* xt = sIn + ib * Cfg::IN_BYTES;
         uint8_t* dyt = xt + (NBOX - 1) * BOX_BYTES;
@@ -2093,7 +2096,8 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             unpack8(xv[q], xs);
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] = yd[q * 8 + k] + osc * yo[q * 8 + k];
-            if (GATED) unpack8(zq[GATED ? h16 * 2 + q : 0], zs);
+            if constexpr (ZSMEM) unpack8(ld_shared_v4(smem_u32(xt + Cfg::ZOFF) + sw128_off(row, half * 4 + h16 * 2 + q)), zs);
+            else if (GATED) unpack8(zq[GATED ? h16 * 2 + q : 0], zs);
             if (MODE != 0) unpack8(dv[q], dys);
             if (MODE == 0) {
 #pragma unroll
@@ -2140,10 +2144,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&bars.out_ready[ib]);
-        }
-        if constexpr (ZAHEAD) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) zq[i] = zn[i];
         }
         if (MODE != 0) {
           if (P == 64) {   // the two column halves of a row belong to one head: combine through shared memory
@@ -2564,7 +2564,7 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // one K = 64 product each adds the state terms dC += dY' S_prev, dB += X' dS_end.  dC / dB stay in TMEM for the whole tile.
 //
 // Separable heads.  exp(cs_i - cs_j) dt_j = a_i b_j with a_i = exp(cs_i), b_j = exp(-cs_j) dt_j, and dC, dB are linear in
-// W'_h, so for a head whose decay over a chunk stays inside the range of the storage type (|cs_end| <= SEP_LOG_RANGE for
+// W'_h, so for a head whose decay over a chunk stays inside the range of the storage type (|cs_end| <= SSD_SEP_LOG_RANGE for
 // every chunk of the call; the cumsum kernel records the per-head maximum) the decay can ride on the OPERANDS:
 //   sum_h W'_h = tril( sum_h (a_h o dY_h) (b_h o X_h)^T ),
 // one accumulator for all such heads of the tile, filled by the tensor core from the boxes the decay warps scale in place
@@ -2576,7 +2576,6 @@ k_bwd_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // With the per-head pass gone for most heads a tile is a short chain of scale -> multiply steps, and what bounds the kernel
 // is how far the loads run ahead of it: the x/dy boxes have a ring of three, the state boxes of two, the tables of four;
 // the B/C tiles (read at the END of a tile by the separable path) and the W' tile are single.
-constexpr float SEP_LOG_RANGE = SSD_SEP_LOG_RANGE;
 
 template <int P>
 struct DbCfg {
@@ -3131,6 +3130,7 @@ struct ScanArgs {
 struct SeqMaps {
   CUtensorMap x, dy, b, c, s, ds;
   CUtensorMap out;     // the output of the persistent scan kernels (y, or the dense dx), written by TMA tile stores
+  CUtensorMap z;       // the gate (forward of the persistent scan kernel)
 };
 
 int sm_count() {
@@ -3148,11 +3148,11 @@ int launch_scan_ws(const Geo& g, const SeqMaps& m, const CUtensorMap& ts, const 
     if (a.z) return launch_scan_ws<P, MODE, N, true>(g, m, ts, a, status, s);
   }
   auto k = k_scan_ws<P, MODE, N, GATED>;
-  constexpr size_t sm = WsCfg<P, MODE, N>::SMEM;
+  constexpr size_t sm = WsCfg<P, MODE, N, GATED>::SMEM;
   cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
   const int ntiles = g.B * g.G * g.nc;
   const int grid = ntiles < sm_count() ? ntiles : sm_count();
-  k<<<grid, WsCfg<P, MODE, N>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, m.out, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
+  k<<<grid, WsCfg<P, MODE, N, GATED>::THREADS, sm, s>>>(g, m.x, m.dy, m.b, m.c, ts, m.out, m.z, a.tab, a.D, (const bf16*)a.z, (bf16*)a.y, (bf16*)a.dypb,
                                  (bf16*)a.dz, (bf16*)a.dx, a.rs0, a.rs1, status);
   SSD_CUDA_CHECK_LAUNCH(MODE == 0 ? "chunk_scan_ws" : (MODE == 1 ? "chunk_scan_bwd_ws" : "dx_ws"));
   return SSD_OK;
@@ -3349,6 +3349,12 @@ int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const
   if (rc) return rc;
   rc = make_seq_map(&m.out, p.y, (long long)g.H * g.P, g.L, g.B, g.ysl, g.ysb, "y");
   if (rc) return rc;
+  if (p.z) {
+    rc = make_seq_map(&m.z, p.z, (long long)g.H * g.P, g.L, g.B, g.zsl, g.zsb, "z");
+    if (rc) return rc;
+  } else {
+    m.z = m.x;
+  }
   ScanArgs a{tab, p.D, p.z, p.y, nullptr, nullptr, nullptr, nullptr, nullptr};
 #define CALL(PP, NN) return launch_scan<PP, NN, 0>(g, m, m.s, a, status, s);
   DISPATCH_PN(CALL)
@@ -3362,6 +3368,7 @@ int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const v
   int rc = make_maps(g, p.x, p.dy, false, p.Bm, p.Cm, prev_bf, nullptr, &m);
   if (rc) return rc;
   m.out = m.x;
+  m.z = m.x;
   ScanArgs a{tab, p.D, p.z, nullptr, dypb, p.dz, nullptr, dcsp, ddot};
 #define CALL(PP, NN) return launch_scan<PP, NN, 1>(g, m, m.s, a, status, s);
   DISPATCH_PN(CALL)
@@ -3378,6 +3385,7 @@ int tensor_dx(const Geo& g, const SsdBwdPtrs& p, const void* dyp, bool dy_dense,
     const long long HP = (long long)g.H * g.P;
     rc = make_seq_map(&m.out, p.dx, HP, g.L, g.B, HP, HP * g.L, "dx");
     if (rc) return rc;
+    m.z = m.x;
   }
   ScanArgs a{tab, p.D, nullptr, nullptr, nullptr, nullptr, p.dx, ddtd, nullptr};
 #define CALL(PP, NN) return launch_scan<PP, NN, 2>(g, m, m.ds, a, status, s);
