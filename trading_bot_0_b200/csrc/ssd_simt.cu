@@ -781,8 +781,8 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_FINISH) {
     if (tc && fused) {
-      int rc = tensor_state_fused(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, states, prev_bf, p.init_state, fin, nullptr,
-                                  nullptr, nullptr, nullptr, status, s);
+      int rc = tensor_state_fused(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, g.fwd_only ? nullptr : states, prev_bf,
+                                  p.init_state, fin, nullptr, nullptr, nullptr, nullptr, status, s);
       if (rc) return rc;
     } else if (tc) {
       int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, nullptr, nullptr, nullptr, nullptr, s);

@@ -3009,7 +3009,7 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
         if (WRITE && valid) {
           // the reverse scan's fp32 values have no reader in this family (the scans take the bf16 copy, the state
           // gradient entering the slice leaves through `last`): a third of its bytes stay unwritten
-          if (!reverse || !st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+          if ((!reverse && !g.fwd_only) || !st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
           if (st_bf)
             *reinterpret_cast<uint2*>(st_bf + boff + (size_t)c * cstride) =
                 make_uint2(pack_bf16(run.x, run.y), pack_bf16(run.z, run.w));
