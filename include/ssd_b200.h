@@ -119,7 +119,9 @@ typedef struct SsdBwdPtrs {
   float* dinit_state;        /* [B,H,P,N] fp32, optional */
   int32_t fwd_saved;         /* 1: `workspace` is the buffer ssd_forward ran in for these same
                                 inputs (its chunk cumsums and chunk-entry states are reused);
-                                0: recompute them */
+                                0: recompute them.  The buffer must have had the backward's size
+                                (ssd_workspace_bytes(dims, 1)) already when the forward ran: a
+                                forward into a forward-sized buffer keeps nothing for a backward. */
   const float* dt_bias;      /* [H] fp32, optional, as in the forward */
   float* ddt_bias;           /* [H] fp32, out, required iff dt_bias given.  With dt_bias / dt_softplus, `ddt` is the
                                 gradient w.r.t. the dt that was passed in (before bias and activation). */
