@@ -1735,12 +1735,21 @@ struct WsCfg {
   // gated forward: the gate's box arrives by TMA beside the x box (a thread-per-row read of it from global memory costs one
   // L1 wavefront per lane and instruction); its 2 x 16 KB take the place of the third M_h slot
   static constexpr int ZB = (GATED_ && MODE == 0) ? 1 : 0;
-  static constexpr int NM = (MODE == 0 && !ZB) ? 3 : 2;             // M_h ring depth = decay groups
+  // M_h ring depth = decay groups.  Three only with one head per block: with two, issuer hl takes head hl of every block
+  // and slot kh % 2 then always belongs to the same issuer, which therefore sees every phase of the slot's barriers (a
+  // wait by parity is only right for a waiter that is at most one phase behind)
+  static constexpr int NM = (MODE == 0 && !ZB && HB == 1) ? 3 : 2;
   static constexpr int CB_BYTES = 2 * NB64 * BOX_BYTES;              // keep + other tile
   static constexpr int ST_BYTES = NB64 * SBOX_BYTES;                 // state boxes of one head block
   static constexpr int ZOFF = NBOX * BOX_BYTES + (SPLIT ? 0 : ST_BYTES);       // the gate's box comes last in a slot
   static constexpr int IN_BYTES = ZOFF + ZB * BOX_BYTES;                       // x [, dy] box [+ state box] [+ z box]
-  static constexpr int NTH = 4 * HB;                                  // table ring depth (one 2 KB table per head)
+  // table ring depth (one 2 KB table per head): a multiple of the number of decay groups, so that a slot is always read by
+  // the same group.  With a depth of 4 and three groups the slot of head 5 had last been head 1's, read by another group:
+  // the group of head 5, coming from head 2, could reach the slot's barrier before head 1's table had landed, pass the wait
+  // on the parity of a phase that had not even begun, and read the slot while head 5's table was still arriving (rows 0-31
+  // of that head wrong about once in 10^4 CTAs).
+  static constexpr int NTH = (NM == 3) ? 6 : 4 * HB;
+  static_assert(NTH % NM == 0 && NTH <= 8, "a table slot must belong to one decay group");
   static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
   static constexpr size_t SMEM = 1024 + NCBS * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + (SPLIT ? ST_BYTES : 0) +
                                  NTH * TAB_BYTES + RED_BYTES;
@@ -2010,8 +2019,8 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       for (int hh = 0; hh < nblk * HB; ++hh, ++kh) {
         if (kh % NM != wg) continue;
         const int ts = kh % NTH;
-        w.wait(&bars.tab_full[ts], (kh / NTH) & 1, 52);
         w.wait(&bars.m_empty[wg], ((kh / NM) & 1) ^ 1, 53);
+        w.wait(&bars.tab_full[ts], (kh / NTH) & 1, 52);
         decay_row<Cfg::NCH>(rb, ch, tm_row, (const float*)(sTab + ts * TAB_BYTES), row, mrow);
         fence_async_smem(); __syncwarp(); if (lane == 0) { mbar_arrive(&bars.m_full[wg]); mbar_arrive(&bars.tab_empty[ts]); }
       }
