@@ -18,7 +18,8 @@ bool tensor_supported(const Geo& g, int dtype, const char** why);
 int tensor_chunk_state(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc,
                        long long bsb, long long bsl, const float* tab, float* out, int* status, cudaStream_t s);
 int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, void* st_bf,
-                         int reverse, bool write, const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw,
+                         int reverse, bool write, const float* fwd_prev, const void* fwd_prev_bf, const float* fwd_fin,
+                         float* sdot, int* sdot_nw,
                          cudaStream_t s);
 // both in one launch where it applies (dstate 64, full pass): fp32 `st` optional, bf16 `st_bf` always
 bool tensor_state_fused_applies(const Geo& g);

@@ -772,7 +772,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_TOTAL) {
     if (tc) {
-      int rc = tensor_state_passing(g, states, cs, nullptr, fin, nullptr, 0, false, nullptr, nullptr, nullptr, nullptr, s);
+      int rc = tensor_state_passing(g, states, cs, nullptr, fin, nullptr, 0, false, nullptr, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
       k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, nullptr, fin, 0);
@@ -785,7 +785,7 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
                                   p.init_state, fin, nullptr, nullptr, nullptr, nullptr, status, s);
       if (rc) return rc;
     } else if (tc) {
-      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, nullptr, nullptr, nullptr, nullptr, s);
+      int rc = tensor_state_passing(g, states, cs, p.init_state, fin, prev_bf, 0, true, nullptr, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
       k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, states, cs, p.init_state, fin, 0);
@@ -891,7 +891,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_TOTAL) {
     if (tc) {
-      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, nullptr, 1, false, nullptr, nullptr, nullptr, nullptr, s);
+      int rc = tensor_state_passing(g, dst, cs, nullptr, dini, nullptr, 1, false, nullptr, nullptr, nullptr, nullptr, nullptr, s);
       if (rc) return rc;
     } else {
       k_state_passing<false><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, nullptr, dini, 1);
@@ -908,7 +908,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       if (rc) return rc;
     } else if (tc) {
       // the reverse scan also leaves the warp-partial sums of <dS_end, S_end> per chunk
-      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, ds_bf, 1, true, states, fin, sdot, &sdot_nw, s);
+      int rc = tensor_state_passing(g, dst, cs, p.dfinal_state, dini, ds_bf, 1, true, states, prev_bf, fin, sdot, &sdot_nw, s);
       if (rc) return rc;
     } else {
       k_state_passing<true><<<dim3(cdiv(g.P * g.N, NT), g.H, g.B), NT, 0, s>>>(g, dst, cs, p.dfinal_state, dini, 1);

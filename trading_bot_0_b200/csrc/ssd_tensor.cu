@@ -2974,13 +2974,18 @@ k_dbc_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant__
 // The reverse scan (state gradient) can also emit, per chunk, this block's warp-partial sums of
 // <dS_end_c, S_end_c> (S_end_c = forward state entering chunk c+1, or the final state), which is
 // the per-chunk term of the dt*A gradient: `sdot` [B, nc, H, gridDim.x * 8].
-template <bool WRITE>
-__global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restrict__ st, const float* __restrict__ cs,
+template <bool WRITE, bool BFDOT = false>
+__global__ void __launch_bounds__(256, BFDOT ? 3 : 1) k_state_passing_v4(Geo g, float* __restrict__ st, const float* __restrict__ cs,
                                                           const float* __restrict__ init, float* __restrict__ last,
                                                           bf16* __restrict__ st_bf, int reverse,
                                                           const float* __restrict__ fwd_prev,
+                                                          const bf16* __restrict__ fwd_prev_bf,
                                                           const float* __restrict__ fwd_fin, float* __restrict__ sdot) {
   extern __shared__ float sdec[];  // [nc]
+  // fp32 chunk-entry states have one reader in this family, the fused state kernel of dstate 64 (its reverse pass takes
+  // them for <dS_end, S_end>).  At other widths this kernel forms that product from the bf16 copy (given as `fwd_prev_bf`)
+  // and the forward scan leaves the fp32 values unwritten: 2 of its 5 bytes per state element
+  const bool keep_f32 = g.N == 64;
   const int h = blockIdx.y, b = blockIdx.z;
   const int PN = g.P * g.N;
   for (int c = threadIdx.x; c < g.nc; c += blockDim.x)
@@ -2995,7 +3000,15 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
   const size_t boff = ((size_t)b * g.nc * g.H + h) * PN + eo;
   float* base = st + boff;
   const int nw = gridDim.x * 8, wslot = blockIdx.x * 8 + (threadIdx.x >> 5);
-  constexpr int U = 4;
+  // chunks in flight per thread.  The scan is bound by the bytes it keeps in flight (B * H * P * N / 4 threads, each with U
+  // loads per stream outstanding): the narrower bf16 loads need more steps to keep as many, within the 85 registers
+  // that leave three blocks per SM (two would put the 384 blocks of a B2 H24 pass into two waves)
+  // chunks in flight per thread.  The scan is bound by the bytes it keeps in flight (B * H * P * N / 4 threads): the
+  // narrower bf16 loads get six steps instead of four, within the 85 registers that leave three blocks per SM (two would
+  // put the 384 blocks of a B2 H24 pass into two waves)
+  constexpr int U = BFDOT ? 6 : 4;
+  float4 fin4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (BFDOT && sdot && valid) fin4 = *reinterpret_cast<const float4*>(fwd_fin + ((size_t)(b * g.H + h)) * PN + eo);
   for (int s0 = 0; s0 < g.nc; s0 += U) {
     float4 v[U], se[U];
 #pragma unroll
@@ -3005,9 +3018,20 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
       if (s < g.nc && valid) {
         const int c = reverse ? g.nc - 1 - s : s;
         v[u] = *reinterpret_cast<const float4*>(base + (size_t)c * cstride);
-        if (sdot)
-          se[u] = (c + 1 < g.nc) ? *reinterpret_cast<const float4*>(fwd_prev + boff + (size_t)(c + 1) * cstride)
-                                 : *reinterpret_cast<const float4*>(fwd_fin + ((size_t)(b * g.H + h)) * PN + eo);
+        if (sdot) {
+          if constexpr (BFDOT) {
+            // an unconditional load (index clamped; the last chunk takes the final state read before the loop instead) and
+            // nothing else: with the bf16 -> fp32 conversion here the loads of the U steps were issued one round after the
+            // other instead of together (0.25 instead of 0.17 ms on 0.8 GB)
+            const bool inner = c + 1 < g.nc;
+            const uint2 q = *reinterpret_cast<const uint2*>(fwd_prev_bf + boff + (size_t)(inner ? c + 1 : c) * cstride);
+            se[u].x = __uint_as_float(q.x);   // raw bits, converted where they are used
+            se[u].y = __uint_as_float(q.y);
+          } else {
+            se[u] = (c + 1 < g.nc) ? *reinterpret_cast<const float4*>(fwd_prev + boff + (size_t)(c + 1) * cstride)
+                                   : *reinterpret_cast<const float4*>(fwd_fin + ((size_t)(b * g.H + h)) * PN + eo);
+          }
+        }
       }
     }
 #pragma unroll
@@ -3018,12 +3042,18 @@ __global__ void __launch_bounds__(256) k_state_passing_v4(Geo g, float* __restri
         if (WRITE && valid) {
           // the reverse scan's fp32 values have no reader in this family (the scans take the bf16 copy, the state
           // gradient entering the slice leaves through `last`): a third of its bytes stay unwritten
-          if ((!reverse && !g.fwd_only) || !st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+          if ((!reverse && !g.fwd_only && keep_f32) || !st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
           if (st_bf)
             *reinterpret_cast<uint2*>(st_bf + boff + (size_t)c * cstride) =
                 make_uint2(pack_bf16(run.x, run.y), pack_bf16(run.z, run.w));
         }
         if (sdot) {
+          if constexpr (BFDOT) {
+            const uint32_t q0 = __float_as_uint(se[u].x), q1 = __float_as_uint(se[u].y);
+            se[u] = (c + 1 < g.nc) ? make_float4(__uint_as_float(q0 << 16), __uint_as_float(q0 & 0xffff0000u),
+                                                 __uint_as_float(q1 << 16), __uint_as_float(q1 & 0xffff0000u))
+                                   : fin4;
+          }
           float d = run.x * se[u].x + run.y * se[u].y + run.z * se[u].z + run.w * se[u].w;
 #pragma unroll
           for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
@@ -3280,14 +3310,18 @@ bool tensor_supported(const Geo& g, int dtype, const char** why) {
 }
 
 int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* init, float* last, void* st_bf,
-                         int reverse, bool write, const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw,
-                         cudaStream_t s) {
+                         int reverse, bool write, const float* fwd_prev, const void* fwd_prev_bf, const float* fwd_fin,
+                         float* sdot, int* sdot_nw, cudaStream_t s) {
   const int PN = g.P * g.N;
   const dim3 grid(cdiv(PN / 4, 256), g.H, g.B);
   const size_t sm = (size_t)g.nc * sizeof(float);
   if (sdot_nw) *sdot_nw = (int)grid.x * 8;
-  if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse, fwd_prev, fwd_fin, sdot);
-  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, nullptr, reverse, nullptr, nullptr, nullptr);
+  // the bf16 copy stands in for the fp32 chunk-entry states wherever the forward scan no longer writes those
+  const bf16* prev_bf = (g.N == 64) ? nullptr : (const bf16*)fwd_prev_bf;
+  if (write && prev_bf && sdot)
+    k_state_passing_v4<true, true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse, nullptr, prev_bf, fwd_fin, sdot);
+  else if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse, fwd_prev, nullptr, fwd_fin, sdot);
+  else k_state_passing_v4<false><<<grid, 256, sm, s>>>(g, st, cs, init, last, nullptr, reverse, nullptr, nullptr, nullptr, nullptr);
   SSD_CUDA_CHECK_LAUNCH(reverse ? (write ? "dstate_passing" : "dstate_total") : (write ? "state_passing" : "state_total"));
   return SSD_OK;
 }
