@@ -1735,10 +1735,11 @@ struct WsCfg {
   // gated forward: the gate's box arrives by TMA beside the x box (a thread-per-row read of it from global memory costs one
   // L1 wavefront per lane and instruction); its 2 x 16 KB take the place of the third M_h slot
   static constexpr int ZB = (GATED_ && MODE == 0) ? 1 : 0;
-  // M_h ring depth = decay groups.  Three only with one head per block: with two, issuer hl takes head hl of every block
-  // and slot kh % 2 then always belongs to the same issuer, which therefore sees every phase of the slot's barriers (a
-  // wait by parity is only right for a waiter that is at most one phase behind)
-  static constexpr int NM = (MODE == 0 && !ZB && HB == 1) ? 3 : 2;
+  // M_h ring depth = decay groups.  A wait by parity is only right for a waiter that is at most one phase behind.  Slot
+  // kh % NM always belongs to decay group kh % NM.  On the issuing side, with two heads per block lane hl issues head hl of
+  // every block: with two slots a slot then always meets the same lane; with three it alternates between the lanes, and
+  // HEAD_ORDER (below) is what keeps the second lane from reaching a slot before the first lane's head has been written.
+  static constexpr int NM = (MODE == 0 && !ZB) ? 3 : 2;
   static constexpr int CB_BYTES = 2 * NB64 * BOX_BYTES;              // keep + other tile
   static constexpr int ST_BYTES = NB64 * SBOX_BYTES;                 // state boxes of one head block
   static constexpr int ZOFF = NBOX * BOX_BYTES + (SPLIT ? 0 : ST_BYTES);       // the gate's box comes last in a slot
@@ -1749,7 +1750,7 @@ struct WsCfg {
   // on the parity of a phase that had not even begun, and read the slot while head 5's table was still arriving (rows 0-31
   // of that head wrong about once in 10^4 CTAs).
   static constexpr int NTH = (NM == 3) ? 6 : 4 * HB;
-  static_assert(NTH % NM == 0 && NTH <= 8, "a table slot must belong to one decay group");
+  static_assert(NTH % NM == 0 && NTH % HB == 0 && NTH <= 8, "a table slot must belong to one decay group and one column half");
   static constexpr int RED_BYTES = (P == 64 && MODE != 0) ? 2 * 256 * 4 : 0;
   static constexpr size_t SMEM = 1024 + NCBS * CB_BYTES + NM * 2 * BOX_BYTES + 2 * IN_BYTES + (SPLIT ? ST_BYTES : 0) +
                                  NTH * TAB_BYTES + RED_BYTES;
@@ -1761,6 +1762,14 @@ struct WsCfg {
   // active issuers: warps W_MMA .. W_MMA + NI - 1, one per head of a head block; with one (64-wide) head per block and
   // dstate 128 the second lane issues the state term (8 instructions per head beside the head's own 8)
   static constexpr int NI = (SPLIT && HB == 1) ? 2 : HB;
+  static constexpr bool STATE_LANE = (SPLIT && HB == 1);             // the second lane issues the state term only
+  // Head 2 kb + 1 (lane 1) takes the slot head 2 kb - 2 (lane 0) had.  Lane 1 has not waited on that use, so its wait by
+  // parity could pass while the slot still shows the phase before it.  Lane 0 therefore reports "head 0 of block kb is
+  // written" on hz[kb % 4] as soon as it has seen it, and lane 1 waits for block kb - 1's report first.  (Lane 0 needs no
+  // such report: the slot of head 2 kb was head 2 kb - 3's, whose block both lanes have finished before either starts
+  // block kb, because the accumulator set of block kb is the one block kb - 2 used.  The lanes are at most two blocks
+  // apart for the same reason, so four report slots never wrap.)
+  static constexpr bool HEAD_ORDER = HB == 2 && NM == 3;
   static constexpr int THREADS = (DW + 4 + WS_EPI_WARPS) * 32;
   // registers per thread after re-balancing (launch share: 80 at 768 threads, 96 at 640)
   static constexpr int R_DECAY = (THREADS == 768) ? 88 : (THREADS == 640 ? 128 : (MODE == 0 ? 80 : 72)),
@@ -1770,7 +1779,7 @@ struct WsCfg {
 
 struct WsBars {
   uint64_t cb_full[2], cb_empty[2], g_full[2], g_empty[2], in_full[2], in_empty[2], acc_full[2], acc_empty[2];
-  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], st_full, st_empty, out_ready[2], done;
+  uint64_t m_full[3], m_empty[3], tab_full[8], tab_empty[8], st_full, st_empty, out_ready[2], hz[4], done;
 };
 
 template <int P, int MODE, int N_ = 64, bool GATED = false>
@@ -1818,6 +1827,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     // a head's table is read by the warps of its decay group and by the epilogue warps of its columns
     for (int i = 0; i < NTH; ++i) { mbar_init(&bars.tab_full[i], 1); mbar_init(&bars.tab_empty[i], 4 * Cfg::NCH + WS_EPI_WARPS / HB); }
     mbar_init(&bars.st_full, 1); mbar_init(&bars.st_empty, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars.hz[i], 1);
     mbar_init(&bars.done, Cfg::NI);
     mbar_fence_init();
   }
@@ -1882,7 +1892,6 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         int b, grp, c;
         tile_coords(t, b, grp, c);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
-          load_tab(kb + 2);
           const int ib = kb & 1;
           w.wait(&bars.in_empty[ib], ((kb >> 1) & 1) ^ 1, 42);
           uint8_t* dst = sIn + ib * Cfg::IN_BYTES;
@@ -1892,8 +1901,11 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           tma_load_3d(dst, &tmX, col, c * QT, b, &bars.in_full[ib]);
           if (NBOX == 2) tma_load_3d(dst + BOX_BYTES, &tmDY, col, c * QT, b, &bars.in_full[ib]);
           if (ZSMEM) tma_load_3d(dst + Cfg::ZOFF, &tmZ, col, c * QT, b, &bars.in_full[ib]);
+          if constexpr (!SPLIT) tma_load_3d(dst + NBOX * BOX_BYTES, &tmS, 0, h0 * P, b * g.nc + c, &bars.in_full[ib]);
+          // tables two blocks ahead, behind this block's boxes: with a ring of three blocks of tables the slot's previous
+          // readers (block kb - 1) start only when the box slot of block kb - 2 comes free, and the boxes must not wait for them
+          load_tab(kb + 2);
           if constexpr (!SPLIT) {
-            tma_load_3d(dst + NBOX * BOX_BYTES, &tmS, 0, h0 * P, b * g.nc + c, &bars.in_full[ib]);
             // the next tile's C/B go out right behind this tile's first block, so the MMA warp can form
             // the next G while this tile is still being worked on
             if (blk == 0 && t + 1 < my_tiles) load_cb(t + 1);
@@ -1939,7 +1951,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint64_t dK0 = desc_sw128_k(keep_t, 0);
         // the lane that issues the state term reads the keep tile; when that is not the lane that formed G (and waited
         // for the tile there), it has to see the tile's arrival itself: the first x box of a tile can land before its C/B
-        if (SPLIT && HB == 1 && mi == 1) w.wait(&bars.cb_full[t % NCBS], (t / NCBS) & 1, 64);
+        if (mi == 1) w.wait(&bars.cb_full[t % NCBS], (t / NCBS) & 1, 64);
         for (int blk = 0; blk < nblk; ++blk, ++kb) {
           const int ib = kb & 1, ab = kb & 1;
           const uint32_t inb = smem_u32(sIn + ib * Cfg::IN_BYTES);
@@ -1947,7 +1959,7 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           w.wait(&bars.in_full[ib], (kb >> 1) & 1, 45);
           w.wait(&bars.acc_empty[ab], ((kb >> 1) & 1) ^ 1, 46);
           if constexpr (SPLIT) {
-            if (mi == ((SPLIT && HB == 1) ? 1 : 0)) {    // the state term first: it needs the keep tile and the state boxes, not M_h
+            if (mi == (Cfg::STATE_LANE ? 1 : 0)) {    // the state term first: it needs the keep tile and the state boxes, not M_h
               w.wait(&bars.st_full, kb & 1, 58);
               tc_fence_after();
 #pragma unroll 1
@@ -1960,9 +1972,11 @@ k_scan_ws(Geo g, const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             }
           }
           for (int hl = 0; hl < HB; ++hl, ++kh) {
-            if (hl != mi) continue;
             const int ms = kh % NM;
+            if ((Cfg::STATE_LANE ? 0 : hl) != mi) continue;
+            if (Cfg::HEAD_ORDER && hl == 1 && kb >= 1) w.wait(&bars.hz[(kb - 1) & 3], ((kb - 1) >> 2) & 1, 65);
             w.wait(&bars.m_full[ms], (kh / NM) & 1, 47);
+            if (Cfg::HEAD_ORDER && hl == 0) mbar_arrive(&bars.hz[kb & 3]);
             tc_fence_after();
             const uint32_t mt = smem_u32(sM + ms * 2 * BOX_BYTES);
             const uint64_t dM0 = (MODE == 2) ? desc_plain_mn(mt, 128, 0, 0) : desc_plain_k(mt, 128, 0);
