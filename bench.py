@@ -887,4 +887,11 @@ def main():
 
 
 if __name__ == "__main__":
+    # One JSON line on stdout is the contract, and libraries under this process write to file descriptor 1 on their own
+    # (NCCL prints its version there when NCCL_DEBUG is set on the box).  So fd 1 is pointed at stderr for the run, and
+    # only this file's prints reach the real stdout.
+    _real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(_real_stdout, "w", buffering=1)
     main()
+    sys.stdout.flush()
