@@ -25,7 +25,7 @@ int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* 
 bool tensor_state_fused_applies(const Geo& g);
 int tensor_state_fused(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc, long long bsb,
                        long long bsl, const float* tab, float* st, void* st_bf, const float* init, float* last,
-                       const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw, int* status, cudaStream_t s);
+                       const void* fwd_prev_bf, const float* fwd_fin, float* sdot, int* sdot_nw, int* status, cudaStream_t s);
 int tensor_chunk_scan(const Geo& g, const SsdFwdPtrs& p, const float* tab, const void* prev_bf, int* status,
                       cudaStream_t s);
 int tensor_scan_bwd(const Geo& g, const SsdBwdPtrs& p, const float* tab, const void* prev_bf, void* dypb, float* dcsp,

@@ -781,7 +781,8 @@ static int fwd_stages_t(const Geo& g, bool tc, const SsdFwdPtrs& p, char* ws, co
   }
   if (stages & SSD_STAGE_FINISH) {
     if (tc && fused) {
-      int rc = tensor_state_fused(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, g.fwd_only ? nullptr : states, prev_bf,
+      // no fp32 copy of the chunk-entry states: every reader in this family takes the bf16 one
+      int rc = tensor_state_fused(g, 0, p.x, g.xsb, g.xsl, p.Bm, g.bsb, g.bsl, tab, nullptr, prev_bf,
                                   p.init_state, fin, nullptr, nullptr, nullptr, nullptr, status, s);
       if (rc) return rc;
     } else if (tc) {
@@ -904,7 +905,7 @@ static int bwd_stages_t(const Geo& g, bool tc, const SsdBwdPtrs& p, char* ws, co
       // local state gradients, the reverse scan and the <dS_end, S_end> partial sums in one kernel (no fp32 copy is kept)
       int rc = tensor_state_fused(g, 1, tc_dy, tc_dense ? (long long)g.L * g.H * g.P : g.ysb,
                                   tc_dense ? (long long)g.H * g.P : g.ysl, p.Cm, g.csb, g.csl, tab, nullptr, ds_bf,
-                                  p.dfinal_state, dini, states, fin, sdot, &sdot_nw, status, s);
+                                  p.dfinal_state, dini, prev_bf, fin, sdot, &sdot_nw, status, s);
       if (rc) return rc;
     } else if (tc) {
       // the reverse scan also leaves the warp-partial sums of <dS_end, S_end> per chunk

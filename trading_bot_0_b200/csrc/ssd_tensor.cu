@@ -705,12 +705,14 @@ __global__ void __launch_bounds__(PsCfg<P, N_>::THREADS, 1) k_state_ps(Geo g, co
 //   MODE 1  backward: c = nc-1 .. 0 from `init` = the gradient w.r.t. the final state (or zero); the value written for
 //           chunk c is the gradient w.r.t. the state LEAVING it (bf16 only: nothing reads an fp32 copy), and the epilogue
 //           also emits per-warp partial sums of <dS_end_c, S_end_c> (the per-chunk term of the dt*A gradient, S_end_c read
-//           from the forward pass's fp32 states), `nw` = 4 * P / 32 partials per (batch, chunk, head) in `sdot`;
+//           from the forward pass's bf16 copy of the chunk-entry states, the fp32 final state for the last chunk), `nw` =
+//           4 * P / 32 partials per (batch, chunk, head) in `sdot`;
 //           `last` receives the gradient w.r.t. the initial state.
 // Pipeline and barriers as in k_state_ps; the B (or C) tile now changes with every tile, so it has a ring of its own.
 template <int P, int MODE>
 struct PfCfg {
-  // the backward kernel gives one slot of the x ring to the S_end tile (128 rows x 64 fp32 as two swizzled 16 KB boxes)
+  // the backward kernel gives one slot of the x ring to the S_end tile (128 rows x 64: one 16 KB bf16 box, or for the last
+  // chunk the fp32 final state as two swizzled 16 KB boxes)
   static constexpr int N = 64, HT = 128 / P, NX = MODE == 1 ? 3 : 4, NB = 3;
   static constexpr int X_BYTES = 2 * BOX_BYTES;
   static constexpr int TBH = 256;
@@ -727,7 +729,7 @@ struct StateScanArgs {
   void* st_bf;          // [B,nc,H,P,N] bf16 out
   const float* init;    // [B,H,P,N] fp32, optional
   float* last;          // [B,H,P,N] fp32 out, optional
-  const float* fwd_prev;  // MODE 1: fp32 chunk-entry states of the forward pass
+  const void* fwd_prev_bf;  // MODE 1: bf16 copy of the forward pass's chunk-entry states (read through a tensor map)
   const float* fwd_fin;   // MODE 1: forward final state
   float* sdot;            // MODE 1: [B,nc,H,SDOT_NW]
 };
@@ -745,7 +747,7 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
   uint8_t* sX = smem;                                  // NX x {two 64-column boxes}: the tile, scaled in place (high part)
   uint8_t* sL = sX + NX * Cfg::X_BYTES;                // low bf16 part of the tile being multiplied
   uint8_t* sB = sL + Cfg::X_BYTES;                     // NB x B (or C) tile
-  uint8_t* sSE = sB + NB * BOX_BYTES;                  // MODE 1: S_end of the tile whose epilogue comes next (fp32, 128B swizzle)
+  uint8_t* sSE = sB + NB * BOX_BYTES;                  // MODE 1: S_end of the tile whose epilogue comes next (128B swizzle)
   uint8_t* sTabs = sSE + Cfg::SE_BYTES;                // NX x the table sections of a tile's heads
   __shared__ __align__(8) uint64_t x_full[NX], x_free[NX], b_full[NB], b_free[NB], half_ready[2], h0_done, mma_done[2], acc_empty[2],
       se_full, se_free;
@@ -817,12 +819,15 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
         const int c = chunk_of(sidx);
         const int h0 = grp * g.hpg + mt * HT;
         if (k >= 1) w.wait(&se_free, (k - 1) & 1, 20);
-        mbar_expect_tx(&se_full, Cfg::SE_BYTES);
-        const bool last_chunk = c + 1 >= g.nc;
-        const CUtensorMap* m = last_chunk ? &tmF : &tmS;
-        const int row0 = last_chunk ? (b * g.H + h0) * P : ((b * g.nc + c + 1) * g.H + h0) * P;
-        tma_load_3d(sSE, m, 0, row0, 0, &se_full);
-        tma_load_3d(sSE + BOX_BYTES, m, 32, row0, 0, &se_full);
+        if (c + 1 >= g.nc) {   // the forward's final state: fp32, two boxes of 32 columns
+          const int row0 = (b * g.H + h0) * P;
+          mbar_expect_tx(&se_full, 2 * BOX_BYTES);
+          tma_load_3d(sSE, &tmF, 0, row0, 0, &se_full);
+          tma_load_3d(sSE + BOX_BYTES, &tmF, 32, row0, 0, &se_full);
+        } else {               // the bf16 copy of the state entering chunk c + 1: one box of 64 columns
+          mbar_expect_tx(&se_full, BOX_BYTES);
+          tma_load_3d(sSE, &tmS, 0, ((b * g.nc + c + 1) * g.H + h0) * P, 0, &se_full);
+        }
         if (++sidx == g.nc) { sidx = 0; ++n; }
       }
     }
@@ -924,12 +929,23 @@ __global__ void __launch_bounds__(PfCfg<P, MODE>::THREADS, 1) k_state_scan_ps(Ge
       if (want_sdot) {
         w.wait(&se_full, k & 1, 21);
         float d = 0.f;
-        const uint32_t sb = smem_u32(sSE) + (part >> 1) * BOX_BYTES;
+        if (c + 1 >= g.nc) {   // block-uniform: the final state, fp32
+          const uint32_t sb = smem_u32(sSE) + (part >> 1) * BOX_BYTES;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 u = ld_shared_v4(sb + sw128_off(row, (part & 1) * 4 + j));
-          d += run[4 * j] * __uint_as_float(u.x) + run[4 * j + 1] * __uint_as_float(u.y) + run[4 * j + 2] * __uint_as_float(u.z) +
-               run[4 * j + 3] * __uint_as_float(u.w);
+          for (int j = 0; j < 4; ++j) {
+            const uint4 u = ld_shared_v4(sb + sw128_off(row, (part & 1) * 4 + j));
+            d += run[4 * j] * __uint_as_float(u.x) + run[4 * j + 1] * __uint_as_float(u.y) + run[4 * j + 2] * __uint_as_float(u.z) +
+                 run[4 * j + 3] * __uint_as_float(u.w);
+          }
+        } else {               // the bf16 copy: this thread's 16 columns are two 16-byte pieces of its row
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint4 u = ld_shared_v4(smem_u32(sSE) + sw128_off(row, part * 2 + j));
+            const uint32_t q[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              d += run[8 * j + 2 * i] * __uint_as_float(q[i] << 16) + run[8 * j + 2 * i + 1] * __uint_as_float(q[i] & 0xffff0000u);
+          }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&se_free);
@@ -2996,10 +3012,8 @@ __global__ void __launch_bounds__(256, BFDOT ? 3 : 1) k_state_passing_v4(Geo g, 
                                                           const bf16* __restrict__ fwd_prev_bf,
                                                           const float* __restrict__ fwd_fin, float* __restrict__ sdot) {
   extern __shared__ float sdec[];  // [nc]
-  // fp32 chunk-entry states have one reader in this family, the fused state kernel of dstate 64 (its reverse pass takes
-  // them for <dS_end, S_end>).  At other widths this kernel forms that product from the bf16 copy (given as `fwd_prev_bf`)
-  // and the forward scan leaves the fp32 values unwritten: 2 of its 5 bytes per state element
-  const bool keep_f32 = g.N == 64;
+  // fp32 chunk-entry states have no reader in this family: the reverse scans form <dS_end, S_end> from the bf16 copy (here
+  // given as `fwd_prev_bf`), so a scan that writes the copy leaves the fp32 values unwritten: 2 of its 5 bytes per element
   const int h = blockIdx.y, b = blockIdx.z;
   const int PN = g.P * g.N;
   for (int c = threadIdx.x; c < g.nc; c += blockDim.x)
@@ -3056,7 +3070,7 @@ __global__ void __launch_bounds__(256, BFDOT ? 3 : 1) k_state_passing_v4(Geo g, 
         if (WRITE && valid) {
           // the reverse scan's fp32 values have no reader in this family (the scans take the bf16 copy, the state
           // gradient entering the slice leaves through `last`): a third of its bytes stay unwritten
-          if ((!reverse && !g.fwd_only && keep_f32) || !st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
+          if (!st_bf) *reinterpret_cast<float4*>(base + (size_t)c * cstride) = run;
           if (st_bf)
             *reinterpret_cast<uint2*>(st_bf + boff + (size_t)c * cstride) =
                 make_uint2(pack_bf16(run.x, run.y), pack_bf16(run.z, run.w));
@@ -3331,7 +3345,7 @@ int tensor_state_passing(const Geo& g, float* st, const float* cs, const float* 
   const size_t sm = (size_t)g.nc * sizeof(float);
   if (sdot_nw) *sdot_nw = (int)grid.x * 8;
   // the bf16 copy stands in for the fp32 chunk-entry states wherever the forward scan no longer writes those
-  const bf16* prev_bf = (g.N == 64) ? nullptr : (const bf16*)fwd_prev_bf;
+  const bf16* prev_bf = (const bf16*)fwd_prev_bf;
   if (write && prev_bf && sdot)
     k_state_passing_v4<true, true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse, nullptr, prev_bf, fwd_fin, sdot);
   else if (write) k_state_passing_v4<true><<<grid, 256, sm, s>>>(g, st, cs, init, last, (bf16*)st_bf, reverse, fwd_prev, nullptr, fwd_fin, sdot);
@@ -3378,17 +3392,18 @@ static int launch_state_scan(const Geo& g, const CUtensorMap& tx, const CUtensor
 
 int tensor_state_fused(const Geo& g, int mode, const void* xdy, long long sb, long long sl, const void* bc, long long bsb,
                        long long bsl, const float* tab, float* st, void* st_bf, const float* init, float* last,
-                       const float* fwd_prev, const float* fwd_fin, float* sdot, int* sdot_nw, int* status, cudaStream_t s) {
+                       const void* fwd_prev_bf, const float* fwd_fin, float* sdot, int* sdot_nw, int* status, cudaStream_t s) {
   CUtensorMap tx, tb;
   int rc = make_seq_map(&tx, xdy, (long long)g.H * g.P, g.L, g.B, sl, sb, "x/dy");
   if (rc) return rc;
   rc = make_seq_map(&tb, bc, (long long)g.G * g.N, g.L, g.B, bsl, bsb, "B/C");
   if (rc) return rc;
-  StateScanArgs a{tab, st, st_bf, init, last, fwd_prev, fwd_fin, sdot};
+  StateScanArgs a{tab, st, st_bf, init, last, fwd_prev_bf, fwd_fin, sdot};
   if (sdot_nw) *sdot_nw = 4 * (g.P / 32);
   CUtensorMap ts = tx, tf = tx;   // placeholders unless the backward kernel reads the forward states
   if (mode == 1 && sdot) {
-    rc = make_f32_rows_map(&ts, fwd_prev, (long long)g.B * g.nc * g.H * g.P, "forward chunk-entry states");
+    const long long rows = (long long)g.B * g.nc * g.H * g.P;   // bf16 [rows, 64]: boxes of 128 rows x 64 columns
+    rc = make_map3(&ts, fwd_prev_bf, 64, rows, 1, 64, rows * 64, 128, "forward chunk-entry states (bf16 copy)");
     if (rc) return rc;
     rc = make_f32_rows_map(&tf, fwd_fin, (long long)g.B * g.H * g.P, "forward final state");
     if (rc) return rc;
