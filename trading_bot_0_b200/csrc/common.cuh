@@ -18,8 +18,6 @@ struct Geo {
   long long xsb, xsl, dtsb, dtsl, bsb, bsl, csb, csl, zsb, zsl, ysb, ysl;
   int dt_softplus;                     // step size = softplus(dt + dt_bias) instead of dt + dt_bias
   int onetile;                         // tensor family: the one-tile-per-CTA kernels for every shape (SSD_ALGO_TENSOR_ONETILE)
-  int fwd_only;                        // forward into a forward-sized workspace: no backward can reuse it, so the tensor family
-                                       // leaves the fp32 chunk-entry states (read only by the backward) unwritten
 };
 
 // The step-size pre-activation of a Mamba-2 layer, fused where dt is first read.  Above 20 softplus is the

@@ -64,7 +64,6 @@ static int make_geo(const SsdDims* d, Geo* g) {
   g->Q = d->chunk; g->nc = (d->seqlen + d->chunk - 1) / d->chunk; g->hpg = d->nheads / d->ngroups;
   g->dt_softplus = d->dt_softplus != 0;
   g->onetile = d->algo == SSD_ALGO_TENSOR_ONETILE;
-  g->fwd_only = 0;
   if (g->B > 65535) { set_error("batch (%d) must be <= 65535 (grid limit)", g->B); return SSD_ERR_UNSUPPORTED; }
   const long long HP = (long long)g->H * g->P, GN = (long long)g->G * g->N;
   auto pick = [](long long v, long long dflt) { return v ? v : dflt; };
@@ -258,7 +257,6 @@ int32_t ssd_forward_staged(const SsdDims* dims, const SsdFwdPtrs* p, void* works
   rc = check_ws(workspace, workspace_bytes, w.total_fwd);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)cuda_stream;
-  g.fwd_only = workspace_bytes < w.total_bwd && stages == SSD_STAGE_ALL;
   SsdFwdPtrs q = *p;
   q.final_state = nullptr;  // kernels always leave the final state in the workspace; copied out below
   const int fam = pick_family(g, dims);
