@@ -81,7 +81,8 @@ def kernel_bytes_per_token(name, c, e=2):
     st = 2 * H * c["P"] * c["N"] * 4 / c["Q"]
     table = {
         "cumsum": H * e, "chunk_state": (hp + gn) * e, "cb": 2 * gn * e,
-        "state_passing": st, "dstate_passing": st, "state_total": st / 2, "dstate_total": st / 2,
+        # fp32 local states in, bf16 chunk-entry states out; the reverse scan also reads the forward's bf16 copy
+        "state_passing": 0.75 * st, "dstate_passing": st, "state_total": st / 2, "dstate_total": st / 2,
         "chunk_scan": (2 * hp + gn) * e + zb, "chunk_scan_bwd_epilogue": (2 * hp + gn) * e + 2 * zb,
         "dstates_local": (hp + gn) * e, "dx": (3 * hp + gn) * e, "dw": 2 * hp * e,
         "dC": (2 * gn + hp) * e, "dB": (2 * gn + hp) * e, "ddt": 4 * H, "sdot": st / 2,
@@ -99,7 +100,8 @@ def kernel_bytes_per_token(name, c, e=2):
 
 
 TRAFFIC_SOURCE = ("derived, not measured in this run: dram__bytes_read.sum per token of an ncu capture at batch 128 "
-                  "(library as of commit 16fc4c5) scaled by the tokens of a launch, plus the kernel's output bytes")
+                  "(library as of commit 16fc4c5) scaled by the tokens of a launch, plus the kernel's output bytes; the two "
+                  "fused state kernels' figures are that capture minus the fp32 chunk-entry states they no longer move")
 
 
 def kernel_traffic_bytes_per_token(name, c, e=2):
@@ -114,10 +116,10 @@ def kernel_traffic_bytes_per_token(name, c, e=2):
     st32 = H * c["P"] * c["N"] * 4 / c["Q"]          # fp32 chunk states, bytes per token, one way
     measured_reads = {"chunk_state_tc": 768.0, "dstates_local_tc": 768.0, "chunk_scan_ws": 1152.6,
                       "scan_bwd_dx_ws": 1920.6, "dBdC_ws": 1923.1,
-                      "chunk_state_scan": 704.6, "dstate_scan": 1216.3}
+                      "chunk_state_scan": 704.6, "dstate_scan": 1216.3 - st32 / 2}   # S_end tile: bf16 now, was fp32
     writes = {"chunk_state_tc": st32, "dstates_local_tc": st32, "chunk_scan_ws": hp * e,
               "scan_bwd_dx_ws": hp * e + 3 * 4 * H, "dBdC_ws": 2 * gn * e,
-              "chunk_state_scan": st32 + st32 / 2, "dstate_scan": st32 / 2 + 4 * 4 * H / c["Q"]}
+              "chunk_state_scan": st32 / 2, "dstate_scan": st32 / 2 + 4 * 4 * H / c["Q"]}
     if name not in measured_reads:
         return None
     return measured_reads[name] + writes[name]
